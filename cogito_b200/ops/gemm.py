@@ -1,0 +1,171 @@
+"""bf16 GEMM with fused epilogues on the tcgen05 tensor cores.
+
+``gemm(a, b, ...)`` computes ``out[m, n] = epilogue(alpha * sum_k A(m, k) B(n, k))``
+where each operand may be stored K-major or MN-major (see
+``include/cogito_kernels.h``).  CUDA tensors run ``cgk_gemm_bf16``; CPU tensors
+run an fp32 restatement of the same formula, which is also the oracle of the GPU
+tests.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+ACT = {"none": 0, None: 0, "gelu": 1, "relu": 2, "silu": 3, "sigmoid": 4, "tanh": 5}
+
+
+def _act_cpu(name, x):
+    if name in (None, "none"):
+        return x
+    if name == "gelu":
+        return torch.nn.functional.gelu(x, approximate="tanh")
+    if name == "relu":
+        return torch.relu(x)
+    if name == "silu":
+        return torch.nn.functional.silu(x)
+    if name == "sigmoid":
+        return torch.sigmoid(x)
+    if name == "tanh":
+        return torch.tanh(x)
+    raise ValueError(name)
+
+
+def _dact_cpu(name, x):
+    x = x.detach().clone().requires_grad_(True)
+    with torch.enable_grad():
+        y = _act_cpu(name, x)
+        (g,) = torch.autograd.grad(y.sum(), x)
+    return g
+
+
+def gemm_reference(a, b, *, a_mn=False, b_mn=False, bias=None, act=None, residual=None,
+                   aux_in=None, dact=None, alpha=1.0, accumulate_into=None, out_dtype=torch.bfloat16,
+                   want_aux=False):
+    """fp32 restatement of the kernel's formula (any device)."""
+    A = a.float().transpose(-1, -2) if a_mn else a.float()
+    B = b.float() if b_mn else b.float().transpose(-1, -2)
+    v = alpha * (A @ B)
+    if bias is not None:
+        v = v + bias.float()
+    aux = v.to(torch.bfloat16) if want_aux else None
+    v = _act_cpu(act, v)
+    if aux_in is not None:
+        v = v * _dact_cpu(dact, aux_in.float())
+    if residual is not None:
+        v = v + residual.float()
+    if accumulate_into is not None:
+        v = v + accumulate_into.float()
+    out = v.to(out_dtype)
+    return (out, aux) if want_aux else out
+
+
+def _ld(t: torch.Tensor) -> int:
+    """Leading dimension of a 2-D (or batched 3-D) row-major view."""
+    assert t.stride(-1) == 1, "innermost dimension must be contiguous"
+    return t.stride(-2) if t.shape[-2] > 1 else max(t.shape[-1], t.stride(-2))
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16,
+         bias: torch.Tensor | None = None, act: str | None = None,
+         residual: torch.Tensor | None = None, aux_out: torch.Tensor | None = None,
+         aux_in: torch.Tensor | None = None, dact: str | None = None,
+         accumulate: bool = False, alpha: float = 1.0, force_simt: bool = False,
+         max_ctas: int = 0) -> torch.Tensor:
+    """``a``: [.., M, K] (or [.., K, M] when ``a_mn``); ``b``: [.., N, K] (or [.., K, N] when ``b_mn``).
+
+    ``out`` may be given (bf16 or fp32; required for ``accumulate``).  ``aux_out``
+    receives the pre-activation value in bf16.  ``aux_in`` / ``dact`` multiply the
+    result by the activation derivative at ``aux_in``.
+    """
+    if a_mn:
+        K, M = a.shape[-2], a.shape[-1]
+    else:
+        M, K = a.shape[-2], a.shape[-1]
+    if b_mn:
+        Kb, N = b.shape[-2], b.shape[-1]
+    else:
+        N, Kb = b.shape[-2], b.shape[-1]
+    if K != Kb:
+        raise ValueError(f"inner dimensions differ: {K} vs {Kb}")
+    batch_shape = a.shape[:-2]
+    if b.shape[:-2] != batch_shape:
+        raise ValueError("batch dimensions of a and b must match")
+    batch = 1
+    for s in batch_shape:
+        batch *= s
+
+    if not a.is_cuda:
+        ref = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, act=act, residual=residual,
+                             aux_in=aux_in, dact=dact, alpha=alpha,
+                             accumulate_into=out if accumulate else None,
+                             out_dtype=out.dtype if out is not None else out_dtype,
+                             want_aux=aux_out is not None)
+        if aux_out is not None:
+            ref, aux = ref
+            aux_out.copy_(aux)
+        if out is not None:
+            out.copy_(ref)
+            return out
+        return ref
+
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("gemm: CUDA operands must be bf16")
+    if a.stride(-1) != 1:
+        a = a.contiguous()
+    if b.stride(-1) != 1:
+        b = b.contiguous()
+    if batch > 1:
+        a = a.reshape(batch, *a.shape[-2:])
+        b = b.reshape(batch, *b.shape[-2:])
+        if a.stride(-1) != 1:
+            a = a.contiguous()
+        if b.stride(-1) != 1:
+            b = b.contiguous()
+    if out is None:
+        if accumulate:
+            raise ValueError("accumulate needs an output tensor")
+        out = torch.empty(*batch_shape, M, N, device=a.device, dtype=out_dtype)
+    else:
+        if out.shape[-2:] != (M, N) or out.stride(-1) != 1:
+            raise ValueError(f"out has shape {tuple(out.shape)}, expected (.., {M}, {N}) row-major")
+    out3 = out.reshape(batch, M, N) if batch > 1 else out
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("gemm: out must be bf16 or fp32")
+
+    g = _lib.GemmArgs()
+    g.A, g.B, g.out = a.data_ptr(), b.data_ptr(), out3.data_ptr()
+    g.M, g.N, g.K, g.batch = M, N, K, batch
+    g.lda, g.ldb, g.ldc = _ld(a), _ld(b), _ld(out3)
+    if batch > 1:
+        g.strideA, g.strideB, g.strideC = a.stride(0), b.stride(0), out3.stride(0)
+    else:
+        g.strideA = g.strideB = g.strideC = 0
+    g.a_mn, g.b_mn = int(a_mn), int(b_mn)
+    g.out_fp32 = int(out.dtype == torch.float32)
+    g.accumulate = int(accumulate)
+    g.alpha = float(alpha)
+    if bias is not None:
+        if bias.numel() != N:
+            raise ValueError("bias must have N elements")
+        g.bias = bias.data_ptr()
+        g.bias_fp32 = int(bias.dtype == torch.float32)
+    g.act = ACT[act]
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape[-2:] == (M, N)
+        g.residual, g.ldr = residual.data_ptr(), _ld(residual)
+    if aux_out is not None:
+        assert aux_out.dtype == torch.bfloat16 and aux_out.shape[-2:] == (M, N)
+        g.aux_out, g.ldaux = aux_out.data_ptr(), _ld(aux_out)
+    if aux_in is not None:
+        assert aux_in.dtype == torch.bfloat16 and aux_in.shape[-2:] == (M, N)
+        g.aux_in, g.ldauxin = aux_in.data_ptr(), _ld(aux_in)
+        g.dact = ACT[dact]
+    g.force_simt = int(force_simt)
+    g.max_ctas = int(max_ctas)
+    _lib.check(_lib.lib().cgk_gemm_bf16(ctypes.byref(g), _lib.stream_ptr()), "cgk_gemm_bf16")
+    _lib.count_launch()
+    return out

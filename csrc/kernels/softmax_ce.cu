@@ -1,0 +1,276 @@
+// Row softmax and fused softmax-cross-entropy for large vocabularies
+// (50 304 / 32 000 columns), bf16 logits, fp32 statistics.
+//
+//  * cgk_softmax_ce_fused: one CTA per row; pass 1 = online max / sum-exp,
+//    pass 2 (row re-read from L2) writes d(logits) in place or to a second
+//    buffer.  Loss per row goes to an fp32 vector.
+//  * cgk_ce_stats + cgk_ce_backward: the same split in two so a vocabulary-
+//    parallel run can all-reduce (max, sum-exp, target-logit) between them.
+//  * cgk_softmax_rows / cgk_softmax_rows_backward: plain row softmax, fp32.
+//
+// Reference counterparts: cg_cross_entropy_loss (src/layers/loss.c:44-78, always
+// applies softmax, clamps p at 1e-7), cg_cuda_softmax_forward/backward
+// (src/cuda/tensor_kernels.c:699-771, host loops).
+#include "../../include/cogito_kernels.h"
+#include "host_common.h"
+#include "sm100.cuh"
+
+namespace cgk {
+
+constexpr int CE_THREADS = 256;
+
+struct MaxSum {
+  float m, s;
+};
+__device__ __forceinline__ MaxSum ms_combine(MaxSum a, MaxSum b) {
+  MaxSum r;
+  r.m = fmaxf(a.m, b.m);
+  if (r.m == -INFINITY) { r.s = 0.0f; return r; }
+  r.s = a.s * __expf(a.m - r.m) + b.s * __expf(b.m - r.m);
+  return r;
+}
+__device__ __forceinline__ void ms_push(MaxSum& a, float x) {
+  if (x > a.m) {
+    a.s = a.s * __expf(a.m - x) + 1.0f;
+    a.m = x;
+  } else {
+    a.s += __expf(x - a.m);
+  }
+}
+
+__device__ MaxSum block_maxsum(MaxSum v, MaxSum* sh) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    MaxSum t;
+    t.m = __shfl_xor_sync(0xffffffffu, v.m, o);
+    t.s = __shfl_xor_sync(0xffffffffu, v.s, o);
+    v = ms_combine(v, t);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  MaxSum r = sh[0];
+  for (int w = 1; w < (int)(blockDim.x >> 5); ++w) r = ms_combine(r, sh[w]);
+  __syncthreads();
+  return r;
+}
+
+__device__ __forceinline__ MaxSum row_maxsum_bf16(const __nv_bfloat16* row, int V) {
+  MaxSum a;
+  a.m = -INFINITY;
+  a.s = 0.0f;
+  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const int nvec = V >> 3;
+    const uint4* p = reinterpret_cast<const uint4*>(row);
+    for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+      uint4 u = p[c];
+      float2 f;
+      f = unpack_bf16x2(u.x); ms_push(a, f.x); ms_push(a, f.y);
+      f = unpack_bf16x2(u.y); ms_push(a, f.x); ms_push(a, f.y);
+      f = unpack_bf16x2(u.z); ms_push(a, f.x); ms_push(a, f.y);
+      f = unpack_bf16x2(u.w); ms_push(a, f.x); ms_push(a, f.y);
+    }
+    for (int c = (nvec << 3) + threadIdx.x; c < V; c += blockDim.x) ms_push(a, __bfloat162float(row[c]));
+  } else {
+    for (int c = threadIdx.x; c < V; c += blockDim.x) ms_push(a, __bfloat162float(row[c]));
+  }
+  return a;
+}
+
+// dl[c] = (exp(l[c] - lse) - [c == tgt]) * scale   for one row
+__device__ __forceinline__ void row_ce_grad(const __nv_bfloat16* row, __nv_bfloat16* drow, int V,
+                                            float lse, int tgt, float scale) {
+  const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(drow) & 15) == 0);
+  int done = 0;
+  if (vec) {
+    const int nvec = V >> 3;
+    const uint4* p = reinterpret_cast<const uint4*>(row);
+    uint4* q = reinterpret_cast<uint4*>(drow);
+    for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+      uint4 u = p[c];
+      float f[8];
+      float2 t;
+      t = unpack_bf16x2(u.x); f[0] = t.x; f[1] = t.y;
+      t = unpack_bf16x2(u.y); f[2] = t.x; f[3] = t.y;
+      t = unpack_bf16x2(u.z); f[4] = t.x; f[5] = t.y;
+      t = unpack_bf16x2(u.w); f[6] = t.x; f[7] = t.y;
+      const int base = c << 3;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float pr = __expf(f[j] - lse);
+        if (base + j == tgt) pr -= 1.0f;
+        f[j] = pr * scale;
+      }
+      uint4 o;
+      o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+      o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+      q[c] = o;
+    }
+    done = nvec << 3;
+  }
+  for (int c = done + threadIdx.x; c < V; c += blockDim.x) {
+    float pr = __expf(__bfloat162float(row[c]) - lse);
+    if (c == tgt) pr -= 1.0f;
+    drow[c] = __float2bfloat16(pr * scale);
+  }
+}
+
+__global__ void __launch_bounds__(CE_THREADS)
+softmax_ce_fused_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
+                        float* __restrict__ loss_rows, __nv_bfloat16* dlogits, int R, int V,
+                        long long ld, float scale_f, const float* __restrict__ scale_ptr,
+                        long long ignore_index) {
+  __shared__ MaxSum sh[CE_THREADS / 32];
+  const float scale = scale_f * (scale_ptr ? *scale_ptr : 1.0f);
+  for (int r = blockIdx.x; r < R; r += gridDim.x) {
+    const __nv_bfloat16* row = logits + (long long)r * ld;
+    const long long tgt = targets[r];
+    const bool ignored = (tgt == ignore_index) || tgt < 0 || tgt >= V;
+    MaxSum ms = block_maxsum(row_maxsum_bf16(row, V), sh);
+    const float lse = ms.m + __logf(ms.s);
+    if (threadIdx.x == 0 && loss_rows)
+      loss_rows[r] = ignored ? 0.0f : (lse - __bfloat162float(row[tgt]));
+    __syncthreads();  // loss reads the target logit before it is overwritten in place
+    if (dlogits) row_ce_grad(row, dlogits + (long long)r * ld, V, lse, ignored ? -1 : (int)tgt,
+                             ignored ? 0.0f : scale);
+  }
+}
+
+// Per-row partial statistics of a vocabulary shard [vocab_start, vocab_start+V).
+__global__ void __launch_bounds__(CE_THREADS)
+ce_stats_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
+                long long vocab_start, float* __restrict__ rowmax, float* __restrict__ rowsum,
+                float* __restrict__ tgt_logit, int R, int V, long long ld) {
+  __shared__ MaxSum sh[CE_THREADS / 32];
+  for (int r = blockIdx.x; r < R; r += gridDim.x) {
+    const __nv_bfloat16* row = logits + (long long)r * ld;
+    MaxSum ms = block_maxsum(row_maxsum_bf16(row, V), sh);
+    if (threadIdx.x == 0) {
+      rowmax[r] = ms.m;
+      rowsum[r] = ms.s;
+      const long long t = targets[r] - vocab_start;
+      tgt_logit[r] = (t >= 0 && t < V) ? __bfloat162float(row[t]) : 0.0f;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(CE_THREADS)
+ce_backward_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
+                   long long vocab_start, const float* __restrict__ lse,
+                   __nv_bfloat16* dlogits, int R, int V, long long ld, float scale_f,
+                   const float* __restrict__ scale_ptr, long long ignore_index) {
+  const float scale = scale_f * (scale_ptr ? *scale_ptr : 1.0f);
+  for (int r = blockIdx.x; r < R; r += gridDim.x) {
+    const long long tg = targets[r];
+    const bool ignored = (tg == ignore_index);
+    const long long t = tg - vocab_start;
+    row_ce_grad(logits + (long long)r * ld, dlogits + (long long)r * ld, V, lse[r],
+                (t >= 0 && t < V) ? (int)t : -1, ignored ? 0.0f : scale);
+  }
+}
+
+// fp32 row softmax.  y may alias x.
+__global__ void __launch_bounds__(CE_THREADS)
+softmax_rows_kernel(const float* __restrict__ x, float* y, int R, int V, float inv_temp) {
+  __shared__ MaxSum sh[CE_THREADS / 32];
+  for (int r = blockIdx.x; r < R; r += gridDim.x) {
+    const float* row = x + (long long)r * V;
+    float* out = y + (long long)r * V;
+    MaxSum a;
+    a.m = -INFINITY;
+    a.s = 0.0f;
+    for (int c = threadIdx.x; c < V; c += blockDim.x) ms_push(a, row[c] * inv_temp);
+    MaxSum ms = block_maxsum(a, sh);
+    const float inv = 1.0f / ms.s;
+    for (int c = threadIdx.x; c < V; c += blockDim.x) out[c] = __expf(row[c] * inv_temp - ms.m) * inv;
+    __syncthreads();
+  }
+}
+
+// dx = y * (dy - sum(dy * y))
+__global__ void __launch_bounds__(CE_THREADS)
+softmax_rows_bwd_kernel(const float* __restrict__ y, const float* __restrict__ dy, float* dx, int R,
+                        int V) {
+  __shared__ float sh[CE_THREADS / 32];
+  for (int r = blockIdx.x; r < R; r += gridDim.x) {
+    const float* yr = y + (long long)r * V;
+    const float* dr = dy + (long long)r * V;
+    float s = 0.0f;
+    for (int c = threadIdx.x; c < V; c += blockDim.x) s += yr[c] * dr[c];
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+    __syncthreads();
+    float tot = 0.0f;
+    for (int w = 0; w < CE_THREADS / 32; ++w) tot += sh[w];
+    __syncthreads();
+    for (int c = threadIdx.x; c < V; c += blockDim.x) dx[(long long)r * V + c] = yr[c] * (dr[c] - tot);
+  }
+}
+
+}  // namespace cgk
+
+using namespace cgk;
+
+static int ce_grid(int R) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int cap = sm_count(dev) * 8;
+  return R < cap ? (R < 1 ? 1 : R) : cap;
+}
+
+// loss_rows[r] = lse(row r) - logit[r, target[r]] (0 for ignored rows).
+// dlogits (may be null, may alias logits) = (softmax - onehot) * scale_f * (*scale_ptr).
+CGK_API int cgk_softmax_ce_fused(const void* logits, const long long* targets, float* loss_rows,
+                                 void* dlogits, int R, int V, long long ld, float scale_f,
+                                 const float* scale_ptr, long long ignore_index, void* stream) {
+  CGK_REQUIRE(logits && targets, "cgk_softmax_ce_fused: null pointer");
+  CGK_REQUIRE(R >= 0 && V > 0 && ld >= V, "cgk_softmax_ce_fused: bad shape");
+  if (R == 0) return 0;
+  softmax_ce_fused_kernel<<<ce_grid(R), CE_THREADS, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)logits, targets, loss_rows, (__nv_bfloat16*)dlogits, R, V, ld, scale_f,
+      scale_ptr, ignore_index);
+  CGK_LAUNCH_CHECK();
+  return 0;
+}
+
+CGK_API int cgk_ce_stats(const void* logits, const long long* targets, long long vocab_start,
+                         float* rowmax, float* rowsum, float* tgt_logit, int R, int V, long long ld,
+                         void* stream) {
+  CGK_REQUIRE(logits && targets && rowmax && rowsum && tgt_logit, "cgk_ce_stats: null pointer");
+  if (R == 0) return 0;
+  ce_stats_kernel<<<ce_grid(R), CE_THREADS, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)logits, targets, vocab_start, rowmax, rowsum, tgt_logit, R, V, ld);
+  CGK_LAUNCH_CHECK();
+  return 0;
+}
+
+CGK_API int cgk_ce_backward(const void* logits, const long long* targets, long long vocab_start,
+                            const float* lse, void* dlogits, int R, int V, long long ld,
+                            float scale_f, const float* scale_ptr, long long ignore_index,
+                            void* stream) {
+  CGK_REQUIRE(logits && targets && lse && dlogits, "cgk_ce_backward: null pointer");
+  if (R == 0) return 0;
+  ce_backward_kernel<<<ce_grid(R), CE_THREADS, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)logits, targets, vocab_start, lse, (__nv_bfloat16*)dlogits, R, V, ld,
+      scale_f, scale_ptr, ignore_index);
+  CGK_LAUNCH_CHECK();
+  return 0;
+}
+
+CGK_API int cgk_softmax_rows(const float* x, float* y, int R, int V, float inv_temp, void* stream) {
+  CGK_REQUIRE(x && y && V > 0, "cgk_softmax_rows: bad argument");
+  if (R == 0) return 0;
+  softmax_rows_kernel<<<ce_grid(R), CE_THREADS, 0, (cudaStream_t)stream>>>(x, y, R, V, inv_temp);
+  CGK_LAUNCH_CHECK();
+  return 0;
+}
+
+CGK_API int cgk_softmax_rows_backward(const float* y, const float* dy, float* dx, int R, int V,
+                                      void* stream) {
+  CGK_REQUIRE(y && dy && dx && V > 0, "cgk_softmax_rows_backward: bad argument");
+  if (R == 0) return 0;
+  softmax_rows_bwd_kernel<<<ce_grid(R), CE_THREADS, 0, (cudaStream_t)stream>>>(y, dy, dx, R, V);
+  CGK_LAUNCH_CHECK();
+  return 0;
+}

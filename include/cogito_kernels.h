@@ -1,0 +1,66 @@
+/* C interface of the sm_100a kernel library (libcogito_kernels.so).
+ *
+ * All functions take raw device pointers and a cudaStream_t passed as void*.
+ * They return 0 on success or a negative code; cgk_last_error() gives the text.
+ * The Python package calls these through ctypes; C and C++ callers include this
+ * header and link the shared library.
+ */
+#ifndef COGITO_KERNELS_H
+#define COGITO_KERNELS_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+const char* cgk_last_error(void);
+int cgk_version(void);
+/* out[4] = {code, where, block, aux}; synchronises `stream`; clears the word. */
+int cgk_read_status(int* out, void* stream);
+
+/* ---- GEMM ------------------------------------------------------------- */
+enum { CGK_ACT_NONE = 0, CGK_ACT_GELU = 1, CGK_ACT_RELU = 2, CGK_ACT_SILU = 3,
+       CGK_ACT_SIGMOID = 4, CGK_ACT_TANH = 5 };
+
+/* out[b,m,n] = epilogue( alpha * sum_k A(b,m,k) * B(b,n,k) )
+ *   a_mn = 0: A is [M rows, K cols] with leading dimension lda   (K contiguous)
+ *   a_mn = 1: A is [K rows, M cols] with leading dimension lda   (M contiguous)
+ *   b_mn = 0: B is [N rows, K cols] with leading dimension ldb   (K contiguous)
+ *   b_mn = 1: B is [K rows, N cols] with leading dimension ldb   (N contiguous)
+ * epilogue, in this order:
+ *   v = alpha*acc (+ bias[n]);  aux_out[m,n] = v (if given);  v = act(v);
+ *   v *= act'(aux_in[m,n]) where act' is the derivative selected by dact (if given);
+ *   v += residual[m,n] (if given);  out = accumulate ? out + v : v
+ * bias / residual / aux tensors are bf16 unless bias_fp32 is set for the bias. */
+typedef struct {
+  const void* A;
+  const void* B;
+  void* out;
+  int32_t M, N, K, batch;
+  int64_t lda, ldb, ldc;
+  int64_t strideA, strideB, strideC; /* batch strides, elements */
+  int32_t a_mn, b_mn;
+  int32_t out_fp32;
+  int32_t accumulate;
+  float alpha;
+  const void* bias;
+  int32_t bias_fp32;
+  int32_t act;
+  const void* residual;
+  int64_t ldr;
+  void* aux_out;
+  int64_t ldaux;
+  const void* aux_in;
+  int64_t ldauxin;
+  int32_t dact;
+  int32_t force_simt; /* testing: use the CUDA-core fallback */
+  int32_t max_ctas;   /* 0 = one persistent CTA per SM */
+} cgk_gemm_args;
+
+int cgk_gemm_bf16(const cgk_gemm_args* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
