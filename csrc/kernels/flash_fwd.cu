@@ -1,0 +1,460 @@
+// Flash-Attention-2 forward on tcgen05 tensor cores.
+//
+// One CTA owns 256 query rows (two 128-row tiles) of one (batch, head) and walks
+// the key/value sequence in tiles of 128.  Per tile and per query tile:
+//     S = Q K^T            tcgen05.mma, fp32 accumulator in TMEM (128 columns)
+//     P = exp2(S*c - m)    softmax warpgroup: tcgen05.ld, online max / sum,
+//                          bf16 P written to 128B-swizzled shared memory
+//     O += P V             tcgen05.mma, O accumulator stays in TMEM for the
+//                          whole key loop; it is rescaled in place only when a
+//                          row maximum grows by more than 2^8 (the final 1/l
+//                          normalisation makes a stale maximum exact)
+// Warp roles: 0 = TMA producer, 1 = MMA issuer, 2 = TMEM allocator,
+// 4..7 = softmax warpgroup of query tile 0, 8..11 = of query tile 1.  The two
+// query tiles share every K/V tile, which halves the L2 -> shared traffic, and
+// their softmax phases overlap each other's MMAs.
+//
+// Supports causal masking (bottom-right aligned when Tq != Tk), a sliding window
+// |k - q| <= w, ALiBi slopes, GQA/MQA (kv head = h * Hk / Hq), head_dim 64 / 128.
+// Layout [batch, seq, heads, head_dim] with arbitrary (16-byte aligned) strides,
+// LSE [batch, heads, seq] as in the reference (include/cg_flash_attn.h:54-57,81).
+//
+// Reference counterparts: flash_attn_fwd_kernel (src/cuda/flash_attn_kernels.c:39-211),
+// its host simulation (:261-396) and cg_flash_attention_forward_cpu
+// (src/attention/flash_attn.c:17-152).
+#include "../../include/cogito_kernels.h"
+#include "host_common.h"
+#include "sm100.cuh"
+
+namespace cgk {
+
+struct FlashFwdDev {
+  int B, Hq, Hk, Tq, Tk;
+  float scale_log2;        // softmax scale * log2(e)
+  int causal;
+  int window;              // < 0: none
+  const float* alibi;      // [Hq] slopes or null
+  __nv_bfloat16* O;
+  long long o_bs, o_ts, o_hs;  // element strides of O: batch, token, head
+  float* lse;              // [B, Hq, Tq] or null
+  int* status;
+};
+
+template <int D>
+struct FwdCfg {
+  static constexpr int BM = 128;          // rows per query tile
+  static constexpr int BN = 128;          // keys per tile
+  static constexpr int DB = D / 64;       // 64-column blocks per row
+  static constexpr int Q_TILE_BYTES = BM * D * 2;
+  static constexpr int KV_TILE_BYTES = BN * D * 2;
+  static constexpr int P_TILE_BYTES = BM * BN * 2;
+  static constexpr int RING = (D == 64) ? 4 : 3;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_KV = OFF_Q + 2 * Q_TILE_BYTES;
+  static constexpr int OFF_P = OFF_KV + RING * KV_TILE_BYTES;
+  static constexpr int OFF_BAR = OFF_P + 2 * P_TILE_BYTES;
+  // barriers: q_full, full[RING], empty[RING], s_full[2], p_ready[2], o_done[2]
+  static constexpr int NUM_BARS = 1 + 2 * RING + 6;
+  static constexpr int TOTAL = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
+  static constexpr int TMEM_S0 = 0;
+  static constexpr int TMEM_O0 = 256;
+  static constexpr int TMEM_COLS = 512;
+};
+
+template <int D>
+__global__ void __launch_bounds__(384, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const FlashFwdDev p) {
+  using C = FwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + C::OFF_BAR;
+  const uint32_t q_full = bar0;
+  auto full_bar = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (1 + C::RING + s); };
+  auto s_full = [&](int t) { return bar0 + 8u * (1 + 2 * C::RING + t); };
+  auto p_ready = [&](int t) { return bar0 + 8u * (1 + 2 * C::RING + 2 + t); };
+  auto o_done = [&](int t) { return bar0 + 8u * (1 + 2 * C::RING + 4 + t); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::NUM_BARS * 8);
+  volatile int* dead = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qblk = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal blocks first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = (int)(((long long)h * p.Hk) / p.Hq);
+  const int q0 = qblk * 2 * C::BM;
+  const int off = p.Tk - p.Tq;  // causal alignment: key k visible to query q iff k <= q + off
+
+  // key-tile range [lo, hi_t) per query tile
+  const int nkv = (p.Tk + C::BN - 1) / C::BN;
+  int lo = 0;
+  if (p.window >= 0) {
+    int first = q0 + off - p.window;
+    lo = first > 0 ? first / C::BN : 0;
+  }
+  int hi_t[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int q_begin = q0 + t * C::BM;
+    int q_end = q_begin + C::BM;
+    if (q_end > p.Tq) q_end = p.Tq;
+    int hi = nkv;
+    if (q_begin >= p.Tq) {
+      hi = lo;  // tile entirely beyond the sequence
+    } else {
+      long long last_key = (long long)p.Tk - 1;
+      if (p.causal) last_key = min(last_key, (long long)q_end - 1 + off);
+      if (p.window >= 0 && !p.causal) last_key = min(last_key, (long long)q_end - 1 + off + p.window);
+      hi = last_key < 0 ? 0 : (int)(last_key / C::BN) + 1;
+      if (hi > nkv) hi = nkv;
+      if (hi < lo) hi = lo;
+    }
+    hi_t[t] = hi;
+  }
+  const int hi = max(hi_t[0], hi_t[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < C::RING; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int t = 0; t < 2; ++t) { mbar_init(s_full(t), 1); mbar_init(p_ready(t), 128); mbar_init(o_done(t), 1); }
+    *dead = 0;
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(tmem_holder), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0 && hi > lo) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      mbar_expect_tx(q_full, 2 * C::Q_TILE_BYTES);
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int db = 0; db < C::DB; ++db)
+          tma_load_4d(sbase + C::OFF_Q + t * C::Q_TILE_BYTES + db * (C::BM * 128), &tmQ, q_full,
+                      db * 64, h, q0 + t * C::BM, b);
+      uint32_t n = 0;  // ring counter
+      bool ok = true;
+      auto load_tile = [&](const CUtensorMap* tm, int j) {
+        const int s = n % C::RING;
+        const uint32_t ph = (n / C::RING) & 1u;
+        if (!mbar_wait(empty_bar(s), ph ^ 1u, dead, p.status, 1100)) { ok = false; return; }
+        mbar_expect_tx(full_bar(s), C::KV_TILE_BYTES);
+#pragma unroll
+        for (int db = 0; db < C::DB; ++db)
+          tma_load_4d(sbase + C::OFF_KV + s * C::KV_TILE_BYTES + db * (C::BN * 128), tm,
+                      full_bar(s), db * 64, hk, j * C::BN, b);
+        ++n;
+      };
+      // order must match the consumer's release order: K_lo, then (K_{j+1}, V_j) per j
+      load_tile(&tmK, lo);
+      for (int j = lo; j < hi && ok; ++j) {
+        if (j + 1 < hi) load_tile(&tmK, j + 1);
+        if (ok) load_tile(&tmV, j);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0 && hi > lo) {
+      const uint32_t idesc_s = make_idesc_bf16(C::BM, C::BN, 0, 0);
+      const uint32_t idesc_o = make_idesc_bf16(C::BM, D, 0, 1);
+      bool ok = true;
+      uint32_t n = 0;            // ring counter (consumption order)
+      uint32_t pcount[2] = {0, 0};
+      auto issue_s = [&](int t, uint32_t kbase) {
+        const uint32_t qb = sbase + C::OFF_Q + t * C::Q_TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t o = (kk >> 2) * (C::BM * 128) + (kk & 3) * 32;
+          umma_f16(tmem_base + C::TMEM_S0 + t * 128, make_smem_desc_sw128(qb + o, 16, 1024),
+                   make_smem_desc_sw128(kbase + o, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(s_full(t));
+      };
+      auto issue_pv = [&](int t, uint32_t vbase, bool acc) {
+        const uint32_t pb = sbase + C::OFF_P + t * C::P_TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < C::BN / 16; ++kk) {
+          // A = P: K-major, 64-key blocks of [128 rows x 128 B]
+          const uint32_t ao = (kk >> 2) * (C::BM * 128) + (kk & 3) * 32;
+          // B = V: MN-major (head_dim contiguous), 16 key rows per step, 64-wide
+          // head_dim blocks C::BN*128 bytes apart
+          const uint32_t bo = kk * 2048;
+          umma_f16(tmem_base + C::TMEM_O0 + t * D, make_smem_desc_sw128(pb + ao, 16, 1024),
+                   make_smem_desc_sw128(vbase + bo, C::BN * 128, 1024), idesc_o,
+                   (acc || kk != 0) ? 1u : 0u);
+        }
+        umma_commit(o_done(t));
+      };
+      if (!mbar_wait(q_full, 0, dead, p.status, 1200)) ok = false;
+      uint32_t kslot_next = 0;  // smem address of K_{j+1} once waited
+      if (ok) {
+        const int s = n % C::RING;
+        if (!mbar_wait(full_bar(s), (n / C::RING) & 1u, dead, p.status, 1201)) ok = false;
+        if (ok) {
+          tc_fence_after();
+          const uint32_t kb = sbase + C::OFF_KV + s * C::KV_TILE_BYTES;
+          for (int t = 0; t < 2; ++t)
+            if (lo < hi_t[t]) issue_s(t, kb);
+          umma_commit(empty_bar(s));
+          ++n;
+        }
+      }
+      for (int j = lo; j < hi && ok; ++j) {
+        const bool has_next = j + 1 < hi;
+        int ks = -1, vs = -1;
+        uint32_t kaddr = 0, vaddr = 0;
+        const int t_last = (j < hi_t[1]) ? 1 : 0;
+        const int t_last_next = (j + 1 < hi_t[1]) ? 1 : 0;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j >= hi_t[t]) continue;
+          if (!mbar_wait(p_ready(t), pcount[t] & 1u, dead, p.status, 1210 + t)) { ok = false; break; }
+          ++pcount[t];
+          tc_fence_after();
+          if (has_next && j + 1 < hi_t[t]) {
+            if (ks < 0) {
+              ks = n % C::RING;
+              if (!mbar_wait(full_bar(ks), (n / C::RING) & 1u, dead, p.status, 1220)) { ok = false; break; }
+              tc_fence_after();
+              kaddr = sbase + C::OFF_KV + ks * C::KV_TILE_BYTES;
+              ++n;
+            }
+            issue_s(t, kaddr);
+            if (t == t_last_next) umma_commit(empty_bar(ks));
+          }
+          if (vs < 0) {
+            // the V tile follows K_{j+1} in the ring; when no tile needs K_{j+1}
+            // the producer did not load it
+            if (has_next && ks < 0) {
+              // K_{j+1} was loaded (has_next) but this tile does not use it; the
+              // other tile (t = 1) will.  Only reachable for t = 0 at its last
+              // key tile, where t = 1 still follows: take the K slot now.
+              ks = n % C::RING;
+              if (!mbar_wait(full_bar(ks), (n / C::RING) & 1u, dead, p.status, 1221)) { ok = false; break; }
+              tc_fence_after();
+              kaddr = sbase + C::OFF_KV + ks * C::KV_TILE_BYTES;
+              ++n;
+            }
+            vs = n % C::RING;
+            if (!mbar_wait(full_bar(vs), (n / C::RING) & 1u, dead, p.status, 1230)) { ok = false; break; }
+            tc_fence_after();
+            vaddr = sbase + C::OFF_KV + vs * C::KV_TILE_BYTES;
+            ++n;
+          }
+          issue_pv(t, vaddr, j > lo);
+          if (t == t_last) umma_commit(empty_bar(vs));
+        }
+        (void)kslot_next;
+      }
+    }
+  } else if (warp >= 4) {
+    // --------------------------- softmax warpgroups ---------------------------
+    const int t = (warp - 4) >> 2;
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;          // row inside the query tile == TMEM lane
+    const int qpos = q0 + t * C::BM + row;
+    const int my_hi = hi_t[t];
+    const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t s_tmem = tmem_base + C::TMEM_S0 + t * 128 + lane_sel;
+    const uint32_t o_tmem = tmem_base + C::TMEM_O0 + t * D + lane_sel;
+    uint8_t* p_smem = smem + C::OFF_P + t * C::P_TILE_BYTES;
+    const float slope = p.alibi ? p.alibi[h] * 1.4426950408889634f : 0.0f;
+    const int qk = qpos + off;                 // last visible key under the causal mask
+    float m = -INFINITY, l = 0.0f;
+    bool ok = true;
+    uint32_t it = 0;
+    for (int j = lo; j < my_hi && ok; ++j, ++it) {
+      if (!mbar_wait(s_full(t), it & 1u, dead, p.status, 1300 + t)) { ok = false; break; }
+      tc_fence_after();
+      const int k0 = j * C::BN;
+      // does any element of this tile need masking?  (warp-uniform)
+      const int tile_q_lo = q0 + t * C::BM + off, tile_q_hi = tile_q_lo + C::BM - 1;
+      bool need_mask = (k0 + C::BN > p.Tk);
+      if (p.causal) need_mask |= (k0 + C::BN - 1 > tile_q_lo);
+      if (p.window >= 0) need_mask |= (k0 < tile_q_hi - p.window) || (!p.causal && k0 + C::BN - 1 > tile_q_lo + p.window);
+      auto score = [&](uint32_t raw, int k) -> float {
+        float s = __uint_as_float(raw) * p.scale_log2;
+        if (p.alibi) s += slope * (float)(k - qk);
+        if (need_mask) {
+          bool vis = k < p.Tk;
+          if (p.causal) vis &= (k <= qk);
+          if (p.window >= 0) vis &= (k >= qk - p.window) && (k <= qk + p.window);
+          if (!vis) s = -INFINITY;
+        }
+        return s;
+      };
+      // pass 1: row maximum
+      float mx = m;
+#pragma unroll 1
+      for (int c = 0; c < C::BN / 32; ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld32(s_tmem + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, score(r[i], k0 + c * 32 + i));
+      }
+      // keep a stale maximum unless it grew by more than 2^8
+      float m_use = (mx > m + 8.0f) ? mx : m;
+      if (m == -INFINITY) m_use = mx;
+      const float alpha = (m == -INFINITY) ? 0.0f : fast_exp2(m - m_use);
+      const bool changed = (m_use != m);
+      // PV of the previous key tile must be done before O is rescaled and before
+      // P is overwritten
+      if (j > lo) {
+        if (!mbar_wait(o_done(t), (it - 1) & 1u, dead, p.status, 1310 + t)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, changed)) {
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            __syncwarp();
+            tmem_ld32(o_tmem + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st32(o_tmem + c * 32, r);
+          }
+          tmem_st_wait();
+        }
+      }
+      l *= alpha;
+      m = m_use;
+      const float m_sub = (m == -INFINITY) ? 0.0f : m;
+      // pass 2: P = exp2(score - m), bf16, into the swizzled operand tile
+#pragma unroll 1
+      for (int c = 0; c < C::BN / 32; ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld32(s_tmem + c * 32, r);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = fast_exp2(score(r[i], k0 + c * 32 + i) - m_sub);
+          const float p1 = fast_exp2(score(r[i + 1], k0 + c * 32 + i + 1) - m_sub);
+          l += p0 + p1;
+          packed[i >> 1] = pack_bf16x2(p0, p1);
+        }
+        uint8_t* blk = p_smem + (c >> 1) * (C::BM * 128);
+        const uint32_t chunk0 = (c & 1) * 4;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 v = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+          *reinterpret_cast<uint4*>(blk + sw128_offset(row, chunk0 + q4)) = v;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_ready(t));
+    }
+    // epilogue: O / l -> global, LSE
+    const bool have = my_hi > lo;
+    if (have && ok) {
+      if (!mbar_wait(o_done(t), (it - 1) & 1u, dead, p.status, 1320 + t)) ok = false;
+      tc_fence_after();
+    }
+    const float inv_l = (l > 0.0f) ? 1.0f / l : 0.0f;
+    const bool row_ok = qpos < p.Tq;
+    __nv_bfloat16* orow = p.O + (long long)b * p.o_bs + (long long)qpos * p.o_ts + (long long)h * p.o_hs;
+#pragma unroll 1
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t r[32];
+      if (have && ok) {
+        __syncwarp();
+        tmem_ld32(o_tmem + c * 32, r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = 0u;
+      }
+      if (row_ok) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 v;
+          v.x = pack_bf16x2(__uint_as_float(r[8 * q4]) * inv_l, __uint_as_float(r[8 * q4 + 1]) * inv_l);
+          v.y = pack_bf16x2(__uint_as_float(r[8 * q4 + 2]) * inv_l, __uint_as_float(r[8 * q4 + 3]) * inv_l);
+          v.z = pack_bf16x2(__uint_as_float(r[8 * q4 + 4]) * inv_l, __uint_as_float(r[8 * q4 + 5]) * inv_l);
+          v.w = pack_bf16x2(__uint_as_float(r[8 * q4 + 6]) * inv_l, __uint_as_float(r[8 * q4 + 7]) * inv_l);
+          *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = v;
+        }
+      }
+    }
+    if (row_ok && p.lse) {
+      const float lse = (l > 0.0f) ? (m * 0.6931471805599453f + __logf(l)) : INFINITY;
+      p.lse[((long long)b * p.Hq + h) * p.Tq + qpos] = lse;
+    }
+  }
+
+  if (*dead) __nanosleep(100000);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// 4-D tensor map over [B, T, H, D] (element strides bs, ts, hs; D contiguous),
+// box = 64 x 1 x rows x 1.
+static int make_qkv_tmap(CUtensorMap* tm, const void* base, int B, int T, int H, int D,
+                         long long bs, long long ts, long long hs, int rows) {
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)T, (uint64_t)B};
+  uint64_t strides[3] = {(uint64_t)hs * 2, (uint64_t)ts * 2, (uint64_t)bs * 2};
+  uint32_t box[4] = {64, 1, (uint32_t)rows, 1};
+  return encode_tmap(tm, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dims, strides, box, Swz::B128);
+}
+
+template <int D>
+static int launch_fwd(const cgk_flash_args& a, const FlashFwdDev& p, cudaStream_t st) {
+  using C = FwdCfg<D>;
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_qkv_tmap(&tq, a.q, a.B, a.Tq, a.Hq, D, a.q_bs, a.q_ts, a.q_hs, C::BM))) return rc;
+  if ((rc = make_qkv_tmap(&tk, a.k, a.B, a.Tk, a.Hk, D, a.k_bs, a.k_ts, a.k_hs, C::BN))) return rc;
+  if ((rc = make_qkv_tmap(&tv, a.v, a.B, a.Tk, a.Hk, D, a.v_bs, a.v_ts, a.v_hs, C::BN))) return rc;
+  CGK_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      C::TOTAL));
+  dim3 grid((a.Tq + 2 * C::BM - 1) / (2 * C::BM), a.Hq, a.B);
+  flash_fwd_kernel<D><<<grid, 384, C::TOTAL, st>>>(tq, tk, tv, p);
+  CGK_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace cgk
+
+using namespace cgk;
+
+CGK_API int cgk_flash_forward(const cgk_flash_args* pa, void* stream) {
+  CGK_REQUIRE(pa, "cgk_flash_forward: null args");
+  const cgk_flash_args& a = *pa;
+  CGK_REQUIRE(a.q && a.k && a.v && a.o, "cgk_flash_forward: null tensor");
+  CGK_REQUIRE(a.D == 64 || a.D == 128, "cgk_flash_forward: head_dim %d not supported (64 or 128)", a.D);
+  CGK_REQUIRE(a.Hq % a.Hk == 0, "cgk_flash_forward: Hq must be a multiple of Hk");
+  CGK_REQUIRE(a.o_hs % 8 == 0 && a.o_ts % 8 == 0 && a.o_bs % 8 == 0 && ((uintptr_t)a.o & 15) == 0,
+              "cgk_flash_forward: output strides must be multiples of 8 elements");
+  if (a.B == 0 || a.Tq == 0 || a.Hq == 0) return 0;
+  int dev = 0;
+  CGK_CUDA_CHECK(cudaGetDevice(&dev));
+  FlashFwdDev p;
+  p.B = a.B; p.Hq = a.Hq; p.Hk = a.Hk; p.Tq = a.Tq; p.Tk = a.Tk;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.causal = a.causal; p.window = a.window;
+  p.alibi = a.alibi_slopes;
+  p.O = (__nv_bfloat16*)a.o; p.o_bs = a.o_bs; p.o_ts = a.o_ts; p.o_hs = a.o_hs;
+  p.lse = a.lse;
+  p.status = device_status(dev);
+  if (a.D == 64) return launch_fwd<64>(a, p, (cudaStream_t)stream);
+  return launch_fwd<128>(a, p, (cudaStream_t)stream);
+}

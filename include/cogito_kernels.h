@@ -60,6 +60,38 @@ typedef struct {
 
 int cgk_gemm_bf16(const cgk_gemm_args* args, void* stream);
 
+/* ---- Flash attention ------------------------------------------------------ */
+/* Tensors are bf16 [batch, seq, heads, head_dim] with head_dim contiguous and the
+ * given element strides (batch, token, head), all multiples of 8.  lse is fp32
+ * [batch, heads_q, seq_q].  head_dim 64 or 128.  Key k is visible to query q iff
+ * (!causal || k <= q + Tk - Tq) and (window < 0 || |k - (q + Tk - Tq)| <= window).
+ * alibi_slopes: fp32 [heads_q] or null; bias = slope * (k - (q + Tk - Tq)). */
+typedef struct {
+  const void* q; const void* k; const void* v;
+  void* o;
+  float* lse;
+  int32_t B, Hq, Hk, Tq, Tk, D;
+  int64_t q_bs, q_ts, q_hs;
+  int64_t k_bs, k_ts, k_hs;
+  int64_t v_bs, v_ts, v_hs;
+  int64_t o_bs, o_ts, o_hs;
+  float scale;
+  int32_t causal;
+  int32_t window;
+  const float* alibi_slopes;
+  /* backward only */
+  const void* d_o;            /* same layout as o */
+  void* dq; void* dk; void* dv;
+  int64_t dq_bs, dq_ts, dq_hs;
+  int64_t dk_bs, dk_ts, dk_hs;
+  int64_t dv_bs, dv_ts, dv_hs;
+  float* delta;               /* scratch fp32 [B, Hq, Tq] */
+  float* dq_accum;            /* scratch fp32 [B, Tq, Hq, D] */
+} cgk_flash_args;
+
+int cgk_flash_forward(const cgk_flash_args* args, void* stream);
+int cgk_flash_backward(const cgk_flash_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
