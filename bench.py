@@ -1,0 +1,203 @@
+#!/usr/bin/env python
+"""Headline benchmark: GPT-2-small training throughput (tokens/s over the whole job).
+
+    python bench.py --gpus N --steps K --warmup W            (N = 1)
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Config (the reference's GPT-2-small line): 12 layers, d_model 768, 12 heads, MLP
+3072, vocab 50304, sequence 2048, global batch 64, bf16, flash attention, Adam;
+tensor parallel over the N GPUs (TP = N), so the total work is fixed ("strong").
+Synthetic data: token ids uniform over the vocabulary, weights N(0, 0.02).
+
+Prints ONE JSON line on rank 0.  `value` is device-timed (CUDA events around
+exactly K steps, max over ranks) with the batch already on the device; `e2e` times
+the same K steps through the public API (`Trainer.step`) including, per step, the
+host->device copy of the batch from pinned memory and a device->host read of the loss.
+
+`--impl reference` reports the reference arm.  The reference (a C11 CPU library
+with no Python packaging and no runnable transformer path) cannot be installed, so
+that arm prints its `unavailable` line.  `--impl torch` runs the same model with
+PyTorch library kernels (cuBLAS + SDPA + NCCL), the comparison point named for the
+configs the reference cannot run.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+REF_UNAVAILABLE = ("pip install of /root/reference failed: \"Neither 'setup.py' nor 'pyproject.toml' found\" "
+                   "(pure-C CMake project whose library target does not compile; no transformer training path)")
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="cogito", choices=["cogito", "reference", "torch"])
+    ap.add_argument("--micro-batch", type=int, default=8)
+    ap.add_argument("--global-batch", type=int, default=64)
+    ap.add_argument("--seq-len", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=12)
+    ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"])
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REF_UNAVAILABLE}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            print(f"bench.py: --gpus {args.gpus} needs torch.distributed.run with {args.gpus} ranks", file=sys.stderr)
+            return 2
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from cogito_b200.bench_support import build_job
+
+    job = build_job(args, rank, world, dev)
+    B, T = args.global_batch, args.seq_len
+    tokens_per_step = B * T
+
+    g = torch.Generator().manual_seed(1234)
+    host_ids = torch.randint(0, job.vocab, (B, T), generator=g).pin_memory()
+    host_tg = torch.randint(0, job.vocab, (B, T), generator=g).pin_memory()
+    dev_ids, dev_tg = host_ids.to(dev), host_tg.to(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms)
+
+    loss_box = [None]
+
+    def step_device():
+        loss_box[0] = job.step(dev_ids, dev_tg)
+
+    def step_e2e():
+        loss_box[0] = float(job.step(host_ids, host_tg))      # H2D copy inside, D2H read of the loss
+
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    job.reset_launch_count()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(step_device, args.steps)
+    launches = job.launch_count()
+    clocks = sampler.stop() if rank == 0 else None
+    step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    final_loss = float(loss_box[0])
+
+    if rank == 0:
+        ms_per_step = ms / args.steps
+        value = tokens_per_step / (ms_per_step * 1e-3)
+        e2e_val = tokens_per_step / (ms_e2e / args.steps * 1e-3)
+        out = {
+            "metric": "train tok/s/box (GPT-2-small, whole job)", "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (uniform token ids, N(0,0.02) weights)", "impl": args.impl,
+            "config": {"model": "gpt2-small", "layers": args.layers, "d_model": 768, "heads": 12, "mlp": 3072,
+                       "vocab": 50304, "global_batch": B, "seq_len": T, "micro_batch": args.micro_batch,
+                       "parallelism": f"{args.parallelism}{world}", "optimizer": "adam",
+                       "l2": "inputs larger than L2: each step streams >10 GB of activations and weights"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_val, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": host_ids.numel() * 8 + host_tg.numel() * 8, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches, "final_loss": final_loss,
+            "model_tflops_per_gpu": job.flops_per_token * value / world / 1e12,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -97,7 +97,7 @@ def _build(sources: list[Path], headers: list[Path], out: Path, compiler: list[s
 
 def build_kernels(verbose: bool = False) -> Path:
     srcs = sorted((ROOT / "csrc" / "kernels").glob("*.cu")) + sorted((ROOT / "csrc" / "comm").glob("*.cu"))
-    hdrs = (list((ROOT / "csrc").rglob("*.cuh")) + list((ROOT / "csrc").rglob("*.h"))
+    hdrs = (list((ROOT / "csrc").rglob("*.cuh")) + list((ROOT / "csrc").rglob("*.h")) + list((ROOT / "csrc").rglob("*.inc"))
             + list((ROOT / "include").glob("*.h")))
     out = LIB_DIR / "libcogito_kernels.so"
     nvcc = _nvcc()

@@ -1,0 +1,5 @@
+"""Layers of the framework (see modules.py and transformer.py)."""
+from .modules import (BatchNorm1d, Dropout, Embedding, Flatten, GELU, LayerNorm, Linear, ReLU, RMSNorm,
+                      Sequential, Sigmoid, SiLU, Softmax, SwiGLU, Tanh)
+from .transformer import (FeedForward, SelfAttention, TransformerBlock, TransformerConfig,
+                          packed_attention)

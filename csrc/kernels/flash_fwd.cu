@@ -28,6 +28,20 @@
 
 namespace cgk {
 
+// Optional phase timers (build with -DCGK_FLASH_TIMING): the first softmax thread
+// of CTA (0,0,0) accumulates the cycles spent in each phase of the key loop.
+#ifdef CGK_FLASH_TIMING
+__device__ long long g_flash_fwd_times[8];
+#define FT_DECL long long ft_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long ft_last = clock64();
+#define FT_MARK(i) { long long ft_now = clock64(); ft_[i] += ft_now - ft_last; ft_last = ft_now; }
+#define FT_FLUSH() if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 128) \
+  { for (int ft_i = 0; ft_i < 8; ++ft_i) g_flash_fwd_times[ft_i] = ft_[ft_i]; }
+#else
+#define FT_DECL
+#define FT_MARK(i)
+#define FT_FLUSH()
+#endif
+
 struct FlashFwdDev {
   int B, Hq, Hk, Tq, Tk;
   float scale_log2;        // softmax scale * log2(e)
@@ -131,7 +145,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 0) {
+  // The softmax warpgroups hold a whole S row in registers; the producer / MMA /
+  // allocator warpgroup gives its share of the register file to them.
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0 && hi > lo) {
       tma_prefetch_desc(&tmQ);
@@ -258,7 +276,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         (void)kslot_next;
       }
     }
-  } else if (warp >= 4) {
+   }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // --------------------------- softmax warpgroups ---------------------------
     const int t = (warp - 4) >> 2;
     const int quad = warp & 3;
@@ -272,10 +292,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const float slope = p.alibi ? p.alibi[h] * 1.4426950408889634f : 0.0f;
     const int qk = qpos + off;                 // last visible key under the causal mask
     float m = -INFINITY, l = 0.0f;
+    FT_DECL
     bool ok = true;
     uint32_t it = 0;
     for (int j = lo; j < my_hi && ok; ++j, ++it) {
+      FT_MARK(7)
       if (!mbar_wait(s_full(t), it & 1u, dead, p.status, 1300 + t)) { ok = false; break; }
+      FT_MARK(0)
       tc_fence_after();
       const int k0 = j * C::BN;
       // does any element of this tile need masking?  (warp-uniform)
@@ -283,28 +306,57 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       bool need_mask = (k0 + C::BN > p.Tk);
       if (p.causal) need_mask |= (k0 + C::BN - 1 > tile_q_lo);
       if (p.window >= 0) need_mask |= (k0 < tile_q_hi - p.window) || (!p.causal && k0 + C::BN - 1 > tile_q_lo + p.window);
-      auto score = [&](uint32_t raw, int k) -> float {
-        float s = __uint_as_float(raw) * p.scale_log2;
-        if (p.alibi) s += slope * (float)(k - qk);
-        if (need_mask) {
-          bool vis = k < p.Tk;
-          if (p.causal) vis &= (k <= qk);
-          if (p.window >= 0) vis &= (k >= qk - p.window) && (k <= qk + p.window);
-          if (!vis) s = -INFINITY;
-        }
-        return s;
+      // Row-wise visible key range [klo, khi] (empty when khi < klo); one unsigned
+      // compare per element then decides visibility.  The ALiBi bias of element
+      // (c, i) is bias0 + slope * (c*32 + i).
+      int klo = 0, khi = p.Tk - 1;
+      if (p.causal) khi = min(khi, qk);
+      if (p.window >= 0) { klo = max(klo, qk - p.window); khi = min(khi, qk + p.window); }
+      const int rel0 = k0 - klo;                          // (k - klo) of the tile's first key
+      const unsigned span = khi >= klo ? (unsigned)(khi - klo) : 0u;
+      const bool none = khi < klo;
+      const float bias0 = p.alibi ? slope * (float)(k0 - qk) : 0.0f;
+      auto score = [&](uint32_t raw, int idx) -> float {    // idx = c*32 + i (compile-time)
+        const float bias = fmaf(slope, (float)idx, bias0);
+        const float sc = fmaf(__uint_as_float(raw), p.scale_log2, bias);
+        const bool vis = ((unsigned)(rel0 + idx) <= span) && !none;
+        return vis ? sc : -INFINITY;
       };
-      // pass 1: row maximum
-      float mx = m;
-#pragma unroll 1
-      for (int c = 0; c < C::BN / 32; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld32(s_tmem + c * 32, r);
-        tmem_ld_wait();
+      // Interior tiles (no mask, no bias) take a path with the minimum instruction
+      // count per element: the softmax warps are issue- and MUFU-bound.
+      const bool fast = !need_mask && !p.alibi && p.scale_log2 > 0.0f;
+      // The whole S row (128 fp32) comes into registers with four loads in flight
+      // and one wait; it is read from TMEM once per key tile.
+      uint32_t r[4][32];
+      __syncwarp();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, score(r[i], k0 + c * 32 + i));
+      for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, r[c]);
+      tmem_ld_wait();
+      float mx;
+      if (fast) {
+        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          m0 = fmaxf(m0, __uint_as_float(r[0][i]));
+          m1 = fmaxf(m1, __uint_as_float(r[1][i]));
+          m2 = fmaxf(m2, __uint_as_float(r[2][i]));
+          m3 = fmaxf(m3, __uint_as_float(r[3][i]));
+        }
+        mx = fmaxf(m, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * p.scale_log2);
+      } else {
+        // masked / biased tile: turn the raw products into final log2-domain scores in place
+        float m0 = m;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float sc = score(r[c][i], c * 32 + i);
+            r[c][i] = __float_as_uint(sc);
+            m0 = fmaxf(m0, sc);
+          }
+        mx = m0;
       }
+      FT_MARK(1)
       // keep a stale maximum unless it grew by more than 2^8
       float m_use = (mx > m + 8.0f) ? mx : m;
       if (m == -INFINITY) m_use = mx;
@@ -318,47 +370,49 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (__any_sync(0xffffffffu, changed)) {
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
-            uint32_t r[32];
+            uint32_t ro[32];
             __syncwarp();
-            tmem_ld32(o_tmem + c * 32, r);
+            tmem_ld32(o_tmem + c * 32, ro);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(o_tmem + c * 32, r);
+            for (int i = 0; i < 32; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * alpha);
+            tmem_st32(o_tmem + c * 32, ro);
           }
           tmem_st_wait();
         }
       }
+      FT_MARK(2)
       l *= alpha;
       m = m_use;
       const float m_sub = (m == -INFINITY) ? 0.0f : m;
-      // pass 2: P = exp2(score - m), bf16, into the swizzled operand tile
-#pragma unroll 1
-      for (int c = 0; c < C::BN / 32; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld32(s_tmem + c * 32, r);
-        tmem_ld_wait();
-        uint32_t packed[16];
+      const float neg_m = -m_sub;
+      const float mul = fast ? p.scale_log2 : 1.0f;   // slow path: r already holds the scores
+      // P = exp2(score - m), bf16, into the swizzled operand tile
+      float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = fast_exp2(score(r[i], k0 + c * 32 + i) - m_sub);
-          const float p1 = fast_exp2(score(r[i + 1], k0 + c * 32 + i + 1) - m_sub);
-          l += p0 + p1;
-          packed[i >> 1] = pack_bf16x2(p0, p1);
-        }
+      for (int c = 0; c < 4; ++c) {
+        float e[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) e[i] = fast_exp2(fmaf(__uint_as_float(r[c][i]), mul, neg_m));
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) { s0 += e[i]; s1 += e[i + 1]; s2 += e[i + 2]; s3 += e[i + 3]; }
         uint8_t* blk = p_smem + (c >> 1) * (C::BM * 128);
         const uint32_t chunk0 = (c & 1) * 4;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 v = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+          uint4 v = make_uint4(pack_bf16x2(e[8 * q4], e[8 * q4 + 1]), pack_bf16x2(e[8 * q4 + 2], e[8 * q4 + 3]),
+                               pack_bf16x2(e[8 * q4 + 4], e[8 * q4 + 5]), pack_bf16x2(e[8 * q4 + 6], e[8 * q4 + 7]));
           *reinterpret_cast<uint4*>(blk + sw128_offset(row, chunk0 + q4)) = v;
         }
       }
+      l += (s0 + s1) + (s2 + s3);
       fence_proxy_async_smem();
       tc_fence_before();
+      FT_MARK(3)
       mbar_arrive(p_ready(t));
+      FT_MARK(4)
     }
+    FT_FLUSH()
     // epilogue: O / l -> global, LSE
     const bool have = my_hi > lo;
     if (have && ok) {
@@ -435,6 +489,12 @@ static int launch_fwd(const cgk_flash_args& a, const FlashFwdDev& p, cudaStream_
 }  // namespace cgk
 
 using namespace cgk;
+
+#ifdef CGK_FLASH_TIMING
+CGK_API int cgk_flash_fwd_times(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, cgk::g_flash_fwd_times, 64);
+}
+#endif
 
 CGK_API int cgk_flash_forward(const cgk_flash_args* pa, void* stream) {
   CGK_REQUIRE(pa, "cgk_flash_forward: null args");

@@ -66,6 +66,14 @@ static EncodeTiledFn get_encode() {
 
 int encode_tmap(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int rank,
                 const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box, Swz swz) {
+  // A thread that has made no runtime call yet (an autograd worker thread, say)
+  // has no current driver context, and the driver-API encoder then fails with
+  // CUDA_ERROR_INVALID_CONTEXT; a no-op runtime call binds the primary context.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   EncodeTiledFn fn = get_encode();
   if (!fn) {
     set_error("cuTensorMapEncodeTiled is not available from this driver");

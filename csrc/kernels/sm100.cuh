@@ -85,6 +85,19 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 
+__device__ __forceinline__ uint32_t mbar_try_wait_suspend(uint32_t bar, uint32_t parity,
+                                                          uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok;
+}
+
 // Bounded wait.  `dead` is a word in shared memory that every role of the CTA
 // polls; `status` is the global status word (may be null).  Returns false when
 // the wait gave up (now or earlier).
@@ -93,7 +106,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t it = 1; it < CGK_WAIT_MAX_ITERS; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
+    // The suspending form parks the thread in hardware until the phase completes
+    // or the hint (ns) expires, so a waiting role does not eat the issue slots
+    // of the warps that share its scheduler.
+    if (mbar_try_wait_suspend(bar, parity, 2000u)) return true;
     if ((it & 127u) == 0u) {
       if (*dead) return false;
       if (globaltimer_ns() - t0 > CGK_WAIT_BUDGET_NS) break;
@@ -211,6 +227,15 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src,
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(m), "r"(src), "r"(x), "r"(y)
                : "memory");
+}
+// Bulk tensor reduction shared -> global: global[tile] += shared[tile] (element type
+// and operation width come from the tensor map; out-of-range parts are clipped).
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, uint32_t src, int x, int y,
+                                                  int z) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+      ::"l"(m), "r"(src), "r"(x), "r"(y), "r"(z)
+      : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -393,9 +418,13 @@ __device__ __forceinline__ float dsilu_f(float x) {
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {
+#ifdef CGK_EXPERIMENT_EXP_OFF
+  return x * 0.001f;
+#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+#endif
 }
 // Vector reduction into global memory (16-byte aligned).
 __device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, float c, float d) {
@@ -405,8 +434,12 @@ __device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, flo
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+#ifdef CGK_EXPERIMENT_PACK_TRUNC
+  return __byte_perm(__float_as_uint(lo), __float_as_uint(hi), 0x7632);
+#else
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+#endif
 }
 __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
   __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);
