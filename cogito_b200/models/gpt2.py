@@ -16,6 +16,7 @@ from ..nn.transformer import TransformerBlock, TransformerConfig
 from ..ops import functional as F
 from ..ops import loss as L
 from ..ops import misc as M
+from ..utils import rng
 
 
 @dataclass
@@ -40,8 +41,10 @@ class GPT2(nn.Module):
     def __init__(self, cfg: GPT2Config = GPT2Config(), device=None, dtype=None):
         super().__init__()
         self.cfg = cfg
-        self.wte = nn.Parameter(torch.randn(cfg.vocab_size, cfg.d_model, device=device, dtype=dtype) * cfg.init_std)
-        self.wpe = nn.Parameter(torch.randn(cfg.max_seq_len, cfg.d_model, device=device, dtype=dtype) * cfg.init_std)
+        self.wte = nn.Parameter(rng.normal_(torch.empty(cfg.vocab_size, cfg.d_model, device=device, dtype=dtype),
+                                            cfg.init_std, rng.layer_generator()))
+        self.wpe = nn.Parameter(rng.normal_(torch.empty(cfg.max_seq_len, cfg.d_model, device=device, dtype=dtype),
+                                            cfg.init_std, rng.layer_generator()))
         bc = cfg.block_config()
         self.blocks = nn.ModuleList([TransformerBlock(bc, device, dtype) for _ in range(cfg.n_layer)])
         self.ln_f = LayerNorm(cfg.d_model, cfg.norm_eps, device=device, dtype=dtype)

@@ -19,6 +19,7 @@ from ..ops import functional as F
 from ..ops import loss as L
 from ..ops import misc as M
 from ..ops import norm as N
+from ..utils import rng
 from ..ops.attention import alibi_slopes, flash_attention, flash_attention_qkvpacked
 
 
@@ -36,11 +37,12 @@ class Linear(nn.Module):
         super().__init__()
         self.in_features, self.out_features, self.act = in_features, out_features, act
         w = torch.empty(out_features, in_features, device=device, dtype=dtype)
+        g = rng.layer_generator()
         if init_std is None:
             limit = math.sqrt(6.0 / (in_features + out_features))
-            nn.init.uniform_(w, -limit, limit)
+            rng.uniform_(w, -limit, limit, g)
         else:
-            nn.init.normal_(w, 0.0, init_std)
+            rng.normal_(w, init_std, g)
         self.weight = nn.Parameter(w)
         self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype)) if bias else None
 
@@ -155,7 +157,8 @@ class BatchNorm1d(nn.Module):
 class Embedding(nn.Module):
     def __init__(self, num_embeddings, dim, init_std=0.02, device=None, dtype=None):
         super().__init__()
-        self.weight = nn.Parameter(torch.randn(num_embeddings, dim, device=device, dtype=dtype) * init_std)
+        w = torch.empty(num_embeddings, dim, device=device, dtype=dtype)
+        self.weight = nn.Parameter(rng.normal_(w, init_std, rng.layer_generator()))
 
     def forward(self, ids, pos_weight=None):
         return M.embedding(ids, self.weight, pos_weight)

@@ -65,7 +65,7 @@ class _PackedAttention(torch.autograd.Function):
         # producer (a GEMM) does not need its own output for its backward, so
         # autograd is not told.  The rotated buffer is what gets saved.
         if rope is not None:
-            M.rope_apply_(x.detach()[:, :, :Hq + Hk], rope[0], rope[1])
+            M.rope_apply_(x.data[:, :, :Hq + Hk], rope[0], rope[1])   # .data: no version bump
         q, k, v = x[:, :, :Hq], x[:, :, Hq:Hq + Hk], x[:, :, Hq + Hk:]
         o, lse = flash_forward(q, k, v, causal=causal, window=window, scale=scale, alibi=alibi)
         ctx.save_for_backward(x, o, lse, alibi if alibi is not None else torch.empty(0))

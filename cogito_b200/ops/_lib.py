@@ -78,6 +78,8 @@ def _declare(L: ctypes.CDLL) -> None:
         "cgk_col2im": [i, vp, vp, i, i, i, i, i, i, i, i, i, ll, vp],
         "cgk_maxpool_forward": [vp, vp, vp, i, i, i, i, i, i, i, i, vp],
         "cgk_maxpool_backward": [vp, vp, vp, i, i, i, i, i, i, vp],
+        "cgk_rope_table": [vp, vp, i, i, f, vp],
+        "cgk_rope_apply": [i, vp, vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, i, vp],
     }
     for name, argtypes in sigs.items():
         fn = getattr(L, name, None)

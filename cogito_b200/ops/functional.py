@@ -78,7 +78,7 @@ class _Linear(torch.autograd.Function):
             x2 = x2.contiguous()
         r2 = residual.reshape(-1, w.shape[0]) if residual is not None else None
         need_aux = act not in (None, "none") and (x.requires_grad or w.requires_grad)
-        aux = torch.empty(x2.shape[0], w.shape[0], device=x.device, dtype=_BF16) if need_aux else None
+        aux = torch.empty(x2.shape[0], w.shape[0], device=x.device, dtype=x.dtype) if need_aux else None
         y = gemm(x2, w, bias=b, act=act, residual=r2, aux_out=aux)
         ctx.save_for_backward(x2, w, aux if aux is not None else torch.empty(0))
         ctx.act = act
@@ -122,7 +122,7 @@ class _MLP(torch.autograd.Function):
         if x2.stride(-1) != 1:
             x2 = x2.contiguous()
         M = x2.shape[0]
-        z = torch.empty(M, w1.shape[0], device=x.device, dtype=_BF16)
+        z = torch.empty(M, w1.shape[0], device=x.device, dtype=x.dtype)
         h = gemm(x2, w1, bias=b1, act=act, aux_out=z)
         r2 = residual.reshape(M, -1) if residual is not None else None
         y = gemm(h, w2, bias=b2, residual=r2)

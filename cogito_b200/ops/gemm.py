@@ -50,7 +50,7 @@ def gemm_reference(a, b, *, a_mn=False, b_mn=False, bias=None, act=None, residua
     v = alpha * (A @ B)
     if bias is not None:
         v = v + bias.float()
-    aux = v.to(torch.bfloat16) if want_aux else None
+    aux = v.to(a.dtype) if want_aux else None   # bf16 operands: the kernel stores the pre-activation in bf16
     v = _act_cpu(act, v)
     if aux_in is not None:
         v = v * _dact_cpu(dact, aux_in.float())
@@ -99,10 +99,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         batch *= s
 
     if not a.is_cuda:
+        cpu_dtype = out_dtype if a.dtype == torch.bfloat16 else a.dtype   # fp32 in -> fp32 out on the host
         ref = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, act=act, residual=residual,
                              aux_in=aux_in, dact=dact, alpha=alpha,
                              accumulate_into=out if accumulate else None,
-                             out_dtype=out.dtype if out is not None else out_dtype,
+                             out_dtype=out.dtype if out is not None else cpu_dtype,
                              want_aux=aux_out is not None)
         if aux_out is not None:
             ref, aux = ref

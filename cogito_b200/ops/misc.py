@@ -187,18 +187,12 @@ def rope_apply_(x, cos_t, sin_t, pos_offset: int = 0, positions=None, backward: 
         pos = pos.clamp(0, cos_t.shape[0] - 1)
         c = cos_t[pos][:, :, None, :]
         s = sin_t[pos][:, :, None, :] * (-1.0 if backward else 1.0)
-        a, b = x[..., :half].float(), x[..., half:].float()
+        a, b = x[..., :half].float().clone(), x[..., half:].float().clone()
         x[..., :half] = (a * c - b * s).to(x.dtype)
         x[..., half:] = (b * c + a * s).to(x.dtype)
         return x
     assert x.stride(3) == 1
     L = _lib.lib()
-    if not hasattr(L, "_rope_declared"):
-        from ctypes import c_float, c_int, c_longlong, c_void_p
-        L.cgk_rope_apply.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                     c_longlong, c_longlong, c_longlong, c_int, c_int, c_int, c_void_p]
-        L.cgk_rope_table.argtypes = [c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]
-        L._rope_declared = True
     if positions is not None:
         positions = positions.to(torch.int32).contiguous()
     _lib.check(L.cgk_rope_apply(_dt(x), x.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(), _lib.ptr(positions),
