@@ -45,7 +45,8 @@ class CogitoJob(_Job):
                 from .parallel.data_parallel import DataParallel
                 parallel = DataParallel(self.model, rank, world, dev)
         scaler = GradScaler(dev, enabled=False)
-        self.opt = FusedAdam(self.model.parameters(), lr=1e-4, scaler=scaler)
+        params = getattr(self.model, "_ordered", None) or list(self.model.parameters())
+        self.opt = FusedAdam(params, lr=1e-4, scaler=scaler)
         if parallel is not None and hasattr(parallel, "attach"):
             parallel.attach(self.opt)
         mb = args.micro_batch

@@ -1,0 +1,203 @@
+"""Fused tensor-parallel primitives: all-gather -> GEMM and GEMM -> reduce-scatter,
+each ONE kernel (``cgk_ag_gemm`` / ``cgk_gemm_rs``, csrc/comm/fused_tp.cu).
+
+``TPWorkspace`` owns the symmetric memory the kernels need: the activation-shard
+buffer and the handshake words of the all-gather, and the double-buffered partial
+slots and arrival counters of the reduce-scatter.  CPU tensors (gloo ranks, or one
+rank) take a reference path built from ``torch.distributed`` collectives, which is
+also the oracle of the GPU tests.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_int32, c_int64, c_void_p
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..ops.gemm import _ld, gemm
+from .symm import SymmetricBuffer
+
+
+class AgArgs(Structure):
+    _fields_ = [("rank", c_int32), ("ranks", c_int32), ("epoch", c_int32), ("chunk_rows", c_int32),
+                ("shard_ptrs", c_void_p * 8), ("signal_ptrs", c_void_p * 8),
+                ("chunk_flags", c_void_p), ("done_count", c_void_p), ("n_copy_ctas", c_int32)]
+
+
+class RsArgs(Structure):
+    _fields_ = [("rank", c_int32), ("ranks", c_int32), ("reserved", c_int32),
+                ("staging_ptrs", c_void_p * 8), ("flag_ptrs", c_void_p * 8),
+                ("ld", c_int64), ("slot_elems", c_int64), ("bias", c_void_p), ("residual", c_void_p),
+                ("ldr", c_int64), ("out", c_void_p), ("ldo", c_int64), ("n_reduce_ctas", c_int32)]
+
+
+_declared = False
+
+
+def _fns():
+    global _declared
+    L = _lib.lib()
+    if not _declared:
+        L.cgk_ag_gemm.argtypes = [POINTER(_lib.GemmArgs), POINTER(AgArgs), c_void_p]
+        L.cgk_gemm_rs.argtypes = [POINTER(_lib.GemmArgs), POINTER(RsArgs), c_void_p]
+        _declared = True
+    return L
+
+
+class TPWorkspace:
+    """Symmetric scratch of one tensor-parallel group on one device.
+
+    max_rows: largest M (gathered rows) of any call; max_cols: largest K of an
+    all-gather / N of a reduce-scatter."""
+
+    def __init__(self, device, group=None, max_rows: int = 16384, max_cols: int = 4096,
+                 chunk_rows: int = 256, copy_ctas: int = 0, reduce_ctas: int = 0):
+        self.device = torch.device(device)
+        self.group = group
+        self.ranks = 1 if group is None else dist.get_world_size(group)
+        self.rank = 0 if group is None else dist.get_rank(group)
+        P = self.ranks
+        self.max_rows, self.max_cols, self.chunk_rows = max_rows, max_cols, chunk_rows
+        self.copy_ctas, self.reduce_ctas = copy_ctas, reduce_ctas
+        self.cuda = self.device.type == "cuda"
+        self.epoch = 0
+        self.parity = 0
+        if not self.cuda:
+            return
+        shard_rows = (max_rows + P - 1) // P
+        self.shard_bytes = shard_rows * max_cols * 2
+        self.sig_off = (self.shard_bytes + 255) // 256 * 256
+        sig_bytes = 256
+        self.slot_elems = shard_rows * max_cols
+        self.stage_off = self.sig_off + sig_bytes
+        stage_bytes = 2 * P * self.slot_elems * 2
+        self.flag_off = (self.stage_off + stage_bytes + 255) // 256 * 256
+        self.flag_words = (shard_rows + 127) // 128
+        flag_bytes = (2 * self.flag_words * 4 + 255) // 256 * 256
+        self.buf = SymmetricBuffer(self.flag_off + flag_bytes, self.device, group)
+        self.shard = self.buf.view(0, (self.shard_bytes,), torch.uint8)
+        nchunks = P * ((shard_rows + chunk_rows - 1) // chunk_rows)
+        self.chunk_flags = torch.zeros(nchunks, dtype=torch.int32, device=self.device)
+        self.done_count = torch.zeros(P, dtype=torch.int32, device=self.device)
+
+    # ------------------------------------------------------------------
+    def shard_view(self, rows: int, cols: int) -> torch.Tensor:
+        return self.buf.view(0, (rows, cols), torch.bfloat16)
+
+
+def _fill_gemm(g, a, b, out, M, N, K, b_mn):
+    g.A, g.B = a.data_ptr(), b.data_ptr()
+    g.out = out.data_ptr() if out is not None else a.data_ptr()
+    g.M, g.N, g.K, g.batch = M, N, K, 1
+    g.lda, g.ldb = _ld(a), _ld(b)
+    g.ldc = _ld(out) if out is not None else N
+    g.a_mn, g.b_mn = 0, int(b_mn)
+    g.alpha = 1.0
+
+
+def ag_gemm(ws: TPWorkspace, x_shard: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False,
+            bias=None, act=None, aux_out=None, out_dtype=torch.bfloat16):
+    """Returns (out [M, N], gathered [M, K]) with M = ranks * x_shard.shape[0].
+
+    out = act(gather(x_shard) @ W^T + bias); ``w`` is [N, K] (or [K, N] with b_mn)."""
+    rows, K = x_shard.shape
+    P = ws.ranks
+    M = rows * P
+    N = w.shape[1] if b_mn else w.shape[0]
+    if not x_shard.is_cuda:
+        if P > 1:
+            parts = [torch.empty_like(x_shard) for _ in range(P)]
+            dist.all_gather(parts, x_shard.contiguous(), group=ws.group)
+            gathered = torch.cat(parts, 0)
+        else:
+            gathered = x_shard
+        out = gemm(gathered, w, b_mn=b_mn, bias=bias, act=act, aux_out=aux_out, out_dtype=out_dtype)
+        return out, gathered
+    if rows % 128 or K % 8:
+        raise ValueError("ag_gemm: rows per rank must be a multiple of 128 and K of 8")
+    if rows * K * 2 > ws.shard_bytes:
+        raise ValueError("ag_gemm: shard larger than the workspace")
+    # the shard must sit in symmetric memory for the peers to read it
+    sv = ws.shard_view(rows, K)
+    if x_shard.data_ptr() != sv.data_ptr():
+        sv.copy_(x_shard)
+    gathered = torch.empty(M, K, device=x_shard.device, dtype=torch.bfloat16)
+    out = torch.empty(M, N, device=x_shard.device, dtype=out_dtype)
+    g = _lib.GemmArgs()
+    _fill_gemm(g, gathered, w, out, M, N, K, b_mn)
+    g.out_fp32 = int(out_dtype == torch.float32)
+    if bias is not None:
+        g.bias, g.bias_fp32 = bias.data_ptr(), int(bias.dtype == torch.float32)
+    g.act = {"none": 0, None: 0, "gelu": 1, "relu": 2, "silu": 3, "sigmoid": 4, "tanh": 5}[act]
+    if aux_out is not None:
+        g.aux_out, g.ldaux = aux_out.data_ptr(), _ld(aux_out)
+    ws.epoch += 1
+    a = AgArgs()
+    a.rank, a.ranks, a.epoch = ws.rank, P, ws.epoch
+    chunk = min(ws.chunk_rows, rows)
+    a.chunk_rows = chunk
+    for r, p in enumerate(ws.buf.peer_ptrs(0)):
+        a.shard_ptrs[r] = p
+    for r, p in enumerate(ws.buf.peer_ptrs(ws.sig_off)):
+        a.signal_ptrs[r] = p
+    a.chunk_flags = ws.chunk_flags.data_ptr()
+    a.done_count = ws.done_count.data_ptr()
+    a.n_copy_ctas = ws.copy_ctas
+    _lib.check(_fns().cgk_ag_gemm(ctypes.byref(g), ctypes.byref(a), _lib.stream_ptr()), "cgk_ag_gemm")
+    _lib.count_launch()
+    return out, gathered
+
+
+def gemm_rs(ws: TPWorkspace, x: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False, bias=None,
+            residual=None):
+    """out_shard [M/ranks, N] = bias + residual + rows-of-this-rank( sum_p x_p @ W_p^T ).
+
+    ``x``: this rank's [M, K_local]; ``w``: [N, K_local] (or [K_local, N] with b_mn)."""
+    M, K = x.shape
+    P = ws.ranks
+    N = w.shape[1] if b_mn else w.shape[0]
+    rows = M // P
+    if not x.is_cuda:
+        partial = gemm(x, w, b_mn=b_mn, out_dtype=torch.float32 if x.dtype == torch.bfloat16 else x.dtype)
+        if P > 1:
+            partial = partial.to(x.dtype).float()       # the kernel ships bf16 partials
+            parts = list(partial.chunk(P, 0))
+            mine = torch.empty_like(parts[0])
+            dist.reduce_scatter(mine, [p.contiguous() for p in parts], group=ws.group)
+        else:
+            mine = partial.float()
+        if bias is not None:
+            mine = mine + bias.float()
+        if residual is not None:
+            mine = mine + residual.float()
+        return mine.to(x.dtype)
+    if M % P or rows % 128 or N % 8:
+        raise ValueError("gemm_rs: rows per rank must be a multiple of 128 and N of 8")
+    if rows * N > ws.slot_elems:
+        raise ValueError("gemm_rs: output shard larger than the workspace")
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    out = torch.empty(rows, N, device=x.device, dtype=torch.bfloat16)
+    g = _lib.GemmArgs()
+    _fill_gemm(g, x, w, None, M, N, K, b_mn)
+    r = RsArgs()
+    r.rank, r.ranks = ws.rank, P
+    par = ws.parity
+    ws.parity ^= 1
+    stage = ws.stage_off + par * P * ws.slot_elems * 2
+    for i, p in enumerate(ws.buf.peer_ptrs(stage)):
+        r.staging_ptrs[i] = p
+    for i, p in enumerate(ws.buf.peer_ptrs(ws.flag_off + par * ws.flag_words * 4)):
+        r.flag_ptrs[i] = p
+    r.ld, r.slot_elems = N, ws.slot_elems
+    if bias is not None:
+        r.bias = bias.data_ptr()
+    if residual is not None:
+        r.residual, r.ldr = residual.data_ptr(), _ld(residual)
+    r.out, r.ldo = out.data_ptr(), N
+    r.n_reduce_ctas = ws.reduce_ctas
+    _lib.check(_fns().cgk_gemm_rs(ctypes.byref(g), ctypes.byref(r), _lib.stream_ptr()), "cgk_gemm_rs")
+    _lib.count_launch()
+    return out

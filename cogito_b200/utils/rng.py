@@ -17,15 +17,16 @@ def manual_seed(seed: int) -> None:
     _state["count"] = 0
 
 
-def layer_generator() -> torch.Generator:
-    """A CPU generator for the next constructed layer."""
+def layer_generator(salt: int = 0) -> torch.Generator:
+    """A CPU generator for the next constructed layer.  `salt` separates the streams of
+    ranks that each build a different shard of the same layer (tensor parallelism)."""
     seed = torch.initial_seed()
     if _state["seed"] != seed:
         _state["seed"] = seed
         _state["count"] = 0
     _state["count"] += 1
     g = torch.Generator()
-    g.manual_seed((seed * 1000003 + 7919 * _state["count"]) % (2 ** 63 - 1))
+    g.manual_seed((seed * 1000003 + 7919 * _state["count"] + 104729 * salt) % (2 ** 63 - 1))
     return g
 
 

@@ -1,0 +1,284 @@
+// Device body of the tcgen05 bf16 GEMM, shared by the plain GEMM kernel and by the
+// fused compute + collective kernels (all-gather -> GEMM, GEMM -> reduce-scatter).
+// See gemm_tcgen05.cu for the description of the pipeline.
+#pragma once
+#include "../../include/cogito_kernels.h"
+#include "sm100.cuh"
+
+namespace cgk {
+
+constexpr int GEMM_MAX_RANKS = 8;
+
+struct GemmDev {
+  int M, N, K, batch;
+  int tiles_m, tiles_n;
+  int a_mn, b_mn;
+  void* out;
+  long long ldc, strideC;
+  int out_fp32, accumulate;
+  float alpha;
+  const void* bias;
+  int bias_fp32;
+  int act;
+  const __nv_bfloat16* residual;
+  long long ldr;
+  __nv_bfloat16* aux_out;
+  long long ldaux;
+  const __nv_bfloat16* aux_in;
+  long long ldauxin;
+  int dact;
+  int* status;
+  // ---- hooks used by the fused kernels (all off when zero / null) ----
+  // A-operand readiness: before loading rows [m0, m0+128) of A the producer waits
+  // until a_ready[m0 / a_ready_rows] >= a_ready_target (flags set by the copy CTAs
+  // of the same kernel).
+  const int* a_ready;
+  int a_ready_rows;
+  int a_ready_target;
+  // m-tile rotation: tile index tm is processed as (tm + m_rot) % tiles_m, so each
+  // rank starts with the rows that are available / needed first.
+  int m_rot;
+  // Reduce-scatter epilogue: rows [o*rs_rows, (o+1)*rs_rows) of the result belong to
+  // rank o and are stored (bf16) at rs_dst[o] + (row - o*rs_rows)*ldc + col; after a
+  // tile is stored, rs_flag[o][(row - o*rs_rows) / 128] is incremented (system scope).
+  int rs_ranks;
+  int rs_rows;
+  __nv_bfloat16* rs_dst[GEMM_MAX_RANKS];
+  int* rs_flag[GEMM_MAX_RANKS];
+};
+
+__device__ __forceinline__ float apply_act(int act, float v) {
+  switch (act) {
+    case CGK_ACT_GELU: return gelu_tanh(v);
+    case CGK_ACT_RELU: return fmaxf(v, 0.0f);
+    case CGK_ACT_SILU: return silu_f(v);
+    case CGK_ACT_SIGMOID: return 1.0f / (1.0f + __expf(-v));
+    case CGK_ACT_TANH: return tanhf(v);
+    default: return v;
+  }
+}
+__device__ __forceinline__ float apply_dact(int act, float x) {
+  switch (act) {
+    case CGK_ACT_GELU: return dgelu_tanh(x);
+    case CGK_ACT_RELU: return x > 0.0f ? 1.0f : 0.0f;
+    case CGK_ACT_SILU: return dsilu_f(x);
+    case CGK_ACT_SIGMOID: { float s = 1.0f / (1.0f + __expf(-x)); return s * (1.0f - s); }
+    case CGK_ACT_TANH: { float t = tanhf(x); return 1.0f - t * t; }
+    default: return 1.0f;
+  }
+}
+
+// Where element (b, m, n) of the result goes.
+__device__ __forceinline__ void* out_address(const GemmDev& g, int b, int m, int n, bool& fp32) {
+  if (g.rs_ranks > 0) {
+    const int o = m / g.rs_rows;
+    fp32 = false;
+    return g.rs_dst[o] + (long long)(m - o * g.rs_rows) * g.ldc + n;
+  }
+  fp32 = g.out_fp32 != 0;
+  const long long off = (long long)b * g.strideC + (long long)m * g.ldc + n;
+  return fp32 ? (void*)(reinterpret_cast<float*>(g.out) + off)
+              : (void*)(reinterpret_cast<__nv_bfloat16*>(g.out) + off);
+}
+
+// Epilogue for one element; shared by the tensor-core kernel's ragged path and
+// the CUDA-core fallback.
+__device__ __forceinline__ void epilogue_scalar(const GemmDev& g, int b, int m, int n, float acc) {
+  float v = g.alpha * acc;
+  if (g.bias) {
+    v += g.bias_fp32 ? reinterpret_cast<const float*>(g.bias)[n]
+                     : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(g.bias)[n]);
+  }
+  if (g.aux_out) g.aux_out[(long long)m * g.ldaux + n] = __float2bfloat16(v);
+  v = apply_act(g.act, v);
+  if (g.aux_in) v *= apply_dact(g.dact, __bfloat162float(g.aux_in[(long long)m * g.ldauxin + n]));
+  if (g.residual) v += __bfloat162float(g.residual[(long long)m * g.ldr + n]);
+  bool fp32;
+  void* dst = out_address(g, b, m, n, fp32);
+  if (fp32) {
+    float* p = reinterpret_cast<float*>(dst);
+    *p = g.accumulate ? (*p + v) : v;
+  } else {
+    __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(dst);
+    *p = __float2bfloat16(g.accumulate ? (__bfloat162float(*p) + v) : v);
+  }
+}
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int GROUP_M = 8;
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ void tile_coords(const GemmDev& g, int t, int& b, int& tm, int& tn) {
+  const int per_batch = g.tiles_m * g.tiles_n;
+  b = t / per_batch;
+  int r = t - b * per_batch;
+  if (g.rs_ranks > 0 || g.a_ready) {
+    // fused kernels walk the result one row of tiles after the other, so that rows
+    // complete (or become available) in a known order
+    tm = r / g.tiles_n;
+    tn = r - tm * g.tiles_n;
+  } else {
+    const int group_sz = GROUP_M * g.tiles_n;
+    const int gidx = r / group_sz;
+    const int first_m = gidx * GROUP_M;
+    const int rows_in_group = min(GROUP_M, g.tiles_m - first_m);
+    const int rr = r - gidx * group_sz;
+    tm = first_m + rr % rows_in_group;
+    tn = rr / rows_in_group;
+  }
+  if (g.m_rot) tm = (tm + g.m_rot) % g.tiles_m;
+}
+
+// cta / nctas: index and count of the CTAs that run this body (the fused kernels
+// give some CTAs of the grid other roles).  256 threads.
+template <int BN, int STAGES>
+__device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUtensorMap& tmB,
+                                             const GemmDev& g, int cta, int nctas,
+                                             uint8_t* smem_raw) {
+  using L = GemmSmem<BN, STAGES>;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::BAR_OFFSET;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + L::BAR_OFFSET + L::NUM_BARS * 8);
+  volatile int* dead = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 128);
+    }
+    *dead = 0;
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int total_tiles = g.batch * g.tiles_m * g.tiles_n;
+  const int kblocks = (g.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      uint32_t kit = 0;
+      bool ok = true;
+      int last_ready_chunk = -1;
+      for (int t = cta; t < total_tiles && ok; t += nctas) {
+        int b, tm, tn;
+        tile_coords(g, t, b, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        if (g.a_ready) {
+          // rows of this tile may span two chunks when a_ready_rows < 128: wait for the last one
+          const int last_row = min(m0 + BM, g.M) - 1;
+          for (int ch = m0 / g.a_ready_rows; ch <= last_row / g.a_ready_rows && ok; ++ch) {
+            if (ch == last_ready_chunk) continue;
+            if (!flag_wait_ge_gpu(g.a_ready + ch, g.a_ready_target, dead, g.status, 110)) ok = false;
+            last_ready_chunk = ch;
+          }
+          if (!ok) break;
+          // the rows were written through the generic proxy by other CTAs
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        for (int kb = 0; kb < kblocks; ++kb, ++kit) {
+          const int s = kit % STAGES;
+          const uint32_t ph = (kit / STAGES) & 1u;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, dead, g.status, 100)) { ok = false; break; }
+          const uint32_t sA = smem_base + s * L::STAGE_BYTES;
+          const uint32_t sB = sA + L::A_BYTES;
+          mbar_expect_tx(full_bar(s), L::STAGE_BYTES);
+          if (!g.a_mn) {
+            tma_load_3d(sA, &tmA, full_bar(s), kb * BK, m0, b);
+          } else {
+#pragma unroll
+            for (int blk = 0; blk < BM / 64; ++blk)
+              tma_load_3d(sA + blk * 8192, &tmA, full_bar(s), m0 + blk * 64, kb * BK, b);
+          }
+          if (!g.b_mn) {
+            tma_load_3d(sB, &tmB, full_bar(s), kb * BK, n0, b);
+          } else {
+#pragma unroll
+            for (int blk = 0; blk < BN / 64; ++blk)
+              tma_load_3d(sB + blk * 8192, &tmB, full_bar(s), n0 + blk * 64, kb * BK, b);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(BM, BN, g.a_mn, g.b_mn);
+      const uint32_t a_lbo = g.a_mn ? 8192u : 16u;
+      const uint32_t b_lbo = g.b_mn ? 8192u : 16u;
+      const uint32_t a_kstep = g.a_mn ? 2048u : 32u;  // bytes per 16 K elements
+      const uint32_t b_kstep = g.b_mn ? 2048u : 32u;
+      uint32_t kit = 0;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = cta; t < total_tiles && ok; t += nctas, ++it) {
+        const int acc = it & 1;
+        const uint32_t aph = (it >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(acc), aph ^ 1u, dead, g.status, 200)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++kit) {
+          const int s = kit % STAGES;
+          const uint32_t ph = (kit / STAGES) & 1u;
+          if (!mbar_wait(full_bar(s), ph, dead, g.status, 201)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = smem_base + s * L::STAGE_BYTES;
+          const uint32_t sB = sA + L::A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t ad = make_smem_desc_sw128(sA + kk * a_kstep, a_lbo, 1024u);
+            const uint64_t bd = make_smem_desc_sw128(sB + kk * b_kstep, b_lbo, 1024u);
+            umma_f16(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+        }
+        if (ok) umma_commit(tfull_bar(acc));
+      }
+    }
+  } else if (warp >= 4) {
+#include "gemm_tc_epilogue.inc"
+  }
+
+  // A role that gave up leaves copies in flight; give them time to land before
+  // the shared memory and TMEM are released.
+  if (*dead) __nanosleep(100000);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace cgk

@@ -60,6 +60,40 @@ typedef struct {
 
 int cgk_gemm_bf16(const cgk_gemm_args* args, void* stream);
 
+/* ---- Fused tensor-parallel kernels (csrc/comm/fused_tp.cu) -------------------- */
+/* All pointer tables are indexed by rank and hold addresses valid on THIS GPU
+ * (peer mappings of symmetric memory); entry [rank] is the local buffer. */
+typedef struct {
+  int32_t rank, ranks;
+  int32_t epoch;            /* > 0; one more than on the previous call with this workspace */
+  int32_t chunk_rows;       /* rows per readiness flag, a multiple of 128 */
+  const void* shard_ptrs[8];   /* [M/ranks, K] bf16 activation shard of each rank */
+  void* signal_ptrs[8];        /* int32[2*ranks] per rank: ready words, then done words */
+  int32_t* chunk_flags;        /* local int32[ranks * ceil(rows/chunk_rows)] */
+  int32_t* done_count;         /* local int32[ranks], zero on entry, zero on exit */
+  int32_t n_copy_ctas;         /* 0 = default */
+} cgk_ag_args;
+
+typedef struct {
+  int32_t rank, ranks;
+  int32_t reserved;
+  void* staging_ptrs[8];    /* per rank: bf16 [ranks][M/ranks][ld] partial slots */
+  void* flag_ptrs[8];       /* per rank: int32[(M/ranks)/128] arrival counters, zero on entry and on exit */
+  int64_t ld;               /* leading dimension of a slot row */
+  int64_t slot_elems;       /* elements between slots */
+  const void* bias;         /* bf16 [N] or null, added after the reduction */
+  const void* residual;     /* bf16 [M/ranks, ldr] or null */
+  int64_t ldr;
+  void* out;                /* bf16 [M/ranks, ldo] */
+  int64_t ldo;
+  int32_t n_reduce_ctas;    /* 0 = default */
+} cgk_rs_args;
+
+/* g->A is the LOCAL gathered buffer [M, K] (filled by the kernel, M = ranks * shard rows). */
+int cgk_ag_gemm(const cgk_gemm_args* g, const cgk_ag_args* x, void* stream);
+/* g describes this rank's partial product [M, N]; g->out is ignored. */
+int cgk_gemm_rs(const cgk_gemm_args* g, const cgk_rs_args* x, void* stream);
+
 /* ---- Flash attention ------------------------------------------------------ */
 /* Tensors are bf16 [batch, seq, heads, head_dim] with head_dim contiguous and the
  * given element strides (batch, token, head), all multiples of 8.  lse is fp32

@@ -1,0 +1,86 @@
+"""Multi-rank logic on CPU ranks (gloo): rank arithmetic, process groups, tensor-parallel
+GPT-2 equivalence with the single-device model."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from cogito_b200.parallel.groups import Coords, group_ranks, rank_of
+
+
+def test_rank_mapping_matches_reference_arithmetic():
+    dp, tp, pp = 2, 2, 2
+    seen = set()
+    for r in range(8):
+        c = Coords(r, dp, tp, pp)
+        assert c.tp_rank == r % tp and c.pp_rank == (r // tp) % pp and c.dp_rank == r // (tp * pp)
+        assert rank_of(c.dp_rank, c.pp_rank, c.tp_rank, tp, pp) == r
+        assert c.tp_color() == c.dp_rank * pp + c.pp_rank
+        assert c.pp_color() == c.dp_rank * tp + c.tp_rank
+        assert c.dp_color() == c.pp_rank * tp + c.tp_rank
+        seen.add((c.dp_rank, c.pp_rank, c.tp_rank))
+    assert len(seen) == 8
+    tpg, ppg, dpg = group_ranks(8, dp, tp, pp)
+    assert sorted(map(tuple, tpg.values())) == [(0, 1), (2, 3), (4, 5), (6, 7)]
+    assert sorted(map(tuple, ppg.values())) == [(0, 2), (1, 3), (4, 6), (5, 7)]
+    assert sorted(map(tuple, dpg.values())) == [(0, 4), (1, 5), (2, 6), (3, 7)]
+    with pytest.raises(ValueError):
+        group_ranks(8, 2, 2, 3)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _tp_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from cogito_b200.models.gpt2 import GPT2, GPT2Config
+        from cogito_b200.optim.fused import FusedAdam
+        from cogito_b200.parallel.tensor_parallel import build_tp_gpt2, shard_gpt2_state
+        from cogito_b200.train import Trainer
+        from cogito_b200.utils.rng import manual_seed
+        manual_seed(0)
+        cfg = GPT2Config(vocab_size=64, n_layer=2, d_model=32, n_head=4, d_ff=64, max_seq_len=16)
+        full = GPT2(cfg)
+        tp, sync = build_tp_gpt2(cfg, rank, world, "cpu", dist.group.WORLD, micro_tokens=64)
+        shard_gpt2_state(full, tp)
+        g = torch.Generator().manual_seed(1)
+        ids = torch.randint(0, 64, (4, 16), generator=g)
+        tg = torch.randint(0, 64, (4, 16), generator=g)
+        of = FusedAdam(full.parameters(), lr=1e-2)
+        ot = FusedAdam(tp._ordered, lr=1e-2)
+        sync.attach(ot)
+        tf = Trainer(full, of, micro_batch=4)
+        tt = Trainer(tp, ot, micro_batch=4, parallel=sync)
+        lf = [float(tf.step(ids, tg)) for _ in range(4)]
+        lt = [float(tt.step(ids, tg)) for _ in range(4)]
+        q.put((rank, lf, lt))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_gpt2_matches_single_device_on_two_cpu_ranks():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, lf, lt in res:
+        assert lf[-1] < lf[0]
+        for a, b in zip(lf, lt):
+            assert abs(a - b) < 2e-3, (rank, lf, lt)
