@@ -27,10 +27,11 @@ class AgArgs(Structure):
 
 
 class RsArgs(Structure):
-    _fields_ = [("rank", c_int32), ("ranks", c_int32), ("reserved", c_int32),
+    _fields_ = [("rank", c_int32), ("ranks", c_int32), ("queue_base", c_int32),
                 ("staging_ptrs", c_void_p * 8), ("flag_ptrs", c_void_p * 8),
                 ("ld", c_int64), ("slot_elems", c_int64), ("bias", c_void_p), ("residual", c_void_p),
-                ("ldr", c_int64), ("out", c_void_p), ("ldo", c_int64), ("n_reduce_ctas", c_int32)]
+                ("ldr", c_int64), ("out", c_void_p), ("ldo", c_int64), ("n_reduce_ctas", c_int32),
+                ("queue", c_void_p)]
 
 
 _declared = False
@@ -42,6 +43,7 @@ def _fns():
     if not _declared:
         L.cgk_ag_gemm.argtypes = [POINTER(_lib.GemmArgs), POINTER(AgArgs), c_void_p]
         L.cgk_gemm_rs.argtypes = [POINTER(_lib.GemmArgs), POINTER(RsArgs), c_void_p]
+        L.cgk_gemm_rs_queue_step.argtypes = [ctypes.c_int, ctypes.c_int]
         _declared = True
     return L
 
@@ -81,6 +83,8 @@ class TPWorkspace:
         nchunks = P * ((shard_rows + chunk_rows - 1) // chunk_rows)
         self.chunk_flags = torch.zeros(nchunks, dtype=torch.int32, device=self.device)
         self.done_count = torch.zeros(P, dtype=torch.int32, device=self.device)
+        self.rs_queue = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.rs_queue_base = 0
 
     # ------------------------------------------------------------------
     def shard_view(self, rows: int, cols: int) -> torch.Tensor:
@@ -124,6 +128,7 @@ def ag_gemm(ws: TPWorkspace, x_shard: torch.Tensor, w: torch.Tensor, *, b_mn: bo
     if x_shard.data_ptr() != sv.data_ptr():
         sv.copy_(x_shard)
     gathered = torch.empty(M, K, device=x_shard.device, dtype=torch.bfloat16)
+    gathered[ws.rank * rows:(ws.rank + 1) * rows].copy_(x_shard)     # own rows: in place before the launch
     out = torch.empty(M, N, device=x_shard.device, dtype=out_dtype)
     g = _lib.GemmArgs()
     _fill_gemm(g, gathered, w, out, M, N, K, b_mn)
@@ -198,6 +203,13 @@ def gemm_rs(ws: TPWorkspace, x: torch.Tensor, w: torch.Tensor, *, b_mn: bool = F
         r.residual, r.ldr = residual.data_ptr(), _ld(residual)
     r.out, r.ldo = out.data_ptr(), N
     r.n_reduce_ctas = ws.reduce_ctas
+    r.queue = ws.rs_queue.data_ptr()
+    r.queue_base = ws.rs_queue_base
+    ws.rs_queue_base += _fns().cgk_gemm_rs_queue_step(M, P)
+    if ws.rs_queue_base > 2 ** 30:       # keep the counter far from overflow
+        torch.cuda.current_stream().synchronize()
+        ws.rs_queue.zero_()
+        ws.rs_queue_base = 0
     _lib.check(_fns().cgk_gemm_rs(ctypes.byref(g), ctypes.byref(r), _lib.stream_ptr()), "cgk_gemm_rs")
     _lib.count_launch()
     return out

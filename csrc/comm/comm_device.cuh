@@ -54,7 +54,7 @@ __device__ __forceinline__ bool relay_copy(Relay& r, const uint8_t* src, uint8_t
   // reading shared memory; since at least idx - RELAY_AHEAD + 1 stores are committed
   // when piece idx is loaded, "at most RELAY_STAGES - RELAY_AHEAD stores still
   // reading" implies that.
-  constexpr int RELAY_AHEAD = 4;
+  constexpr int RELAY_AHEAD = 6;
   long long issued = 0, stored = 0;
   const uint32_t base = r.count;
   while (stored < pieces) {

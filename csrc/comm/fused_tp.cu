@@ -69,10 +69,12 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int p = 0; p < P; ++p)
       if (p != me) st_release_sys(a.sig[p] + me, a.epoch);
   }
-  const int items = P * a.chunks_per_shard;
+  // the own shard is copied into the gathered buffer before the launch; only the
+  // peers' shards go through the relay, nearest ring neighbour first
+  const int items = (P - 1) * a.chunks_per_shard;
   bool ok = true;
   for (int it = c; it < items && ok; it += a.n_copy) {
-    const int d = it / a.chunks_per_shard, j = it % a.chunks_per_shard;
+    const int d = 1 + it / a.chunks_per_shard, j = it % a.chunks_per_shard;
     const int src = (me + d) % P;
     if (src != me) {
       if (!flag_wait_ge_sys(my_sig + src, a.epoch, g.status, 3000 + src, CGK_PEER_WAIT_BUDGET_NS)) { ok = false; break; }
@@ -105,6 +107,8 @@ struct RsDev {
   int N;
   int target;               // flag value that marks a row block complete
   int* flags;               // local, [rows / 128]; a row block's counter is cleared once it is reduced
+  int* queue;               // local work counter, grows by (blocks + CTAs) per call
+  int queue_base;           // its value when this call starts
   const __nv_bfloat16* staging;   // local, [P][rows][ld]
   long long ld;             // leading dimension of a slot
   long long slot_elems;
@@ -120,57 +124,78 @@ __global__ void __launch_bounds__(256, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const GemmDev g, const RsDev r) {
   extern __shared__ uint8_t smem_raw[];
-  if ((int)blockIdx.x >= r.n_reduce) {
+  if ((int)blockIdx.x >= r.n_reduce)
     gemm_tc_body<BN, STAGES>(tmA, tmB, g, (int)blockIdx.x - r.n_reduce, (int)gridDim.x - r.n_reduce,
                              smem_raw);
-    return;
-  }
-  // ------------------------------ reduce CTAs ------------------------------
-  __shared__ int ok_word;
+  // ------------------------------ reduce phase ------------------------------
+  // A few CTAs reduce from the start; every GEMM CTA joins once it has run out of
+  // tiles.  Row blocks are handed out in order through one counter.
+  __shared__ int rb_word;
   const int blocks = (r.rows + 127) / 128;
   const int vec_per_row = r.N >> 3;
-  for (int rb = (int)blockIdx.x; rb < blocks; rb += r.n_reduce) {
-    if (threadIdx.x == 0)
-      ok_word = flag_wait_ge_sys(r.flags + rb, r.target, g.status, 3200, CGK_PEER_WAIT_BUDGET_NS) ? 1 : 0;
+  for (;;) {
     __syncthreads();
-    if (!ok_word) return;
+    if (threadIdx.x == 0) {
+      int rb = atomicAdd(r.queue, 1) - r.queue_base;
+      if (rb < blocks && !flag_wait_ge_sys(r.flags + rb, r.target, g.status, 3200, CGK_PEER_WAIT_BUDGET_NS))
+        rb = blocks;     // give up: the status word says why
+      rb_word = rb;
+    }
+    __syncthreads();
+    const int rb = rb_word;
+    if (rb >= blocks) break;
     const int row0 = rb * 128;
     const int nrows = min(128, r.rows - row0);
-    for (int i = threadIdx.x; i < nrows * vec_per_row; i += blockDim.x) {
-      const int row = row0 + i / vec_per_row, v = i % vec_per_row;
-      float acc[8];
+    // U vectors per thread per round so that about eight 16-byte loads are in flight
+    const int U = r.ranks >= 8 ? 1 : (r.ranks >= 4 ? 2 : (r.ranks >= 2 ? 4 : 8));
+    const int total = nrows * vec_per_row;
+    for (int i0 = threadIdx.x; i0 < total; i0 += blockDim.x * U) {
+      uint4 ld[8];
+#pragma unroll 4
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i >= total) break;
+        const int row = row0 + i / vec_per_row, v = i % vec_per_row;
+        float acc[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
-      for (int s = 0; s < r.ranks; ++s) {
-        // peers wrote these lines; read them past the L1
-        const uint4 u = __ldcg(reinterpret_cast<const uint4*>(r.staging + s * r.slot_elems +
-                                                              (long long)row * r.ld) + v);
-        float2 f;
-        f = unpack_bf16x2(u.x); acc[0] += f.x; acc[1] += f.y;
-        f = unpack_bf16x2(u.y); acc[2] += f.x; acc[3] += f.y;
-        f = unpack_bf16x2(u.z); acc[4] += f.x; acc[5] += f.y;
-        f = unpack_bf16x2(u.w); acc[6] += f.x; acc[7] += f.y;
+        for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+        // peers wrote these lines; read them past the L1.  The loads of all slots are
+        // issued before the first add.
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          if (s < r.ranks)
+            ld[s] = __ldcg(reinterpret_cast<const uint4*>(r.staging + s * r.slot_elems + (long long)row * r.ld) + v);
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          if (s < r.ranks) {
+            float2 f;
+            f = unpack_bf16x2(ld[s].x); acc[0] += f.x; acc[1] += f.y;
+            f = unpack_bf16x2(ld[s].y); acc[2] += f.x; acc[3] += f.y;
+            f = unpack_bf16x2(ld[s].z); acc[4] += f.x; acc[5] += f.y;
+            f = unpack_bf16x2(ld[s].w); acc[6] += f.x; acc[7] += f.y;
+          }
+        }
+        if (r.bias) {
+          const uint4 u4 = __ldg(reinterpret_cast<const uint4*>(r.bias) + v);
+          float2 f;
+          f = unpack_bf16x2(u4.x); acc[0] += f.x; acc[1] += f.y;
+          f = unpack_bf16x2(u4.y); acc[2] += f.x; acc[3] += f.y;
+          f = unpack_bf16x2(u4.z); acc[4] += f.x; acc[5] += f.y;
+          f = unpack_bf16x2(u4.w); acc[6] += f.x; acc[7] += f.y;
+        }
+        if (r.residual) {
+          const uint4 u4 = *(reinterpret_cast<const uint4*>(r.residual + (long long)row * r.ldr) + v);
+          float2 f;
+          f = unpack_bf16x2(u4.x); acc[0] += f.x; acc[1] += f.y;
+          f = unpack_bf16x2(u4.y); acc[2] += f.x; acc[3] += f.y;
+          f = unpack_bf16x2(u4.z); acc[4] += f.x; acc[5] += f.y;
+          f = unpack_bf16x2(u4.w); acc[6] += f.x; acc[7] += f.y;
+        }
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+        *(reinterpret_cast<uint4*>(r.out + (long long)row * r.ldo) + v) = o;
       }
-      if (r.bias) {
-        const uint4 u = __ldg(reinterpret_cast<const uint4*>(r.bias) + v);
-        float2 f;
-        f = unpack_bf16x2(u.x); acc[0] += f.x; acc[1] += f.y;
-        f = unpack_bf16x2(u.y); acc[2] += f.x; acc[3] += f.y;
-        f = unpack_bf16x2(u.z); acc[4] += f.x; acc[5] += f.y;
-        f = unpack_bf16x2(u.w); acc[6] += f.x; acc[7] += f.y;
-      }
-      if (r.residual) {
-        const uint4 u = *(reinterpret_cast<const uint4*>(r.residual + (long long)row * r.ldr) + v);
-        float2 f;
-        f = unpack_bf16x2(u.x); acc[0] += f.x; acc[1] += f.y;
-        f = unpack_bf16x2(u.y); acc[2] += f.x; acc[3] += f.y;
-        f = unpack_bf16x2(u.z); acc[4] += f.x; acc[5] += f.y;
-        f = unpack_bf16x2(u.w); acc[6] += f.x; acc[7] += f.y;
-      }
-      uint4 o;
-      o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-      o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
-      *(reinterpret_cast<uint4*>(r.out + (long long)row * r.ldo) + v) = o;
     }
     // every arrival of this call has been counted; the next writers of this counter
     // belong to a later call on the same buffer parity, which cannot start before
@@ -243,12 +268,14 @@ CGK_API int cgk_ag_gemm(const cgk_gemm_args* pg, const cgk_ag_args* px, void* st
   a.chunk_flags = x.chunk_flags;
   a.done_count = x.done_count;
   const int sms = sm_count(dev);
-  a.n_copy = x.n_copy_ctas > 0 ? x.n_copy_ctas : (x.ranks > 1 ? 12 : 2);
+  a.n_copy = x.n_copy_ctas > 0 ? x.n_copy_ctas : (x.ranks > 1 ? 20 : 1);
   if (a.n_copy > sms / 2) a.n_copy = sms / 2;
   g.a_ready = a.chunk_flags;
   g.a_ready_rows = x.chunk_rows;
   g.a_ready_target = x.epoch;
   g.m_rot = x.rank * (rows / BM);
+  g.a_ready_skip_first = x.rank * a.chunks_per_shard;
+  g.a_ready_skip_count = a.chunks_per_shard;
   const int gemm_ctas = sms - a.n_copy;
   switch (pick_bn(ga, gemm_ctas)) {
     case 256: return launch_ag<256, 4>(ga, g, a, sms, (cudaStream_t)stream);
@@ -276,7 +303,7 @@ CGK_API int cgk_gemm_rs(const cgk_gemm_args* pg, const cgk_rs_args* px, void* st
   if (rc) return rc;
   const int rows = ga.M / x.ranks;
   const int sms = sm_count(dev);
-  int n_reduce = x.n_reduce_ctas > 0 ? x.n_reduce_ctas : 16;
+  int n_reduce = x.n_reduce_ctas > 0 ? x.n_reduce_ctas : 8;
   if (n_reduce > sms / 2) n_reduce = sms / 2;
   const int gemm_ctas = sms - n_reduce;
   const int bn = pick_bn(ga, gemm_ctas);
@@ -294,6 +321,8 @@ CGK_API int cgk_gemm_rs(const cgk_gemm_args* pg, const cgk_rs_args* px, void* st
   r.rows = rows; r.N = ga.N;
   r.target = x.ranks * ((ga.N + 63) / 64);
   r.flags = (int*)x.flag_ptrs[x.rank];
+  r.queue = x.queue;
+  r.queue_base = x.queue_base;
   r.staging = (const __nv_bfloat16*)x.staging_ptrs[x.rank];
   r.ld = x.ld; r.slot_elems = x.slot_elems;
   r.bias = (const __nv_bfloat16*)x.bias;
@@ -304,4 +333,12 @@ CGK_API int cgk_gemm_rs(const cgk_gemm_args* pg, const cgk_rs_args* px, void* st
     case 128: return launch_rs<128, 6>(ga, g, r, sms, (cudaStream_t)stream);
     default: return launch_rs<64, 8>(ga, g, r, sms, (cudaStream_t)stream);
   }
+}
+
+// Every CTA of the launch takes one ticket past the last row block before it leaves.
+CGK_API int cgk_gemm_rs_queue_step(int M, int ranks) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int rows = M / (ranks > 0 ? ranks : 1);
+  return (rows + 127) / 128 + sm_count(dev);
 }

@@ -35,6 +35,7 @@ struct GemmDev {
   const int* a_ready;
   int a_ready_rows;
   int a_ready_target;
+  int a_ready_skip_first, a_ready_skip_count;   // chunks that are in place before the launch
   // m-tile rotation: tile index tm is processed as (tm + m_rot) % tiles_m, so each
   // rank starts with the rows that are available / needed first.
   int m_rot;
@@ -115,7 +116,9 @@ struct GemmSmem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4;
-  static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;  // + alignment slack
+  // per-warp transposition area of the reduce-scatter epilogue (4 warps x 4 KiB)
+  static constexpr int EPI_OFFSET = (BAR_OFFSET + NUM_BARS * 8 + 16 + 127) / 128 * 128;
+  static constexpr int TOTAL = EPI_OFFSET + 4 * 4096 + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ void tile_coords(const GemmDev& g, int t, int& b, int& tm, int& tn) {
@@ -201,6 +204,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUten
           const int last_row = min(m0 + BM, g.M) - 1;
           for (int ch = m0 / g.a_ready_rows; ch <= last_row / g.a_ready_rows && ok; ++ch) {
             if (ch == last_ready_chunk) continue;
+            if (ch >= g.a_ready_skip_first && ch < g.a_ready_skip_first + g.a_ready_skip_count) continue;
             if (!flag_wait_ge_gpu(g.a_ready + ch, g.a_ready_target, dead, g.status, 110)) ok = false;
             last_ready_chunk = ch;
           }

@@ -76,7 +76,8 @@ typedef struct {
 
 typedef struct {
   int32_t rank, ranks;
-  int32_t reserved;
+  int32_t queue_base;       /* value of *queue when the call starts: the sum over earlier calls
+                               of (row blocks + CTAs of the launch); see cgk_gemm_rs_queue_step */
   void* staging_ptrs[8];    /* per rank: bf16 [ranks][M/ranks][ld] partial slots */
   void* flag_ptrs[8];       /* per rank: int32[(M/ranks)/128] arrival counters, zero on entry and on exit */
   int64_t ld;               /* leading dimension of a slot row */
@@ -87,12 +88,15 @@ typedef struct {
   void* out;                /* bf16 [M/ranks, ldo] */
   int64_t ldo;
   int32_t n_reduce_ctas;    /* 0 = default */
+  int32_t* queue;           /* local int32 work counter, zero before the first call */
 } cgk_rs_args;
 
 /* g->A is the LOCAL gathered buffer [M, K] (filled by the kernel, M = ranks * shard rows). */
 int cgk_ag_gemm(const cgk_gemm_args* g, const cgk_ag_args* x, void* stream);
 /* g describes this rank's partial product [M, N]; g->out is ignored. */
 int cgk_gemm_rs(const cgk_gemm_args* g, const cgk_rs_args* x, void* stream);
+/* By how much one cgk_gemm_rs call with M rows advances *queue on the current device. */
+int cgk_gemm_rs_queue_step(int M, int ranks);
 
 /* ---- Flash attention ------------------------------------------------------ */
 /* Tensors are bf16 [batch, seq, heads, head_dim] with head_dim contiguous and the
