@@ -46,7 +46,10 @@ class CogitoJob(_Job):
                 parallel = DataParallel(self.model, rank, world, dev)
         scaler = GradScaler(dev, enabled=False)
         params = getattr(self.model, "_ordered", None) or list(self.model.parameters())
-        self.opt = FusedAdam(params, lr=1e-4, scaler=scaler)
+        if world > 1 and args.parallelism == "dp":
+            self.opt = parallel.make_optimizer(lr=1e-4, scaler=scaler)      # fused all-reduce + Adam kernel
+        else:
+            self.opt = FusedAdam(params, lr=1e-4, scaler=scaler)
         if parallel is not None and hasattr(parallel, "attach"):
             parallel.attach(self.opt)
         mb = args.micro_batch

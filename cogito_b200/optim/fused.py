@@ -25,7 +25,9 @@ class FlatParams:
     """Flattens parameters into one buffer (padded per tensor to 16 bytes worth of
     elements) and keeps per-parameter views."""
 
-    def __init__(self, params, align: int = 8):
+    def __init__(self, params, align: int = 8, alloc=None, pad_to: int = 1):
+        """alloc(nelems, dtype) -> 1-D tensor lets the caller place the flat buffer (for
+        instance in symmetric memory); pad_to rounds the total length up."""
         self.params = [p for p in params if p.requires_grad]
         if not self.params:
             raise ValueError("no trainable parameters")
@@ -38,8 +40,12 @@ class FlatParams:
                 raise ValueError("all parameters must live on one device")
             self.offsets.append(off)
             off += (p.numel() + align - 1) // align * align
-        self.total = off
-        self.flat = torch.zeros(self.total, device=self.device, dtype=self.dtype)
+        self.total = (off + pad_to - 1) // pad_to * pad_to
+        if alloc is not None:
+            self.flat = alloc(self.total, self.dtype)
+            self.flat.zero_()
+        else:
+            self.flat = torch.zeros(self.total, device=self.device, dtype=self.dtype)
         for p, o in zip(self.params, self.offsets):
             view = self.flat[o:o + p.numel()].view(p.shape)
             view.copy_(p.data)

@@ -98,6 +98,33 @@ int cgk_gemm_rs(const cgk_gemm_args* g, const cgk_rs_args* x, void* stream);
 /* By how much one cgk_gemm_rs call with M rows advances *queue on the current device. */
 int cgk_gemm_rs_queue_step(int M, int ranks);
 
+/* ---- Fused data-parallel optimizer step (csrc/comm/dp_adam.cu) ------------------ */
+/* Pointer tables are indexed by rank (peer mappings of symmetric memory).  This rank
+ * owns elements [begin, begin + count) of the flat parameter space. */
+typedef struct {
+  int32_t rank, ranks, epoch;      /* epoch > 0, +1 per call */
+  int32_t grid_ctas;               /* CTAs to launch, <= SM count (all must be resident) */
+  const void* grad_ptrs[8];        /* fp32 flat gradients of every rank */
+  void* param_lp_ptrs[8];          /* bf16 flat parameters of every rank, or all null */
+  void* param_fp_ptrs[8];          /* fp32 flat parameters of every rank (used when no bf16 copy) */
+  void* signal_ptrs[8];            /* int32[64] per rank, zero before the first call */
+  float* master;                   /* local fp32 master slice [count], or null */
+  float* m; float* v;              /* local Adam moments [count] */
+  float* gsum;                     /* local scratch [count] */
+  int64_t begin, count;
+  float lr, beta1, beta2, eps, weight_decay, max_grad_norm;
+  float grad_mul;                  /* multiplies the summed gradient (1/ranks = mean) */
+  float growth, backoff, min_scale, max_scale;
+  int32_t window;
+  void* scaler;                    /* local scaler state (cgk_scaler_state_bytes) */
+  float* block_part;               /* local scratch [2 * grid_ctas] */
+  void* grid_bar;                  /* local uint32 counter, zero before the first call */
+  uint32_t grid_bar_base;          /* 2 * grid_ctas * (number of earlier calls) */
+} cgk_dp_adam_args;
+
+int cgk_dp_adam_step(const cgk_dp_adam_args* args, void* stream);
+int cgk_dp_adam_max_ctas(void);
+
 /* ---- Flash attention ------------------------------------------------------ */
 /* Tensors are bf16 [batch, seq, heads, head_dim] with head_dim contiguous and the
  * given element strides (batch, token, head), all multiples of 8.  lse is fp32

@@ -84,3 +84,49 @@ def test_tensor_parallel_gpt2_matches_single_device_on_two_cpu_ranks():
         assert lf[-1] < lf[0]
         for a, b in zip(lf, lt):
             assert abs(a - b) < 2e-3, (rank, lf, lt)
+
+
+def _dp_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from cogito_b200.optim.fused import FusedAdam
+        from cogito_b200.parallel.data_parallel import DPFusedAdam
+        from cogito_b200 import nn as cnn
+        from cogito_b200.ops import loss as L
+        from cogito_b200.utils.rng import manual_seed
+        manual_seed(0)
+        mk = lambda: cnn.Sequential(cnn.Linear(12, 16, act="relu"), cnn.Linear(16, 4))
+        ref, dp = mk(), mk()
+        dp.load_state_dict(ref.state_dict())
+        o_ref = FusedAdam(ref.parameters(), lr=1e-2, master_weights=False)
+        o_dp = DPFusedAdam(dp.parameters(), dist.group.WORLD, lr=1e-2)
+        g = torch.Generator().manual_seed(3)
+        X = torch.randn(8, 12, generator=g)
+        Y = torch.randint(0, 4, (8,), generator=g)
+        for _ in range(5):
+            o_ref.zero_grad(); o_dp.zero_grad()
+            L.softmax_cross_entropy_small(ref(X), Y).backward()
+            half = slice(rank * 4, rank * 4 + 4)
+            L.softmax_cross_entropy_small(dp(X[half]), Y[half]).backward()
+            o_ref.step(); o_dp.step()
+        diff = max(float((a - b).abs().max()) for a, b in zip(ref.parameters(), dp.parameters()))
+        q.put((rank, diff))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_dp_fused_adam_matches_full_batch_on_two_cpu_ranks():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_dp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, diff in res:
+        assert diff < 1e-5, (rank, diff)
