@@ -116,7 +116,9 @@ def build_capi(verbose: bool = False) -> Path:
         return out
     cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
     _build(srcs, hdrs, out, [cxx] + CXX_FLAGS + ["-I", str(ROOT / "include")],
-           [cxx, "-shared", "-fPIC", "-lpthread", "-ldl"], "capi", verbose)
+           # a toolchain that links libstdc++ statically must not export (or be interposed on)
+           # its copy inside a process that already holds another libstdc++
+           [cxx, "-shared", "-fPIC", "-Wl,--exclude-libs,ALL", "-Wl,-Bsymbolic", "-lpthread", "-ldl"], "capi", verbose)
     return out
 
 
