@@ -80,6 +80,15 @@ def _declare(L: ctypes.CDLL) -> None:
         "cgk_maxpool_backward": [vp, vp, vp, i, i, i, i, i, i, vp],
         "cgk_rope_table": [vp, vp, i, i, f, vp],
         "cgk_rope_apply": [i, vp, vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, i, vp],
+        "cgk_int4_quantize": [vp, ll, i, vp, vp, vp],
+        "cgk_int4_dequantize": [vp, vp, ll, i, vp, vp, vp],
+        "cgk_int4_gemm": [vp, ll, vp, vp, vp, vp, ll, vp, i, i, i, i, vp],
+        "cgk_int4_tile_weights": [vp, vp, i, i, i, vp, vp],
+        "cgk_kv_int4_append": [vp, vp, vp, i, vp],
+        "cgk_kv_int4_attention": [vp, vp, vp, i, i, f, i, vp, vp],
+        "cgk_sample": [vp, i, ll, i, i, f, i, f, c_ulonglong, vp, vp, vp, vp],
+        "cgk_spec_accept": [vp, vp, vp, i, i, i, c_ulonglong, vp, vp, vp, vp, vp, vp],
+        "cgk_tree_mask": [vp, i, i, vp, vp, vp],
     }
     for name, argtypes in sigs.items():
         fn = getattr(L, name, None)
@@ -89,6 +98,9 @@ def _declare(L: ctypes.CDLL) -> None:
     for name, argtypes in {
         "cgk_norm_backward_scratch_elems": [i, i],
         "cgk_colsum_scratch_elems": [ll, i],
+        "cgk_kv_int4_attention_scratch_floats": [i, i, i, i, i],
+        "cgk_int4_tiles_bytes": [i, i],
+        "cgk_int4_gemm_counters": [i, i],
     }.items():
         fn = getattr(L, name)
         fn.argtypes = argtypes

@@ -1,0 +1,186 @@
+"""INT4 Llama serving engine and the draft/verify speculative decoding loop.
+
+One engine step runs ``Tq`` new tokens per sequence through the model against the paged INT4
+KV cache: RMSNorm -> INT4 GEMM (q|k|v) -> RoPE at the sequence's own positions -> quantise and
+append K/V -> attention over the cache -> INT4 GEMM (+ residual) -> RMSNorm -> INT4 GEMM
+(gate|up) -> SwiGLU -> INT4 GEMM (+ residual).  The cache lengths move only when the caller
+commits, so a verify pass over ``gamma + 1`` tokens followed by a partial commit is the rollback
+of the rejected positions.
+
+Reference counterparts: cg_speculative_decoder / cg_speculative_generate / cg_draft_generate /
+cg_target_verify (include/cg_speculative.h:30-112, generate/step/draft/verify declared only),
+cg_matmul_int4 and cg_kv_cache_int4_* (src/quantize/int4.c:90-289).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..models.llama import Llama, LlamaConfig
+from ..ops import misc as M
+from ..ops.norm import rms_norm
+from ..quant.int4 import Int4Linear
+from .kv_cache import PagedKVCacheInt4
+from .sampling import sample, spec_accept
+
+
+class LlamaInt4Engine:
+    def __init__(self, model: Llama, batch: int, max_seq_len: int | None = None, weight_group: int = 128,
+                 kv_group: int = 32, page_size: int = 64):
+        cfg: LlamaConfig = model.cfg
+        self.cfg = cfg
+        dev = model.wte.device
+        self.device = dev
+        self.dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+        self.wte = model.wte.detach().to(self.dtype)
+        self.layers = []
+        for blk in model.blocks:
+            self.layers.append(dict(
+                norm1=blk.norm1.weight.detach().to(self.dtype), norm2=blk.norm2.weight.detach().to(self.dtype),
+                qkv=Int4Linear.from_linear(blk.attn.qkv, weight_group), proj=Int4Linear.from_linear(blk.attn.proj, weight_group),
+                gate_up=Int4Linear.from_linear(blk.mlp.gate_up, weight_group), down=Int4Linear.from_linear(blk.mlp.down, weight_group)))
+        self.norm_f = model.norm_f.weight.detach().to(self.dtype)
+        self.lm_head = Int4Linear.from_linear(model.lm_head, weight_group)
+        self.max_seq_len = max_seq_len or cfg.max_seq_len
+        self.cache = PagedKVCacheInt4(cfg.n_layer, batch, self.max_seq_len, cfg.n_kv_head, cfg.head_dim, kv_group,
+                                      page_size, dev)
+        self.rope = M.rope_tables(self.max_seq_len, cfg.head_dim, cfg.rope_theta, dev)
+        self.batch = batch
+
+    def weight_bytes(self) -> int:
+        n = 0
+        for l in self.layers:
+            for k in ("qkv", "proj", "gate_up", "down"):
+                n += l[k].packed.numel() + l[k].scales.numel() * 4
+        return n + self.lm_head.packed.numel() + self.lm_head.scales.numel() * 4
+
+    def reset(self):
+        self.cache.reset()
+
+    @torch.no_grad()
+    def forward(self, tokens: torch.Tensor, commit: bool = False) -> torch.Tensor:
+        """tokens [batch, Tq] (int) at positions lengths[b] + t -> logits [batch, Tq, V] (fp32)."""
+        cfg = self.cfg
+        B, Tq = tokens.shape
+        Hq, Hk, D = cfg.n_head, cfg.n_kv_head, cfg.head_dim
+        x = self.wte[tokens.long()]                                            # [B, Tq, d]
+        positions = self.cache.lengths[:, None] + torch.arange(Tq, device=self.device, dtype=torch.int32)[None]
+        for i, l in enumerate(self.layers):
+            h = rms_norm(x, l["norm1"], cfg.norm_eps)
+            qkv = l["qkv"](h).view(B, Tq, Hq + 2 * Hk, D)
+            M.rope_apply_(qkv[:, :, :Hq + Hk], self.rope[0], self.rope[1], positions=positions)
+            self.cache.append(i, qkv[:, :, Hq:Hq + Hk], qkv[:, :, Hq + Hk:])
+            o = self.cache.attention(i, qkv[:, :, :Hq].contiguous())
+            x = x + l["proj"](o.reshape(B, Tq, Hq * D))
+            h = rms_norm(x, l["norm2"], cfg.norm_eps)
+            x = x + l["down"](M.swiglu(l["gate_up"](h)))
+        logits = self.lm_head(rms_norm(x, self.norm_f, cfg.norm_eps)).float()
+        if commit:
+            self.cache.commit(Tq)
+        return logits
+
+
+@dataclass
+class SpecStats:
+    steps: int = 0
+    drafted: int = 0
+    accepted: int = 0
+    generated: int = 0
+
+    @property
+    def acceptance_rate(self) -> float:
+        return self.accepted / self.drafted if self.drafted else 0.0
+
+
+class SpeculativeDecoder:
+    """Draft ``gamma`` tokens with the small engine, verify them with one pass of the large one,
+    accept / correct on the device, commit both caches to the accepted length."""
+
+    def __init__(self, draft: LlamaInt4Engine, target: LlamaInt4Engine, gamma: int = 4, temperature: float = 1.0,
+                 top_k: int = 50, top_p: float = 0.9, seed: int = 0):
+        if draft.cfg.vocab_size != target.cfg.vocab_size or draft.batch != target.batch:
+            raise ValueError("draft and target must share vocabulary and batch size")
+        self.draft, self.target, self.gamma = draft, target, gamma
+        self.temperature, self.top_k, self.top_p, self.seed = temperature, top_k, top_p, seed
+        self.stats = SpecStats()
+        dev = target.device
+        self._step = torch.zeros(1, dtype=torch.int64, device=dev)
+        self._stats_dev = torch.zeros(2, dtype=torch.int32, device=dev)
+
+    def _dist(self, logits2d, step, return_probs=True):
+        return sample(logits2d, self.temperature, self.top_k, self.top_p, self.seed, step, return_probs=return_probs)
+
+    @torch.no_grad()
+    def prefill(self, prompts: torch.Tensor) -> torch.Tensor:
+        """prompts [batch, L]: fills both caches with L-1 tokens and returns the last token of each
+        prompt, which is the first input of the decoding loop."""
+        self.draft.reset()
+        self.target.reset()
+        if prompts.shape[1] > 1:
+            self.draft.forward(prompts[:, :-1], commit=True)
+            self.target.forward(prompts[:, :-1], commit=True)
+        return prompts[:, -1].clone()
+
+    @torch.no_grad()
+    def step(self, last: torch.Tensor):
+        """last [batch]: newest token of every sequence, not yet in the caches.  Returns
+        (n_accepted [batch], out_tokens [batch, gamma + 1]); out_tokens[b, :n+1] extend sequence b."""
+        g, B = self.gamma, last.shape[0]
+        dev = self.target.device
+        V = self.target.cfg.vocab_size
+        self._step += 1
+        # ---- draft gamma tokens autoregressively
+        drafted = torch.empty(B, g, dtype=torch.int32, device=dev)
+        q = torch.empty(B, g, V, dtype=torch.float32, device=dev)
+        cur = last.view(B, 1)
+        base_len = self.draft.cache.lengths.clone()
+        for i in range(g):
+            logits = self.draft.forward(cur, commit=True)[:, 0]
+            tok, probs = self._dist(logits, self._step * 64 + i)
+            drafted[:, i], q[:, i] = tok, probs
+            cur = tok.view(B, 1)
+        # ---- one target pass over [last, d1 .. dg]
+        verify_in = torch.cat([last.view(B, 1).to(torch.int32), drafted], 1)
+        logits = self.target.forward(verify_in, commit=False)                     # [B, g+1, V]
+        _, p = self._dist(logits.view(B * (g + 1), V), self._step * 64 + 32)
+        p = p.view(B, g + 1, V)
+        # ---- accept / correct; the kernel advances the target lengths by n + 1
+        n_acc, out = spec_accept(drafted, q, p, self.seed, self._step, lengths=self.target.cache.lengths, stats=self._stats_dev)
+        # the draft cache holds last + d1..d(g-1); keep last + the accepted drafts that it has
+        self.draft.cache.lengths.copy_(base_len + torch.minimum(n_acc + 1, torch.full_like(n_acc, g)))
+        self._pending_all_accepted = n_acc == g
+        return n_acc, out
+
+    @torch.no_grad()
+    def generate(self, prompts: torch.Tensor, max_new_tokens: int):
+        """Returns a list of per-sequence token lists (prompt + generated) and the statistics."""
+        B = prompts.shape[0]
+        seqs = [prompts[b].tolist() for b in range(B)]
+        last = self.prefill(prompts)
+        produced = 0
+        while produced < max_new_tokens:
+            n_acc, out = self.step(last)
+            n_host, out_host = n_acc.tolist(), out.tolist()
+            # sequences that accepted every draft have not run d_g through the draft model yet
+            full = [b for b in range(B) if n_host[b] == self.gamma]
+            if full:
+                self._catch_up_draft(out, n_acc)
+            for b in range(B):
+                seqs[b].extend(out_host[b][:n_host[b] + 1])
+            last = out[torch.arange(B, device=out.device), n_acc.long()].clone()
+            self.stats.steps += 1
+            self.stats.drafted += self.gamma * B
+            self.stats.accepted += sum(n_host)
+            produced += min(n_host) + 1
+            self.stats.generated += sum(n + 1 for n in n_host)
+        return seqs, self.stats
+
+    def _catch_up_draft(self, out, n_acc):
+        """Where all gamma drafts were accepted the draft cache lacks d_gamma: run it through
+        (for every sequence, at its own position) and keep the result only for those rows."""
+        g = self.gamma
+        keep = (n_acc == g).to(torch.int32)
+        tok = out[:, g - 1].view(-1, 1)
+        self.draft.forward(tok, commit=False)
+        self.draft.cache.lengths += keep

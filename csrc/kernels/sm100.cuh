@@ -103,16 +103,17 @@ __device__ __forceinline__ uint32_t mbar_try_wait_suspend(uint32_t bar, uint32_t
 // the wait gave up (now or earlier).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* dead,
                                           int* status, int where) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  for (uint32_t it = 1; it < CGK_WAIT_MAX_ITERS; ++it) {
-    // The suspending form parks the thread in hardware until the phase completes
-    // or the hint (ns) expires, so a waiting role does not eat the issue slots
-    // of the warps that share its scheduler.
-    if (mbar_try_wait_suspend(bar, parity, 2000u)) return true;
-    if ((it & 127u) == 0u) {
+  // Plain try_wait: it already blocks for a short, hardware-chosen time.  The clock is not
+  // read before 256 polls have failed: a %globaltimer read costs about as much as a short
+  // pipeline step, and most waits end within a few polls.
+  uint64_t t0 = 0;
+  for (uint32_t it = 0; it < CGK_WAIT_MAX_ITERS; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 255u) {
       if (*dead) return false;
-      if (globaltimer_ns() - t0 > CGK_WAIT_BUDGET_NS) break;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > CGK_WAIT_BUDGET_NS) break;
     }
   }
   *dead = 1;
@@ -149,12 +150,13 @@ __device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
 // Wait until *flag >= want (system scope).  Returns false on timeout.
 __device__ __forceinline__ bool flag_wait_ge_sys(const int* flag, int want, int* status, int where,
                                                  uint64_t budget_ns = CGK_WAIT_BUDGET_NS) {
-  if (ld_acquire_sys(flag) >= want) return true;
-  const uint64_t t0 = globaltimer_ns();
-  for (uint32_t it = 1; it < CGK_WAIT_MAX_ITERS; ++it) {
+  uint64_t t0 = 0;                                   // read lazily: see mbar_wait
+  for (uint32_t it = 0; it < CGK_WAIT_MAX_ITERS; ++it) {
     if (ld_acquire_sys(flag) >= want) return true;
-    if ((it & 31u) == 0u) {
-      if (globaltimer_ns() - t0 > budget_ns) break;
+    if ((it & 31u) == 31u) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget_ns) break;
       __nanosleep(64);
     }
   }
@@ -163,13 +165,14 @@ __device__ __forceinline__ bool flag_wait_ge_sys(const int* flag, int want, int*
 }
 __device__ __forceinline__ bool flag_wait_ge_gpu(const int* flag, int want, volatile int* dead,
                                                  int* status, int where) {
-  if (ld_acquire_gpu(flag) >= want) return true;
-  const uint64_t t0 = globaltimer_ns();
-  for (uint32_t it = 1; it < CGK_WAIT_MAX_ITERS; ++it) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0; it < CGK_WAIT_MAX_ITERS; ++it) {
     if (ld_acquire_gpu(flag) >= want) return true;
-    if ((it & 31u) == 0u) {
+    if ((it & 31u) == 31u) {
       if (dead && *dead) return false;
-      if (globaltimer_ns() - t0 > CGK_WAIT_BUDGET_NS) break;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > CGK_WAIT_BUDGET_NS) break;
       __nanosleep(32);
     }
   }

@@ -157,6 +157,57 @@ typedef struct {
 int cgk_flash_forward(const cgk_flash_args* args, void* stream);
 int cgk_flash_backward(const cgk_flash_args* args, void* stream);
 
+/* ---- Serving: INT4 weights, paged INT4 KV cache, sampling, speculative decoding ---- */
+/* Packed INT4 format: groups of `group` consecutive elements of the row-major tensor,
+ * scale = absmax / 7 (1 when < 1e-10), q = clamp(round(x / scale), -8, 7), two values per
+ * byte with the even index in the low nibble, fp32 scales. */
+int cgk_int4_quantize(const float* x, long long n, int group, void* packed, float* scales, void* stream);
+int cgk_int4_dequantize(const void* packed, const float* scales, long long n, int group, float* out_f32,
+                        void* out_bf16, void* stream);
+/* Tile-major reordering of reference-format weights for cgk_int4_gemm: packed [K, N/2] bytes +
+ * fp32 scales per flat group -> [N/128][K/64][4608] (64 rows of 64 bytes, then fp32 scales
+ * [64][2]).  N % 128 == 0, K % 64 == 0, group a multiple of 64 dividing N. */
+long long cgk_int4_tiles_bytes(int K, int N);
+int cgk_int4_tile_weights(const void* packed, const float* scales, int K, int N, int group, void* tiles, void* stream);
+/* out[M,N] (bf16, leading dimension ldo) = x[M,K] (bf16) . dequant(w)[K,N] (+ bias).
+ * acc (fp32 [M, N]) and counters (int32 [cgk_int4_gemm_counters(M, N)]) serve split-K: zero
+ * before the first call, left zero by every call; both may be null, which forces one split.
+ * splits 0 = pick so that the SMs are covered in whole waves. */
+long long cgk_int4_gemm_counters(int M, int N);
+int cgk_int4_gemm(const void* x, long long ldx, const void* w_tiles, float* acc, int* counters, void* out,
+                  long long ldo, const void* bias, int M, int N, int K, int splits, void* stream);
+
+/* One layer of a paged INT4 KV cache: pages[num_pages][page_size][heads][D/2] bytes and
+ * scales[num_pages][page_size][heads][D/group] fp32 for K and V; page_table[batch][max_pages]
+ * maps logical to pool pages; lengths[batch] tokens are valid.  D 64 or 128. */
+typedef struct {
+  void* k_pages; void* v_pages; float* k_scales; float* v_scales;
+  const int32_t* page_table; const int32_t* lengths;
+  int32_t batch, heads, D, group, page_size, max_pages;
+} cgk_kv_args;
+/* k_new, v_new: bf16 [batch, T, heads, D]; written at positions lengths[b] .. lengths[b]+T-1
+ * (lengths is not changed: cgk_spec_accept or the caller commits). */
+int cgk_kv_int4_append(const cgk_kv_args* a, const void* k_new, const void* v_new, int T, void* stream);
+long long cgk_kv_int4_attention_scratch_floats(int batch, int Hq, int Tq, int D, int splits);
+/* q, out: bf16 [batch, Tq, Hq, D]; the Tq newest tokens are already in the cache; query t sees
+ * keys 0 .. lengths[b] + t.  Hq a multiple of heads (grouped-query attention). */
+int cgk_kv_int4_attention(const cgk_kv_args* a, const void* q, void* out, int Tq, int Hq, float scale,
+                          int splits, float* scratch, void* stream);
+/* Per row: logits / temperature -> top_k (1..1024, 0 = 1024) -> top_p -> sample.  temperature
+ * <= 0: argmax.  Random stream = (seed, row, *step).  probs_out: fp32 [rows, V] or null. */
+int cgk_sample(const void* logits, int logits_bf16, long long ld, int rows, int V, float temperature, int top_k,
+               float top_p, unsigned long long seed, const long long* step, int* tokens, float* probs_out,
+               void* stream);
+/* draft_tokens [B, gamma]; q [B, gamma, V]; p [B, gamma+1, V].  Accept token i with probability
+ * min(1, p/q); replace the first rejected one by a sample of max(0, p - q); append a bonus token
+ * when all pass.  out_tokens [B, gamma+1]; lengths[b] += n_accepted[b] + 1 (null: untouched);
+ * stats[0] += gamma, stats[1] += accepted (null: untouched). */
+int cgk_spec_accept(const int* draft_tokens, const float* q, const float* p, int batch, int gamma, int V,
+                    unsigned long long seed, const long long* step, int* n_accepted, int* out_tokens,
+                    int* lengths, int* stats, void* stream);
+/* mask [(L+n), (L+n)], 0 or -1e9: causal prefix; tree node i sees the prefix, its ancestors, itself. */
+int cgk_tree_mask(const int* parents, int n, int L, float* mask_f32, void* mask_bf16, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
