@@ -69,9 +69,11 @@ class ParallelContext:
     tp_group: object = None
     pp_group: object = None
     dp_group: object = None
+    mp_group: object = None          # all ranks of one model replica (same dp rank)
     tp_ranks: list = field(default_factory=list)
     pp_ranks: list = field(default_factory=list)
     dp_ranks: list = field(default_factory=list)
+    mp_ranks: list = field(default_factory=list)
 
     @property
     def prev_stage(self) -> int | None:
@@ -101,4 +103,9 @@ def init_parallel(dp: int = 1, tp: int = 1, pp: int = 1) -> ParallelContext:
             if rank in ranks:
                 setattr(ctx, attr, g)
                 setattr(ctx, rattr, ranks)
+    for d in range(dp):
+        ranks = [r for r in range(world) if Coords(r, dp, tp, pp).dp_rank == d]
+        g = dist.new_group(ranks)
+        if rank in ranks:
+            ctx.mp_group, ctx.mp_ranks = g, ranks
     return ctx

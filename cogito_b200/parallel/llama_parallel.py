@@ -1,0 +1,232 @@
+"""Llama under DP x TP x PP: tensor-parallel blocks (grouped-query attention with RoPE,
+SwiGLU) on the fused all-gather->GEMM / GEMM->reduce-scatter kernels, split into pipeline
+stages that run the 1F1B schedule, replicated over data-parallel groups whose optimizer step
+is the fused all-reduce + Adam kernel.
+
+Reference counterparts: cg_3d_parallel / cg_pipeline_parallel / cg_tensor_parallel_linear
+(include/cg_pipeline.h:44-75,170-200), rank mapping src/pipeline/pipeline.c (tp fastest, then
+pp, then dp); the transformer switches of cg_transformer_config (include/cg_transformer.h).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from ..models.llama import LlamaConfig
+from ..nn.modules import RMSNorm
+from ..nn.transformer import packed_attention
+from ..ops import loss as L
+from ..ops import misc as M
+from ..optim.fused import FusedAdam, GradScaler
+from ..utils import rng
+from .data_parallel import DPFusedAdam
+from .groups import ParallelContext
+from .pipeline import PipelineExecutor
+from .tensor_parallel import _ColumnRow, _LMHead, _VocabParallelCE
+from .tp_ops import TPWorkspace
+
+
+class TPLlamaBlock(nn.Module):
+    def __init__(self, cfg: LlamaConfig, ws: TPWorkspace, device=None, dtype=None):
+        super().__init__()
+        P = ws.ranks
+        if cfg.n_head % P or cfg.n_kv_head % P or cfg.d_ff % P:
+            raise ValueError("heads, kv heads and d_ff must divide evenly over the tensor-parallel ranks")
+        self.cfg, self.ws = cfg, ws
+        self.hq, self.hk, self.hd, self.fl = cfg.n_head // P, cfg.n_kv_head // P, cfg.head_dim, cfg.d_ff // P
+        d = cfg.d_model
+        mk = lambda *shape: nn.Parameter(rng.normal_(torch.empty(*shape, device=device, dtype=dtype), cfg.init_std,
+                                                      rng.layer_generator(ws.rank + 1)))
+        self.norm1 = RMSNorm(d, cfg.norm_eps, device=device, dtype=dtype)
+        self.norm2 = RMSNorm(d, cfg.norm_eps, device=device, dtype=dtype)
+        self.w_qkv = mk((self.hq + 2 * self.hk) * self.hd, d)        # local q heads | k heads | v heads
+        self.w_proj = mk(d, self.hq * self.hd)
+        self.w_gate_up = mk(2 * self.fl, d)                          # local gate | up
+        self.w_down = mk(d, self.fl)
+        for p in list(self.norm1.parameters()) + list(self.norm2.parameters()):
+            p.tp_replicated = True
+        self._rope = None
+
+    def _tables(self, device):
+        if self._rope is None or self._rope[0].device != device:
+            self._rope = M.rope_tables(self.cfg.max_seq_len, self.hd, self.cfg.rope_theta, device)
+        return self._rope
+
+    def forward(self, x_shard, batch_tokens):
+        B, T = batch_tokens
+        Hq, Hk, D = self.hq, self.hk, self.hd
+        rope = self._tables(x_shard.device)
+
+        def attend(qkv):
+            x = qkv.view(B, T, Hq + 2 * Hk, D)
+            o = packed_attention(x, Hq, Hk, causal=True, scale=1.0 / math.sqrt(D), rope=rope)
+            return o.reshape(B * T, Hq * D)
+
+        x_shard = _ColumnRow.apply(self.norm1(x_shard), self.w_qkv, None, self.w_proj, None, None, x_shard, self.ws, attend)
+        return _ColumnRow.apply(self.norm2(x_shard), self.w_gate_up, None, self.w_down, None, None, x_shard, self.ws, M.swiglu)
+
+
+class _SeqShardEmbedding(torch.autograd.Function):
+    """Vocabulary-sharded embedding whose output is the sequence-sharded residual stream:
+    x_shard = reduce_scatter_r(wte_r[ids])."""
+
+    @staticmethod
+    def forward(ctx, ids, wte, ws):
+        B, T = ids.shape
+        P, r = ws.ranks, ws.rank
+        partial = M.embedding(ids, wte.detach(), None, r * wte.shape[0]).reshape(B * T, -1)
+        if P > 1:
+            shard = torch.empty(B * T // P, partial.shape[1], device=partial.device, dtype=partial.dtype)
+            dist.reduce_scatter_tensor(shard, partial.contiguous(), group=ws.group)
+        else:
+            shard = partial
+        ctx.save_for_backward(ids)
+        ctx.ws, ctx.wte = ws, wte
+        return shard
+
+    @staticmethod
+    def backward(ctx, dshard):
+        (ids,) = ctx.saved_tensors
+        ws, wte = ctx.ws, ctx.wte
+        P, r = ws.ranks, ws.rank
+        B, T = ids.shape
+        dshard = dshard.contiguous()
+        if P > 1:
+            full = torch.empty(B * T, dshard.shape[1], device=dshard.device, dtype=dshard.dtype)
+            dist.all_gather_into_tensor(full, dshard, group=ws.group)
+        else:
+            full = dshard
+        Vl = wte.shape[0]
+        local = ids.reshape(-1) - r * Vl
+        ok = (local >= 0) & (local < Vl)
+        target = wte.main_grad if getattr(wte, "main_grad", None) is not None else torch.zeros_like(wte, dtype=torch.float32)
+        target.index_add_(0, local[ok], full[ok].float())
+        return None, (None if getattr(wte, "main_grad", None) is not None else target.to(wte.dtype)), None
+
+
+class LlamaStage(nn.Module):
+    """The layers [first, last) of a Llama on one pipeline stage, tensor-parallel over `ws`.
+    The first stage owns the embedding, the last the final norm, the output head and the loss."""
+
+    def __init__(self, cfg: LlamaConfig, ws: TPWorkspace, stage: int, num_stages: int, device=None, dtype=None):
+        super().__init__()
+        if cfg.n_layer % num_stages:
+            raise ValueError("layers must divide evenly over the pipeline stages")
+        self.cfg, self.ws, self.stage, self.S = cfg, ws, stage, num_stages
+        per = cfg.n_layer // num_stages
+        self.first, self.last = stage * per, (stage + 1) * per
+        P = ws.ranks
+        if cfg.vocab_size % P:
+            raise ValueError("vocabulary must divide evenly over the tensor-parallel ranks")
+        Vl = cfg.vocab_size // P
+        mk = lambda *shape: nn.Parameter(rng.normal_(torch.empty(*shape, device=device, dtype=dtype), cfg.init_std,
+                                                      rng.layer_generator(ws.rank + 1)))
+        self.wte = mk(Vl, cfg.d_model) if stage == 0 else None
+        self.blocks = nn.ModuleList([TPLlamaBlock(cfg, ws, device, dtype) for _ in range(per)])
+        if stage == num_stages - 1:
+            self.norm_f = RMSNorm(cfg.d_model, cfg.norm_eps, device=device, dtype=dtype)
+            for p in self.norm_f.parameters():
+                p.tp_replicated = True
+            self.w_head = mk(Vl, cfg.d_model)
+        else:
+            self.norm_f, self.w_head = None, None
+
+    def forward(self, x, batch_tokens, targets=None, grad_scale=1.0):
+        """x: token ids [B, T] on the first stage, else the sequence-sharded activation
+        [B*T/tp, d].  Returns the activation, or the loss on the last stage when targets are given."""
+        if self.stage == 0:
+            x = _SeqShardEmbedding.apply(x, self.wte, self.ws)
+        for blk in self.blocks:
+            x = blk(x, batch_tokens)
+        if self.stage != self.S - 1:
+            return x
+        logits = _LMHead.apply(self.norm_f(x), self.w_head, self.ws)
+        if targets is None:
+            return logits
+        return _VocabParallelCE.apply(logits, targets, grad_scale, self.ws)
+
+    def ordered_parameters(self):
+        rep = [p for p in self.parameters() if getattr(p, "tp_replicated", False)]
+        shd = [p for p in self.parameters() if not getattr(p, "tp_replicated", False)]
+        return rep + shd
+
+
+def shard_llama_state(full, stage: LlamaStage) -> None:
+    """Copy the weights of a single-device ``Llama`` into this rank's stage / TP shards."""
+    cfg, ws = stage.cfg, stage.ws
+    P, r = ws.ranks, ws.rank
+    Hq, Hk, D, d, I = cfg.n_head, cfg.n_kv_head, cfg.head_dim, cfg.d_model, cfg.d_ff
+    hq, hk, fl, Vl = Hq // P, Hk // P, I // P, cfg.vocab_size // P
+
+    def put(dst, src):
+        with torch.no_grad():
+            dst.copy_(src.to(dst.device, dst.dtype))
+
+    if stage.wte is not None:
+        put(stage.wte, full.wte[r * Vl:(r + 1) * Vl])
+    for fb, tb in zip(list(full.blocks)[stage.first:stage.last], stage.blocks):
+        put(tb.norm1.weight, fb.norm1.weight); put(tb.norm2.weight, fb.norm2.weight)
+        w = fb.attn.qkv.weight
+        q, k, v = w[:Hq * D].view(Hq, D, d), w[Hq * D:(Hq + Hk) * D].view(Hk, D, d), w[(Hq + Hk) * D:].view(Hk, D, d)
+        put(tb.w_qkv, torch.cat([q[r * hq:(r + 1) * hq].reshape(-1, d), k[r * hk:(r + 1) * hk].reshape(-1, d),
+                                 v[r * hk:(r + 1) * hk].reshape(-1, d)]))
+        put(tb.w_proj, fb.attn.proj.weight[:, r * hq * D:(r + 1) * hq * D])
+        gu = fb.mlp.gate_up.weight
+        put(tb.w_gate_up, torch.cat([gu[r * fl:(r + 1) * fl], gu[I + r * fl:I + (r + 1) * fl]]))
+        put(tb.w_down, fb.mlp.down.weight[:, r * fl:(r + 1) * fl])
+    if stage.norm_f is not None:
+        put(stage.norm_f.weight, full.norm_f.weight)
+        put(stage.w_head, full.lm_head.weight[r * Vl:(r + 1) * Vl])
+
+
+class Trainer3D:
+    """One rank of a DP x TP x PP job.  ``step(ids, targets)`` takes this data-parallel replica's
+    batch [M * micro_batch, T] (every rank of the replica passes the same tensors) and runs M
+    micro-batches through the 1F1B schedule, then the optimizer step: replicated-parameter
+    gradients are summed over the TP group, all gradients averaged over the DP group inside
+    the fused Adam kernel (or a plain all-reduce on CPU ranks)."""
+
+    def __init__(self, cfg: LlamaConfig, ctx: ParallelContext, device, num_microbatches: int, micro_batch: int, seq_len: int,
+                 lr: float = 1e-4, loss_scale: float | None = 65536.0, max_grad_norm: float = 1.0, weight_decay: float = 0.0):
+        self.cfg, self.ctx, self.device = cfg, ctx, torch.device(device)
+        self.M, self.mb, self.T = num_microbatches, micro_batch, seq_len
+        cuda = self.device.type == "cuda"
+        dtype = torch.bfloat16 if cuda else None
+        c = ctx.coords
+        tokens = micro_batch * seq_len
+        if tokens % c.tp:
+            raise ValueError("micro_batch * seq_len must divide by the tensor-parallel size")
+        self.ws = TPWorkspace(self.device, ctx.tp_group if c.tp > 1 else None, max_rows=tokens,
+                              max_cols=max(cfg.d_model, 1))
+        self.stage = LlamaStage(cfg, self.ws, c.pp_rank, c.pp, self.device, dtype)
+        self.scaler = GradScaler(self.device, enabled=loss_scale is not None, init_scale=loss_scale or 1.0)
+        params = self.stage.ordered_parameters()
+        kw = dict(lr=lr, scaler=self.scaler, max_grad_norm=max_grad_norm, weight_decay=weight_decay)
+        self.opt = DPFusedAdam(params, ctx.dp_group, **kw) if c.dp > 1 else FusedAdam(params, **kw)
+        self.n_rep = 0
+        for p, o in zip(self.opt.fp.params, self.opt.fp.offsets):
+            if getattr(p, "tp_replicated", False):
+                self.n_rep = o + (p.numel() + 7) // 8 * 8
+        act_dtype = torch.bfloat16 if cuda else torch.float32
+        self.pipe = PipelineExecutor(c.pp_rank, c.pp, num_microbatches, ctx.prev_stage, ctx.next_stage,
+                                     (tokens // c.tp, cfg.d_model), act_dtype, self.device)
+
+    def step(self, ids: torch.Tensor, targets: torch.Tensor):
+        M_, mb, T = self.M, self.mb, self.T
+        self.opt.zero_grad()
+        ids_m, tgt_m = ids.view(M_, mb, T), targets.view(M_, mb, T)
+        scale = self.scaler.scale_tensor if (self.scaler.enabled and self.device.type == "cuda") else self.scaler.scale
+
+        def stage_fn(x, m):
+            gs = scale / M_ if not isinstance(scale, torch.Tensor) else scale / M_
+            return self.stage(x, (mb, T), tgt_m[m] if self.ctx.coords.pp_rank == self.ctx.coords.pp - 1 else None, gs)
+
+        loss = self.pipe.run(stage_fn, first_inputs=[ids_m[m] for m in range(M_)])
+        if self.ctx.coords.tp > 1 and self.n_rep:
+            dist.all_reduce(self.opt.grad[:self.n_rep], group=self.ctx.tp_group)
+        # a loss-scale overflow must skip the step on every pipeline stage alike: share the flag
+        self.opt.step()
+        return loss

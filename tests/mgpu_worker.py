@@ -1,0 +1,102 @@
+"""Worker of the multi-GPU tests: run under torchrun, one rank per GPU.
+
+    torchrun --nproc-per-node N tests/mgpu_worker.py <mode> [dp tp pp]
+
+mode tp  : tensor-parallel GPT-2 (fused all-gather->GEMM / GEMM->reduce-scatter) against the
+           single-device model trained on the same batch
+mode dp  : fused all-reduce + Adam optimizer step against the single-device full-batch run
+mode 3d  : DP x TP x PP Llama (1F1B) against the single-device model
+Every rank prints one line "RESULT <json>"; the test reads rank 0's.
+"""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+
+def main():
+    mode = sys.argv[1]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from cogito_b200.ops import _lib
+    from cogito_b200.optim.fused import FusedAdam
+    from cogito_b200.train import Trainer
+    from cogito_b200.utils.rng import manual_seed
+    manual_seed(0)
+    out = {"mode": mode, "world": world}
+    g = torch.Generator().manual_seed(1)
+    if mode == "tp":
+        from cogito_b200.models.gpt2 import GPT2, GPT2Config
+        from cogito_b200.parallel.tensor_parallel import build_tp_gpt2, shard_gpt2_state
+        heads = max(4, world)                      # head_dim stays 64, heads divide over the ranks
+        cfg = GPT2Config(vocab_size=1024 * world, n_layer=2, d_model=64 * heads, n_head=heads, d_ff=256 * heads, max_seq_len=256)
+        full = GPT2(cfg, device=dev, dtype=torch.bfloat16)
+        tp, sync = build_tp_gpt2(cfg, rank, world, dev, dist.group.WORLD, micro_tokens=2 * 256)
+        shard_gpt2_state(full, tp)
+        ids = torch.randint(0, cfg.vocab_size, (4, 256), generator=g).to(dev)
+        tg = torch.randint(0, cfg.vocab_size, (4, 256), generator=g).to(dev)
+        of, ot = FusedAdam(full.parameters(), lr=1e-3), FusedAdam(tp._ordered, lr=1e-3)
+        sync.attach(ot)
+        tf, tt = Trainer(full, of, micro_batch=2), Trainer(tp, ot, micro_batch=2, parallel=sync)
+        out["ref"] = [float(tf.step(ids, tg)) for _ in range(4)]
+        out["got"] = [float(tt.step(ids, tg)) for _ in range(4)]
+    elif mode == "dp":
+        from cogito_b200.models.gpt2 import GPT2, GPT2Config
+        from cogito_b200.parallel.data_parallel import DPFusedAdam
+        cfg = GPT2Config(vocab_size=2048, n_layer=2, d_model=256, n_head=4, d_ff=1024, max_seq_len=128)
+        full = GPT2(cfg, device=dev, dtype=torch.bfloat16)
+        mine = GPT2(cfg, device=dev, dtype=torch.bfloat16)
+        mine.load_state_dict(full.state_dict())
+        ids = torch.randint(0, 2048, (2 * world, 128), generator=g).to(dev)
+        tg = torch.randint(0, 2048, (2 * world, 128), generator=g).to(dev)
+        tf = Trainer(full, FusedAdam(full.parameters(), lr=1e-3), micro_batch=2)
+        td = Trainer(mine, DPFusedAdam(mine.parameters(), dist.group.WORLD, lr=1e-3), micro_batch=2)
+        out["ref"] = [float(tf.step(ids, tg)) for _ in range(4)]
+        got = []
+        for _ in range(4):
+            loss = td.step(ids[2 * rank:2 * rank + 2], tg[2 * rank:2 * rank + 2]).detach().float()
+            dist.all_reduce(loss)
+            got.append(float(loss) / world)
+        out["got"] = got
+    elif mode == "3d":
+        dp, tp, pp = (int(a) for a in sys.argv[2:5])
+        from cogito_b200.models.llama import Llama, LlamaConfig
+        from cogito_b200.parallel.groups import init_parallel
+        from cogito_b200.parallel.llama_parallel import Trainer3D, shard_llama_state
+        cfg = LlamaConfig(vocab_size=2048, n_layer=4, d_model=256, n_head=4, n_kv_head=2, d_ff=512, max_seq_len=256)
+        full = Llama(cfg, device=dev, dtype=torch.bfloat16)
+        ctx = init_parallel(dp, tp, pp)
+        M, mb, T = 4, 1, 256
+        t3 = Trainer3D(cfg, ctx, dev, num_microbatches=M, micro_batch=mb, seq_len=T, lr=1e-3, loss_scale=None, max_grad_norm=0.0)
+        shard_llama_state(full, t3.stage)
+        ids = torch.randint(0, 2048, (dp * M * mb, T), generator=g).to(dev)
+        tg = torch.randint(0, 2048, (dp * M * mb, T), generator=g).to(dev)
+        tf = Trainer(full, FusedAdam(full.parameters(), lr=1e-3), micro_batch=mb)
+        out["ref"] = [float(tf.step(ids, tg)) for _ in range(3)]
+        d = ctx.coords.dp_rank
+        got = []
+        for _ in range(3):
+            loss = t3.step(ids[d * M * mb:(d + 1) * M * mb], tg[d * M * mb:(d + 1) * M * mb])
+            v = torch.zeros(2, device=dev)
+            if loss is not None and ctx.coords.tp_rank == 0:
+                v[0], v[1] = loss.float(), 1.0
+            dist.all_reduce(v)
+            got.append(float(v[0] / v[1]))
+        out["got"] = got
+        out["p2p_bytes"] = t3.pipe.p2p_bytes
+    else:
+        raise SystemExit(f"unknown mode {mode}")
+    out["status"] = list(_lib.read_status())
+    print("RESULT " + json.dumps(out), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,60 @@
+"""Multi-GPU tests: fused tensor-parallel kernels, fused data-parallel optimizer, 3-D Llama.
+Each launches tests/mgpu_worker.py under torchrun on the GPUs of this box."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _run(n, *args, timeout=600):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(HERE, "mgpu_worker.py"), *map(str, args)]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
+    assert len(lines) == n, r.stdout[-2000:]
+    return [json.loads(l[7:]) for l in lines]
+
+
+def _close(res, tol):
+    for out in res:
+        assert out["status"][0] == 0, out
+        assert out["ref"][-1] < out["ref"][0]
+        for a, b in zip(out["ref"], out["got"]):
+            assert abs(a - b) < tol, out
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_tensor_parallel_gpt2(n):
+    _close(_run(n, "tp"), 0.05)
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_data_parallel_fused_adam(n):
+    _close(_run(n, "dp"), 0.05)
+
+
+@pytest.mark.parametrize("dp,tp,pp", [(1, 1, 2), (1, 2, 1), (2, 1, 1), (1, 2, 2), (2, 2, 2)])
+def test_3d_llama(dp, tp, pp):
+    res = _run(dp * tp * pp, "3d", dp, tp, pp)
+    _close(res, 0.05)
+    if pp > 1:
+        assert any(r["p2p_bytes"] > 0 for r in res)
