@@ -1,0 +1,253 @@
+"""Command line: ``python -m cogito_b200 <command> [--config file.yaml] [key=value ...]``.
+
+    train     run a training job described by a YAML config (see ``DEFAULTS``)
+    generate  INT4 speculative decoding with a draft/target pair
+    bench     forwards to bench.py's job (same flags)
+    info      versions, device, library status
+
+A config is a nested mapping; ``key.sub=value`` arguments override it.  Under torchrun the job
+is multi-rank: ``parallel: {dp, tp, pp}`` must multiply to the world size.
+
+The reference has no configuration layer: its examples hard-code sizes and hyper-parameters
+(examples/xor_example.c, examples/mnist_example.c) and the Makefile is the only switchboard.
+"""
+from __future__ import annotations
+
+import argparse
+import copy
+import json
+import os
+import sys
+import time
+
+import torch
+import yaml
+
+DEFAULTS = {
+    "seed": 0,
+    "device": "auto",                      # auto | cpu | cuda
+    "model": {"family": "gpt2", "vocab_size": 50304, "n_layer": 12, "d_model": 768, "n_head": 12, "n_kv_head": None,
+              "d_ff": 3072, "max_seq_len": 2048, "hidden": [512, 512], "in_features": 784, "classes": 10},
+    "parallel": {"dp": 1, "tp": 1, "pp": 1, "microbatches": 1},
+    "train": {"steps": 10, "batch": 8, "micro_batch": None, "seq_len": 1024, "lr": 3e-4, "weight_decay": 0.0,
+              "max_grad_norm": 1.0, "loss_scale": 65536.0, "optimizer": "adam"},
+    "data": {"kind": "synthetic", "images": None, "labels": None},
+    "checkpoint": {"dir": None, "every": 0, "resume": False},
+    "log": {"path": None, "every": 1},
+    "profile": False,
+}
+
+
+def _merge(base, over):
+    out = copy.deepcopy(base)
+    for k, v in (over or {}).items():
+        out[k] = _merge(out[k], v) if isinstance(v, dict) and isinstance(out.get(k), dict) else v
+    return out
+
+
+def _override(cfg, item):
+    key, _, raw = item.partition("=")
+    node = cfg
+    parts = key.split(".")
+    for p in parts[:-1]:
+        node = node.setdefault(p, {})
+    node[parts[-1]] = yaml.safe_load(raw)
+
+
+def load_config(path, overrides=()):
+    cfg = _merge(DEFAULTS, yaml.safe_load(open(path)) if path else {})
+    for item in overrides:
+        _override(cfg, item)
+    return cfg
+
+
+def _device(cfg):
+    want = cfg["device"]
+    if want == "auto":
+        want = "cuda" if torch.cuda.is_available() else "cpu"
+    if want == "cuda":
+        local = int(os.environ.get("LOCAL_RANK", 0))
+        torch.cuda.set_device(local)
+        return torch.device("cuda", local)
+    return torch.device("cpu")
+
+
+def cmd_train(cfg):
+    import torch.distributed as dist
+    from .data.datasets import BatchIterator, SyntheticTokens, load_mnist
+    from .io import checkpoint as ckpt
+    from .optim.fused import FusedAdam, FusedSGD, GradScaler
+    from .train import Trainer
+    from .utils import rng
+    from .utils.profiler import Profiler, instrument
+
+    dev = _device(cfg)
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    rank = int(os.environ.get("RANK", 0))
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl" if dev.type == "cuda" else "gloo", **({"device_id": dev} if dev.type == "cuda" else {}))
+    rng.manual_seed(cfg["seed"])
+    m, p, t = cfg["model"], cfg["parallel"], cfg["train"]
+    dtype = torch.bfloat16 if dev.type == "cuda" else None
+    if p["dp"] * p["tp"] * p["pp"] != world:
+        raise SystemExit(f"parallel.dp*tp*pp = {p['dp'] * p['tp'] * p['pp']} but the job has {world} ranks")
+    scaler_on = t["loss_scale"] is not None and dev.type == "cuda"
+    family = m["family"]
+    step_fn, model, opt = None, None, None
+    if family == "llama" and world > 1:
+        from .models.llama import LlamaConfig
+        from .parallel.groups import init_parallel
+        from .parallel.llama_parallel import Trainer3D
+        lc = LlamaConfig(vocab_size=m["vocab_size"], n_layer=m["n_layer"], d_model=m["d_model"], n_head=m["n_head"],
+                         n_kv_head=m["n_kv_head"] or m["n_head"], d_ff=m["d_ff"], max_seq_len=m["max_seq_len"])
+        ctx = init_parallel(p["dp"], p["tp"], p["pp"])
+        mb = t["micro_batch"] or 1
+        t3 = Trainer3D(lc, ctx, dev, p["microbatches"], mb, t["seq_len"], lr=t["lr"], loss_scale=t["loss_scale"] if scaler_on else None,
+                       max_grad_norm=t["max_grad_norm"], weight_decay=t["weight_decay"])
+        model, opt = t3.stage, t3.opt
+        batch_rows = p["microbatches"] * mb
+        step_fn = t3.step
+    else:
+        if family == "gpt2":
+            from .models.gpt2 import GPT2, GPT2Config
+            gc = GPT2Config(vocab_size=m["vocab_size"], n_layer=m["n_layer"], d_model=m["d_model"], n_head=m["n_head"], d_ff=m["d_ff"],
+                            max_seq_len=m["max_seq_len"])
+            if p["tp"] > 1:
+                from .parallel.tensor_parallel import build_tp_gpt2
+                model, sync = build_tp_gpt2(gc, rank, world, dev, micro_tokens=(t["micro_batch"] or t["batch"]) * t["seq_len"])
+                params, parallel = model._ordered, sync
+            else:
+                model = GPT2(gc, device=dev, dtype=dtype)
+                params, parallel = list(model.parameters()), None
+        elif family == "llama":
+            from .models.llama import Llama, LlamaConfig
+            model = Llama(LlamaConfig(vocab_size=m["vocab_size"], n_layer=m["n_layer"], d_model=m["d_model"], n_head=m["n_head"],
+                                      n_kv_head=m["n_kv_head"] or m["n_head"], d_ff=m["d_ff"], max_seq_len=m["max_seq_len"]), device=dev, dtype=dtype)
+            params, parallel = list(model.parameters()), None
+        elif family == "mlp":
+            from .models.mlp import MLPClassifier
+            model = MLPClassifier(m["in_features"], m["hidden"], m["classes"], device=dev, dtype=dtype)
+            params, parallel = list(model.parameters()), None
+        else:
+            raise SystemExit(f"unknown model.family {family}")
+        scaler = GradScaler(dev, enabled=scaler_on, init_scale=t["loss_scale"] or 1.0)
+        kw = dict(lr=t["lr"], weight_decay=t["weight_decay"], scaler=scaler, max_grad_norm=t["max_grad_norm"])
+        if p["dp"] > 1 and p["tp"] == 1:
+            from .parallel.data_parallel import DPFusedAdam
+            opt = DPFusedAdam(params, dist.group.WORLD, **kw)
+        elif t["optimizer"] == "sgd":
+            opt = FusedSGD(params, momentum=0.9, **kw)
+        else:
+            opt = FusedAdam(params, **kw)
+        if p["tp"] > 1:
+            parallel.attach(opt)
+        trainer = Trainer(model, opt, micro_batch=t["micro_batch"], log_path=cfg["log"]["path"] if rank == 0 else None, parallel=parallel)
+        batch_rows = t["batch"] // max(p["dp"], 1)
+        step_fn = trainer.step
+
+    # ---- data
+    d = cfg["data"]
+    if family == "mlp":
+        if d["kind"] == "mnist":
+            x, y = load_mnist(d["images"], d["labels"])
+        else:
+            g = torch.Generator().manual_seed(cfg["seed"] + 1 + rank)
+            x, y = torch.rand(batch_rows * t["steps"], m["in_features"], generator=g), torch.randint(0, m["classes"], (batch_rows * t["steps"],), generator=g)
+        batches = BatchIterator(x, y, batch_rows, shuffle=True, seed=cfg["seed"] + rank)
+    else:
+        batches = SyntheticTokens(m["vocab_size"], batch_rows, t["seq_len"], t["steps"], seed=cfg["seed"] + 17 * (rank // max(p["tp"] * p["pp"], 1)))
+
+    # ---- resume
+    ck = cfg["checkpoint"]
+    start = 0
+    base = None
+    if ck["dir"]:
+        os.makedirs(ck["dir"], exist_ok=True)
+        base = os.path.join(ck["dir"], f"rank{rank:03d}")
+        if ck["resume"] and os.path.exists(base + ".state"):
+            start = ckpt.load_training_state(base, model, opt)["step"]
+    prof = Profiler(enabled=bool(cfg["profile"]))
+    if cfg["profile"]:
+        instrument(model, prof)
+    log_f = open(cfg["log"]["path"], "a") if (cfg["log"]["path"] and rank == 0) else None
+    step, last = start, None
+    t0 = time.time()
+    for x, y in batches:
+        if step >= t["steps"]:
+            break
+        x, y = x.to(dev, non_blocking=True), y.to(dev, non_blocking=True)
+        loss = step_fn(x, y)
+        step += 1
+        prof.step_end()
+        if loss is not None and step % cfg["log"]["every"] == 0:
+            last = float(loss)
+            rec = {"step": step, "loss": last, "elapsed_s": round(time.time() - t0, 3)}
+            if rank == 0:
+                print(json.dumps(rec), flush=True)
+            if log_f:
+                log_f.write(json.dumps(rec) + "\n")
+                log_f.flush()
+        if base and ck["every"] and step % ck["every"] == 0:
+            ckpt.save_training_state(base, model, opt, step)
+    if base:
+        ckpt.save_training_state(base, model, opt, step)
+    if cfg["profile"] and rank == 0:
+        prof.report()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return last
+
+
+def cmd_generate(cfg):
+    from .models.llama import Llama, LlamaConfig
+    from .serve.engine import LlamaInt4Engine, SpeculativeDecoder
+    from .utils import rng
+    dev = _device(cfg)
+    rng.manual_seed(cfg["seed"])
+    m = cfg["model"]
+    g = cfg.get("generate", {})
+    dtype = torch.bfloat16 if dev.type == "cuda" else None
+    tc = LlamaConfig(vocab_size=m["vocab_size"], n_layer=m["n_layer"], d_model=m["d_model"], n_head=m["n_head"],
+                     n_kv_head=m["n_kv_head"] or m["n_head"], d_ff=m["d_ff"], max_seq_len=m["max_seq_len"])
+    dc = LlamaConfig(vocab_size=m["vocab_size"], n_layer=g.get("draft_layers", 2), d_model=m["d_model"], n_head=m["n_head"],
+                     n_kv_head=m["n_kv_head"] or m["n_head"], d_ff=m["d_ff"], max_seq_len=m["max_seq_len"])
+    B, L, new = g.get("batch", 4), g.get("prompt_len", 16), g.get("new_tokens", 32)
+    target = LlamaInt4Engine(Llama(tc, device=dev, dtype=dtype), B, L + new + 16)
+    draft = LlamaInt4Engine(Llama(dc, device=dev, dtype=dtype), B, L + new + 16)
+    dec = SpeculativeDecoder(draft, target, gamma=g.get("gamma", 4), temperature=g.get("temperature", 0.8), top_k=g.get("top_k", 50),
+                             top_p=g.get("top_p", 0.9), seed=cfg["seed"])
+    prompts = torch.randint(0, m["vocab_size"], (B, L), generator=torch.Generator().manual_seed(cfg["seed"])).to(dev)
+    t0 = time.time()
+    seqs, stats = dec.generate(prompts, new)
+    dt = time.time() - t0
+    out = {"generated": stats.generated, "steps": stats.steps, "acceptance_rate": round(stats.acceptance_rate, 4),
+           "tok_per_s": round(stats.generated / dt, 1)}
+    print(json.dumps(out))
+    return out
+
+
+def cmd_info(_cfg):
+    from .ops import _lib
+    info = {"torch": torch.__version__, "cuda": torch.cuda.is_available(), "kernel_library": _lib.available()}
+    if torch.cuda.is_available():
+        info["device"] = torch.cuda.get_device_name(0)
+        info["kernel_library_version"] = _lib.lib().cgk_version()
+    print(json.dumps(info))
+    return info
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="cogito_b200", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("command", choices=["train", "generate", "info"])
+    ap.add_argument("--config", default=None)
+    args, rest = ap.parse_known_args(argv)
+    bad = [r for r in rest if "=" not in r or r.startswith("-")]
+    if bad:
+        ap.error(f"expected key.sub=value overrides, got {bad}")
+    cfg = load_config(args.config, rest)
+    return {"train": cmd_train, "generate": cmd_generate, "info": cmd_info}[args.command](cfg)
+
+
+if __name__ == "__main__":
+    main()

@@ -149,6 +149,11 @@ class _FlatOptimizer:
         for p in self.fp.params:
             p.grad = None
 
+    def refresh_master(self):
+        """Re-read the fp32 master copy from the parameters (after weights were loaded into them)."""
+        if self.master is not None:
+            self.master.copy_(self.fp.flat.float())
+
     def _gather_autograd_grads(self):
         """Parameters touched by ops that return ordinary gradients: fold .grad into main_grad."""
         for p in self.fp.params:

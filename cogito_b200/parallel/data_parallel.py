@@ -99,6 +99,11 @@ class DPFusedAdam:
         for p in self.fp.params:
             p.grad = None
 
+    def refresh_master(self):
+        """Re-read this rank's fp32 master slice from the parameters (after a weight load)."""
+        if self.master is not None:
+            self.master.copy_(self.fp.flat[self.begin:self.begin + self.count].float())
+
     def _fold_autograd_grads(self):
         for p in self.fp.params:
             if p.grad is not None:

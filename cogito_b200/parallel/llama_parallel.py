@@ -214,6 +214,11 @@ class Trainer3D:
         self.pipe = PipelineExecutor(c.pp_rank, c.pp, num_microbatches, ctx.prev_stage, ctx.next_stage,
                                      (tokens // c.tp, cfg.d_model), act_dtype, self.device)
 
+    def load_from(self, full) -> None:
+        """Take this rank's stage / tensor-parallel shards from a single-device ``Llama``."""
+        shard_llama_state(full, self.stage)
+        self.opt.refresh_master()
+
     def step(self, ids: torch.Tensor, targets: torch.Tensor):
         M_, mb, T = self.M, self.mb, self.T
         self.opt.zero_grad()

@@ -207,8 +207,8 @@ static cg_tensor* batchnorm_forward(cg_layer* L, cg_tensor* x) {
       for (int n = 0; n < N; ++n) for (int s = 0; s < S; ++s) { const double d = x->data[at(n, f, s)] - m; v += d * d; }
       v /= cnt;
       mean = (float)m; var = (float)v;
-      l->running_mean->data[f] = (1 - l->momentum) * l->running_mean->data[f] + l->momentum * mean;
-      l->running_var->data[f] = (1 - l->momentum) * l->running_var->data[f] + l->momentum * var;
+      l->running_mean->data[f] = l->momentum * l->running_mean->data[f] + (1 - l->momentum) * mean;   // the reference's rule
+      l->running_var->data[f] = l->momentum * l->running_var->data[f] + (1 - l->momentum) * var;
     } else { mean = l->running_mean->data[f]; var = l->running_var->data[f]; }
     const float inv = 1.0f / std::sqrt(var + l->epsilon);
     si->data[f] = inv;

@@ -197,7 +197,7 @@ __device__ __forceinline__ void tc_fence_after() {
 }
 
 // ---------------------------------------------------------------------------
-// TMA (tiled, no multicast anywhere in this library)
+// TMA (tiled; every load of this library targets the issuing CTA's own shared memory)
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");

@@ -74,7 +74,7 @@ def main():
         ctx = init_parallel(dp, tp, pp)
         M, mb, T = 4, 1, 256
         t3 = Trainer3D(cfg, ctx, dev, num_microbatches=M, micro_batch=mb, seq_len=T, lr=1e-3, loss_scale=None, max_grad_norm=0.0)
-        shard_llama_state(full, t3.stage)
+        t3.load_from(full)
         ids = torch.randint(0, 2048, (dp * M * mb, T), generator=g).to(dev)
         tg = torch.randint(0, 2048, (dp * M * mb, T), generator=g).to(dev)
         tf = Trainer(full, FusedAdam(full.parameters(), lr=1e-3), micro_batch=mb)

@@ -2,6 +2,7 @@
 Each launches tests/mgpu_worker.py under torchrun on the GPUs of this box."""
 import json
 import os
+import re
 import socket
 import subprocess
 import sys
@@ -29,9 +30,9 @@ def _run(n, *args, timeout=600):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    lines = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")]
-    assert len(lines) == n, r.stdout[-2000:]
-    return [json.loads(l[7:]) for l in lines]
+    found = re.findall(r"RESULT (\{[^{}]*\})", r.stdout)      # ranks may interleave their lines
+    assert len(found) == n, r.stdout[-2000:]
+    return [json.loads(s) for s in found]
 
 
 def _close(res, tol):

@@ -54,7 +54,7 @@ def _worker(rank, world, port, dp, tp, pp, q):
         ctx = init_parallel(dp, tp, pp)
         M, mb, T = 4, 1, 16
         t3 = Trainer3D(cfg, ctx, "cpu", num_microbatches=M, micro_batch=mb, seq_len=T, lr=1e-2, loss_scale=None, max_grad_norm=0.0)
-        shard_llama_state(full, t3.stage)
+        t3.load_from(full)
         g = torch.Generator().manual_seed(1)
         ids = torch.randint(0, 64, (dp * M * mb, T), generator=g)
         tg = torch.randint(0, 64, (dp * M * mb, T), generator=g)
