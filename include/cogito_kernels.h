@@ -205,6 +205,9 @@ int cgk_sample(const void* logits, int logits_bf16, long long ld, int rows, int 
 int cgk_spec_accept(const int* draft_tokens, const float* q, const float* p, int batch, int gamma, int V,
                     unsigned long long seed, const long long* step, int* n_accepted, int* out_tokens,
                     int* lengths, int* stats, void* stream);
+/* Self-test of the bounded waits: one thread waits until *flag >= want or budget_ns (<= 5 s)
+ * passes; on a timeout the status word reads {2, 900, 0, want} and *reached (optional) is 0. */
+int cgk_selftest_bounded_wait(const int* flag, int want, unsigned long long budget_ns, int* reached, void* stream);
 /* mask [(L+n), (L+n)], 0 or -1e9: causal prefix; tree node i sees the prefix, its ancestors, itself. */
 int cgk_tree_mask(const int* parents, int n, int L, float* mask_f32, void* mask_bf16, void* stream);
 
