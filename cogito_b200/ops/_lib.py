@@ -84,6 +84,8 @@ def _declare(L: ctypes.CDLL) -> None:
         "cgk_int4_dequantize": [vp, vp, ll, i, vp, vp, vp],
         "cgk_int4_gemm": [vp, ll, vp, vp, vp, vp, ll, vp, i, i, i, i, vp],
         "cgk_int4_tile_weights": [vp, vp, i, i, i, vp, vp],
+        "cgk_int4_wa_gemm": [vp, ll, vp, vp, vp, vp, ll, vp, i, i, i, i, vp],
+        "cgk_int4_wa_tile_weights": [vp, vp, i, i, i, vp, vp],
         "cgk_kv_int4_append": [vp, vp, vp, i, vp],
         "cgk_kv_int4_attention": [vp, vp, vp, i, i, f, i, vp, vp],
         "cgk_sample": [vp, i, ll, i, i, f, i, f, c_ulonglong, vp, vp, vp, vp],
@@ -100,6 +102,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "cgk_colsum_scratch_elems": [ll, i],
         "cgk_kv_int4_attention_scratch_floats": [i, i, i, i, i],
         "cgk_int4_tiles_bytes": [i, i],
+        "cgk_int4_wa_tiles_bytes": [i, i],
         "cgk_int4_gemm_counters": [i, i],
     }.items():
         fn = getattr(L, name)

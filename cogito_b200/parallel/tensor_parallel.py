@@ -102,13 +102,21 @@ def _ag_gemm_bwd(ws, dy_shard, w, aux_in=None, dact=None):
     return F.unary_backward(dact, aux_in, out), g
 
 
+def head_span(n_head: int, ranks: int, rank: int):
+    """(first head, number of heads) of `rank`: the first ``n_head % ranks`` ranks hold one more."""
+    base, extra = divmod(n_head, ranks)
+    return rank * base + min(rank, extra), base + (1 if rank < extra else 0)
+
+
 class TPAttention(nn.Module):
     def __init__(self, d_model, n_head, ws: TPWorkspace, causal=True, init_std=0.02, device=None, dtype=None):
         super().__init__()
-        P = ws.ranks
-        if n_head % P:
-            raise ValueError("heads must divide evenly over the tensor-parallel ranks")
-        self.ws, self.h_local, self.hd, self.causal = ws, n_head // P, d_model // n_head, causal
+        if n_head < ws.ranks:
+            raise ValueError("tensor parallelism needs at least one attention head per rank")
+        # heads that do not divide evenly (GPT-2-small: 12 heads over 8 ranks) are dealt out
+        # 2,2,2,2,1,1,1,1: only the attention core is unbalanced, every GEMM keeps its fused path
+        first, count = head_span(n_head, ws.ranks, ws.rank)
+        self.ws, self.h_local, self.hd, self.causal = ws, count, d_model // n_head, causal
         nl = 3 * self.h_local * self.hd
         g = rng.layer_generator(ws.rank + 1)
         self.w_qkv = nn.Parameter(rng.normal_(torch.empty(nl, d_model, device=device, dtype=dtype), init_std, g))
@@ -371,7 +379,7 @@ def shard_gpt2_state(full, tp: TPGPT2) -> None:
     P, r = tp.ws.ranks, tp.ws.rank
     cfg = tp.cfg
     H, D = cfg.n_head, cfg.d_model // cfg.n_head
-    Hl = H // P
+    h0, Hl = head_span(H, P, r)
 
     def put(dst, src):
         with torch.no_grad():
@@ -383,11 +391,11 @@ def shard_gpt2_state(full, tp: TPGPT2) -> None:
     for fb, tb in zip(full.blocks, tp.blocks):
         put(tb.ln1.weight, fb.norm1.weight); put(tb.ln1.bias, fb.norm1.bias)
         put(tb.ln2.weight, fb.norm2.weight); put(tb.ln2.bias, fb.norm2.bias)
-        wq = fb.attn.qkv.weight.view(3, H, D, cfg.d_model)[:, r * Hl:(r + 1) * Hl]
-        bq = fb.attn.qkv.bias.view(3, H, D)[:, r * Hl:(r + 1) * Hl]
+        wq = fb.attn.qkv.weight.view(3, H, D, cfg.d_model)[:, h0:h0 + Hl]
+        bq = fb.attn.qkv.bias.view(3, H, D)[:, h0:h0 + Hl]
         put(tb.attn.w_qkv, wq.reshape(3 * Hl * D, cfg.d_model))
         put(tb.attn.b_qkv, bq.reshape(3 * Hl * D))
-        put(tb.attn.w_proj, fb.attn.proj.weight[:, r * Hl * D:(r + 1) * Hl * D])
+        put(tb.attn.w_proj, fb.attn.proj.weight[:, h0 * D:(h0 + Hl) * D])
         put(tb.attn.b_proj, fb.attn.proj.bias)
         fl = cfg.d_ff // P
         put(tb.mlp.w1, fb.mlp.up.weight[r * fl:(r + 1) * fl]); put(tb.mlp.b1, fb.mlp.up.bias[r * fl:(r + 1) * fl])

@@ -11,6 +11,8 @@ each weight row once; on CPU the same product is computed from the dequantised w
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..ops import _lib
@@ -68,6 +70,8 @@ def dequantize_int4(packed: torch.Tensor, scales: torch.Tensor, n: int, group: i
 class Int4Linear(torch.nn.Module):
     """y = x @ W^T (+ bias) with W stored as packed INT4 of W^T ([in, out], groups along out)."""
 
+    kernel = os.environ.get("COGITO_INT4_KERNEL", "wb")     # "wb": weights as the B operand; "wa": as the A operand
+
     def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None = None, group: int = 128):
         super().__init__()
         out_f, in_f = weight.shape
@@ -80,6 +84,7 @@ class Int4Linear(torch.nn.Module):
         self.register_buffer("bias", None if bias is None else bias.detach().to(torch.bfloat16))
         self._acc = None
         self._tiles = None
+        self._tiles_wa = False
 
     @classmethod
     def from_linear(cls, lin, group: int = 128) -> "Int4Linear":
@@ -107,18 +112,23 @@ class Int4Linear(torch.nn.Module):
             return gemm(x2.to(torch.bfloat16).contiguous(), w, b_mn=True, bias=self.bias).view(*lead, N)
         x2 = x2.to(torch.bfloat16).contiguous()
         L = _lib.lib()
-        if self._tiles is None or self._tiles.device != x2.device:
+        # "wa": weights on the M side of the tensor core (needs one scale per k for a 128-feature tile)
+        wa = self.kernel == "wa" and self.group % 128 == 0 and K % 128 == 0
+        if self._tiles is None or self._tiles.device != x2.device or self._tiles_wa != wa:
             # one-time tile-major reordering of the same quantised values
-            self._tiles = torch.empty(L.cgk_int4_tiles_bytes(K, N), dtype=torch.uint8, device=x2.device)
-            _lib.check(L.cgk_int4_tile_weights(self.packed.data_ptr(), self.scales.data_ptr(), K, N, self.group,
-                                               self._tiles.data_ptr(), _lib.stream_ptr()), "cgk_int4_tile_weights")
+            nbytes, tile = (L.cgk_int4_wa_tiles_bytes, L.cgk_int4_wa_tile_weights) if wa else (L.cgk_int4_tiles_bytes, L.cgk_int4_tile_weights)
+            self._tiles = torch.empty(nbytes(K, N), dtype=torch.uint8, device=x2.device)
+            self._tiles_wa = wa
+            _lib.check(tile(self.packed.data_ptr(), self.scales.data_ptr(), K, N, self.group,
+                            self._tiles.data_ptr(), _lib.stream_ptr()), "cgk_int4_tile_weights")
             _lib.count_launch()
         if self._acc is None or self._acc.numel() < M * N or self._acc.device != x2.device:
             # split-K scratch: zero once, every call leaves it zero again
             self._acc = torch.zeros(M * N, dtype=torch.float32, device=x2.device)
             self._counters = torch.zeros(L.cgk_int4_gemm_counters(M, N), dtype=torch.int32, device=x2.device)
         out = torch.empty(M, N, dtype=torch.bfloat16, device=x2.device)
-        _lib.check(L.cgk_int4_gemm(x2.data_ptr(), K, self._tiles.data_ptr(), self._acc.data_ptr(), self._counters.data_ptr(),
-                                   out.data_ptr(), N, _lib.ptr(self.bias), M, N, K, splits, _lib.stream_ptr()), "cgk_int4_gemm")
+        _lib.check((L.cgk_int4_wa_gemm if wa else L.cgk_int4_gemm)(
+            x2.data_ptr(), K, self._tiles.data_ptr(), self._acc.data_ptr(), self._counters.data_ptr(),
+            out.data_ptr(), N, _lib.ptr(self.bias), M, N, K, splits, _lib.stream_ptr()), "cgk_int4_gemm")
         _lib.count_launch()
         return out.view(*lead, N)

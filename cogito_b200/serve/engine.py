@@ -16,37 +16,74 @@ from __future__ import annotations
 from dataclasses import dataclass
 
 import torch
+import torch.distributed as dist
 
 from ..models.llama import Llama, LlamaConfig
 from ..ops import misc as M
+from ..ops.attention import flash_forward
 from ..ops.norm import rms_norm
-from ..quant.int4 import Int4Linear
+from ..quant.int4 import Int4Linear, dequantize_int4, quantize_int4
 from .kv_cache import PagedKVCacheInt4
 from .sampling import sample, spec_accept
 
 
 class LlamaInt4Engine:
+    """``tp_group``: a process group over which the engine is tensor parallel.  Every rank is given
+    the full model and keeps its slice: q/k/v heads and the gate/up columns are split (column
+    parallel), the attention output and down projections take the matching input slice (row
+    parallel) and their partial results are summed over the group; the vocabulary projection
+    is split into 128-aligned slices whose logits are gathered.  The slices are cut before
+    quantisation on group boundaries, so every rank holds exactly the values the unsplit engine
+    holds and the sampled tokens agree on all ranks (same Philox stream)."""
+
     def __init__(self, model: Llama, batch: int, max_seq_len: int | None = None, weight_group: int = 128,
-                 kv_group: int = 32, page_size: int = 64):
+                 kv_group: int = 32, page_size: int = 64, tp_group=None):
         cfg: LlamaConfig = model.cfg
         self.cfg = cfg
         dev = model.wte.device
         self.device = dev
         self.dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+        self.tp_group = tp_group
+        self.tp = dist.get_world_size(tp_group) if tp_group is not None else 1
+        r = self.tp_rank = dist.get_rank(tp_group) if tp_group is not None else 0
+        tp, D, d = self.tp, cfg.head_dim, cfg.d_model
+        if cfg.n_head % tp or cfg.n_kv_head % tp or cfg.d_ff % tp:
+            raise ValueError("heads, kv heads and d_ff must be divisible by the tensor-parallel size")
+        self.Hq, self.Hk, ff = cfg.n_head // tp, cfg.n_kv_head // tp, cfg.d_ff // tp
+        nq, nk = cfg.n_head * D, cfg.n_kv_head * D
+
+        def rows(w, *spans):                    # concatenation of row ranges [start, start + n) of a [out, in] weight
+            return torch.cat([w[s:s + n] for s, n in spans], 0) if tp > 1 else w
+
         self.wte = model.wte.detach().to(self.dtype)
         self.layers = []
         for blk in model.blocks:
+            qkv_w, gu_w = blk.attn.qkv.weight.data, blk.mlp.gate_up.weight.data
+            qkv = rows(qkv_w, (r * self.Hq * D, self.Hq * D), (nq + r * self.Hk * D, self.Hk * D), (nq + nk + r * self.Hk * D, self.Hk * D))
+            gate_up = rows(gu_w, (r * ff, ff), (cfg.d_ff + r * ff, ff))
+            proj = blk.attn.proj.weight.data[:, r * self.Hq * D:(r + 1) * self.Hq * D] if tp > 1 else blk.attn.proj.weight.data
+            down = blk.mlp.down.weight.data[:, r * ff:(r + 1) * ff] if tp > 1 else blk.mlp.down.weight.data
             self.layers.append(dict(
                 norm1=blk.norm1.weight.detach().to(self.dtype), norm2=blk.norm2.weight.detach().to(self.dtype),
-                qkv=Int4Linear.from_linear(blk.attn.qkv, weight_group), proj=Int4Linear.from_linear(blk.attn.proj, weight_group),
-                gate_up=Int4Linear.from_linear(blk.mlp.gate_up, weight_group), down=Int4Linear.from_linear(blk.mlp.down, weight_group)))
+                qkv=Int4Linear(qkv, None, weight_group), proj=Int4Linear(proj, None, weight_group),
+                gate_up=Int4Linear(gate_up, None, weight_group), down=Int4Linear(down, None, weight_group)))
         self.norm_f = model.norm_f.weight.detach().to(self.dtype)
-        self.lm_head = Int4Linear.from_linear(model.lm_head, weight_group)
+        V = cfg.vocab_size
+        if tp > 1:
+            # 128-aligned vocabulary slices, the last one zero-padded; the padding is cut after the gather
+            self.v_slice = (V + tp * 128 - 1) // (tp * 128) * 128
+            lo, hi = min(V, r * self.v_slice), min(V, (r + 1) * self.v_slice)
+            head = torch.zeros(self.v_slice, d, dtype=model.lm_head.weight.dtype, device=dev)
+            head[:hi - lo] = model.lm_head.weight.data[lo:hi]
+            self.lm_head = Int4Linear(head, None, weight_group)
+        else:
+            self.lm_head = Int4Linear.from_linear(model.lm_head, weight_group)
         self.max_seq_len = max_seq_len or cfg.max_seq_len
-        self.cache = PagedKVCacheInt4(cfg.n_layer, batch, self.max_seq_len, cfg.n_kv_head, cfg.head_dim, kv_group,
+        self.cache = PagedKVCacheInt4(cfg.n_layer, batch, self.max_seq_len, self.Hk, cfg.head_dim, kv_group,
                                       page_size, dev)
         self.rope = M.rope_tables(self.max_seq_len, cfg.head_dim, cfg.rope_theta, dev)
         self.batch = batch
+        self._fresh = True                     # nothing committed since the last reset
 
     def weight_bytes(self) -> int:
         n = 0
@@ -57,25 +94,52 @@ class LlamaInt4Engine:
 
     def reset(self):
         self.cache.reset()
+        self._fresh = True
+
+    def _sum(self, partial: torch.Tensor) -> torch.Tensor:
+        """Sum of a row-parallel projection's partial results over the tensor-parallel group."""
+        if self.tp > 1:
+            dist.all_reduce(partial, group=self.tp_group)
+        return partial
+
+    def _fake_quant(self, t: torch.Tensor) -> torch.Tensor:
+        """bf16 [B, T, H, D] -> the values an INT4 cache entry of it dequantises to."""
+        g = self.cache.group
+        flat = t.float().contiguous()
+        packed, scales = quantize_int4(flat, g)
+        return dequantize_int4(packed, scales, flat.numel(), g, torch.bfloat16).view(t.shape)
 
     @torch.no_grad()
     def forward(self, tokens: torch.Tensor, commit: bool = False) -> torch.Tensor:
         """tokens [batch, Tq] (int) at positions lengths[b] + t -> logits [batch, Tq, V] (fp32)."""
         cfg = self.cfg
         B, Tq = tokens.shape
-        Hq, Hk, D = cfg.n_head, cfg.n_kv_head, cfg.head_dim
+        Hq, Hk, D = self.Hq, self.Hk, cfg.head_dim                             # this rank's heads
         x = self.wte[tokens.long()]                                            # [B, Tq, d]
+        fresh = self._fresh and Tq >= 16 and self.device.type == "cuda" and D in (64, 128)
+        self._fresh = False
         positions = self.cache.lengths[:, None] + torch.arange(Tq, device=self.device, dtype=torch.int32)[None]
         for i, l in enumerate(self.layers):
             h = rms_norm(x, l["norm1"], cfg.norm_eps)
             qkv = l["qkv"](h).view(B, Tq, Hq + 2 * Hk, D)
             M.rope_apply_(qkv[:, :, :Hq + Hk], self.rope[0], self.rope[1], positions=positions)
             self.cache.append(i, qkv[:, :, Hq:Hq + Hk], qkv[:, :, Hq + Hk:])
-            o = self.cache.attention(i, qkv[:, :, :Hq].contiguous())
-            x = x + l["proj"](o.reshape(B, Tq, Hq * D))
+            if fresh:
+                # prompt over an empty cache: causal flash attention over the values the cache now
+                # holds (K and V pass through the same quantise / dequantise), no history to stream
+                kq, vq = (self._fake_quant(qkv[:, :, a:a + Hk]) for a in (Hq, Hq + Hk))
+                o = flash_forward(qkv[:, :, :Hq], kq, vq, causal=True)[0]
+            else:
+                o = self.cache.attention(i, qkv[:, :, :Hq].contiguous())
+            x = x + self._sum(l["proj"](o.reshape(B, Tq, Hq * D)))
             h = rms_norm(x, l["norm2"], cfg.norm_eps)
-            x = x + l["down"](M.swiglu(l["gate_up"](h)))
-        logits = self.lm_head(rms_norm(x, self.norm_f, cfg.norm_eps)).float()
+            x = x + self._sum(l["down"](M.swiglu(l["gate_up"](h))))
+        logits = self.lm_head(rms_norm(x, self.norm_f, cfg.norm_eps))
+        if self.tp > 1:
+            parts = [torch.empty_like(logits) for _ in range(self.tp)]
+            dist.all_gather(parts, logits.contiguous(), group=self.tp_group)
+            logits = torch.cat(parts, -1)[..., :cfg.vocab_size]
+        logits = logits.float()
         if commit:
             self.cache.commit(Tq)
         return logits

@@ -9,6 +9,7 @@
 
 #include "host_common.h"
 #include "sm100.cuh"
+#include "kv_dev.cuh"
 #include "cogito_kernels.h"
 
 namespace {
@@ -64,14 +65,7 @@ __global__ void int4_dequantize_kernel(const uint8_t* __restrict__ packed, const
 }
 
 // ------------------------------------------------------------ KV cache (A3)
-// Pool layout per layer: pages[num_pages][page_size][heads][D/2] bytes and
-// scales[num_pages][page_size][heads][D/group] fp32; page_table[batch][max_pages] maps a
-// sequence's logical page to a pool page; lengths[batch] tokens are valid.
-struct KvDev {
-  uint8_t* k_pages; uint8_t* v_pages; float* k_scales; float* v_scales;
-  const int* page_table; const int* lengths;
-  int batch, heads, D, group, page_size, max_pages;
-};
+// The pool layout and the KvDev view are in kv_dev.cuh.
 // k_new / v_new: bf16 [batch, T, heads, D]; token t of sequence b lands at position lengths[b] + t.
 // One warp per (b, t, head).
 __global__ void kv_append_kernel(KvDev c, const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new, int T, int* status) {
@@ -490,7 +484,13 @@ CGK_API int cgk_kv_int4_attention(const cgk_kv_args* a, const void* q, void* out
   const dim3 grid(splits, a->heads, a->batch);
   const long long rows = (long long)a->batch * Hq * Tq;
   const int cblocks = (int)((rows * D + 255) / 256 < 1184 ? (rows * D + 255) / 256 : 1184);
-  if (D == 128) {
+  if (D == 128 && a->group % 32 == 0) {
+    // tensor-core path (kv_attn_tc.cu); the CUDA-core kernel below covers the other shapes
+    int dev = 0;
+    CGK_CUDA_CHECK(cudaGetDevice(&dev));
+    CGK_CUDA_CHECK(launch_kv_attention_tc(kv_dev(a), (const __nv_bfloat16*)q, Tq, Hq, scale, splits, part_acc, part_ml, device_status(dev), st));
+    kv_combine_kernel<128><<<cblocks, 256, 0, st>>>(part_acc, part_ml, splits, a->batch, a->heads, Tq, Hq, (__nv_bfloat16*)out);
+  } else if (D == 128) {
     CGK_CUDA_CHECK(cudaFuncSetAttribute(kv_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kv_attention_kernel<128><<<grid, 128, smem, st>>>(kv_dev(a), (const __nv_bfloat16*)q, Tq, Hq, scale, splits, part_acc, part_ml);
     CGK_LAUNCH_CHECK();

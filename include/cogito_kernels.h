@@ -176,6 +176,14 @@ int cgk_int4_tile_weights(const void* packed, const float* scales, int K, int N,
 long long cgk_int4_gemm_counters(int M, int N);
 int cgk_int4_gemm(const void* x, long long ldx, const void* w_tiles, float* acc, int* counters, void* out,
                   long long ldo, const void* bias, int M, int N, int K, int splits, void* stream);
+/* The same product with the weights on the M side of the tensor core (time grows with the rows
+ * of x instead of always paying for 128), the group scale folded into x and a bit-trick-only
+ * nibble conversion.  Needs group % 128 == 0.  Tiles: [N/128][K/64][4352] (4096 bytes of
+ * nibbles [feature][8 words], then 64 fp32 scales); acc / counters as for cgk_int4_gemm. */
+long long cgk_int4_wa_tiles_bytes(int K, int N);
+int cgk_int4_wa_tile_weights(const void* packed, const float* scales, int K, int N, int group, void* tiles, void* stream);
+int cgk_int4_wa_gemm(const void* x, long long ldx, const void* tiles, float* acc, int* counters, void* out,
+                     long long ldo, const void* bias, int M, int N, int K, int splits, void* stream);
 
 /* One layer of a paged INT4 KV cache: pages[num_pages][page_size][heads][D/2] bytes and
  * scales[num_pages][page_size][heads][D/group] fp32 for K and V; page_table[batch][max_pages]

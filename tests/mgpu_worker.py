@@ -34,16 +34,17 @@ def main():
     if mode == "tp":
         from cogito_b200.models.gpt2 import GPT2, GPT2Config
         from cogito_b200.parallel.tensor_parallel import build_tp_gpt2, shard_gpt2_state
-        heads = max(4, world)                      # head_dim stays 64, heads divide over the ranks
+        heads = world + world // 2                 # head_dim 64; uneven on purpose (8 ranks: 12 heads, dealt 2,2,2,2,1,1,1,1)
+        mb = max(2, world // 2)                    # every rank keeps at least 128 rows of a micro-batch
         cfg = GPT2Config(vocab_size=1024 * world, n_layer=2, d_model=64 * heads, n_head=heads, d_ff=256 * heads, max_seq_len=256)
         full = GPT2(cfg, device=dev, dtype=torch.bfloat16)
-        tp, sync = build_tp_gpt2(cfg, rank, world, dev, dist.group.WORLD, micro_tokens=2 * 256)
+        tp, sync = build_tp_gpt2(cfg, rank, world, dev, dist.group.WORLD, micro_tokens=mb * 256)
         shard_gpt2_state(full, tp)
-        ids = torch.randint(0, cfg.vocab_size, (4, 256), generator=g).to(dev)
-        tg = torch.randint(0, cfg.vocab_size, (4, 256), generator=g).to(dev)
+        ids = torch.randint(0, cfg.vocab_size, (2 * mb, 256), generator=g).to(dev)
+        tg = torch.randint(0, cfg.vocab_size, (2 * mb, 256), generator=g).to(dev)
         of, ot = FusedAdam(full.parameters(), lr=1e-3), FusedAdam(tp._ordered, lr=1e-3)
         sync.attach(ot)
-        tf, tt = Trainer(full, of, micro_batch=2), Trainer(tp, ot, micro_batch=2, parallel=sync)
+        tf, tt = Trainer(full, of, micro_batch=mb), Trainer(tp, ot, micro_batch=mb, parallel=sync)
         out["ref"] = [float(tf.step(ids, tg)) for _ in range(4)]
         out["got"] = [float(tt.step(ids, tg)) for _ in range(4)]
     elif mode == "dp":

@@ -39,7 +39,7 @@ def _free_port():
     return p
 
 
-def _tp_worker(rank, world, port, q):
+def _tp_worker(rank, world, port, q, heads=4):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -50,7 +50,7 @@ def _tp_worker(rank, world, port, q):
         from cogito_b200.train import Trainer
         from cogito_b200.utils.rng import manual_seed
         manual_seed(0)
-        cfg = GPT2Config(vocab_size=64, n_layer=2, d_model=32, n_head=4, d_ff=64, max_seq_len=16)
+        cfg = GPT2Config(vocab_size=64, n_layer=2, d_model=8 * heads, n_head=heads, d_ff=64, max_seq_len=16)
         full = GPT2(cfg)
         tp, sync = build_tp_gpt2(cfg, rank, world, "cpu", dist.group.WORLD, micro_tokens=64)
         shard_gpt2_state(full, tp)
@@ -69,11 +69,12 @@ def _tp_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_tensor_parallel_gpt2_matches_single_device_on_two_cpu_ranks():
+@pytest.mark.parametrize("heads", [4, 3])        # 3 heads over 2 ranks: one rank holds two, the other one
+def test_tensor_parallel_gpt2_matches_single_device_on_two_cpu_ranks(heads):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q, heads)) for r in range(2)]
     for p in procs:
         p.start()
     res = [q.get(timeout=240) for _ in procs]

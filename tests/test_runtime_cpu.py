@@ -187,7 +187,7 @@ def _elastic_worker(rank, world, port, tmp, q):
         sub = dist.PrefixStore(f"attempt{attempt}", store)
         dist.init_process_group("gloo", store=sub, rank=state["ranks"].index(rank), world_size=len(state["ranks"]),
                                 timeout=timedelta(seconds=20))
-        hb = Heartbeat(dist.PrefixStore(f"hb{attempt}", store), state["ranks"].index(rank), len(state["ranks"]), interval=0.1, timeout=1.5).start()
+        hb = Heartbeat(dist.PrefixStore(f"hb{attempt}", store), state["ranks"].index(rank), len(state["ranks"]), interval=0.1, timeout=4.0).start()
         return {"hb": hb, "attempt": attempt}
 
     def train(info):

@@ -28,12 +28,14 @@ def test_int4_quantize_dequantize_bit_exact_with_host():
 
 @pytest.mark.parametrize("M,K,N,group,splits", [(16, 512, 256, 128, 0), (80, 1024, 384, 128, 2), (5, 256, 128, 64, 1),
                                                 (130, 512, 256, 128, 0), (1, 4096, 512, 128, 0)])
-def test_int4_gemm_matches_dequantised_product(M, K, N, group, splits):
+@pytest.mark.parametrize("kernel", ["wb", "wa"])
+def test_int4_gemm_matches_dequantised_product(M, K, N, group, splits, kernel):
     torch.manual_seed(M + K)
     w = torch.randn(N, K) * 0.05
     bias = torch.randn(N) * 0.1
     lin = Int4Linear(w, bias, group).to(DEV)
-    x = torch.randn(M, K).bfloat16()
+    lin.kernel = kernel
+    x = (torch.randn(M, K) + 0.5).bfloat16()                # a DC offset exercises the row-sum correction of "wa"
     got = lin(x.to(DEV), splits=splits).float().cpu()
     # oracle: the same packed weights, dequantised on the host, fp32 product
     wt = dequantize_int4(lin.packed.cpu(), lin.scales.cpu(), K * N, group).view(K, N)
@@ -43,7 +45,8 @@ def test_int4_gemm_matches_dequantised_product(M, K, N, group, splits):
     _lib.assert_device_ok()
 
 
-@pytest.mark.parametrize("D,group,Hk,Hq,Tq", [(128, 32, 2, 8, 5), (64, 16, 1, 4, 1), (128, 128, 2, 2, 3)])
+@pytest.mark.parametrize("D,group,Hk,Hq,Tq", [(128, 32, 2, 8, 5), (64, 16, 1, 4, 1), (128, 128, 2, 2, 3),
+                                                 (128, 64, 2, 16, 5), (128, 32, 1, 4, 40), (128, 16, 1, 2, 2)])
 def test_kv_append_and_attention_match_host(D, group, Hk, Hq, Tq):
     torch.manual_seed(D + Tq)
     B, hist = 3, 150
@@ -62,6 +65,25 @@ def test_kv_append_and_attention_match_host(D, group, Hk, Hq, Tq):
     for splits in (1, 4):
         got = gpu.attention(1, q.to(DEV), splits=splits).float().cpu()
         ref = cpu.attention(1, q.float())
+        assert (got - ref).abs().max().item() < 2e-2
+    _lib.assert_device_ok()
+
+
+def test_kv_attention_long_history_many_key_blocks():
+    torch.manual_seed(3)
+    B, hist, Hk, Hq, D, Tq = 2, 700, 2, 8, 128, 5
+    gpu = PagedKVCacheInt4(1, B, 1024, Hk, D, 32, page_size=32, device=DEV)
+    cpu = PagedKVCacheInt4(1, B, 1024, Hk, D, 32, page_size=32)
+    k, v = torch.randn(B, hist, Hk, D).bfloat16(), torch.randn(B, hist, Hk, D).bfloat16()
+    for c, d in ((gpu, DEV), (cpu, "cpu")):
+        c.append(0, k.to(d), v.to(d))
+        c.commit(torch.tensor([hist, hist - 301], dtype=torch.int32, device=d))
+    kn, vn, q = (torch.randn(B, Tq, h, D).bfloat16() for h in (Hk, Hk, Hq))
+    for c, d in ((gpu, DEV), (cpu, "cpu")):
+        c.append(0, kn.to(d), vn.to(d))
+    ref = cpu.attention(0, q.float())
+    for splits in (1, 3, 0):
+        got = gpu.attention(0, q.to(DEV), splits=splits).float().cpu()
         assert (got - ref).abs().max().item() < 2e-2
     _lib.assert_device_ok()
 
