@@ -36,10 +36,19 @@ class Timer:
         self.iters, self.warmup = iters, warmup
         self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
 
-    def __call__(self, fn):
+    def __call__(self, fn, graph=False):
+        """graph=True replays the call from a CUDA graph: for kernels of a few microseconds the
+        Python wrapper is slower than the device, and the events would time the host."""
         for _ in range(self.warmup):
             fn()
         torch.cuda.synchronize()
+        if graph:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            fn = g.replay
+            fn()
+            torch.cuda.synchronize()
         ts = []
         for _ in range(self.iters):
             self.flush.zero_()
@@ -142,7 +151,7 @@ def case_int4_gemm(t, small):
     for M, K, N in ([(16, 4096, 32000)] if small else [(16, 4096, 4096), (80, 4096, 11008), (80, 11008, 4096), (16, 4096, 32000)]):
         lin = Int4Linear(torch.randn(N, K, device="cuda") * 0.02, None, 128)
         x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
-        emit("int4_gemm", t(lambda: lin(x)), bytes_=K * N / 2 + K * N / 128 * 4, flops=2.0 * M * N * K, M=M, N=N, K=K)
+        emit("int4_gemm", t(lambda: lin(x), graph=True), kernel=lin.kernel, bytes_=K * N / 2 + K * N / 128 * 4, flops=2.0 * M * N * K, M=M, N=N, K=K)
 
 
 def case_kv_attn(t, small):
@@ -154,14 +163,15 @@ def case_kv_attn(t, small):
     c.commit(hist)
     c.append(0, mk(Tq, 8), mk(Tq, 8))
     q = mk(Tq, 32)
-    emit("kv_int4_attention", t(lambda: c.attention(0, q)), bytes_=B * hist * 8 * (128 + 2 * 16.0), B=B, history=hist, Tq=Tq)
+    emit("kv_int4_attention", t(lambda: c.attention(0, q), graph=True), bytes_=B * hist * 8 * (128 + 2 * 16.0), B=B, history=hist, Tq=Tq)
 
 
 def case_sample(t, small):
     from cogito_b200.serve.sampling import sample
     rows, V = (16 if small else 80), 32000
     lg = torch.randn(rows, V, device="cuda")
-    emit("sample_topk_topp", t(lambda: sample(lg, 0.8, 50, 0.9, 1, 0, return_probs=True)), bytes_=rows * V * 8.0, rows=rows, vocab=V)
+    step = torch.zeros(1, dtype=torch.int64, device="cuda")
+    emit("sample_topk_topp", t(lambda: sample(lg, 0.8, 50, 0.9, 1, step, return_probs=True), graph=True), bytes_=rows * V * 8.0, rows=rows, vocab=V)
 
 
 CASES = {k[5:]: v for k, v in globals().items() if k.startswith("case_")}

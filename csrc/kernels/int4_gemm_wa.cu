@@ -1,27 +1,34 @@
-// INT4 weight-only GEMM, weights on the M side of the tensor core ("weights as A").
+// INT4 weight-only GEMM, weights on the M side of the tensor core and fed from tensor memory.
 // out[M,N] = X[M,K] (bf16) . dequant(W)[K,N] (+ bias), W in the reference's format
 // (src/quantize/int4.c:10-59: row-major [K,N], flat groups along N, fp32 scale per group).
 //
-// With few rows in X (decode: 16 .. 128) the product is bound by the weight stream, and three
-// things decide whether the stream runs at memory speed:
-//   * the tensor core multiplies 128 weight rows by round_up(M, 16) token columns per
-//     instruction, so its time shrinks with the batch instead of always paying for 128 rows of X;
-//   * the scale of a weight depends on (k, n / group).  With group % 128 == 0 a CTA's 128 output
-//     features share one scale per k, which is moved into X: x'[t,k] = x[t,k] * s[k] is computed
-//     once per CTA on M x 128 elements a step instead of 128 x 128 weights;
-//   * nibbles become bf16 by bit tricks only: u = nibble ^ 8 = q + 8, bf16 bits 0x4300 | u is
+// With few rows in X (decode: 16 .. 128) the product is bound by the weight stream, and on this
+// machine the first limit a streaming kernel meets is shared-memory bandwidth (128 B per clock
+// per SM): a converted bf16 tile written to shared memory and read back by the MMA costs eight
+// times the bytes of the nibbles it came from.  So:
+//   * the weights are the A operand (128 output features = 128 TMEM lanes) and are written by
+//     the conversion warps straight into tensor memory (tcgen05.st); the MMA reads A from TMEM
+//     and only the small X tile from shared memory.  Shared memory carries the raw nibbles once in
+//     and once out, nothing else of the weights;
+//   * the tensor core multiplies 128 features by round_up(M, 16) token columns per instruction,
+//     so its time shrinks with the batch;
+//   * the scale of a weight depends on (k, n / group).  With group % 128 == 0 a CTA's 128 features
+//     share one scale per k, which is moved into X: x'[t,k] = x[t,k] * s[k], computed on M x 128
+//     elements a step instead of 128 x 128 weights;
+//   * nibbles become bf16 by bit tricks only: u = nibble ^ 8 = q + 8, and bf16 bits 0x4300 | u are
 //     128 + u exactly.  The MMA therefore sums x' . (q + 136) and the epilogue subtracts
 //     136 * sum_k x'[t,k], which the scaling warps accumulate in fp32 on the side.
 // The tile stream is prepared once per weight (cgk_int4_wa_tile_weights): per (128 features,
-// 64 k) block 4096 bytes of nibbles [feature][8 words], where nibble j of a word holds k element
-// 2j and nibble j+4 element 2j+1 (the order in which the bit trick emits pairs), then 64 scales.
+// 64 k) block 4096 bytes of nibbles as [k half][feature][4 words], where nibble j of a word holds k
+// element 2j and nibble j+4 element 2j+1 (the order in which the bit trick emits pairs), then the
+// block's 64 scales.
 //
-//   warp 0      bulk copies of weight blocks into a deep ring (8 issuing lanes, slot bound to lane)
+//   warp 0      TMA: the weight stream, one 8704-byte step per copy, into a deep ring
 //   warp 1      tcgen05.mma issue; accumulator [128 features x tokens] in TMEM
 //   warp 2      TMEM allocation
 //   warp 3      TMA: X tiles [tokens, 64 k]
 //   warps 4-7   scale X in place, accumulate the row sums; epilogue
-//   warps 8-23  nibbles -> bf16 operand tile (K-major, 128-byte swizzle)
+//   warps 8-23  nibbles -> bf16 pairs -> TMEM (warp w: features 32 (w % 4) .., k quarter w / 4 of the step)
 // Split-K: partial sums go to an fp32 buffer with red.add; the CTA that arrives last at the
 // tile's counter adds the bias, writes bf16 and leaves buffer and counter zeroed.
 #include <cuda_bf16.h>
@@ -34,12 +41,12 @@ namespace {
 using namespace cgk;
 
 constexpr int WF = 128, WK = 64, WSUB = 2;                     // features per tile, k per block, blocks per step
-constexpr int W_ISSUE = 8, W_BSTAGES = 3, W_MAX_RAW = 16, W_MAX_X = 8, W_CONVERT_WARPS = 16;
+constexpr int W_ASTAGES = 3, W_MAX_RAW = 16, W_MAX_X = 8, W_CONVERT_WARPS = 16;
 constexpr int W_NIB = WF * WK / 2, W_RAW = W_NIB + WK * 4;     // 4096 + 256
-constexpr int W_BBYTES = WF * WK * 2;                          // converted block: 16 KiB
+constexpr int W_ACOLS = WSUB * WK / 2;                         // TMEM columns of one A stage (two bf16 per column)
 constexpr int W_THREADS = 256 + 32 * W_CONVERT_WARPS;
-constexpr int W_SMEM = 226 * 1024;
-constexpr int W_RING_BUDGET = W_SMEM - 1024 - W_BSTAGES * WSUB * W_BBYTES - 2048 - 512;
+constexpr int W_SMEM = 200 * 1024;
+constexpr int W_RING_BUDGET = W_SMEM - 1024 - 2048 - 512;      // shared by the X and W rings
 
 struct WaDev {
   const uint8_t* tiles;            // [N/128][K/64][4352]
@@ -52,44 +59,54 @@ struct WaDev {
   int* status;
 };
 
-__device__ __forceinline__ void wa_bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
+// Profiling build (-DCGK_WA_TIMING): CTA (0,0) sums, per role, the cycles spent in each wait and in
+// the work between them; cgk_int4_wa_times copies the sums out.
+#ifdef CGK_WA_TIMING
+__device__ long long wa_t[32];
+#define WT_DECL long long wt_[4] = {0, 0, 0, 0}; long long wt0_ = clock64();
+#define WT_LAP(i) { const long long n_ = clock64(); wt_[i] += n_ - wt0_; wt0_ = n_; }
+#define WT_STORE(base, n) if (blockIdx.x == 0 && blockIdx.y == 0) { for (int q_ = 0; q_ < n; ++q_) wa_t[base + q_] = wt_[q_]; }
+#else
+#define WT_DECL
+#define WT_LAP(i)
+#define WT_STORE(base, n)
+#endif
 
 __global__ void __launch_bounds__(W_THREADS, 1)
-int4_wa_kernel(const __grid_constant__ CUtensorMap tmX, const WaDev g) {
+int4_wa_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const WaDev g) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t x_bytes = (uint32_t)g.x_rows * 128u;                                // one [tokens, 64 k] block
   const uint32_t sX = base;
-  const uint32_t sB = sX + (uint32_t)g.x_stages * WSUB * x_bytes;                    // multiple of 2 KiB
-  const uint32_t sRaw = sB + W_BSTAGES * WSUB * W_BBYTES;
-  const uint32_t sBar = base + W_SMEM - 2048 - 512;
+  const uint32_t sRaw = sX + (uint32_t)g.x_stages * WSUB * x_bytes;                  // multiple of 2 KiB
+  const uint32_t sBar = base + W_SMEM - 1024 - 2048 - 512;
   float* xsum_s = reinterpret_cast<float*>(gen + (sBar - base) + 1024);              // [128]
   volatile int* dead = reinterpret_cast<volatile int*>(gen + (sBar - base) + 960);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + (sBar - base) + 968);
   volatile int* is_last = reinterpret_cast<volatile int*>(gen + (sBar - base) + 976);
+  volatile int* go_s = reinterpret_cast<volatile int*>(gen + (sBar - base) + 980);   // [2] scaling, [2] conversion: "the wait succeeded", by step parity
   auto x_full = [&](int s) { return sBar + 8u * s; };
   auto x_empty = [&](int s) { return sBar + 8u * (W_MAX_X + s); };
   auto xs_full = [&](int s) { return sBar + 8u * (2 * W_MAX_X + s); };
-  auto b_full = [&](int s) { return sBar + 8u * (3 * W_MAX_X + s); };
-  auto b_empty = [&](int s) { return sBar + 8u * (3 * W_MAX_X + W_BSTAGES + s); };
-  auto raw_full = [&](int s) { return sBar + 8u * (3 * W_MAX_X + 2 * W_BSTAGES + s); };
-  auto raw_empty = [&](int s) { return sBar + 8u * (3 * W_MAX_X + 2 * W_BSTAGES + W_MAX_RAW + s); };
-  const uint32_t acc_full = sBar + 8u * (3 * W_MAX_X + 2 * W_BSTAGES + 2 * W_MAX_RAW);
+  auto a_full = [&](int s) { return sBar + 8u * (3 * W_MAX_X + s); };
+  auto a_empty = [&](int s) { return sBar + 8u * (3 * W_MAX_X + W_ASTAGES + s); };
+  auto raw_full = [&](int s) { return sBar + 8u * (3 * W_MAX_X + 2 * W_ASTAGES + s); };
+  auto raw_empty = [&](int s) { return sBar + 8u * (3 * W_MAX_X + 2 * W_ASTAGES + W_MAX_RAW + s); };
+  const uint32_t acc_full = sBar + 8u * (3 * W_MAX_X + 2 * W_ASTAGES + 2 * W_MAX_RAW);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tiles = g.N / WF, k_tiles = g.K / (WSUB * WK);
   const int nt = blockIdx.x % n_tiles, split = blockIdx.x / n_tiles, mt = blockIdx.y;
   const int n0 = nt * WF, ks0 = split * g.ksteps, m0 = mt * 128;
   const int ksteps = g.ksteps, x_stages = g.x_stages, raw_stages = g.raw_stages, x_rows = g.x_rows;
-  const uint32_t tmem_cols = x_rows <= 32 ? 32u : x_rows <= 64 ? 64u : 128u;
+  // TMEM: accumulator columns first, then W_ASTAGES operand stages
+  const uint32_t acc_cols = x_rows <= 32 ? 32u : x_rows <= 64 ? 64u : 128u;
+  const uint32_t tmem_cols = acc_cols + W_ASTAGES * W_ACOLS <= 256 ? 256u : 512u;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < W_MAX_X; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 1); mbar_init(xs_full(s), 4); }
-    for (int s = 0; s < W_BSTAGES; ++s) { mbar_init(b_full(s), W_CONVERT_WARPS); mbar_init(b_empty(s), 1); }
+    for (int s = 0; s < W_ASTAGES; ++s) { mbar_init(a_full(s), W_CONVERT_WARPS); mbar_init(a_empty(s), 1); }
     for (int s = 0; s < W_MAX_RAW; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), W_CONVERT_WARPS + 4); }
     mbar_init(acc_full, 1);
     *dead = 0;
@@ -100,53 +117,64 @@ int4_wa_kernel(const __grid_constant__ CUtensorMap tmX, const WaDev g) {
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem = *tmem_slot, tmem_a = tmem + acc_cols;
 
   if (warp == 0) {
-    // One thread's bulk copies run one after the other, so several lanes issue; a ring slot always
-    // belongs to the same lane, which keeps its uses in order (an mbarrier has one phase bit).
-    if (lane < W_ISSUE) {
-      const uint8_t* src = g.tiles + ((long long)nt * k_tiles + ks0) * (WSUB * W_RAW);
+    if (lane == 0) {
+      // the tile stream seen as rows of 128 bytes: one step is 68 rows, fetched by one tiled TMA copy
+      // (plain 1-D bulk copies issued by one thread ran one after the other at ~20 GB/s)
+      tma_prefetch_desc(&tmW);
+      const int row0 = (nt * k_tiles + ks0) * (WSUB * W_RAW / 128);
+      WT_DECL
       for (int i = 0; i < ksteps; ++i) {
         const int r = i % raw_stages;
-        if (r % W_ISSUE != lane) continue;
-        if (!mbar_wait(raw_empty(r), ((i / raw_stages) & 1) ^ 1, dead, g.status, 320)) break;
+        if (!mbar_wait_backoff(raw_empty(r), ((i / raw_stages) & 1) ^ 1, dead, g.status, 320, 100)) break;
+        WT_LAP(0)
         mbar_expect_tx(raw_full(r), WSUB * W_RAW);
-        wa_bulk_load(sRaw + r * (WSUB * W_RAW), src + (long long)i * (WSUB * W_RAW), WSUB * W_RAW, raw_full(r));
+        tma_load_2d(sRaw + r * (WSUB * W_RAW), &tmW, raw_full(r), 0, row0 + i * (WSUB * W_RAW / 128));
+        WT_LAP(1)
       }
+      WT_STORE(0, 2)
     }
   } else if (warp == 3) {
     if (lane == 0) {
       tma_prefetch_desc(&tmX);
+      WT_DECL
       for (int i = 0; i < ksteps; ++i) {
         const int s = i % x_stages;
-        if (!mbar_wait(x_empty(s), ((i / x_stages) & 1) ^ 1, dead, g.status, 321)) break;
+        if (!mbar_wait_backoff(x_empty(s), ((i / x_stages) & 1) ^ 1, dead, g.status, 321, 100)) break;
+        WT_LAP(0)
         mbar_expect_tx(x_full(s), WSUB * x_bytes);
 #pragma unroll
         for (int sub = 0; sub < WSUB; ++sub)
           tma_load_2d(sX + (s * WSUB + sub) * x_bytes, &tmX, x_full(s), ((ks0 + i) * WSUB + sub) * WK, m0);
+        WT_LAP(1)
       }
+      WT_STORE(2, 2)
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc_bf16(WF, x_rows, 0, 0);
       bool ok = true;
+      WT_DECL
       for (int i = 0; i < ksteps && ok; ++i) {
-        const int sx = i % x_stages, sb = i % W_BSTAGES;
-        if (!mbar_wait(xs_full(sx), (i / x_stages) & 1, dead, g.status, 322) ||
-            !mbar_wait(b_full(sb), (i / W_BSTAGES) & 1, dead, g.status, 323)) { ok = false; break; }
+        const int sx = i % x_stages, sa = i % W_ASTAGES;
+        if (!mbar_wait(xs_full(sx), (i / x_stages) & 1, dead, g.status, 322)) { ok = false; break; }
+        WT_LAP(0)
+        if (!mbar_wait(a_full(sa), (i / W_ASTAGES) & 1, dead, g.status, 323)) { ok = false; break; }
+        WT_LAP(1)
         tc_fence_after();
 #pragma unroll
-        for (int sub = 0; sub < WSUB; ++sub) {
-          const uint32_t w_addr = sB + (sb * WSUB + sub) * W_BBYTES, x_addr = sX + (sx * WSUB + sub) * x_bytes;
-#pragma unroll
-          for (int kk = 0; kk < WK / 16; ++kk)
-            umma_f16(tmem, make_smem_desc_sw128(w_addr + kk * 32, 16u, 1024u), make_smem_desc_sw128(x_addr + kk * 32, 16u, 1024u), idesc,
-                     (i | sub | kk) != 0 ? 1u : 0u);
+        for (int kk = 0; kk < WSUB * WK / 16; ++kk) {
+          // 16 k per instruction: 8 TMEM columns of A, 32 bytes along a row of the X block
+          const uint32_t x_addr = sX + (sx * WSUB + kk / (WK / 16)) * x_bytes + (kk % (WK / 16)) * 32;
+          umma_f16_ts(tmem, tmem_a + sa * W_ACOLS + kk * 8, make_smem_desc_sw128(x_addr, 16u, 1024u), idesc, (i | kk) != 0 ? 1u : 0u);
         }
         umma_commit(x_empty(sx));
-        umma_commit(b_empty(sb));
+        umma_commit(a_empty(sa));
+        WT_LAP(2)
       }
+      WT_STORE(4, 3)
       if (ok) umma_commit(acc_full);
     }
   } else if (warp >= 4 && warp < 8) {
@@ -157,13 +185,18 @@ int4_wa_kernel(const __grid_constant__ CUtensorMap tmX, const WaDev g) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) xs[j] = 0.0f;
     bool ok = true;
+    WT_DECL
     for (int i = 0; i < ksteps && ok; ++i) {
       const int r = i % raw_stages, s = i % x_stages;
-      int got = 1;
-      if (lane == 0) got = mbar_wait(raw_full(r), (i / raw_stages) & 1, dead, g.status, 324) &&
-                           mbar_wait(x_full(s), (i / x_stages) & 1, dead, g.status, 325);
-      got = __shfl_sync(0xffffffffu, got, 0);
-      if (!got) { ok = false; break; }
+      // one thread polls for the four warps (every poll is a shared-memory access), a hardware
+      // barrier releases the others; a wait that gave up has set *dead
+      if (tid == 0)
+        go_s[i & 1] = mbar_wait_backoff(raw_full(r), (i / raw_stages) & 1, dead, g.status, 324, 40) &&
+                      mbar_wait_backoff(x_full(s), (i / x_stages) & 1, dead, g.status, 325, 40);
+      WT_LAP(0)
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      WT_LAP(1)
+      if (!go_s[i & 1]) { ok = false; break; }      // the same word for all 128 threads: they leave together
 #pragma unroll
       for (int sub = 0; sub < WSUB; ++sub) {
         const float4* sc4 = reinterpret_cast<const float4*>(gen + (sRaw - base) + (r * WSUB + sub) * W_RAW + W_NIB) + ch * 2;
@@ -184,10 +217,13 @@ int4_wa_kernel(const __grid_constant__ CUtensorMap tmX, const WaDev g) {
           }
         }
       }
+      WT_LAP(2)
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) { mbar_arrive(xs_full(s)); mbar_arrive(raw_empty(r)); }
+      WT_LAP(3)
     }
+    if (threadIdx.x == 128) { WT_STORE(8, 4) }
     // row sums: the 8 threads that share a row sit in one quarter of a warp
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -219,35 +255,41 @@ int4_wa_kernel(const __grid_constant__ CUtensorMap tmX, const WaDev g) {
       if (g.splits > 1) __threadfence();
     }
   } else if (warp >= 8) {
-    // ---- conversion: one 16-byte unit (32 k of one feature = half an operand row) per thread and block
-    const int tid = threadIdx.x - 256;                 // 0 .. 511
+    // ---- conversion: thread = (feature, quarter of the step's k): one 16-byte unit of nibbles
+    // becomes 16 bf16 pairs, stored as 16 TMEM columns of the feature's lane
+    const int cw = warp - 8, quad = cw & 3, kq = cw >> 2, sub = kq >> 1, h = kq & 1, f = quad * 32 + lane;
     bool ok = true;
+    WT_DECL
     for (int i = 0; i < ksteps && ok; ++i) {
-      const int r = i % raw_stages, s = i % W_BSTAGES;
-      int got = 1;
-      if (lane == 0) got = mbar_wait(raw_full(r), (i / raw_stages) & 1, dead, g.status, 327) &&
-                           mbar_wait(b_empty(s), ((i / W_BSTAGES) & 1) ^ 1, dead, g.status, 328);
-      got = __shfl_sync(0xffffffffu, got, 0);
-      if (!got) { ok = false; break; }
+      const int r = i % raw_stages, s = i % W_ASTAGES;
+      if (threadIdx.x == 256)
+        go_s[2 + (i & 1)] = mbar_wait_backoff(raw_full(r), (i / raw_stages) & 1, dead, g.status, 327, 40) &&
+                            mbar_wait_backoff(a_empty(s), ((i / W_ASTAGES) & 1) ^ 1, dead, g.status, 328, 40);
+      WT_LAP(0)
+      asm volatile("bar.sync 2, 512;" ::: "memory");
+      WT_LAP(1)
+      if (!go_s[2 + (i & 1)]) { ok = false; break; }
+      tc_fence_after();
+      const uint4 raw = *reinterpret_cast<const uint4*>(gen + (sRaw - base) + (r * WSUB + sub) * W_RAW + h * (W_NIB / 2) + f * 16);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+      uint32_t t[16];
 #pragma unroll
-      for (int it = 0; it < (WSUB * WF * 2) / (32 * W_CONVERT_WARPS); ++it) {
-        const int u = it * (32 * W_CONVERT_WARPS) + tid, sub = u >> 8, f = (u & 255) >> 1, h = u & 1;
-        const uint4 raw = *reinterpret_cast<const uint4*>(gen + (sRaw - base) + (r * WSUB + sub) * W_RAW + (u & 255) * 16);
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-        const uint32_t dst = sB + (s * WSUB + sub) * W_BBYTES;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const uint32_t v = w[c] ^ 0x88888888u;
-          const uint32_t t0 = (v & 0x000F000Fu) | 0x43004300u, t1 = ((v >> 4) & 0x000F000Fu) | 0x43004300u,
-                         t2 = ((v >> 8) & 0x000F000Fu) | 0x43004300u, t3 = ((v >> 12) & 0x000F000Fu) | 0x43004300u;
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + sw128_offset((uint32_t)f, (uint32_t)(h * 4 + c))),
-                       "r"(t0), "r"(t1), "r"(t2), "r"(t3) : "memory");
-        }
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t v = w[c] ^ 0x88888888u;
+        t[4 * c] = (v & 0x000F000Fu) | 0x43004300u;
+        t[4 * c + 1] = ((v >> 4) & 0x000F000Fu) | 0x43004300u;
+        t[4 * c + 2] = ((v >> 8) & 0x000F000Fu) | 0x43004300u;
+        t[4 * c + 3] = ((v >> 12) & 0x000F000Fu) | 0x43004300u;
       }
-      fence_proxy_async_smem();
+      WT_LAP(2)
+      tmem_st16(tmem_a + ((uint32_t)(quad * 32) << 16) + s * W_ACOLS + kq * 16, t);
+      tmem_st_wait();
+      tc_fence_before();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(b_full(s)); mbar_arrive(raw_empty(r)); }
+      if (lane == 0) { mbar_arrive(a_full(s)); mbar_arrive(raw_empty(r)); }
+      WT_LAP(3)
     }
+    if (threadIdx.x == 256) { WT_STORE(12, 4) }
   }
   tc_fence_before();
   __syncthreads();
@@ -282,8 +324,8 @@ __global__ void int4_wa_tile_kernel(const uint8_t* __restrict__ packed, const fl
   for (long long blk = blockIdx.x; blk < blocks; blk += gridDim.x) {
     const int nt = (int)(blk / k_tiles), kt = (int)(blk % k_tiles);
     uint8_t* dst = tiles + blk * W_RAW;
-    for (int i = threadIdx.x; i < W_NIB / 4; i += blockDim.x) {       // word i: feature i / 8, k elements 8 (i % 8) ..
-      const int f = nt * WF + (i >> 3), k0 = kt * WK + (i & 7) * 8;
+    for (int i = threadIdx.x; i < W_NIB / 4; i += blockDim.x) {       // word i: k half i / 512, feature (i % 512) / 4, word i % 4
+      const int f = nt * WF + ((i & 511) >> 2), k0 = kt * WK + (i >> 9) * 32 + (i & 3) * 8;
       uint32_t word = 0;
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -299,6 +341,12 @@ __global__ void int4_wa_tile_kernel(const uint8_t* __restrict__ packed, const fl
 }
 }  // namespace
 
+#ifdef CGK_WA_TIMING
+CGK_API int cgk_int4_wa_times(long long* out) {
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpyFromSymbol(out, wa_t, sizeof(long long) * 32);
+}
+#endif
 CGK_API long long cgk_int4_wa_tiles_bytes(int K, int N) { return (long long)(N / WF) * (K / WK) * W_RAW; }
 // Reorders reference-format weights (packed [K, N/2] bytes, fp32 scales per flat group) into the
 // stream cgk_int4_wa_gemm reads.  group: a multiple of 128 that divides N.
@@ -334,7 +382,7 @@ CGK_API int cgk_int4_wa_gemm(const void* x, long long ldx, const void* tiles, fl
   CGK_REQUIRE(ksteps % splits == 0, "cgk_int4_wa_gemm: K/128 = %d is not divisible by splits = %d", ksteps, splits);
   CGK_REQUIRE(splits == 1 || (acc && counters), "cgk_int4_wa_gemm: split-K needs the acc and counters buffers");
   const int x_rows = m_tiles > 1 ? 128 : (M + 15) / 16 * 16;
-  int x_stages = (W_RING_BUDGET / 4) / (WSUB * x_rows * 128);
+  int x_stages = (W_RING_BUDGET / 3) / (WSUB * x_rows * 128);
   if (x_stages < 2) x_stages = 2;
   if (x_stages > W_MAX_X) x_stages = W_MAX_X;
   int raw_stages = (W_RING_BUDGET - x_stages * WSUB * x_rows * 128) / (WSUB * W_RAW);
@@ -342,6 +390,13 @@ CGK_API int cgk_int4_wa_gemm(const void* x, long long ldx, const void* tiles, fl
   CUtensorMap tmX;
   int rc = encode_tmap_bf16_2d(&tmX, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, (uint32_t)x_rows, WK);
   if (rc) return rc;
+  CUtensorMap tmW;
+  {
+    const uint64_t dims[2] = {128, (uint64_t)cgk_int4_wa_tiles_bytes(K, N) / 128}, strides[1] = {128};
+    const uint32_t box[2] = {128, WSUB * W_RAW / 128};
+    rc = encode_tmap(&tmW, tiles, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, dims, strides, box, Swz::None);
+    if (rc) return rc;
+  }
   static bool attr_set[64] = {};
   if (dev < 64 && !attr_set[dev]) {
     CGK_CUDA_CHECK(cudaFuncSetAttribute(int4_wa_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM));
@@ -349,7 +404,7 @@ CGK_API int cgk_int4_wa_gemm(const void* x, long long ldx, const void* tiles, fl
   }
   WaDev g{(const uint8_t*)tiles, acc, counters, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)bias, M, N, K,
           splits, ksteps / splits, x_rows, x_stages, raw_stages, device_status(dev)};
-  int4_wa_kernel<<<dim3(n_tiles * splits, m_tiles), W_THREADS, W_SMEM, (cudaStream_t)stream>>>(tmX, g);
+  int4_wa_kernel<<<dim3(n_tiles * splits, m_tiles), W_THREADS, W_SMEM, (cudaStream_t)stream>>>(tmX, tmW, g);
   CGK_LAUNCH_CHECK();
   return 0;
 }

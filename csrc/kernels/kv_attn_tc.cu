@@ -80,6 +80,7 @@ kv_attention_tc_kernel(KvDev c, const __nv_bfloat16* __restrict__ q, int Tq, int
   float* lred = reinterpret_cast<float*>(sm + S::OFF_LRED);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + S::OFF_MISC);
   volatile int* dead = reinterpret_cast<volatile int*>(sm + S::OFF_MISC + 4);
+  volatile int* go = reinterpret_cast<volatile int*>(sm + S::OFF_MISC + 8);      // [2] "the wait succeeded"
   const uint32_t bar_s = sb + S::OFF_BAR, bar_o = bar_s + 8;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, quad = warp & 3, half = warp >> 2;
@@ -165,7 +166,11 @@ kv_attention_tc_kernel(KvDev c, const __nv_bfloat16* __restrict__ q, int Tq, int
       umma_commit(bar_s);
     }
     if (kb + KVT_KB < k_end) fetch(kb + KVT_KB);
-    ok = mbar_wait(bar_s, phase, dead, status, 610);
+    // one thread polls (a poll is a shared-memory access; 256 pollers would crowd out the work), a
+    // block barrier releases the rest, who read that thread's verdict
+    if (tid == 0) go[0] = mbar_wait(bar_s, phase, dead, status, 610);
+    __syncthreads();
+    ok = go[0] != 0;
     if (!ok) break;
     tc_fence_after();
     uint32_t sr[CPT];
@@ -205,7 +210,9 @@ kv_attention_tc_kernel(KvDev c, const __nv_bfloat16* __restrict__ q, int Tq, int
                  make_smem_desc_sw128(sb + S::OFF_P + (kk >> 2) * (NP * 128) + (kk & 3) * 32, 16, 1024), idesc_o, kk != 0);
       umma_commit(bar_o);
     }
-    ok = mbar_wait(bar_o, phase, dead, status, 611);
+    if (tid == 0) go[1] = mbar_wait(bar_o, phase, dead, status, 611);
+    __syncthreads();
+    ok = go[1] != 0;
     if (!ok) break;
     tc_fence_after();
     uint32_t orr[CPT];

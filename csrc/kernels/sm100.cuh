@@ -121,6 +121,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// The same wait for roles with slack (producers ahead of a deep ring, helper warps): sleeps
+// `sleep_ns` after every failed poll.  A poll is a shared-memory access; a dozen threads polling
+// in a tight loop take a large share of the SM's shared-memory issue slots from the warps that
+// do the work (measured: a streaming kernel ran 2-3x slower per step with 20 tight pollers).
+__device__ __forceinline__ bool mbar_wait_backoff(uint32_t bar, uint32_t parity, volatile int* dead,
+                                                  int* status, int where, uint32_t sleep_ns) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0; it < CGK_WAIT_MAX_ITERS; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(sleep_ns);
+    if ((it & 63u) == 63u) {
+      if (*dead) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > CGK_WAIT_BUDGET_NS) break;
+    }
+  }
+  *dead = 1;
+  report_status(status, KST_MBAR_TIMEOUT, where, (int)parity);
+  return false;
+}
+
 // ---------------------------------------------------------------------------
 // global-memory flags (same-GPU or peer), bounded
 // ---------------------------------------------------------------------------
@@ -337,6 +359,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
         "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
         "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+        "r"(r[14]), "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() {
