@@ -95,21 +95,30 @@ class Int4Linear(torch.nn.Module):
         return dequantize_int4(self.packed, self.scales, self.in_features * self.out_features, self.group, dtype) \
             .view(self.in_features, self.out_features)
 
-    def forward(self, x: torch.Tensor, splits: int = 0) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, splits: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+        """``out``: an optional contiguous [rows, out_features] buffer for the result (bf16 on CUDA),
+        e.g. a slot of symmetric memory that a collective kernel reads next."""
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.in_features)
         M = x2.shape[0]
+
+        def done(y):
+            if out is None:
+                return y.view(*lead, self.out_features)
+            out.copy_(y.view(out.shape))
+            return out.view(*lead, self.out_features)
+
         if not x2.is_cuda:
             y = x2.float() @ self.dequantized()
             if self.bias is not None:
                 y = y + self.bias.float()
-            return y.to(x.dtype).view(*lead, self.out_features)
+            return done(y.to(x.dtype))
         N, K = self.out_features, self.in_features
         if N % 128 or K % 64 or self.group % 64:
             # shapes the streaming kernel does not cover: dequantise once, then the bf16 GEMM
             from ..ops.gemm import gemm
             w = self.dequantized(torch.bfloat16)
-            return gemm(x2.to(torch.bfloat16).contiguous(), w, b_mn=True, bias=self.bias).view(*lead, N)
+            return done(gemm(x2.to(torch.bfloat16).contiguous(), w, b_mn=True, bias=self.bias))
         x2 = x2.to(torch.bfloat16).contiguous()
         L = _lib.lib()
         # "wa": weights on the M side of the tensor core (needs one scale per k for a 128-feature tile)
@@ -126,7 +135,10 @@ class Int4Linear(torch.nn.Module):
             # split-K scratch: zero once, every call leaves it zero again
             self._acc = torch.zeros(M * N, dtype=torch.float32, device=x2.device)
             self._counters = torch.zeros(L.cgk_int4_gemm_counters(M, N), dtype=torch.int32, device=x2.device)
-        out = torch.empty(M, N, dtype=torch.bfloat16, device=x2.device)
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=x2.device)
+        elif out.dtype != torch.bfloat16 or not out.is_contiguous() or out.numel() != M * N:
+            raise ValueError("out must be a contiguous bf16 [rows, out_features] tensor")
         _lib.check((L.cgk_int4_wa_gemm if wa else L.cgk_int4_gemm)(
             x2.data_ptr(), K, self._tiles.data_ptr(), self._acc.data_ptr(), self._counters.data_ptr(),
             out.data_ptr(), N, _lib.ptr(self.bias), M, N, K, splits, _lib.stream_ptr()), "cgk_int4_gemm")

@@ -34,10 +34,12 @@ class LlamaInt4Engine:
     parallel) and their partial results are summed over the group; the vocabulary projection
     is split into 128-aligned slices whose logits are gathered.  The slices are cut before
     quantisation on group boundaries, so every rank holds exactly the values the unsplit engine
-    holds and the sampled tokens agree on all ranks (same Philox stream)."""
+    holds and the sampled tokens agree on all ranks (same Philox stream).  Steps of up to ``ar_tokens``
+    tokens per sequence use the fused all-reduce + residual + RMSNorm kernel over peer memory; longer
+    ones (prompts) fall back to the process group's all-reduce."""
 
     def __init__(self, model: Llama, batch: int, max_seq_len: int | None = None, weight_group: int = 128,
-                 kv_group: int = 32, page_size: int = 64, tp_group=None):
+                 kv_group: int = 32, page_size: int = 64, tp_group=None, ar_tokens: int = 64):
         cfg: LlamaConfig = model.cfg
         self.cfg = cfg
         dev = model.wte.device
@@ -83,6 +85,9 @@ class LlamaInt4Engine:
                                       page_size, dev)
         self.rope = M.rope_tables(self.max_seq_len, cfg.head_dim, cfg.rope_theta, dev)
         self.batch = batch
+        if tp > 1:
+            from ..parallel.serve_comm import ServeAllReduce
+            self.ar = ServeAllReduce(tp_group, dev, max_rows=batch * ar_tokens, cols=d)
         self._fresh = True                     # nothing committed since the last reset
 
     def weight_bytes(self) -> int:
@@ -96,11 +101,19 @@ class LlamaInt4Engine:
         self.cache.reset()
         self._fresh = True
 
-    def _sum(self, partial: torch.Tensor) -> torch.Tensor:
-        """Sum of a row-parallel projection's partial results over the tensor-parallel group."""
+    def _proj_add_norm(self, lin: Int4Linear, inp: torch.Tensor, x: torch.Tensor, norm_w: torch.Tensor) -> torch.Tensor:
+        """x += (sum over the tensor-parallel ranks of) lin(inp), in place; returns rmsnorm(x) * norm_w.
+        With several ranks the projection writes into symmetric memory and one kernel does the sum over
+        the peers, the residual add and the norm."""
+        rows = x.shape[0] * x.shape[1]
+        if self.tp > 1 and rows <= self.ar.max_rows:
+            lin(inp.reshape(rows, -1), out=self.ar.slot(rows))
+            return self.ar.reduce_add(x.view(rows, -1), rows, norm_w, self.cfg.norm_eps).view_as(x)
+        y = lin(inp)
         if self.tp > 1:
-            dist.all_reduce(partial, group=self.tp_group)
-        return partial
+            dist.all_reduce(y, group=self.tp_group)
+        x += y.view_as(x)
+        return rms_norm(x, norm_w, self.cfg.norm_eps)
 
     def _fake_quant(self, t: torch.Tensor) -> torch.Tensor:
         """bf16 [B, T, H, D] -> the values an INT4 cache entry of it dequantises to."""
@@ -119,8 +132,8 @@ class LlamaInt4Engine:
         fresh = self._fresh and Tq >= 16 and self.device.type == "cuda" and D in (64, 128)
         self._fresh = False
         positions = self.cache.lengths[:, None] + torch.arange(Tq, device=self.device, dtype=torch.int32)[None]
+        h = rms_norm(x, self.layers[0]["norm1"], cfg.norm_eps)
         for i, l in enumerate(self.layers):
-            h = rms_norm(x, l["norm1"], cfg.norm_eps)
             qkv = l["qkv"](h).view(B, Tq, Hq + 2 * Hk, D)
             M.rope_apply_(qkv[:, :, :Hq + Hk], self.rope[0], self.rope[1], positions=positions)
             self.cache.append(i, qkv[:, :, Hq:Hq + Hk], qkv[:, :, Hq + Hk:])
@@ -131,10 +144,10 @@ class LlamaInt4Engine:
                 o = flash_forward(qkv[:, :, :Hq], kq, vq, causal=True)[0]
             else:
                 o = self.cache.attention(i, qkv[:, :, :Hq].contiguous())
-            x = x + self._sum(l["proj"](o.reshape(B, Tq, Hq * D)))
-            h = rms_norm(x, l["norm2"], cfg.norm_eps)
-            x = x + self._sum(l["down"](M.swiglu(l["gate_up"](h))))
-        logits = self.lm_head(rms_norm(x, self.norm_f, cfg.norm_eps))
+            h = self._proj_add_norm(l["proj"], o.reshape(B, Tq, Hq * D), x, l["norm2"])
+            nxt = self.layers[i + 1]["norm1"] if i + 1 < len(self.layers) else self.norm_f
+            h = self._proj_add_norm(l["down"], M.swiglu(l["gate_up"](h)), x, nxt)
+        logits = self.lm_head(h)
         if self.tp > 1:
             parts = [torch.empty_like(logits) for _ in range(self.tp)]
             dist.all_gather(parts, logits.contiguous(), group=self.tp_group)

@@ -32,6 +32,7 @@
 // Split-K: partial sums go to an fp32 buffer with red.add; the CTA that arrives last at the
 // tile's counter adds the bias, writes bf16 and leaves buffer and counter zeroed.
 #include <cuda_bf16.h>
+#include <stdlib.h>
 
 #include "host_common.h"
 #include "sm100.cuh"
@@ -56,6 +57,7 @@ struct WaDev {
   int M, N, K;
   int splits, ksteps;              // 128-k steps per CTA
   int x_rows, x_stages, raw_stages;
+  int dbg;                         // profiling build only: 1 skip the X scaling, 2 skip the conversion, 4 skip the MMAs
   int* status;
 };
 
@@ -66,7 +68,9 @@ __device__ long long wa_t[32];
 #define WT_DECL long long wt_[4] = {0, 0, 0, 0}; long long wt0_ = clock64();
 #define WT_LAP(i) { const long long n_ = clock64(); wt_[i] += n_ - wt0_; wt0_ = n_; }
 #define WT_STORE(base, n) if (blockIdx.x == 0 && blockIdx.y == 0) { for (int q_ = 0; q_ < n; ++q_) wa_t[base + q_] = wt_[q_]; }
+#define WA_DBG(bit) (g.dbg & (bit))
 #else
+#define WA_DBG(bit) 0
 #define WT_DECL
 #define WT_LAP(i)
 #define WT_STORE(base, n)
@@ -168,7 +172,7 @@ int4_wa_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         for (int kk = 0; kk < WSUB * WK / 16; ++kk) {
           // 16 k per instruction: 8 TMEM columns of A, 32 bytes along a row of the X block
           const uint32_t x_addr = sX + (sx * WSUB + kk / (WK / 16)) * x_bytes + (kk % (WK / 16)) * 32;
-          umma_f16_ts(tmem, tmem_a + sa * W_ACOLS + kk * 8, make_smem_desc_sw128(x_addr, 16u, 1024u), idesc, (i | kk) != 0 ? 1u : 0u);
+          if (!WA_DBG(4)) umma_f16_ts(tmem, tmem_a + sa * W_ACOLS + kk * 8, make_smem_desc_sw128(x_addr, 16u, 1024u), idesc, (i | kk) != 0 ? 1u : 0u);
         }
         umma_commit(x_empty(sx));
         umma_commit(a_empty(sa));
@@ -199,6 +203,7 @@ int4_wa_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       if (!go_s[i & 1]) { ok = false; break; }      // the same word for all 128 threads: they leave together
 #pragma unroll
       for (int sub = 0; sub < WSUB; ++sub) {
+        if (WA_DBG(1)) break;
         const float4* sc4 = reinterpret_cast<const float4*>(gen + (sRaw - base) + (r * WSUB + sub) * W_RAW + W_NIB) + ch * 2;
         const float4 s0 = sc4[0], s1 = sc4[1];
         uint8_t* xt = gen + (sX - base) + (s * WSUB + sub) * x_bytes;
@@ -270,6 +275,7 @@ int4_wa_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       WT_LAP(1)
       if (!go_s[2 + (i & 1)]) { ok = false; break; }
       tc_fence_after();
+      if (!WA_DBG(2)) {
       const uint4 raw = *reinterpret_cast<const uint4*>(gen + (sRaw - base) + (r * WSUB + sub) * W_RAW + h * (W_NIB / 2) + f * 16);
       const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
       uint32_t t[16];
@@ -284,6 +290,7 @@ int4_wa_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       WT_LAP(2)
       tmem_st16(tmem_a + ((uint32_t)(quad * 32) << 16) + s * W_ACOLS + kq * 16, t);
       tmem_st_wait();
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) { mbar_arrive(a_full(s)); mbar_arrive(raw_empty(r)); }
@@ -403,7 +410,7 @@ CGK_API int cgk_int4_wa_gemm(const void* x, long long ldx, const void* tiles, fl
     attr_set[dev] = true;
   }
   WaDev g{(const uint8_t*)tiles, acc, counters, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)bias, M, N, K,
-          splits, ksteps / splits, x_rows, x_stages, raw_stages, device_status(dev)};
+          splits, ksteps / splits, x_rows, x_stages, raw_stages, getenv("CGK_WA_DEBUG") ? atoi(getenv("CGK_WA_DEBUG")) : 0, device_status(dev)};
   int4_wa_kernel<<<dim3(n_tiles * splits, m_tiles), W_THREADS, W_SMEM, (cudaStream_t)stream>>>(tmX, tmW, g);
   CGK_LAUNCH_CHECK();
   return 0;

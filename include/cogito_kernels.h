@@ -125,6 +125,13 @@ typedef struct {
 int cgk_dp_adam_step(const cgk_dp_adam_args* args, void* stream);
 int cgk_dp_adam_max_ctas(void);
 
+/* Tensor-parallel serving: x[t,:] += sum over ranks of partial_p[t,:], then (w given)
+ * h = rmsnorm(x) * w, in one launch over peer memory (one-shot all-reduce, sums in rank order).
+ * partial[p] / sig[p]: rank p's slot of this epoch and its flag array (ranks ints) as mapped
+ * here; epoch 1, 2, 3, ... identical on all ranks; slots alternate between two buffers. */
+int cgk_serve_allreduce(const void* const* partial, int* const* sig, int rank, int ranks, int epoch, void* x,
+                        const void* w, void* h, int rows, int cols, float eps, void* stream);
+
 /* ---- Flash attention ------------------------------------------------------ */
 /* Tensors are bf16 [batch, seq, heads, head_dim] with head_dim contiguous and the
  * given element strides (batch, token, head), all multiples of 8.  lse is fp32

@@ -91,6 +91,33 @@ def main():
             got.append(float(v[0] / v[1]))
         out["got"] = got
         out["p2p_bytes"] = t3.pipe.p2p_bytes
+    elif mode == "serve":
+        # tensor-parallel INT4 engine (fused all-reduce + residual + RMSNorm over peer memory) against
+        # the unsplit engine on the same GPU; head_dim 128 keeps every slice on a weight-group boundary
+        from cogito_b200.models.llama import Llama, LlamaConfig
+        from cogito_b200.serve.engine import LlamaInt4Engine, SpeculativeDecoder
+        cfg = LlamaConfig(vocab_size=2048, n_layer=2, d_model=128 * world, n_head=world, n_kv_head=world, d_ff=256 * world, max_seq_len=256)
+        dcfg = LlamaConfig(vocab_size=2048, n_layer=1, d_model=128 * world, n_head=world, n_kv_head=world, d_ff=128 * world, max_seq_len=256)
+        target = Llama(cfg, device=dev, dtype=torch.bfloat16)
+        draft = Llama(dcfg, device=dev, dtype=torch.bfloat16)
+        one = LlamaInt4Engine(target, batch=4)
+        tp = LlamaInt4Engine(target, batch=4, tp_group=dist.group.WORLD)
+        prompt = torch.randint(0, 2048, (4, 40), generator=g).to(dev)
+        a, b = one.forward(prompt, commit=True), tp.forward(prompt, commit=True)
+        nxt = torch.randint(0, 2048, (4, 5), generator=g).to(dev)
+        a2, b2 = one.forward(nxt), tp.forward(nxt)
+        scale = float(a.abs().max())
+        out["ref"] = [0.0, 0.0]
+        out["got"] = [float((a - b).abs().max()) / scale, float((a2 - b2).abs().max()) / scale]
+        dec = SpeculativeDecoder(LlamaInt4Engine(draft, batch=4, tp_group=dist.group.WORLD), tp, gamma=3, temperature=0.8, top_k=20, top_p=0.9, seed=5)
+        seqs, stats = dec.generate(prompt, 16)
+        flat = torch.tensor([t for s in seqs for t in s[:56]], device=dev, dtype=torch.int64)
+        lo, hi = flat.clone(), flat.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        out["tokens_agree"] = bool((lo == hi).all())
+        out["fused"] = bool(tp.ar.fused)
+        out["acceptance"] = stats.acceptance_rate
     else:
         raise SystemExit(f"unknown mode {mode}")
     out["status"] = list(_lib.read_status())

@@ -59,3 +59,11 @@ def test_3d_llama(dp, tp, pp):
     _close(res, 0.05)
     if pp > 1:
         assert any(r["p2p_bytes"] > 0 for r in res)
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_tensor_parallel_int4_serving(n):
+    for out in _run(n, "serve"):
+        assert out["status"][0] == 0, out
+        assert out["fused"] and out["tokens_agree"], out
+        assert max(out["got"]) < 0.03, out              # logits of the split engine vs the unsplit one, relative to their range
