@@ -70,7 +70,11 @@ def dequantize_int4(packed: torch.Tensor, scales: torch.Tensor, n: int, group: i
 class Int4Linear(torch.nn.Module):
     """y = x @ W^T (+ bias) with W stored as packed INT4 of W^T ([in, out], groups along out)."""
 
-    kernel = os.environ.get("COGITO_INT4_KERNEL", "wb")     # "wb": weights as the B operand; "wa": as the A operand
+    # Which tcgen05 kernel multiplies: "wb" keeps the weights as the B operand (converted tile in shared
+    # memory, 128 token rows per instruction), "wa" makes them the A operand fed from tensor memory (cost
+    # follows the token count; needs group % 128 == 0).  "auto": "wa" up to 32 token rows, where it measured
+    # faster, "wb" above.  Each kernel has its own tile-major copy of the weights, made on first use.
+    kernel = os.environ.get("COGITO_INT4_KERNEL", "auto")
 
     def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None = None, group: int = 128):
         super().__init__()
@@ -83,8 +87,7 @@ class Int4Linear(torch.nn.Module):
         self.register_buffer("scales", scales)
         self.register_buffer("bias", None if bias is None else bias.detach().to(torch.bfloat16))
         self._acc = None
-        self._tiles = None
-        self._tiles_wa = False
+        self._tiles = {}                      # kernel kind -> tile-major weights
 
     @classmethod
     def from_linear(cls, lin, group: int = 128) -> "Int4Linear":
@@ -122,14 +125,14 @@ class Int4Linear(torch.nn.Module):
         x2 = x2.to(torch.bfloat16).contiguous()
         L = _lib.lib()
         # "wa": weights on the M side of the tensor core (needs one scale per k for a 128-feature tile)
-        wa = self.kernel == "wa" and self.group % 128 == 0 and K % 128 == 0
-        if self._tiles is None or self._tiles.device != x2.device or self._tiles_wa != wa:
+        wa = (self.kernel == "wa" or (self.kernel == "auto" and M <= 32)) and self.group % 128 == 0 and K % 128 == 0
+        tiles = self._tiles.get(wa)
+        if tiles is None or tiles.device != x2.device:
             # one-time tile-major reordering of the same quantised values
             nbytes, tile = (L.cgk_int4_wa_tiles_bytes, L.cgk_int4_wa_tile_weights) if wa else (L.cgk_int4_tiles_bytes, L.cgk_int4_tile_weights)
-            self._tiles = torch.empty(nbytes(K, N), dtype=torch.uint8, device=x2.device)
-            self._tiles_wa = wa
+            tiles = self._tiles[wa] = torch.empty(nbytes(K, N), dtype=torch.uint8, device=x2.device)
             _lib.check(tile(self.packed.data_ptr(), self.scales.data_ptr(), K, N, self.group,
-                            self._tiles.data_ptr(), _lib.stream_ptr()), "cgk_int4_tile_weights")
+                            tiles.data_ptr(), _lib.stream_ptr()), "cgk_int4_tile_weights")
             _lib.count_launch()
         if self._acc is None or self._acc.numel() < M * N or self._acc.device != x2.device:
             # split-K scratch: zero once, every call leaves it zero again
@@ -140,7 +143,7 @@ class Int4Linear(torch.nn.Module):
         elif out.dtype != torch.bfloat16 or not out.is_contiguous() or out.numel() != M * N:
             raise ValueError("out must be a contiguous bf16 [rows, out_features] tensor")
         _lib.check((L.cgk_int4_wa_gemm if wa else L.cgk_int4_gemm)(
-            x2.data_ptr(), K, self._tiles.data_ptr(), self._acc.data_ptr(), self._counters.data_ptr(),
+            x2.data_ptr(), K, tiles.data_ptr(), self._acc.data_ptr(), self._counters.data_ptr(),
             out.data_ptr(), N, _lib.ptr(self.bias), M, N, K, splits, _lib.stream_ptr()), "cgk_int4_gemm")
         _lib.count_launch()
         return out.view(*lead, N)

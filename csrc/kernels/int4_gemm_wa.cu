@@ -2,14 +2,20 @@
 // out[M,N] = X[M,K] (bf16) . dequant(W)[K,N] (+ bias), W in the reference's format
 // (src/quantize/int4.c:10-59: row-major [K,N], flat groups along N, fp32 scale per group).
 //
-// With few rows in X (decode: 16 .. 128) the product is bound by the weight stream, and on this
-// machine the first limit a streaming kernel meets is shared-memory bandwidth (128 B per clock
-// per SM): a converted bf16 tile written to shared memory and read back by the MMA costs eight
-// times the bytes of the nibbles it came from.  So:
-//   * the weights are the A operand (128 output features = 128 TMEM lanes) and are written by
-//     the conversion warps straight into tensor memory (tcgen05.st); the MMA reads A from TMEM
-//     and only the small X tile from shared memory.  Shared memory carries the raw nibbles once in
-//     and once out, nothing else of the weights;
+// With few rows in X (decode: 16 .. 128) the product is bound by the weight stream.  What was
+// measured on the way to this design:
+//   * a shared-memory ring filled by TMA or bulk copies streams from HBM at 17-30 GB/s per SM
+//     however deep the ring is or how many threads issue; plain 16-byte loads with a few requests
+//     in flight per thread reach the memory's bandwidth.  Nibbles, scales and X therefore go
+//     global -> registers, software-prefetched, never through a copy engine;
+//   * a converted bf16 tile written to shared memory and read back by the MMA costs eight times
+//     the bytes of its nibbles, and the SM's 128 B/clk of shared-memory bandwidth becomes the
+//     limit.  The weights are therefore the A operand (128 output features = 128 TMEM lanes),
+//     written straight into tensor memory (tcgen05.st); the MMA reads A from TMEM and only the
+//     small X tile from shared memory;
+//   * a warp-specialised pipeline of five roles chained by mbarriers spent ~1000 cycles per
+//     128-k step on the hand-offs alone.  Here every thread does the same work per step and two
+//     block barriers order it; two CTAs per SM overlap one CTA's barriers with the other's loads;
 //   * the tensor core multiplies 128 features by round_up(M, 16) token columns per instruction,
 //     so its time shrinks with the batch;
 //   * the scale of a weight depends on (k, n / group).  With group % 128 == 0 a CTA's 128 features
@@ -17,22 +23,18 @@
 //     elements a step instead of 128 x 128 weights;
 //   * nibbles become bf16 by bit tricks only: u = nibble ^ 8 = q + 8, and bf16 bits 0x4300 | u are
 //     128 + u exactly.  The MMA therefore sums x' . (q + 136) and the epilogue subtracts
-//     136 * sum_k x'[t,k], which the scaling warps accumulate in fp32 on the side.
+//     136 * sum_k x'[t,k], accumulated in fp32 on the side.
 // The tile stream is prepared once per weight (cgk_int4_wa_tile_weights): per (128 features,
 // 64 k) block 4096 bytes of nibbles as [k half][feature][4 words], where nibble j of a word holds k
 // element 2j and nibble j+4 element 2j+1 (the order in which the bit trick emits pairs), then the
 // block's 64 scales.
 //
-//   warp 0      TMA: the weight stream, one 8704-byte step per copy, into a deep ring
-//   warp 1      tcgen05.mma issue; accumulator [128 features x tokens] in TMEM
-//   warp 2      TMEM allocation
-//   warp 3      TMA: X tiles [tokens, 64 k]
-//   warps 4-7   scale X in place, accumulate the row sums; epilogue
-//   warps 8-23  nibbles -> bf16 pairs -> TMEM (warp w: features 32 (w % 4) .., k quarter w / 4 of the step)
-// Split-K: partial sums go to an fp32 buffer with red.add; the CTA that arrives last at the
-// tile's counter adds the bias, writes bf16 and leaves buffer and counter zeroed.
+// One step = 128 k.  Thread (warp w, lane l): feature 32 (w % 4) + l, 64-k block w / 4 of the step:
+// two 16-byte units of nibbles -> 32 TMEM columns; and the X chunks (token row, 8 k) number
+// tid, tid + 256, ... of the step.  Split-K: partial sums go to an fp32 buffer with red.add; the CTA
+// that arrives last at the tile's counter adds the bias, writes bf16 and leaves buffer and counter
+// zeroed.
 #include <cuda_bf16.h>
-#include <stdlib.h>
 
 #include "host_common.h"
 #include "sm100.cuh"
@@ -42,272 +44,254 @@ namespace {
 using namespace cgk;
 
 constexpr int WF = 128, WK = 64, WSUB = 2;                     // features per tile, k per block, blocks per step
-constexpr int W_ASTAGES = 3, W_MAX_RAW = 16, W_MAX_X = 8, W_CONVERT_WARPS = 16;
 constexpr int W_NIB = WF * WK / 2, W_RAW = W_NIB + WK * 4;     // 4096 + 256
+constexpr int W_STEP = WSUB * W_RAW;                           // bytes of the stream per 128-k step
 constexpr int W_ACOLS = WSUB * WK / 2;                         // TMEM columns of one A stage (two bf16 per column)
-constexpr int W_THREADS = 256 + 32 * W_CONVERT_WARPS;
-constexpr int W_SMEM = 200 * 1024;
-constexpr int W_RING_BUDGET = W_SMEM - 1024 - 2048 - 512;      // shared by the X and W rings
+constexpr int W_PREFETCH = 4;                                  // steps of nibbles held in registers
+constexpr int W_CONV_THREADS = 256, W_THREADS = W_CONV_THREADS + 32;   // conversion warps + the MMA warp
+constexpr int W_STAGES = 3;                                    // operand stages (TMEM columns of A, shared-memory tiles of X')
+constexpr int W_MAXCH = 8;                                     // X chunks per thread and step: 128 tokens x 16 chunks / 256
 
 struct WaDev {
   const uint8_t* tiles;            // [N/128][K/64][4352]
+  const __nv_bfloat16* x; long long ldx;
   float* acc; int* counters;       // split-K scratch (zero between calls)
   __nv_bfloat16* out; long long ldo;
   const __nv_bfloat16* bias;
   int M, N, K;
   int splits, ksteps;              // 128-k steps per CTA
-  int x_rows, x_stages, raw_stages;
-  int dbg;                         // profiling build only: 1 skip the X scaling, 2 skip the conversion, 4 skip the MMAs
+  int x_rows;                      // token columns of the MMA: round_up(min(M, 128), 16)
   int* status;
 };
 
-// Profiling build (-DCGK_WA_TIMING): CTA (0,0) sums, per role, the cycles spent in each wait and in
-// the work between them; cgk_int4_wa_times copies the sums out.
+// Profiling build (-DCGK_WA_TIMING): thread 0 of CTA (0,0) sums the cycles between the marked points of
+// a step; cgk_int4_wa_times copies the sums out.
 #ifdef CGK_WA_TIMING
-__device__ long long wa_t[32];
-#define WT_DECL long long wt_[4] = {0, 0, 0, 0}; long long wt0_ = clock64();
+__device__ long long wa_t[8];
+#define WT_DECL long long wt_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long wt0_ = clock64();
 #define WT_LAP(i) { const long long n_ = clock64(); wt_[i] += n_ - wt0_; wt0_ = n_; }
-#define WT_STORE(base, n) if (blockIdx.x == 0 && blockIdx.y == 0) { for (int q_ = 0; q_ < n; ++q_) wa_t[base + q_] = wt_[q_]; }
-#define WA_DBG(bit) (g.dbg & (bit))
+#define WT_STORE if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) { for (int q_ = 0; q_ < 8; ++q_) wa_t[q_] = wt_[q_]; }
 #else
-#define WA_DBG(bit) 0
 #define WT_DECL
 #define WT_LAP(i)
-#define WT_STORE(base, n)
+#define WT_STORE
 #endif
 
-__global__ void __launch_bounds__(W_THREADS, 1)
-int4_wa_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const WaDev g) {
+__device__ __forceinline__ uint4 ldg_stream_16(const void* p) {     // read once: do not keep in L1
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+template <int NCH>                   // X chunks per thread and step (x_rows * 16 / 256, rounded up)
+__global__ void __launch_bounds__(W_THREADS, NCH <= 2 ? 2 : 1)
+int4_wa_kernel(const WaDev g) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t x_bytes = (uint32_t)g.x_rows * 128u;                                // one [tokens, 64 k] block
-  const uint32_t sX = base;
-  const uint32_t sRaw = sX + (uint32_t)g.x_stages * WSUB * x_bytes;                  // multiple of 2 KiB
-  const uint32_t sBar = base + W_SMEM - 1024 - 2048 - 512;
-  float* xsum_s = reinterpret_cast<float*>(gen + (sBar - base) + 1024);              // [128]
-  volatile int* dead = reinterpret_cast<volatile int*>(gen + (sBar - base) + 960);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gen + (sBar - base) + 968);
-  volatile int* is_last = reinterpret_cast<volatile int*>(gen + (sBar - base) + 976);
-  volatile int* go_s = reinterpret_cast<volatile int*>(gen + (sBar - base) + 980);   // [2] scaling, [2] conversion: "the wait succeeded", by step parity
-  auto x_full = [&](int s) { return sBar + 8u * s; };
-  auto x_empty = [&](int s) { return sBar + 8u * (W_MAX_X + s); };
-  auto xs_full = [&](int s) { return sBar + 8u * (2 * W_MAX_X + s); };
-  auto a_full = [&](int s) { return sBar + 8u * (3 * W_MAX_X + s); };
-  auto a_empty = [&](int s) { return sBar + 8u * (3 * W_MAX_X + W_ASTAGES + s); };
-  auto raw_full = [&](int s) { return sBar + 8u * (3 * W_MAX_X + 2 * W_ASTAGES + s); };
-  auto raw_empty = [&](int s) { return sBar + 8u * (3 * W_MAX_X + 2 * W_ASTAGES + W_MAX_RAW + s); };
-  const uint32_t acc_full = sBar + 8u * (3 * W_MAX_X + 2 * W_ASTAGES + 2 * W_MAX_RAW);
+  const int x_rows = g.x_rows;
+  const uint32_t x_bytes = (uint32_t)x_rows * 128u;                  // one [tokens, 64 k] block, 128-byte swizzle
+  const uint32_t sX = base;                                          // W_STAGES stages x WSUB blocks
+  uint8_t* misc = gen + W_STAGES * WSUB * x_bytes;
+  const uint32_t sBar = base + W_STAGES * WSUB * x_bytes;            // a_full[], a_empty[], acc_full
+  float* xsum_s = reinterpret_cast<float*>(misc + 128);              // [128]
+  volatile int* dead = reinterpret_cast<volatile int*>(misc + 64);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 68);
+  volatile int* is_last = reinterpret_cast<volatile int*>(misc + 72);
+  volatile int* go_s = reinterpret_cast<volatile int*>(misc + 76);   // [2], by step parity
+  auto a_full = [&](int s) { return sBar + 8u * s; };
+  auto a_empty = [&](int s) { return sBar + 8u * (W_STAGES + s); };
+  const uint32_t acc_full = sBar + 8u * 2 * W_STAGES;
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_tiles = g.N / WF, k_tiles = g.K / (WSUB * WK);
   const int nt = blockIdx.x % n_tiles, split = blockIdx.x / n_tiles, mt = blockIdx.y;
-  const int n0 = nt * WF, ks0 = split * g.ksteps, m0 = mt * 128;
-  const int ksteps = g.ksteps, x_stages = g.x_stages, raw_stages = g.raw_stages, x_rows = g.x_rows;
-  // TMEM: accumulator columns first, then W_ASTAGES operand stages
+  const int n0 = nt * WF, ks0 = split * g.ksteps, m0 = mt * 128, ksteps = g.ksteps;
+  const uint8_t* stream = g.tiles + ((long long)nt * k_tiles + ks0) * W_STEP;        // this CTA's slab, W_STEP bytes a step
   const uint32_t acc_cols = x_rows <= 32 ? 32u : x_rows <= 64 ? 64u : 128u;
-  const uint32_t tmem_cols = acc_cols + W_ASTAGES * W_ACOLS <= 256 ? 256u : 512u;
+  const uint32_t tmem_cols = acc_cols + W_STAGES * W_ACOLS <= 256 ? 256u : 512u;     // accumulator, then the operand stages
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < W_MAX_X; ++s) { mbar_init(x_full(s), 1); mbar_init(x_empty(s), 1); mbar_init(xs_full(s), 4); }
-    for (int s = 0; s < W_ASTAGES; ++s) { mbar_init(a_full(s), W_CONVERT_WARPS); mbar_init(a_empty(s), 1); }
-    for (int s = 0; s < W_MAX_RAW; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), W_CONVERT_WARPS + 4); }
+  if (tid == 0) {
+    for (int s = 0; s < W_STAGES; ++s) { mbar_init(a_full(s), W_CONV_THREADS / 32); mbar_init(a_empty(s), 1); }
     mbar_init(acc_full, 1);
     *dead = 0;
     *is_last = 0;
     mbar_fence_init();
   }
-  if (warp == 2) { tmem_alloc(smem_u32(tmem_slot), tmem_cols); tmem_relinquish(); }
+  if (warp == 0) { tmem_alloc(smem_u32(tmem_slot), tmem_cols); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot, tmem_a = tmem + acc_cols;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      // the tile stream seen as rows of 128 bytes: one step is 68 rows, fetched by one tiled TMA copy
-      // (plain 1-D bulk copies issued by one thread ran one after the other at ~20 GB/s)
-      tma_prefetch_desc(&tmW);
-      const int row0 = (nt * k_tiles + ks0) * (WSUB * W_RAW / 128);
-      WT_DECL
-      for (int i = 0; i < ksteps; ++i) {
-        const int r = i % raw_stages;
-        if (!mbar_wait_backoff(raw_empty(r), ((i / raw_stages) & 1) ^ 1, dead, g.status, 320, 100)) break;
-        WT_LAP(0)
-        mbar_expect_tx(raw_full(r), WSUB * W_RAW);
-        tma_load_2d(sRaw + r * (WSUB * W_RAW), &tmW, raw_full(r), 0, row0 + i * (WSUB * W_RAW / 128));
-        WT_LAP(1)
-      }
-      WT_STORE(0, 2)
-    }
-  } else if (warp == 3) {
-    if (lane == 0) {
-      tma_prefetch_desc(&tmX);
-      WT_DECL
-      for (int i = 0; i < ksteps; ++i) {
-        const int s = i % x_stages;
-        if (!mbar_wait_backoff(x_empty(s), ((i / x_stages) & 1) ^ 1, dead, g.status, 321, 100)) break;
-        WT_LAP(0)
-        mbar_expect_tx(x_full(s), WSUB * x_bytes);
+  // X chunk c = tid + 256 j: block (c / 8) / x_rows, token row (c / 8) % x_rows, piece c % 8 (k = 8 (c % 8) ..)
+  const int ch = tid & 7;
+  const int chunks = WSUB * x_rows * 8;                              // per step
+  float xs[NCH];
 #pragma unroll
-        for (int sub = 0; sub < WSUB; ++sub)
-          tma_load_2d(sX + (s * WSUB + sub) * x_bytes, &tmX, x_full(s), ((ks0 + i) * WSUB + sub) * WK, m0);
-        WT_LAP(1)
-      }
-      WT_STORE(2, 2)
-    }
-  } else if (warp == 1) {
+  for (int j = 0; j < NCH; ++j) xs[j] = 0.0f;
+  bool ok = true;
+
+  if (warp == W_CONV_THREADS / 32) {
+    // ---- MMA warp: one thread issues; a stage is free again when its MMAs have completed
     if (lane == 0) {
       const uint32_t idesc = make_idesc_bf16(WF, x_rows, 0, 0);
-      bool ok = true;
-      WT_DECL
-      for (int i = 0; i < ksteps && ok; ++i) {
-        const int sx = i % x_stages, sa = i % W_ASTAGES;
-        if (!mbar_wait(xs_full(sx), (i / x_stages) & 1, dead, g.status, 322)) { ok = false; break; }
-        WT_LAP(0)
-        if (!mbar_wait(a_full(sa), (i / W_ASTAGES) & 1, dead, g.status, 323)) { ok = false; break; }
-        WT_LAP(1)
+      for (int i = 0; i < ksteps; ++i) {
+        const int s = i % W_STAGES;
+        if (!mbar_wait(a_full(s), (i / W_STAGES) & 1, dead, g.status, 332)) break;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < WSUB * WK / 16; ++kk) {
-          // 16 k per instruction: 8 TMEM columns of A, 32 bytes along a row of the X block
-          const uint32_t x_addr = sX + (sx * WSUB + kk / (WK / 16)) * x_bytes + (kk % (WK / 16)) * 32;
-          if (!WA_DBG(4)) umma_f16_ts(tmem, tmem_a + sa * W_ACOLS + kk * 8, make_smem_desc_sw128(x_addr, 16u, 1024u), idesc, (i | kk) != 0 ? 1u : 0u);
+          // 16 k per instruction: 8 TMEM columns of A, 32 bytes along a row of the X' block
+          const uint32_t x_addr = sX + (s * WSUB + kk / (WK / 16)) * x_bytes + (kk % (WK / 16)) * 32;
+          umma_f16_ts(tmem, tmem_a + s * W_ACOLS + kk * 8, make_smem_desc_sw128(x_addr, 16u, 1024u), idesc, (i | kk) != 0 ? 1u : 0u);
         }
-        umma_commit(x_empty(sx));
-        umma_commit(a_empty(sa));
-        WT_LAP(2)
+        umma_commit(a_empty(s));
+        if (i + 1 == ksteps) umma_commit(acc_full);
       }
-      WT_STORE(4, 3)
-      if (ok) umma_commit(acc_full);
     }
-  } else if (warp >= 4 && warp < 8) {
-    // ---- X scaling: chunk (row t, 16-byte piece ch) of both 64-k blocks of the step.  The piece a
-    // thread owns is always ch = tid % 8, its rows are tid / 8 + 16 j.
-    const int tid = threadIdx.x - 128, ch = tid & 7, trow = tid >> 3, slots = x_rows >> 4;
-    float xs[8];
+  } else {
+    // ---- conversion warps: this thread's share of a step
+    const int quad = warp & 3, sub = warp >> 2, f = quad * 32 + lane;
+    const uint8_t* wsrc = stream + sub * W_RAW + f * 16;             // k half 0; half 1 is W_NIB / 2 further
+    constexpr int NB = NCH == 1 ? 1 : WSUB;                          // scale blocks a thread needs (one chunk: one block)
+    const int blk0 = NCH == 1 ? (tid >> 3) / x_rows : 0;
+    uint4 raw[W_PREFETCH][2];
+    uint4 xr[2][NCH];                                                // X chunks and scales of the next two steps, by step parity
+    float4 sc[2][NB][2];
+    auto load_w = [&](int d, int step) {
+      raw[d][0] = ldg_stream_16(wsrc + (long long)step * W_STEP);
+      raw[d][1] = ldg_stream_16(wsrc + (long long)step * W_STEP + W_NIB / 2);
+    };
+    auto load_x = [&](int p, int step) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) xs[j] = 0.0f;
-    bool ok = true;
+      for (int j = 0; j < NCH; ++j) {
+        const int c = tid + j * W_CONV_THREADS, rowb = c >> 3, blk = rowb / x_rows, t = rowb - blk * x_rows;
+        xr[p][j] = make_uint4(0, 0, 0, 0);
+        if (c < chunks && m0 + t < g.M)
+          xr[p][j] = __ldg(reinterpret_cast<const uint4*>(g.x + (long long)(m0 + t) * g.ldx + ((long long)(ks0 + step) * WSUB + blk) * WK + ch * 8));
+      }
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const float4* sp = reinterpret_cast<const float4*>(stream + (long long)step * W_STEP + (blk0 + b) * W_RAW + W_NIB + ch * 32);
+        sc[p][b][0] = __ldg(sp); sc[p][b][1] = __ldg(sp + 1);
+      }
+    };
+#pragma unroll
+    for (int d = 0; d < W_PREFETCH; ++d) { raw[d][0] = raw[d][1] = make_uint4(0, 0, 0, 0); if (d < ksteps) load_w(d, d); }
+    load_x(0, 0);
+    if (ksteps > 1) load_x(1, 1);
     WT_DECL
-    for (int i = 0; i < ksteps && ok; ++i) {
-      const int r = i % raw_stages, s = i % x_stages;
-      // one thread polls for the four warps (every poll is a shared-memory access), a hardware
-      // barrier releases the others; a wait that gave up has set *dead
-      if (tid == 0)
-        go_s[i & 1] = mbar_wait_backoff(raw_full(r), (i / raw_stages) & 1, dead, g.status, 324, 40) &&
-                      mbar_wait_backoff(x_full(s), (i / x_stages) & 1, dead, g.status, 325, 40);
-      WT_LAP(0)
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      WT_LAP(1)
-      if (!go_s[i & 1]) { ok = false; break; }      // the same word for all 128 threads: they leave together
+    for (int i0 = 0; i0 < ksteps && ok; i0 += W_PREFETCH) {
 #pragma unroll
-      for (int sub = 0; sub < WSUB; ++sub) {
-        if (WA_DBG(1)) break;
-        const float4* sc4 = reinterpret_cast<const float4*>(gen + (sRaw - base) + (r * WSUB + sub) * W_RAW + W_NIB) + ch * 2;
-        const float4 s0 = sc4[0], s1 = sc4[1];
-        uint8_t* xt = gen + (sX - base) + (s * WSUB + sub) * x_bytes;
+      for (int d = 0; d < W_PREFETCH; ++d) {
+        const int i = i0 + d;
+        if (i >= ksteps || !ok) break;
+        const int s = i % W_STAGES;
+        // stage s (TMEM operand columns and the X' tile) was last read by the MMAs of step i - W_STAGES;
+        // one thread polls, a hardware barrier releases the rest
+        if (tid == 0) go_s[d & 1] = i < W_STAGES ? 1 : (int)mbar_wait(a_empty(s), ((i / W_STAGES) - 1) & 1, dead, g.status, 330);
+        WT_LAP(0)
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        WT_LAP(1)
+        if (!go_s[d & 1]) { ok = false; break; }
+        tc_fence_after();
+        // nibbles -> bf16 pairs -> 32 TMEM columns of this feature's lane
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (j < slots) {
-            const int t = trow + 16 * j;
-            uint4* p = reinterpret_cast<uint4*>(xt + sw128_offset((uint32_t)t, (uint32_t)ch));
-            const uint4 v = *p;
-            const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
-            uint4 o = make_uint4(pack_bf16x2(a.x * s0.x, a.y * s0.y), pack_bf16x2(b.x * s0.z, b.y * s0.w),
-                                 pack_bf16x2(c.x * s1.x, c.y * s1.y), pack_bf16x2(d.x * s1.z, d.y * s1.w));
+        for (int hh = 0; hh < 2; ++hh) {
+          const uint32_t w[4] = {raw[d][hh].x, raw[d][hh].y, raw[d][hh].z, raw[d][hh].w};
+          uint32_t t[16];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint32_t v = w[c] ^ 0x88888888u;
+            t[4 * c] = (v & 0x000F000Fu) | 0x43004300u;
+            t[4 * c + 1] = ((v >> 4) & 0x000F000Fu) | 0x43004300u;
+            t[4 * c + 2] = ((v >> 8) & 0x000F000Fu) | 0x43004300u;
+            t[4 * c + 3] = ((v >> 12) & 0x000F000Fu) | 0x43004300u;
+          }
+          tmem_st16(tmem_a + ((uint32_t)(quad * 32) << 16) + s * W_ACOLS + sub * 32 + hh * 16, t);
+        }
+        WT_LAP(2)
+        if (i + W_PREFETCH < ksteps) load_w(d, i + W_PREFETCH);
+        // X chunks: times the scale of their k, rounded to bf16, summed for the offset correction, stored swizzled
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+          const int c = tid + j * W_CONV_THREADS, rowb = c >> 3, blk = rowb / x_rows, t = rowb - blk * x_rows;
+          if (c < chunks) {
+            const int bi = NCH == 1 ? 0 : blk;
+            const float4 s0 = bi ? sc[d & 1][NB - 1][0] : sc[d & 1][0][0], s1 = bi ? sc[d & 1][NB - 1][1] : sc[d & 1][0][1];
+            const uint4 xv = xr[d & 1][j];
+            const float2 a = unpack_bf16x2(xv.x), b = unpack_bf16x2(xv.y), cc = unpack_bf16x2(xv.z), e = unpack_bf16x2(xv.w);
+            const uint4 o = make_uint4(pack_bf16x2(a.x * s0.x, a.y * s0.y), pack_bf16x2(b.x * s0.z, b.y * s0.w),
+                                       pack_bf16x2(cc.x * s1.x, cc.y * s1.y), pack_bf16x2(e.x * s1.z, e.y * s1.w));
             const float2 ra = unpack_bf16x2(o.x), rb = unpack_bf16x2(o.y), rc = unpack_bf16x2(o.z), rd = unpack_bf16x2(o.w);
             xs[j] += ((ra.x + ra.y) + (rb.x + rb.y)) + ((rc.x + rc.y) + (rd.x + rd.y));
-            *p = o;
+            *reinterpret_cast<uint4*>(gen + (s * WSUB + blk) * x_bytes + sw128_offset((uint32_t)t, (uint32_t)ch)) = o;
           }
         }
+        WT_LAP(3)
+        if (i + 2 < ksteps) load_x(d & 1, i + 2);
+        tmem_st_wait();
+        WT_LAP(4)
+        fence_proxy_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(a_full(s));
+        WT_LAP(5)
       }
-      WT_LAP(2)
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) { mbar_arrive(xs_full(s)); mbar_arrive(raw_empty(r)); }
-      WT_LAP(3)
     }
-    if (threadIdx.x == 128) { WT_STORE(8, 4) }
-    // row sums: the 8 threads that share a row sit in one quarter of a warp
+    WT_STORE
+  }
+  // ---- row sums of x': a chunk's row is fixed per (thread, j); sum the 8 pieces of a row, then over the blocks
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float v = xs[j];
-      v += __shfl_xor_sync(0xffffffffu, v, 1); v += __shfl_xor_sync(0xffffffffu, v, 2); v += __shfl_xor_sync(0xffffffffu, v, 4);
-      if (ch == 0 && j < slots) xsum_s[trow + 16 * j] = v;
-    }
+  for (int j = 0; j < NCH; ++j) {
+    float v = xs[j];
+    v += __shfl_xor_sync(0xffffffffu, v, 1); v += __shfl_xor_sync(0xffffffffu, v, 2); v += __shfl_xor_sync(0xffffffffu, v, 4);
+    xs[j] = v;
+  }
+  for (int i = tid; i < 128; i += W_THREADS) xsum_s[i] = 0.0f;
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int c = tid + j * W_CONV_THREADS, rowb = c >> 3, blk = rowb / x_rows, t = rowb - blk * x_rows;
+    if (ch == 0 && c < chunks && tid < W_CONV_THREADS) atomicAdd(xsum_s + t, xs[j]);         // two blocks per row: two adds per row
+  }
+  __syncthreads();
+  // ---- epilogue (warps 0-3): lane = output feature, column = token
+  if (warp < 4 && ok) {
+    if (tid == 0) go_s[0] = (int)mbar_wait(acc_full, 0, dead, g.status, 331);
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    // ---- epilogue: lane = output feature, column = token
-    if (ok && mbar_wait(acc_full, 0, dead, g.status, 326)) {
+    if (go_s[0]) {
       tc_fence_after();
-      const int f = n0 + (warp & 3) * 32 + lane;
-      const float bias = (g.bias && g.splits == 1) ? __bfloat162float(g.bias[f]) : 0.0f;
+      const int fo = n0 + warp * 32 + lane;
+      const float bias = (g.bias && g.splits == 1) ? __bfloat162float(g.bias[fo]) : 0.0f;
 #pragma unroll 1
       for (int c = 0; c < x_rows; c += 16) {
         uint32_t rr[16];
-        tmem_ld16(tmem + ((uint32_t)((warp & 3) * 32) << 16) + c, rr);
+        tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c, rr);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int t = m0 + c + j;
           if (t < g.M) {
             const float v = __uint_as_float(rr[j]) - 136.0f * xsum_s[c + j];
-            if (g.splits == 1) g.out[(long long)t * g.ldo + f] = __float2bfloat16(v + bias);
-            else atomicAdd(g.acc + (long long)t * g.N + f, v);
+            if (g.splits == 1) g.out[(long long)t * g.ldo + fo] = __float2bfloat16(v + bias);
+            else atomicAdd(g.acc + (long long)t * g.N + fo, v);
           }
         }
       }
       if (g.splits > 1) __threadfence();
     }
-  } else if (warp >= 8) {
-    // ---- conversion: thread = (feature, quarter of the step's k): one 16-byte unit of nibbles
-    // becomes 16 bf16 pairs, stored as 16 TMEM columns of the feature's lane
-    const int cw = warp - 8, quad = cw & 3, kq = cw >> 2, sub = kq >> 1, h = kq & 1, f = quad * 32 + lane;
-    bool ok = true;
-    WT_DECL
-    for (int i = 0; i < ksteps && ok; ++i) {
-      const int r = i % raw_stages, s = i % W_ASTAGES;
-      if (threadIdx.x == 256)
-        go_s[2 + (i & 1)] = mbar_wait_backoff(raw_full(r), (i / raw_stages) & 1, dead, g.status, 327, 40) &&
-                            mbar_wait_backoff(a_empty(s), ((i / W_ASTAGES) & 1) ^ 1, dead, g.status, 328, 40);
-      WT_LAP(0)
-      asm volatile("bar.sync 2, 512;" ::: "memory");
-      WT_LAP(1)
-      if (!go_s[2 + (i & 1)]) { ok = false; break; }
-      tc_fence_after();
-      if (!WA_DBG(2)) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(gen + (sRaw - base) + (r * WSUB + sub) * W_RAW + h * (W_NIB / 2) + f * 16);
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-      uint32_t t[16];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const uint32_t v = w[c] ^ 0x88888888u;
-        t[4 * c] = (v & 0x000F000Fu) | 0x43004300u;
-        t[4 * c + 1] = ((v >> 4) & 0x000F000Fu) | 0x43004300u;
-        t[4 * c + 2] = ((v >> 8) & 0x000F000Fu) | 0x43004300u;
-        t[4 * c + 3] = ((v >> 12) & 0x000F000Fu) | 0x43004300u;
-      }
-      WT_LAP(2)
-      tmem_st16(tmem_a + ((uint32_t)(quad * 32) << 16) + s * W_ACOLS + kq * 16, t);
-      tmem_st_wait();
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) { mbar_arrive(a_full(s)); mbar_arrive(raw_empty(r)); }
-      WT_LAP(3)
-    }
-    if (threadIdx.x == 256) { WT_STORE(12, 4) }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem, tmem_cols); }
+  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, tmem_cols); }
   if (g.splits > 1) {
-    if (threadIdx.x == 0) *is_last = (atomicAdd(g.counters + mt * n_tiles + nt, 1) == g.splits - 1) && !*dead;
+    if (tid == 0) *is_last = (atomicAdd(g.counters + mt * n_tiles + nt, 1) == g.splits - 1) && !*dead;
     __syncthreads();
     if (*is_last) {
       __threadfence();
       const int rows = min(128, g.M - m0);
-      for (int i = threadIdx.x; i < rows * (WF / 4); i += W_THREADS) {
+      for (int i = tid; i < rows * (WF / 4); i += W_THREADS) {
         const int t = i / (WF / 4), c4 = (i % (WF / 4)) * 4;
         float4* src = reinterpret_cast<float4*>(g.acc + (long long)(m0 + t) * g.N + n0 + c4);
         float4 v = __ldcg(src);
@@ -318,7 +302,7 @@ int4_wa_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         }
         *reinterpret_cast<uint2*>(g.out + (long long)(m0 + t) * g.ldo + n0 + c4) = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
       }
-      if (threadIdx.x == 0) g.counters[mt * n_tiles + nt] = 0;
+      if (tid == 0) g.counters[mt * n_tiles + nt] = 0;
     }
   }
 }
@@ -346,12 +330,20 @@ __global__ void int4_wa_tile_kernel(const uint8_t* __restrict__ packed, const fl
       reinterpret_cast<float*>(dst + W_NIB)[i] = scales[((long long)(kt * WK + i) * N + nt * WF) / group];
   }
 }
+
+template <int NCH>
+int launch_wa(const WaDev& g, dim3 grid, int smem, cudaStream_t st) {
+  CGK_CUDA_CHECK(cudaFuncSetAttribute(int4_wa_kernel<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  int4_wa_kernel<NCH><<<grid, W_THREADS, smem, st>>>(g);
+  CGK_LAUNCH_CHECK();
+  return 0;
+}
 }  // namespace
 
 #ifdef CGK_WA_TIMING
 CGK_API int cgk_int4_wa_times(long long* out) {
   cudaDeviceSynchronize();
-  return (int)cudaMemcpyFromSymbol(out, wa_t, sizeof(long long) * 32);
+  return (int)cudaMemcpyFromSymbol(out, wa_t, sizeof(long long) * 8);
 }
 #endif
 CGK_API long long cgk_int4_wa_tiles_bytes(int K, int N) { return (long long)(N / WF) * (K / WK) * W_RAW; }
@@ -376,42 +368,34 @@ CGK_API int cgk_int4_wa_gemm(const void* x, long long ldx, const void* tiles, fl
   using namespace cgk;
   CGK_REQUIRE(x && tiles && out, "cgk_int4_wa_gemm: null pointer");
   CGK_REQUIRE(M > 0 && N > 0 && K > 0 && N % WF == 0 && K % (WSUB * WK) == 0, "cgk_int4_wa_gemm: need N %% 128 == 0 and K %% 128 == 0 (got M=%d N=%d K=%d)", M, N, K);
-  CGK_REQUIRE(ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)tiles & 15) == 0 && ldo % 4 == 0 && ((uintptr_t)out & 7) == 0 && ((uintptr_t)acc & 15) == 0,
+  CGK_REQUIRE(ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)tiles & 15) == 0 && ((uintptr_t)acc & 15) == 0 && ldo % 4 == 0 && ((uintptr_t)out & 7) == 0,
               "cgk_int4_wa_gemm: misaligned operand");
   int dev = 0;
   CGK_CUDA_CHECK(cudaGetDevice(&dev));
   const int sms = sm_count(dev), n_tiles = N / WF, m_tiles = (M + 127) / 128, ksteps = K / (WSUB * WK);
+  const int x_rows = m_tiles > 1 ? 128 : (M + 15) / 16 * 16;
+  const int nch = (WSUB * x_rows * 8 + W_CONV_THREADS - 1) / W_CONV_THREADS;
+  const int per_sm = nch <= 2 ? 2 : 1;                     // resident CTAs per SM (registers, TMEM columns)
   if (splits <= 0) {
     splits = 1;
     const int max_s = (acc && counters) ? 16 : 1;
-    for (int s = 2; s <= max_s && ksteps % s == 0 && ksteps / s >= 2 && n_tiles * m_tiles * s <= sms; s *= 2) splits = s;
+    for (int s = 2; s <= max_s && ksteps % s == 0 && ksteps / s >= 4 && n_tiles * m_tiles * s <= sms * per_sm; s *= 2) splits = s;
   }
   CGK_REQUIRE(ksteps % splits == 0, "cgk_int4_wa_gemm: K/128 = %d is not divisible by splits = %d", ksteps, splits);
   CGK_REQUIRE(splits == 1 || (acc && counters), "cgk_int4_wa_gemm: split-K needs the acc and counters buffers");
-  const int x_rows = m_tiles > 1 ? 128 : (M + 15) / 16 * 16;
-  int x_stages = (W_RING_BUDGET / 3) / (WSUB * x_rows * 128);
-  if (x_stages < 2) x_stages = 2;
-  if (x_stages > W_MAX_X) x_stages = W_MAX_X;
-  int raw_stages = (W_RING_BUDGET - x_stages * WSUB * x_rows * 128) / (WSUB * W_RAW);
-  if (raw_stages > W_MAX_RAW) raw_stages = W_MAX_RAW;
-  CUtensorMap tmX;
-  int rc = encode_tmap_bf16_2d(&tmX, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, (uint32_t)x_rows, WK);
-  if (rc) return rc;
-  CUtensorMap tmW;
-  {
-    const uint64_t dims[2] = {128, (uint64_t)cgk_int4_wa_tiles_bytes(K, N) / 128}, strides[1] = {128};
-    const uint32_t box[2] = {128, WSUB * W_RAW / 128};
-    rc = encode_tmap(&tmW, tiles, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, dims, strides, box, Swz::None);
-    if (rc) return rc;
+  const int smem = 1024 + W_STAGES * WSUB * x_rows * 128 + 128 + 512 + 1024;
+  WaDev g{(const uint8_t*)tiles, (const __nv_bfloat16*)x, ldx, acc, counters, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)bias, M, N, K,
+          splits, ksteps / splits, x_rows, device_status(dev)};
+  const dim3 grid(n_tiles * splits, m_tiles);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (nch) {
+    case 1: return launch_wa<1>(g, grid, smem, st);
+    case 2: return launch_wa<2>(g, grid, smem, st);
+    case 3: return launch_wa<3>(g, grid, smem, st);
+    case 4: return launch_wa<4>(g, grid, smem, st);
+    case 5: return launch_wa<5>(g, grid, smem, st);
+    case 6: return launch_wa<6>(g, grid, smem, st);
+    case 7: return launch_wa<7>(g, grid, smem, st);
+    default: return launch_wa<W_MAXCH>(g, grid, smem, st);
   }
-  static bool attr_set[64] = {};
-  if (dev < 64 && !attr_set[dev]) {
-    CGK_CUDA_CHECK(cudaFuncSetAttribute(int4_wa_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM));
-    attr_set[dev] = true;
-  }
-  WaDev g{(const uint8_t*)tiles, acc, counters, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)bias, M, N, K,
-          splits, ksteps / splits, x_rows, x_stages, raw_stages, getenv("CGK_WA_DEBUG") ? atoi(getenv("CGK_WA_DEBUG")) : 0, device_status(dev)};
-  int4_wa_kernel<<<dim3(n_tiles * splits, m_tiles), W_THREADS, W_SMEM, (cudaStream_t)stream>>>(tmX, tmW, g);
-  CGK_LAUNCH_CHECK();
-  return 0;
 }
