@@ -40,12 +40,18 @@ def parse():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="cogito", choices=["cogito", "reference", "torch"])
-    ap.add_argument("--micro-batch", type=int, default=8)
+    ap.add_argument("--micro-batch", type=int, default=0,
+                    help="sequences per micro-batch; 0 = 8, times the number of GPUs under tensor parallelism "
+                         "(activations are sharded over the ranks, so the collectives grow instead of multiplying)")
     ap.add_argument("--global-batch", type=int, default=64)
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=12)
     ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"])
-    return ap.parse_args()
+    args = ap.parse_args()
+    if args.micro_batch <= 0:
+        tp = args.gpus if (args.parallelism == "tp" and args.impl == "cogito") else 1
+        args.micro_batch = min(args.global_batch, 8 * tp)
+    return args
 
 
 class ClockSampler:

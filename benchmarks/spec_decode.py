@@ -35,6 +35,7 @@ def main():
     ap.add_argument("--gamma", type=int, default=4)
     ap.add_argument("--kv-heads", type=int, default=32)
     ap.add_argument("--self-draft", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
 
     from cogito_b200.models.llama import Llama, LlamaConfig
@@ -66,7 +67,8 @@ def main():
         draft = LlamaInt4Engine(Llama(dcfg, device=dev, dtype=torch.bfloat16), args.batch, cap, tp_group=group)
     model = None
     torch.cuda.empty_cache()
-    dec = SpeculativeDecoder(draft, target, gamma=args.gamma, temperature=0.8, top_k=50, top_p=0.9, seed=0)
+    dec = SpeculativeDecoder(draft, target, gamma=args.gamma, temperature=0.8, top_k=50, top_p=0.9, seed=0,
+                             use_graph=False if args.no_graph else None)
     prompts = torch.randint(0, 32000, (args.batch, args.prompt), generator=torch.Generator().manual_seed(1)).to(dev)
 
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
@@ -81,11 +83,9 @@ def main():
     ev[1].record()
     produced, steps, generated, accepted = 0, 0, 0, 0
     while produced < args.new:
-        n_acc, out = dec.step(last)
-        n_host = n_acc.tolist()
-        if max(n_host) == args.gamma:
-            dec._catch_up_draft(out, n_acc)
-        last = out[torch.arange(args.batch, device=dev), n_acc.long()].clone()
+        n_acc, out, nxt = dec.advance(last)
+        n_host = n_acc.tolist()                              # the per-step host read a serving loop needs to emit tokens
+        last = nxt.clone()
         produced += min(n_host) + 1
         generated += sum(n + 1 for n in n_host)
         accepted += sum(n_host)
@@ -101,7 +101,8 @@ def main():
             "metric": "int4_speculative_decode_tokens_per_s", "value": round(generated / decode_ms * 1e3, 1), "unit": "tokens/s",
             "n_gpus": world, "decode_ms": round(decode_ms, 2), "prefill_ms": round(prefill_ms, 2), "steps": steps,
             "ms_per_step": round(decode_ms / steps, 3), "acceptance_rate": round(accepted / (steps * args.batch * args.gamma), 4),
-            "generated": generated, "launches_per_step": round(_lib.launches() / max(1, steps), 1),
+            "generated": generated, "cuda_graph": dec._graph is not None,
+            "launches_per_step": getattr(dec, "graph_launches", None) if dec._graph is not None else round(_lib.launches() / max(1, steps), 1),
             "weight_bytes_per_gpu": target.weight_bytes() + draft.weight_bytes(),
             "config": {"layers": args.layers, "draft_layers": args.draft_layers, "batch": args.batch, "prompt": args.prompt, "new": args.new,
                        "gamma": args.gamma, "kv_heads": args.kv_heads, "tp": world, "self_draft": args.self_draft, "data": "synthetic"}}), flush=True)

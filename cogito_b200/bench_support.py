@@ -37,7 +37,7 @@ class CogitoJob(_Job):
         self.vocab = cfg.vocab_size
         if world > 1 and args.parallelism == "tp":
             from .parallel.tensor_parallel import build_tp_gpt2
-            self.model, parallel = build_tp_gpt2(cfg, rank, world, dev)
+            self.model, parallel = build_tp_gpt2(cfg, rank, world, dev, micro_tokens=args.micro_batch * args.seq_len)
         else:
             self.model = GPT2(cfg, device=dev, dtype=torch.bfloat16)
             parallel = None

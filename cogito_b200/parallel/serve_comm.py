@@ -37,11 +37,12 @@ class ServeAllReduce:
             self.slot_bytes = (max_rows * cols * 2 + 255) // 256 * 256
             self.buf = SymmetricBuffer(2 * self.slot_bytes + 256, device, group)
             L = _lib.lib()
-            L.cgk_serve_allreduce.argtypes = [POINTER(c_void_p), POINTER(c_void_p), c_int, c_int, c_int, c_void_p,
+            L.cgk_serve_allreduce.argtypes = [POINTER(c_void_p), POINTER(c_void_p), c_int, c_int, c_void_p, c_void_p,
                                               c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]
             L.cgk_serve_allreduce.restype = c_int
             self._fn = L.cgk_serve_allreduce
             self._sig = (c_void_p * self.P)(*self.buf.peer_ptrs(2 * self.slot_bytes))
+            self._counters = torch.zeros(2, dtype=torch.int32, device=self.device)   # the kernel numbers its calls here
             self._slots = [(c_void_p * self.P)(*self.buf.peer_ptrs(s * self.slot_bytes)) for s in range(2)]
         else:
             self._local = None
@@ -63,7 +64,7 @@ class ServeAllReduce:
         self.epoch += 1
         if self.fused:
             h = torch.empty_like(x) if norm_weight is not None else None
-            _lib.check(self._fn(self._slots[self.epoch & 1], self._sig, self.rank, self.P, self.epoch, x.data_ptr(),
+            _lib.check(self._fn(self._slots[self.epoch & 1], self._sig, self.rank, self.P, self._counters.data_ptr(), x.data_ptr(),
                                 _lib.ptr(norm_weight), _lib.ptr(h), rows, self.cols, eps, _lib.stream_ptr()),
                        "cgk_serve_allreduce")
             _lib.count_launch()

@@ -13,12 +13,15 @@ cg_matmul_int4 and cg_kv_cache_int4_* (src/quantize/int4.c:90-289).
 """
 from __future__ import annotations
 
+import os
+import warnings
 from dataclasses import dataclass
 
 import torch
 import torch.distributed as dist
 
 from ..models.llama import Llama, LlamaConfig
+from ..ops import _lib
 from ..ops import misc as M
 from ..ops.attention import flash_forward
 from ..ops.norm import rms_norm
@@ -175,7 +178,7 @@ class SpeculativeDecoder:
     accept / correct on the device, commit both caches to the accepted length."""
 
     def __init__(self, draft: LlamaInt4Engine, target: LlamaInt4Engine, gamma: int = 4, temperature: float = 1.0,
-                 top_k: int = 50, top_p: float = 0.9, seed: int = 0):
+                 top_k: int = 50, top_p: float = 0.9, seed: int = 0, use_graph: bool | None = None):
         if draft.cfg.vocab_size != target.cfg.vocab_size or draft.batch != target.batch:
             raise ValueError("draft and target must share vocabulary and batch size")
         self.draft, self.target, self.gamma = draft, target, gamma
@@ -184,6 +187,15 @@ class SpeculativeDecoder:
         dev = target.device
         self._step = torch.zeros(1, dtype=torch.int64, device=dev)
         self._stats_dev = torch.zeros(2, dtype=torch.int32, device=dev)
+        # One decoding step is ~200 small kernels; launched from Python the host is several times slower
+        # than the device.  On CUDA the whole step (gamma draft passes, verify, accept, cache bookkeeping)
+        # is captured once into a CUDA graph and replayed.  Everything the step depends on lives on the
+        # device (cache lengths, random-stream counter, the call counter of the fused tensor-parallel
+        # all-reduce), so the recorded launches stay valid.  COGITO_SERVE_GRAPH=0 turns it off.
+        env = os.environ.get("COGITO_SERVE_GRAPH", "1") != "0"
+        self.use_graph = (dev.type == "cuda" and env) if use_graph is None else use_graph
+        self._graph = None
+        self._eager_steps = 0
 
     def _dist(self, logits2d, step, return_probs=True):
         return sample(logits2d, self.temperature, self.top_k, self.top_p, self.seed, step, return_probs=return_probs)
@@ -230,6 +242,43 @@ class SpeculativeDecoder:
         return n_acc, out
 
     @torch.no_grad()
+    def step_full(self, last: torch.Tensor):
+        """One complete step with nothing decided on the host: ``step``, then the draft pass over d_gamma
+        for every sequence (kept only where all drafts were accepted).  Returns (n_accepted, out_tokens,
+        next ``last``)."""
+        n_acc, out = self.step(last)
+        self._catch_up_draft(out, n_acc)
+        nxt = out.gather(1, n_acc.long().view(-1, 1)).view(-1)
+        return n_acc, out, nxt
+
+    @torch.no_grad()
+    def advance(self, last: torch.Tensor):
+        """``step_full`` replayed from a CUDA graph when enabled (captured after two eager steps, which
+        create every lazily allocated workspace).  The returned tensors are overwritten by the next call."""
+        if not self.use_graph:
+            return self.step_full(last)
+        if self._graph is None:
+            if self._eager_steps < 2:
+                self._eager_steps += 1
+                return self.step_full(last)
+            self._g_last = last.clone()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = _lib.launches()
+            try:
+                with torch.cuda.graph(graph):
+                    self._g_out = self.step_full(self._g_last)
+            except Exception as e:                               # something in the step cannot be captured here
+                warnings.warn(f"decode step not captured ({e!r}); launching it from Python")
+                self.use_graph = False
+                return self.step_full(last)
+            self._graph = graph
+            self.graph_launches = _lib.launches() - before      # kernels of this library in one replay
+        self._g_last.copy_(last)
+        self._graph.replay()
+        return self._g_out
+
+    @torch.no_grad()
     def generate(self, prompts: torch.Tensor, max_new_tokens: int):
         """Returns a list of per-sequence token lists (prompt + generated) and the statistics."""
         B = prompts.shape[0]
@@ -237,15 +286,11 @@ class SpeculativeDecoder:
         last = self.prefill(prompts)
         produced = 0
         while produced < max_new_tokens:
-            n_acc, out = self.step(last)
+            n_acc, out, nxt = self.advance(last)
             n_host, out_host = n_acc.tolist(), out.tolist()
-            # sequences that accepted every draft have not run d_g through the draft model yet
-            full = [b for b in range(B) if n_host[b] == self.gamma]
-            if full:
-                self._catch_up_draft(out, n_acc)
             for b in range(B):
                 seqs[b].extend(out_host[b][:n_host[b] + 1])
-            last = out[torch.arange(B, device=out.device), n_acc.long()].clone()
+            last = nxt.clone()
             self.stats.steps += 1
             self.stats.drafted += self.gamma * B
             self.stats.accepted += sum(n_host)

@@ -35,7 +35,8 @@ struct ServeArDev {
   __nv_bfloat16* x;                  // [rows, cols] residual stream, updated in place
   const __nv_bfloat16* w;            // [cols] RMSNorm weight or null
   __nv_bfloat16* h;                  // [rows, cols] normalised output (when w)
-  int rank, ranks, epoch, rows, cols;
+  int* counters;                     // local: [0] calls completed (the epoch of this call is that + 1), [1] CTAs done in this call
+  int rank, ranks, rows, cols;
   float eps;
   int* status;
 };
@@ -48,23 +49,42 @@ __device__ __forceinline__ uint4 ld_peer_16(const void* p) {
   return v;
 }
 
+__device__ __forceinline__ void reduce_row(const ServeArDev& d, int row, int tid, float* red_s);
+
 __global__ void __launch_bounds__(SAR_THREADS)
 serve_allreduce_kernel(const ServeArDev d) {
-  __shared__ int ok_s;
+  __shared__ int ok_s, epoch_s;
   __shared__ float red_s[SAR_THREADS / 32];
   const int P = d.ranks, row = blockIdx.x, tid = threadIdx.x;
+  // The epoch is counted on the device (a launch replayed from a CUDA graph cannot take it as an
+  // argument): every CTA reads the count of completed calls; the CTA that finishes last raises it,
+  // which is after every CTA of this launch has read it.
+  if (tid == 0) { epoch_s = *reinterpret_cast<volatile int*>(d.counters) + 1; ok_s = 1; }
+  __syncthreads();
+  const int epoch = epoch_s;
   // 1. signal (one CTA is enough: the partial was complete before this kernel started)
   if (blockIdx.x == 0 && tid < P) {
     __threadfence_system();
-    st_release_sys(d.sig[tid] + d.rank, d.epoch);
+    st_release_sys(d.sig[tid] + d.rank, epoch);
   }
   // 2. wait for every peer's signal in my own flag array
-  if (tid == 0) ok_s = 1;
+  if (tid < P && !flag_wait_ge_sys(d.sig[d.rank] + tid, epoch, d.status, 4000 + tid, CGK_PEER_WAIT_BUDGET_NS)) ok_s = 0;
   __syncthreads();
-  if (tid < P && !flag_wait_ge_sys(d.sig[d.rank] + tid, d.epoch, d.status, 4000 + tid, CGK_PEER_WAIT_BUDGET_NS)) ok_s = 0;
+  if (ok_s) reduce_row(d, row, tid, red_s);
   __syncthreads();
-  if (!ok_s) return;
-  // 3. sum, residual, norm
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(d.counters + 1, 1) == (int)gridDim.x - 1) {
+      d.counters[1] = 0;
+      __threadfence();
+      atomicAdd(d.counters, 1);
+    }
+  }
+}
+
+// 3. sum, residual, norm of one row by one CTA
+__device__ __forceinline__ void reduce_row(const ServeArDev& d, int row, int tid, float* red_s) {
+  const int P = d.ranks;
   const int vecs = d.cols / 8;                         // 16-byte pieces per row
   float acc[SAR_MAX_VEC][8];
   float ss = 0.0f;
@@ -130,12 +150,13 @@ serve_allreduce_kernel(const ServeArDev d) {
 }  // namespace cgk
 
 // partial[p], sig[p]: the addresses of rank p's slot / flag array as mapped in THIS process.
-// x, h: [rows, cols] bf16, local.  cols a multiple of 8, at most 16384.  epoch: 1, 2, 3, ... the
-// same on every rank for the same call.  w null: no norm.
-CGK_API int cgk_serve_allreduce(const void* const* partial, int* const* sig, int rank, int ranks, int epoch, void* x,
+// x, h: [rows, cols] bf16, local.  cols a multiple of 8, at most 16384.  counters: two local ints, zero
+// before the first call (the kernel numbers the calls itself; every rank makes the same calls in the
+// same order).  w null: no norm.
+CGK_API int cgk_serve_allreduce(const void* const* partial, int* const* sig, int rank, int ranks, int* counters, void* x,
                                 const void* w, void* h, int rows, int cols, float eps, void* stream) {
   using namespace cgk;
-  CGK_REQUIRE(partial && sig && x && ranks >= 1 && ranks <= 8 && rank >= 0 && rank < ranks && epoch > 0, "cgk_serve_allreduce: bad argument");
+  CGK_REQUIRE(partial && sig && x && ranks >= 1 && ranks <= 8 && rank >= 0 && rank < ranks && counters, "cgk_serve_allreduce: bad argument");
   CGK_REQUIRE(rows > 0 && cols > 0 && cols % 8 == 0 && cols <= SAR_THREADS * SAR_MAX_VEC * 8, "cgk_serve_allreduce: cols must be a multiple of 8, at most 16384");
   CGK_REQUIRE(!w || h, "cgk_serve_allreduce: a norm weight needs an output");
   int dev = 0;
@@ -147,7 +168,7 @@ CGK_API int cgk_serve_allreduce(const void* const* partial, int* const* sig, int
     d.sig[p] = sig[p];
   }
   d.x = (__nv_bfloat16*)x; d.w = (const __nv_bfloat16*)w; d.h = (__nv_bfloat16*)h;
-  d.rank = rank; d.ranks = ranks; d.epoch = epoch; d.rows = rows; d.cols = cols; d.eps = eps;
+  d.rank = rank; d.ranks = ranks; d.counters = counters; d.rows = rows; d.cols = cols; d.eps = eps;
   d.status = device_status(dev);
   serve_allreduce_kernel<<<rows, SAR_THREADS, 0, (cudaStream_t)stream>>>(d);
   CGK_LAUNCH_CHECK();

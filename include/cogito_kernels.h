@@ -127,9 +127,10 @@ int cgk_dp_adam_max_ctas(void);
 
 /* Tensor-parallel serving: x[t,:] += sum over ranks of partial_p[t,:], then (w given)
  * h = rmsnorm(x) * w, in one launch over peer memory (one-shot all-reduce, sums in rank order).
- * partial[p] / sig[p]: rank p's slot of this epoch and its flag array (ranks ints) as mapped
- * here; epoch 1, 2, 3, ... identical on all ranks; slots alternate between two buffers. */
-int cgk_serve_allreduce(const void* const* partial, int* const* sig, int rank, int ranks, int epoch, void* x,
+ * partial[p] / sig[p]: rank p's slot of this call and its flag array (ranks ints) as mapped
+ * here; slots alternate between two buffers; counters: two local ints, zero before the first
+ * call, in which the kernel numbers the calls (so that a CUDA graph can replay it). */
+int cgk_serve_allreduce(const void* const* partial, int* const* sig, int rank, int ranks, int* counters, void* x,
                         const void* w, void* h, int rows, int cols, float eps, void* stream);
 
 /* ---- Flash attention ------------------------------------------------------ */
