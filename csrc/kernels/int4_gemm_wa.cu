@@ -154,25 +154,34 @@ int4_wa_kernel(const WaDev g) {
     const int quad = warp & 3, sub = warp >> 2, f = quad * 32 + lane;
     const uint8_t* wsrc = stream + sub * W_RAW + f * 16;             // k half 0; half 1 is W_NIB / 2 further
     constexpr int NB = NCH == 1 ? 1 : WSUB;                          // scale blocks a thread needs (one chunk: one block)
-    const int blk0 = NCH == 1 ? (tid >> 3) / x_rows : 0;
+    // Everything that does not change from step to step is worked out once: where each of this thread's
+    // X chunks comes from (advances by 128 elements a step) and where it goes inside a stage's X' tile.
+    const __nv_bfloat16* xsrc[NCH];                                   // null: padding row or no chunk
+    uint32_t xdst[NCH];
+    int xblk[NCH];
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int c = tid + j * W_CONV_THREADS, rowb = c >> 3, blk = rowb / x_rows, t = rowb - blk * x_rows;
+      xblk[j] = c < chunks ? blk : -1;
+      xdst[j] = (uint32_t)blk * x_bytes + sw128_offset((uint32_t)t, (uint32_t)ch);
+      xsrc[j] = (c < chunks && m0 + t < g.M) ? g.x + (long long)(m0 + t) * g.ldx + ((long long)ks0 * WSUB + blk) * WK + ch * 8 : nullptr;
+    }
+    const uint8_t* ssrc = stream + (NCH == 1 ? (tid >> 3) / x_rows : 0) * W_RAW + W_NIB + ch * 32;
     uint4 raw[W_PREFETCH][2];
     uint4 xr[2][NCH];                                                // X chunks and scales of the next two steps, by step parity
     float4 sc[2][NB][2];
     auto load_w = [&](int d, int step) {
-      raw[d][0] = ldg_stream_16(wsrc + (long long)step * W_STEP);
-      raw[d][1] = ldg_stream_16(wsrc + (long long)step * W_STEP + W_NIB / 2);
+      const uint8_t* p = wsrc + (long long)step * W_STEP;
+      raw[d][0] = ldg_stream_16(p);
+      raw[d][1] = ldg_stream_16(p + W_NIB / 2);
     };
     auto load_x = [&](int p, int step) {
 #pragma unroll
-      for (int j = 0; j < NCH; ++j) {
-        const int c = tid + j * W_CONV_THREADS, rowb = c >> 3, blk = rowb / x_rows, t = rowb - blk * x_rows;
-        xr[p][j] = make_uint4(0, 0, 0, 0);
-        if (c < chunks && m0 + t < g.M)
-          xr[p][j] = __ldg(reinterpret_cast<const uint4*>(g.x + (long long)(m0 + t) * g.ldx + ((long long)(ks0 + step) * WSUB + blk) * WK + ch * 8));
-      }
+      for (int j = 0; j < NCH; ++j)
+        xr[p][j] = xsrc[j] ? __ldg(reinterpret_cast<const uint4*>(xsrc[j] + step * (WSUB * WK))) : make_uint4(0, 0, 0, 0);
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
-        const float4* sp = reinterpret_cast<const float4*>(stream + (long long)step * W_STEP + (blk0 + b) * W_RAW + W_NIB + ch * 32);
+        const float4* sp = reinterpret_cast<const float4*>(ssrc + (long long)step * W_STEP + b * W_RAW);
         sc[p][b][0] = __ldg(sp); sc[p][b][1] = __ldg(sp + 1);
       }
     };
@@ -180,16 +189,18 @@ int4_wa_kernel(const WaDev g) {
     for (int d = 0; d < W_PREFETCH; ++d) { raw[d][0] = raw[d][1] = make_uint4(0, 0, 0, 0); if (d < ksteps) load_w(d, d); }
     load_x(0, 0);
     if (ksteps > 1) load_x(1, 1);
+    const uint32_t t_st = tmem_a + ((uint32_t)(quad * 32) << 16) + sub * 32;      // + stage * W_ACOLS + half * 16
+    int s = 0;                                                       // stage of the step, and the parity its a_empty wait needs
+    uint32_t par = 1;
     WT_DECL
     for (int i0 = 0; i0 < ksteps && ok; i0 += W_PREFETCH) {
 #pragma unroll
       for (int d = 0; d < W_PREFETCH; ++d) {
         const int i = i0 + d;
         if (i >= ksteps || !ok) break;
-        const int s = i % W_STAGES;
         // stage s (TMEM operand columns and the X' tile) was last read by the MMAs of step i - W_STAGES;
         // one thread polls, a hardware barrier releases the rest
-        if (tid == 0) go_s[d & 1] = i < W_STAGES ? 1 : (int)mbar_wait(a_empty(s), ((i / W_STAGES) - 1) & 1, dead, g.status, 330);
+        if (tid == 0) go_s[d & 1] = (int)mbar_wait(a_empty(s), par, dead, g.status, 330);
         WT_LAP(0)
         asm volatile("bar.sync 1, 256;" ::: "memory");
         WT_LAP(1)
@@ -208,16 +219,16 @@ int4_wa_kernel(const WaDev g) {
             t[4 * c + 2] = ((v >> 8) & 0x000F000Fu) | 0x43004300u;
             t[4 * c + 3] = ((v >> 12) & 0x000F000Fu) | 0x43004300u;
           }
-          tmem_st16(tmem_a + ((uint32_t)(quad * 32) << 16) + s * W_ACOLS + sub * 32 + hh * 16, t);
+          tmem_st16(t_st + s * W_ACOLS + hh * 16, t);
         }
         WT_LAP(2)
         if (i + W_PREFETCH < ksteps) load_w(d, i + W_PREFETCH);
         // X chunks: times the scale of their k, rounded to bf16, summed for the offset correction, stored swizzled
+        uint8_t* xstage = gen + s * (WSUB * x_bytes);
 #pragma unroll
         for (int j = 0; j < NCH; ++j) {
-          const int c = tid + j * W_CONV_THREADS, rowb = c >> 3, blk = rowb / x_rows, t = rowb - blk * x_rows;
-          if (c < chunks) {
-            const int bi = NCH == 1 ? 0 : blk;
+          if (xblk[j] >= 0) {
+            const int bi = NCH == 1 ? 0 : xblk[j];
             const float4 s0 = bi ? sc[d & 1][NB - 1][0] : sc[d & 1][0][0], s1 = bi ? sc[d & 1][NB - 1][1] : sc[d & 1][0][1];
             const uint4 xv = xr[d & 1][j];
             const float2 a = unpack_bf16x2(xv.x), b = unpack_bf16x2(xv.y), cc = unpack_bf16x2(xv.z), e = unpack_bf16x2(xv.w);
@@ -225,7 +236,7 @@ int4_wa_kernel(const WaDev g) {
                                        pack_bf16x2(cc.x * s1.x, cc.y * s1.y), pack_bf16x2(e.x * s1.z, e.y * s1.w));
             const float2 ra = unpack_bf16x2(o.x), rb = unpack_bf16x2(o.y), rc = unpack_bf16x2(o.z), rd = unpack_bf16x2(o.w);
             xs[j] += ((ra.x + ra.y) + (rb.x + rb.y)) + ((rc.x + rc.y) + (rd.x + rd.y));
-            *reinterpret_cast<uint4*>(gen + (s * WSUB + blk) * x_bytes + sw128_offset((uint32_t)t, (uint32_t)ch)) = o;
+            *reinterpret_cast<uint4*>(xstage + xdst[j]) = o;
           }
         }
         WT_LAP(3)
@@ -237,6 +248,7 @@ int4_wa_kernel(const WaDev g) {
         __syncwarp();
         if (lane == 0) mbar_arrive(a_full(s));
         WT_LAP(5)
+        if (++s == W_STAGES) { s = 0; par ^= 1; }
       }
     }
     WT_STORE
