@@ -135,6 +135,10 @@ class _FlatOptimizer:
             raise ValueError("low-precision parameters need fp32 master weights")
         for p, g in zip(self.fp.params, self.fp.views(self.grad)):
             p.main_grad = g
+        # Model-parallel training: (overflow flag, sum of squares) of this rank's gradients -> the values of
+        # the whole model replica.  A callable (found: tensor[1] int32, norm_sq: tensor[1] float32) -> None
+        # that updates both in place (see parallel.llama_parallel.ModelParallelStats); None = local values.
+        self.stats_sync = None
         self._scratch = None
         if dev.type == "cuda":
             ne = _lib.lib().cgk_grad_stats_scratch_elems(n)
@@ -171,6 +175,9 @@ class _FlatOptimizer:
         _lib.check(_lib.lib().cgk_grad_stats(self.grad.data_ptr(), self.grad.numel(), self.scaler.state.data_ptr(),
                                              self._scratch.data_ptr(), 0, _lib.stream_ptr()), "cgk_grad_stats")
         _lib.count_launch(2)
+        if self.stats_sync is not None:
+            st = self.scaler.state
+            self.stats_sync(st.view(torch.int32)[2:3], st[5:6])
 
     def _scaler_update(self):
         s = self.scaler
@@ -186,6 +193,12 @@ class _FlatOptimizer:
         """Returns (unscaled+clipped grad, skip)."""
         g = self.grad
         found = not bool(torch.isfinite(g).all())
+        norm_sq = None
+        if self.stats_sync is not None:
+            f = torch.tensor([int(found)], dtype=torch.int32)
+            n2 = (torch.nan_to_num(g, nan=0.0, posinf=0.0, neginf=0.0) ** 2).sum().reshape(1)
+            self.stats_sync(f, n2)
+            found, norm_sq = bool(f.item()), float(n2)
         # the gradients carry the scale the loss was multiplied with, i.e. the
         # value before this step's update of the scaler
         inv = 1.0 / self.scaler._host["scale"] if self.scaler.enabled else 1.0
@@ -194,7 +207,7 @@ class _FlatOptimizer:
             return None, True
         g = g * inv
         if self.max_grad_norm > 0:
-            norm = float(g.norm())
+            norm = float(g.norm()) if norm_sq is None else math.sqrt(norm_sq) * inv
             if norm > self.max_grad_norm:
                 g = g * (self.max_grad_norm / (norm + 1e-6))
         return g, False

@@ -182,6 +182,24 @@ def shard_llama_state(full, stage: LlamaStage) -> None:
         put(stage.w_head, full.lm_head.weight[r * Vl:(r + 1) * Vl])
 
 
+class ModelParallelStats:
+    """(overflow flag, sum of squares of the gradients) of one rank -> of the whole model replica, i.e.
+    over the tensor- and pipeline-parallel ranks of one data-parallel replica.  Parameters that every
+    tensor-parallel rank holds in full (the first ``n_rep`` elements of the flat gradient, identical on
+    those ranks once their gradients have been all-reduced) are counted once."""
+
+    def __init__(self, ctx, opt, n_rep: int):
+        self.ctx, self.opt, self.n_rep = ctx, opt, n_rep
+
+    def __call__(self, found: torch.Tensor, norm_sq: torch.Tensor) -> None:
+        c = self.ctx.coords
+        if c.tp > 1 and self.n_rep and c.tp_rank != 0:
+            g = torch.nan_to_num(self.opt.grad[:self.n_rep], nan=0.0, posinf=0.0, neginf=0.0)
+            norm_sq -= (g * g).sum()
+        dist.all_reduce(found, op=dist.ReduceOp.MAX, group=self.ctx.mp_group)
+        dist.all_reduce(norm_sq, op=dist.ReduceOp.SUM, group=self.ctx.mp_group)
+
+
 class Trainer3D:
     """One rank of a DP x TP x PP job.  ``step(ids, targets)`` takes this data-parallel replica's
     batch [M * micro_batch, T] (every rank of the replica passes the same tensors) and runs M
@@ -210,6 +228,11 @@ class Trainer3D:
         for p, o in zip(self.opt.fp.params, self.opt.fp.offsets):
             if getattr(p, "tp_replicated", False):
                 self.n_rep = o + (p.numel() + 7) // 8 * 8
+        if c.tp * c.pp > 1 and c.dp == 1:
+            # overflow flag and clipping norm of the whole replica, not of this rank's slice.  (With data
+            # parallelism on top the optimizer step is the fused all-reduce + Adam kernel, which takes its
+            # statistics inside the kernel over the data-parallel ranks only.)
+            self.opt.stats_sync = ModelParallelStats(ctx, self.opt, self.n_rep)
         act_dtype = torch.bfloat16 if cuda else torch.float32
         self.pipe = PipelineExecutor(c.pp_rank, c.pp, num_microbatches, ctx.prev_stage, ctx.next_stage,
                                      (tokens // c.tp, cfg.d_model), act_dtype, self.device)
@@ -232,6 +255,5 @@ class Trainer3D:
         loss = self.pipe.run(stage_fn, first_inputs=[ids_m[m] for m in range(M_)])
         if self.ctx.coords.tp > 1 and self.n_rep:
             dist.all_reduce(self.opt.grad[:self.n_rep], group=self.ctx.tp_group)
-        # a loss-scale overflow must skip the step on every pipeline stage alike: share the flag
-        self.opt.step()
+        self.opt.step()           # overflow flag and gradient norm are those of the whole replica (stats_sync)
         return loss

@@ -66,7 +66,15 @@ def _worker(rank, world, port, dp, tp, pp, q):
         for _ in range(3):
             loss = t3.step(mine_ids, mine_tg)
             lt.append(None if loss is None else float(loss))
-        q.put((rank, ctx.coords.dp_rank, ctx.coords.pp_rank, lf, lt, t3.pipe.p2p_bytes))
+        # the gradients of the last step are still in the flat buffers: the replica-wide sum of squares that
+        # the optimizer clips with must equal the single-device one (replicated parameters counted once)
+        norm_ref = float((ref.opt.grad.double() ** 2).sum())
+        norm_mp = None
+        if dp == 1 and tp * pp > 1:
+            f, n2 = torch.zeros(1, dtype=torch.int32), (t3.opt.grad ** 2).sum().reshape(1).clone()
+            t3.opt.stats_sync(f, n2)
+            norm_mp = float(n2)
+        q.put((rank, ctx.coords.dp_rank, ctx.coords.pp_rank, lf, lt, t3.pipe.p2p_bytes, norm_ref, norm_mp))
     finally:
         dist.destroy_process_group()
 
@@ -90,16 +98,18 @@ def test_3d_llama_matches_single_device(dp, tp, pp):
     assert ref[-1] < ref[0]
     # step 0: each replica's loss is over its own half of the batch; their mean is the full-batch loss
     first = {}
-    for rank, d, p_, lf, lt, nbytes in last:
+    for rank, d, p_, lf, lt, nbytes, *_ in last:
         first.setdefault(d, lt[0])
         assert nbytes > 0 or pp == 1
     assert abs(sum(first.values()) / len(first) - ref[0]) < 2e-3
     # later steps: parameters stayed in lock-step with the single-device run
     for step in (1, 2):
         vals = {}
-        for rank, d, p_, lf, lt, nbytes in last:
+        for rank, d, p_, lf, lt, nbytes, *_ in last:
             vals.setdefault(d, lt[step])
         assert abs(sum(vals.values()) / len(vals) - ref[step]) < 3e-3, (step, vals, ref)
     for r in res:
         if r[2] != pp - 1:
             assert all(v is None for v in r[4])
+        if dp == 1:
+            assert r[7] is not None and abs(r[7] - r[6]) < 5e-3 * r[6], (r[6], r[7])
