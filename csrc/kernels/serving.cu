@@ -263,7 +263,9 @@ __global__ void kv_combine_kernel(const float* __restrict__ part_acc, const floa
 // argmax.  top_k is clamped to [1, 1024] (0 = 1024).  probs_out (optional, fp32 [rows, V])
 // receives the final distribution (zeros outside the kept set).
 __device__ __forceinline__ uint32_t float_key(float f) { const uint32_t u = __float_as_uint(f); return (u & 0x80000000u) ? ~u : u | 0x80000000u; }
+__device__ __forceinline__ float key_float(uint32_t k) { return __uint_as_float((k & 0x80000000u) ? k ^ 0x80000000u : ~k); }
 constexpr int SAMPLE_THREADS = 1024, MAX_TOPK = 1024;
+constexpr int SAMPLE_REGS = 32;       // rows of up to 32 * 1024 logits are read once and kept as sort keys in registers
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const void* __restrict__ logits, int logits_bf16, long long ld, int V, float temperature, int top_k, float top_p,
@@ -272,16 +274,22 @@ sample_kernel(const void* __restrict__ logits, int logits_bf16, long long ld, in
   __shared__ float s_red[32];
   __shared__ float cand_v[MAX_TOPK];
   __shared__ int cand_i[MAX_TOPK];
-  __shared__ uint32_t s_prefix;
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   auto load = [&](int i) -> float {
     const float v = logits_bf16 ? __bfloat162float(((const __nv_bfloat16*)logits)[row * ld + i]) : ((const float*)logits)[row * ld + i];
     return temperature > 0.0f ? v / temperature : v;
   };
-  auto block_max = [&](float v) { v = warp_max(v); if (lane == 0) s_red[warp] = v; __syncthreads(); v = lane < 32 ? s_red[lane] : -INFINITY; v = warp_max(v); __syncthreads(); return v; };
   auto block_sum = [&](float v) { v = warp_sum(v); if (lane == 0) s_red[warp] = v; __syncthreads(); v = s_red[lane]; v = warp_sum(v); __syncthreads(); return v; };
   const int k = temperature > 0.0f ? (top_k <= 0 || top_k > MAX_TOPK ? MAX_TOPK : top_k) : 1;
   const int kk = k < V ? k : V;
+  // The 32 selection rounds and the two gathering passes below each look at every logit: from registers
+  // when the row fits (key 0 stands for "no element": it is below the key of any float), else from memory.
+  const bool in_regs = V <= SAMPLE_REGS * SAMPLE_THREADS;
+  uint32_t key[SAMPLE_REGS];
+  if (in_regs) {
+#pragma unroll
+    for (int j = 0; j < SAMPLE_REGS; ++j) { const int i = tid + j * SAMPLE_THREADS; key[j] = i < V ? float_key(load(i)) : 0u; }
+  }
   // radix bisection (32 rounds) for the key of the kk-th largest value
   uint32_t prefix = 0;
   for (int bit = 31; bit >= 0; --bit) {
@@ -289,7 +297,12 @@ sample_kernel(const void* __restrict__ logits, int logits_bf16, long long ld, in
     __syncthreads();
     const uint32_t want = prefix | (1u << bit);
     uint32_t mine = 0;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) mine += (float_key(load(i)) >> bit) >= (want >> bit);
+    if (in_regs) {
+#pragma unroll
+      for (int j = 0; j < SAMPLE_REGS; ++j) mine += (key[j] >> bit) >= (want >> bit);
+    } else {
+      for (int i = tid; i < V; i += SAMPLE_THREADS) mine += (float_key(load(i)) >> bit) >= (want >> bit);
+    }
     mine = (uint32_t)__reduce_add_sync(0xffffffffu, mine);
     if (lane == 0 && mine) atomicAdd(&s_count, mine);
     __syncthreads();
@@ -299,16 +312,19 @@ sample_kernel(const void* __restrict__ logits, int logits_bf16, long long ld, in
   // gather the candidates: everything above the threshold, then ties until kk slots are used
   if (tid == 0) s_count = 0;
   __syncthreads();
-  for (int i = tid; i < V; i += SAMPLE_THREADS) {
-    const float v = load(i);
-    if (float_key(v) > prefix) { const uint32_t slot = atomicAdd(&s_count, 1u); if (slot < (uint32_t)kk) { cand_v[slot] = v; cand_i[slot] = i; } }
+  auto take = [&](uint32_t kv, int i) { const uint32_t slot = atomicAdd(&s_count, 1u); if (slot < (uint32_t)kk) { cand_v[slot] = key_float(kv); cand_i[slot] = i; } };
+  if (in_regs) {
+#pragma unroll
+    for (int j = 0; j < SAMPLE_REGS; ++j) if (key[j] > prefix) take(key[j], tid + j * SAMPLE_THREADS);
+  } else {
+    for (int i = tid; i < V; i += SAMPLE_THREADS) { const uint32_t kv = float_key(load(i)); if (kv > prefix) take(kv, i); }
   }
   __syncthreads();
-  if (tid == 0) s_prefix = s_count;
-  __syncthreads();
-  for (int i = tid; i < V; i += SAMPLE_THREADS) {
-    const float v = load(i);
-    if (float_key(v) == prefix) { const uint32_t slot = atomicAdd(&s_count, 1u); if (slot < (uint32_t)kk) { cand_v[slot] = v; cand_i[slot] = i; } }
+  if (in_regs) {
+#pragma unroll
+    for (int j = 0; j < SAMPLE_REGS; ++j) if (key[j] == prefix) take(key[j], tid + j * SAMPLE_THREADS);
+  } else {
+    for (int i = tid; i < V; i += SAMPLE_THREADS) { const uint32_t kv = float_key(load(i)); if (kv == prefix) take(kv, i); }
   }
   __syncthreads();
   const int n = (int)min(s_count, (uint32_t)kk);
