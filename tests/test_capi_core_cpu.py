@@ -103,6 +103,18 @@ def test_xor_example_compiles_as_c11_and_converges(tmp_path):
     assert "live tensors 0" in r.stdout
 
 
+def test_mnist_example_trains_with_the_library_layers_loader_and_adam(tmp_path):
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if not cc:
+        pytest.skip("no C compiler")
+    exe = tmp_path / "mnist"
+    subprocess.check_call([cc, "-std=c11", "-Wall", "-Werror", "-I", str(ROOT / "include"), str(ROOT / "examples" / "mnist.c"),
+                           "-L", str(ROOT / "cogito_b200" / "lib"), "-lcogito", "-lm", "-o", str(exe)])
+    r = subprocess.run([str(exe)], env={"LD_LIBRARY_PATH": str(ROOT / "cogito_b200" / "lib")}, capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout              # exit code 0 = final training accuracy above 0.9
+    assert "epoch 5" in r.stdout
+
+
 def test_layers_match_torch_forward_and_backward():
     lib = L()
     # conv -> batchnorm -> relu -> maxpool -> flatten -> linear, loss = sum(out * w)
