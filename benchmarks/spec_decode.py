@@ -35,6 +35,7 @@ def main():
     ap.add_argument("--gamma", type=int, default=4)
     ap.add_argument("--kv-heads", type=int, default=32)
     ap.add_argument("--self-draft", action="store_true")
+    ap.add_argument("--tp-graph", action="store_true", help="replay the step from a CUDA graph under tensor parallelism too")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
 
@@ -68,7 +69,7 @@ def main():
     model = None
     torch.cuda.empty_cache()
     dec = SpeculativeDecoder(draft, target, gamma=args.gamma, temperature=0.8, top_k=50, top_p=0.9, seed=0,
-                             use_graph=False if args.no_graph else None)
+                             use_graph=False if args.no_graph else (True if args.tp_graph else None))
     prompts = torch.randint(0, 32000, (args.batch, args.prompt), generator=torch.Generator().manual_seed(1)).to(dev)
 
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
@@ -106,7 +107,9 @@ def main():
             "weight_bytes_per_gpu": target.weight_bytes() + draft.weight_bytes(),
             "config": {"layers": args.layers, "draft_layers": args.draft_layers, "batch": args.batch, "prompt": args.prompt, "new": args.new,
                        "gamma": args.gamma, "kv_heads": args.kv_heads, "tp": world, "self_draft": args.self_draft, "data": "synthetic"}}), flush=True)
+    dec.close()                                           # drop the captured collectives before the process group goes
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

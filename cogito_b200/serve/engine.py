@@ -191,13 +191,12 @@ class SpeculativeDecoder:
         # than the device.  On CUDA the whole step (gamma draft passes, verify, accept, cache bookkeeping)
         # is captured once into a CUDA graph and replayed.  Everything the step depends on lives on the
         # device (cache lengths, random-stream counter, the call counter of the fused tensor-parallel
-        # all-reduce), so the recorded launches stay valid.  Default: on for unsplit engines.  A split
-        # engine's step also contains the process group's all-gather of the logits; it captures and
-        # replays correctly (use_graph=True), but a process that still holds such a graph did not leave
-        # torch.distributed's shutdown on 2 GPUs, so call close() before destroying the process group.
-        # COGITO_SERVE_GRAPH=0 turns graphs off altogether.
+        # all-reduce), so the recorded launches stay valid.  A split engine's graph also records the process
+        # group's all-gather of the logits: call close() before destroying the process group (a process that
+        # still held such a graph did not leave torch.distributed's shutdown).  COGITO_SERVE_GRAPH=0 turns
+        # graphs off.
         env = os.environ.get("COGITO_SERVE_GRAPH", "1") != "0"
-        self.use_graph = (dev.type == "cuda" and env and target.tp == 1 and draft.tp == 1) if use_graph is None else use_graph
+        self.use_graph = (dev.type == "cuda" and env) if use_graph is None else use_graph
         self._graph = None
         self._eager_steps = 0
 

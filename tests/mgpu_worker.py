@@ -118,6 +118,8 @@ def main():
         out["tokens_agree"] = bool((lo == hi).all())
         out["fused"] = bool(tp.ar.fused)
         out["acceptance"] = stats.acceptance_rate
+        out["graph"] = dec._graph is not None
+        dec.close()                               # the captured step holds collectives of the process group
     else:
         raise SystemExit(f"unknown mode {mode}")
     out["status"] = list(_lib.read_status())
