@@ -30,7 +30,7 @@ import sys
 import threading
 import time
 
-REF_UNAVAILABLE = ("pip install of /root/reference failed: \"Neither 'setup.py' nor 'pyproject.toml' found\" "
+REF_UNAVAILABLE = ("pip install of the reference failed: \"Neither 'setup.py' nor 'pyproject.toml' found\" "
                    "(pure-C CMake project whose library target does not compile; no transformer training path)")
 
 
