@@ -101,6 +101,25 @@ class Heartbeat:
         if dead:
             raise RankFailure(dead)
 
+    def guard(self, fn, *args, **kw):
+        """Runs a collective.  A peer that left while this rank was already inside it shows up as a
+        transport error (connection reset, timeout) rather than as a stale heartbeat: on such an error
+        wait up to ``timeout`` + 1 s for the heartbeats to name the dead ranks and raise ``RankFailure``
+        with them; if every peer is alive the original error is raised."""
+        try:
+            return fn(*args, **kw)
+        except RankFailure:
+            raise
+        except Exception as e:
+            end = time.time() + self.timeout + 1.0
+            while True:
+                dead = self.dead_ranks()
+                if dead:
+                    raise RankFailure(dead) from e
+                if time.time() >= end:
+                    raise
+                time.sleep(min(0.1, max(self.interval, 0.01)))
+
 
 def check_device():
     """Raise when a kernel of this library reported a bounded wait that ran out."""

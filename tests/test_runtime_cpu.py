@@ -162,6 +162,23 @@ def test_heartbeat_detects_silent_and_exited_ranks():
     assert hbs[0].dead_ranks() == [1, 2]
 
 
+def test_guard_turns_a_transport_error_into_a_rank_failure_only_when_a_peer_is_dead():
+    store = DictStore()
+    hbs = [Heartbeat(store, r, 2, interval=0, timeout=0.2).start() for r in range(2)]
+
+    def broken():
+        raise RuntimeError("Connection reset by peer")
+
+    assert hbs[0].guard(lambda a: a + 1, 1) == 2
+    hbs[1].announce_exit()                               # the peer left while we were inside the collective
+    with pytest.raises(RankFailure) as e:
+        hbs[0].guard(broken)
+    assert e.value.dead == [1]
+    hbs[1].beat()                                        # alive again: the error is not a rank failure
+    with pytest.raises(RuntimeError, match="Connection reset"):
+        Heartbeat(store, 0, 1, interval=0, timeout=0.1).start().guard(broken)
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -205,7 +222,7 @@ def _elastic_worker(rank, world, port, tmp, q):
             for p in model.parameters():                 # data-parallel gradient agreement check
                 pass
             v = loss.detach().clone()
-            dist.all_reduce(v)
+            hb.guard(dist.all_reduce, v)                  # a rank that left mid-collective surfaces as RankFailure too
             losses.append((info["attempt"], step, float(v) / dist.get_world_size()))
             ckpt.save_training_state(base, model, tr.opt, step + 1)
             import time
