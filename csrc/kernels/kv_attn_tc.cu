@@ -6,7 +6,7 @@
 //   1. all threads turn the block's K and V nibbles into bf16 operand tiles in shared memory
 //      (128-byte swizzle; the same image serves K as a K-major A operand and V as an MN-major one),
 //   2. S^T[128 keys, NP] = K . Q^T           (tcgen05.mma, accumulator in TMEM, keys on the lanes),
-//   3. every thread owns one key: scale, mask, block max over the keys (redux + shared memory),
+//   3. every thread owns one key: scale, mask; row maxima through a row-major copy in shared memory,
 //      p = 2^(s - m) written as the K-major B operand P[NP, 128 keys],
 //   4. O^T[128 d, NP] = V^T . P^T            (tcgen05.mma), read back and folded into the
 //      running, rescaled accumulator in registers.
@@ -31,18 +31,15 @@ template <int NP>
 struct KvtSmem {
   static constexpr uint32_t Q_BYTES = NP * KVT_D * 2, P_BYTES = NP * KVT_KB * 2;
   static constexpr uint32_t OFF_K = 0, OFF_V = KVT_TILE, OFF_Q = 2 * KVT_TILE, OFF_P = OFF_Q + Q_BYTES;
-  static constexpr uint32_t OFF_WMAX = OFF_P + P_BYTES;                 // float [4][NP]
+  static constexpr uint32_t T_STRIDE = KVT_KB + 4;                      // floats per row of the transposed score tile (padded)
+  static constexpr uint32_t OFF_T = OFF_P + P_BYTES;                    // float [NP][T_STRIDE]: scores, row-major, for the row maxima
+  static constexpr uint32_t OFF_WMAX = OFF_T + NP * T_STRIDE * 4;       // float [3][NP]: new maximum, rescale factor, running maximum per row
   static constexpr uint32_t OFF_LRED = OFF_WMAX + 4 * NP * 4;           // float [4][NP]
   static constexpr uint32_t OFF_BAR = OFF_LRED + 4 * NP * 4;            // two mbarriers
   static constexpr uint32_t OFF_MISC = OFF_BAR + 16;                    // tmem slot, dead flag
   static constexpr uint32_t TOTAL = OFF_MISC + 16 + 1024;               // + slack for the 1 KiB alignment
 };
 
-__device__ __forceinline__ float redux_max_f32(float v) {
-  float r;
-  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
-  return r;
-}
 // position p (0..7) of a converted word holds element (p & 1) * 4 + (p >> 1)
 __device__ __forceinline__ int kvt_perm(int p) { return ((p & 1) << 2) | (p >> 1); }
 
@@ -89,7 +86,9 @@ kv_attention_tc_kernel(KvDev c, const __nv_bfloat16* __restrict__ q, int Tq, int
   extern __shared__ uint8_t kvt_raw[];
   uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(kvt_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sb = smem_u32(sm);
-  float* wmax = reinterpret_cast<float*>(sm + S::OFF_WMAX);
+  float* tsc = reinterpret_cast<float*>(sm + S::OFF_T);
+  float* rowstat = reinterpret_cast<float*>(sm + S::OFF_WMAX);      // [0] new maximum, [NP] rescale factor, [2 NP] running maximum
+  constexpr int TS = (int)S::T_STRIDE;
   float* lred = reinterpret_cast<float*>(sm + S::OFF_LRED);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + S::OFF_MISC);
   volatile int* dead = reinterpret_cast<volatile int*>(sm + S::OFF_MISC + 4);
@@ -158,9 +157,10 @@ kv_attention_tc_kernel(KvDev c, const __nv_bfloat16* __restrict__ q, int Tq, int
     }
   };
 
-  float acc[CPT], l_part[CPT], m_run[CPT];
+  float acc[CPT], l_part[CPT];
 #pragma unroll
-  for (int j = 0; j < CPT; ++j) { acc[j] = 0.0f; l_part[j] = 0.0f; m_run[j] = -INFINITY; }
+  for (int j = 0; j < CPT; ++j) { acc[j] = 0.0f; l_part[j] = 0.0f; }
+  if (tid < NP) rowstat[2 * NP + tid] = -INFINITY;                   // ordered before its first use by the barriers of the first block
   const uint32_t idesc_s = make_idesc_bf16(128, NP, 0, 0), idesc_o = make_idesc_bf16(128, NP, 1, 0);
   uint32_t phase = 0;
   bool ok = true;
@@ -201,23 +201,40 @@ kv_attention_tc_kernel(KvDev c, const __nv_bfloat16* __restrict__ q, int Tq, int
     for (int j = 0; j < CPT; ++j) {
       const int t = (r0 + half * CPT + j) / rep;
       s[j] = (key >= k_end || key > len - Tq + t) ? -INFINITY : __uint_as_float(sr[j]) * scale_log2;   // causal among the new tokens
-      const float wm = redux_max_f32(s[j]);
-      if (lane == 0) wmax[quad * NP + half * CPT + j] = wm;
+      tsc[(half * CPT + j) * TS + kin] = s[j];                      // row-major copy: the keys of a row lie on the lanes here
     }
     KT_LAP(5)
+    __syncthreads();
+    {
+      // row maximum over the block's 128 keys by TPR threads (a warp-wide redux per row and thread cost
+      // ~100 cycles each), then ONE thread per row folds it into the running maximum and works out the
+      // rescale factor, instead of every thread repeating the exponential
+      constexpr int TPR = KVT_THREADS / NP, F4 = KVT_KB / 4 / TPR;
+      const int r = tid / TPR, seg = tid % TPR;
+      const float4* row4 = reinterpret_cast<const float4*>(tsc + r * TS);
+      float mb = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < F4; ++i) { const float4 v = row4[i * TPR + seg]; mb = fmaxf(fmaxf(mb, fmaxf(v.x, v.y)), fmaxf(v.z, v.w)); }
+#pragma unroll
+      for (int o = 1; o < TPR; o <<= 1) mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, o));
+      if (seg == 0) {
+        const float mo = rowstat[2 * NP + r], mn = fmaxf(mo, mb);
+        rowstat[r] = mn;
+        rowstat[NP + r] = mo > -INFINITY ? fast_exp2(mo - mn) : 1.0f;
+        rowstat[2 * NP + r] = mn;
+      }
+    }
     __syncthreads();
     KT_LAP(6)
     float corr[CPT];
 #pragma unroll
     for (int j = 0; j < CPT; ++j) {
       const int r = half * CPT + j;
-      const float mb = fmaxf(fmaxf(wmax[r], wmax[NP + r]), fmaxf(wmax[2 * NP + r], wmax[3 * NP + r]));
-      const float mn = fmaxf(m_run[j], mb);
-      corr[j] = m_run[j] > -INFINITY ? fast_exp2(m_run[j] - mn) : 1.0f;
+      const float mn = rowstat[r];
+      corr[j] = rowstat[NP + r];
       const float p = s[j] > -INFINITY ? fast_exp2(s[j] - mn) : 0.0f;
       const __nv_bfloat16 pb = __float2bfloat16(p);
       l_part[j] = l_part[j] * corr[j] + __bfloat162float(pb);
-      m_run[j] = mn;
       *reinterpret_cast<__nv_bfloat16*>(sm + S::OFF_P + (kin >> 6) * (NP * 128) + sw128_offset(r, (kin & 63) >> 3) + (kin & 7) * 2) = pb;
     }
     KT_LAP(7)
@@ -266,7 +283,7 @@ kv_attention_tc_kernel(KvDev c, const __nv_bfloat16* __restrict__ q, int Tq, int
         const long long row = ((long long)(b * c.heads + hk) * R + r0 + r) * splits + split;
         part_acc[row * D + d] = acc[j];
         if (L == 0) {
-          part_ml[row * 2] = m_run[j] * 0.69314718056f;          // the combine step works with natural logarithms
+          part_ml[row * 2] = rowstat[2 * NP + r] * 0.69314718056f;         // the combine step works with natural logarithms
           part_ml[row * 2 + 1] = lred[r] + lred[NP + r] + lred[2 * NP + r] + lred[3 * NP + r];
         }
       }
