@@ -24,6 +24,7 @@ from ..optim.fused import FusedAdam, GradScaler
 from ..utils import rng
 from .data_parallel import DPFusedAdam
 from .groups import ParallelContext
+from .interleaved import InterleavedExecutor
 from .pipeline import PipelineExecutor
 from .tensor_parallel import _ColumnRow, _LMHead, _VocabParallelCE
 from .tp_ops import TPWorkspace
@@ -208,7 +209,11 @@ class Trainer3D:
     the fused Adam kernel (or a plain all-reduce on CPU ranks)."""
 
     def __init__(self, cfg: LlamaConfig, ctx: ParallelContext, device, num_microbatches: int, micro_batch: int, seq_len: int,
-                 lr: float = 1e-4, loss_scale: float | None = 65536.0, max_grad_norm: float = 1.0, weight_decay: float = 0.0):
+                 lr: float = 1e-4, loss_scale: float | None = 65536.0, max_grad_norm: float = 1.0, weight_decay: float = 0.0,
+                 virtual_stages: int = 1):
+        """virtual_stages > 1: every pipeline rank holds that many model chunks (virtual stage = chunk * pp +
+        pp_rank) and the step runs the interleaved 1F1B schedule (parallel/interleaved.py); the number of
+        micro-batches must then be a multiple of pp."""
         self.cfg, self.ctx, self.device = cfg, ctx, torch.device(device)
         self.M, self.mb, self.T = num_microbatches, micro_batch, seq_len
         cuda = self.device.type == "cuda"
@@ -219,9 +224,13 @@ class Trainer3D:
             raise ValueError("micro_batch * seq_len must divide by the tensor-parallel size")
         self.ws = TPWorkspace(self.device, ctx.tp_group if c.tp > 1 else None, max_rows=tokens,
                               max_cols=max(cfg.d_model, 1))
-        self.stage = LlamaStage(cfg, self.ws, c.pp_rank, c.pp, self.device, dtype)
+        V = self.V = virtual_stages
+        self.stages = [LlamaStage(cfg, self.ws, ch * c.pp + c.pp_rank, c.pp * V, self.device, dtype) for ch in range(V)]
+        self.stage = self.stages[0]
         self.scaler = GradScaler(self.device, enabled=loss_scale is not None, init_scale=loss_scale or 1.0)
-        params = self.stage.ordered_parameters()
+        # replicated parameters of every chunk first: their gradients are one contiguous slice
+        allp = [p for st in self.stages for p in st.parameters()]
+        params = [p for p in allp if getattr(p, "tp_replicated", False)] + [p for p in allp if not getattr(p, "tp_replicated", False)]
         kw = dict(lr=lr, scaler=self.scaler, max_grad_norm=max_grad_norm, weight_decay=weight_decay)
         self.opt = DPFusedAdam(params, ctx.dp_group, **kw) if c.dp > 1 else FusedAdam(params, **kw)
         self.n_rep = 0
@@ -234,12 +243,17 @@ class Trainer3D:
             # statistics inside the kernel over the data-parallel ranks only.)
             self.opt.stats_sync = ModelParallelStats(ctx, self.opt, self.n_rep)
         act_dtype = torch.bfloat16 if cuda else torch.float32
-        self.pipe = PipelineExecutor(c.pp_rank, c.pp, num_microbatches, ctx.prev_stage, ctx.next_stage,
-                                     (tokens // c.tp, cfg.d_model), act_dtype, self.device)
+        if V == 1:
+            self.pipe = PipelineExecutor(c.pp_rank, c.pp, num_microbatches, ctx.prev_stage, ctx.next_stage,
+                                         (tokens // c.tp, cfg.d_model), act_dtype, self.device)
+        else:
+            self.pipe = InterleavedExecutor(c.pp_rank, ctx.pp_ranks if c.pp > 1 else [0], V, num_microbatches,
+                                            (tokens // c.tp, cfg.d_model), act_dtype, self.device)
 
     def load_from(self, full) -> None:
         """Take this rank's stage / tensor-parallel shards from a single-device ``Llama``."""
-        shard_llama_state(full, self.stage)
+        for st in self.stages:
+            shard_llama_state(full, st)
         self.opt.refresh_master()
 
     def step(self, ids: torch.Tensor, targets: torch.Tensor):
@@ -248,11 +262,18 @@ class Trainer3D:
         ids_m, tgt_m = ids.view(M_, mb, T), targets.view(M_, mb, T)
         scale = self.scaler.scale_tensor if (self.scaler.enabled and self.device.type == "cuda") else self.scaler.scale
 
-        def stage_fn(x, m):
-            gs = scale / M_ if not isinstance(scale, torch.Tensor) else scale / M_
-            return self.stage(x, (mb, T), tgt_m[m] if self.ctx.coords.pp_rank == self.ctx.coords.pp - 1 else None, gs)
+        c = self.ctx.coords
+        last_virtual = c.pp * self.V - 1
 
-        loss = self.pipe.run(stage_fn, first_inputs=[ids_m[m] for m in range(M_)])
+        def chunk_fn(ch):
+            stage, is_last = self.stages[ch], ch * c.pp + c.pp_rank == last_virtual
+
+            def stage_fn(x, m):
+                return stage(x, (mb, T), tgt_m[m] if is_last else None, scale / M_)
+            return stage_fn
+
+        first = [ids_m[m] for m in range(M_)]
+        loss = self.pipe.run(chunk_fn(0), first_inputs=first) if self.V == 1 else self.pipe.run([chunk_fn(ch) for ch in range(self.V)], first)
         if self.ctx.coords.tp > 1 and self.n_rep:
             dist.all_reduce(self.opt.grad[:self.n_rep], group=self.ctx.tp_group)
         self.opt.step()           # overflow flag and gradient norm are those of the whole replica (stats_sync)

@@ -5,7 +5,9 @@
 mode tp  : tensor-parallel GPT-2 (fused all-gather->GEMM / GEMM->reduce-scatter) against the
            single-device model trained on the same batch
 mode dp  : fused all-reduce + Adam optimizer step against the single-device full-batch run
-mode 3d  : DP x TP x PP Llama (1F1B) against the single-device model
+mode 3d  : DP x TP x PP Llama (1F1B; a fourth number > 1 = chunks per rank, interleaved 1F1B) against the
+           single-device model
+mode serve: tensor-parallel INT4 engine and speculative decoder against the unsplit engine
 Every rank prints one line "RESULT <json>"; the test reads rank 0's.
 """
 import json
@@ -67,6 +69,7 @@ def main():
         out["got"] = got
     elif mode == "3d":
         dp, tp, pp = (int(a) for a in sys.argv[2:5])
+        virtual = int(sys.argv[5]) if len(sys.argv) > 5 else 1      # chunks per pipeline rank (interleaved 1F1B)
         from cogito_b200.models.llama import Llama, LlamaConfig
         from cogito_b200.parallel.groups import init_parallel
         from cogito_b200.parallel.llama_parallel import Trainer3D, shard_llama_state
@@ -74,7 +77,8 @@ def main():
         full = Llama(cfg, device=dev, dtype=torch.bfloat16)
         ctx = init_parallel(dp, tp, pp)
         M, mb, T = 4, 1, 256
-        t3 = Trainer3D(cfg, ctx, dev, num_microbatches=M, micro_batch=mb, seq_len=T, lr=1e-3, loss_scale=None, max_grad_norm=0.0)
+        t3 = Trainer3D(cfg, ctx, dev, num_microbatches=M, micro_batch=mb, seq_len=T, lr=1e-3, loss_scale=None, max_grad_norm=0.0,
+                       virtual_stages=virtual)
         t3.load_from(full)
         ids = torch.randint(0, 2048, (dp * M * mb, T), generator=g).to(dev)
         tg = torch.randint(0, 2048, (dp * M * mb, T), generator=g).to(dev)

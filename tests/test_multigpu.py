@@ -67,3 +67,10 @@ def test_tensor_parallel_int4_serving(n):
         assert out["status"][0] == 0, out
         assert out["fused"] and out["tokens_agree"], out
         assert max(out["got"]) < 0.06, out              # logits of the split engine vs the unsplit one, relative to their range (bf16 sums in another order)
+
+
+def test_3d_llama_interleaved_schedule():
+    """Two pipeline ranks with two model chunks each (virtual stages 0..3), tick-synchronous executor over NCCL."""
+    res = _run(2, "3d", 1, 1, 2, 2)
+    _close(res, 0.05)
+    assert max(r["p2p_bytes"] for r in res) > 0

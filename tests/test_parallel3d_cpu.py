@@ -36,7 +36,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, dp, tp, pp, q):
+def _worker(rank, world, port, dp, tp, pp, q, virtual=1):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     torch.set_num_threads(1)
@@ -53,7 +53,8 @@ def _worker(rank, world, port, dp, tp, pp, q):
         full = Llama(cfg)
         ctx = init_parallel(dp, tp, pp)
         M, mb, T = 4, 1, 16
-        t3 = Trainer3D(cfg, ctx, "cpu", num_microbatches=M, micro_batch=mb, seq_len=T, lr=1e-2, loss_scale=None, max_grad_norm=0.0)
+        t3 = Trainer3D(cfg, ctx, "cpu", num_microbatches=M, micro_batch=mb, seq_len=T, lr=1e-2, loss_scale=None, max_grad_norm=0.0,
+                       virtual_stages=virtual)
         t3.load_from(full)
         g = torch.Generator().manual_seed(1)
         ids = torch.randint(0, 64, (dp * M * mb, T), generator=g)
@@ -79,13 +80,13 @@ def _worker(rank, world, port, dp, tp, pp, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("dp,tp,pp", [(1, 1, 2), (1, 2, 2), (2, 2, 2)])
-def test_3d_llama_matches_single_device(dp, tp, pp):
+@pytest.mark.parametrize("dp,tp,pp,virtual", [(1, 1, 2, 1), (1, 2, 2, 1), (2, 2, 2, 1), (1, 2, 2, 2)])   # last: interleaved 1F1B, 2 chunks per rank
+def test_3d_llama_matches_single_device(dp, tp, pp, virtual):
     world = dp * tp * pp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, dp, tp, pp, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, dp, tp, pp, q, virtual)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=600) for _ in procs]
