@@ -28,7 +28,7 @@ DEFAULTS = {
     "device": "auto",                      # auto | cpu | cuda
     "model": {"family": "gpt2", "vocab_size": 50304, "n_layer": 12, "d_model": 768, "n_head": 12, "n_kv_head": None,
               "d_ff": 3072, "max_seq_len": 2048, "hidden": [512, 512], "in_features": 784, "classes": 10},
-    "parallel": {"dp": 1, "tp": 1, "pp": 1, "microbatches": 1},
+    "parallel": {"dp": 1, "tp": 1, "pp": 1, "microbatches": 1, "virtual_stages": 1},
     "train": {"steps": 10, "batch": 8, "micro_batch": None, "seq_len": 1024, "lr": 3e-4, "weight_decay": 0.0,
               "max_grad_norm": 1.0, "loss_scale": 65536.0, "optimizer": "adam"},
     "data": {"kind": "synthetic", "images": None, "labels": None},
@@ -103,7 +103,8 @@ def cmd_train(cfg):
         ctx = init_parallel(p["dp"], p["tp"], p["pp"])
         mb = t["micro_batch"] or 1
         t3 = Trainer3D(lc, ctx, dev, p["microbatches"], mb, t["seq_len"], lr=t["lr"], loss_scale=t["loss_scale"] if scaler_on else None,
-                       max_grad_norm=t["max_grad_norm"], weight_decay=t["weight_decay"])
+                       max_grad_norm=t["max_grad_norm"], weight_decay=t["weight_decay"],
+                       virtual_stages=p.get("virtual_stages", 1) or 1)
         model, opt = t3.stage, t3.opt
         batch_rows = p["microbatches"] * mb
         step_fn = t3.step
