@@ -232,15 +232,20 @@ class Trainer3D:
         allp = [p for st in self.stages for p in st.parameters()]
         params = [p for p in allp if getattr(p, "tp_replicated", False)] + [p for p in allp if not getattr(p, "tp_replicated", False)]
         kw = dict(lr=lr, scaler=self.scaler, max_grad_norm=max_grad_norm, weight_decay=weight_decay)
-        self.opt = DPFusedAdam(params, ctx.dp_group, **kw) if c.dp > 1 else FusedAdam(params, **kw)
+        # Loss scaling and norm clipping decide per step from statistics of the WHOLE replica (all tp x pp
+        # ranks): an overflow seen on one pipeline stage must skip the step on every stage.  The fused
+        # all-reduce + Adam kernel takes its statistics inside the kernel, over the data-parallel ranks of
+        # one (tp, pp) coordinate only, so it is used when neither is on (or the replica is one rank);
+        # otherwise gradients are averaged over the data-parallel group with one all-reduce and FusedAdam
+        # steps with the replica-wide statistics.
+        need_replica_stats = c.tp * c.pp > 1 and (loss_scale is not None or max_grad_norm > 0)
+        self._dp_allreduce = c.dp > 1 and need_replica_stats
+        self.opt = DPFusedAdam(params, ctx.dp_group, **kw) if (c.dp > 1 and not need_replica_stats) else FusedAdam(params, **kw)
         self.n_rep = 0
         for p, o in zip(self.opt.fp.params, self.opt.fp.offsets):
             if getattr(p, "tp_replicated", False):
                 self.n_rep = o + (p.numel() + 7) // 8 * 8
-        if c.tp * c.pp > 1 and c.dp == 1:
-            # overflow flag and clipping norm of the whole replica, not of this rank's slice.  (With data
-            # parallelism on top the optimizer step is the fused all-reduce + Adam kernel, which takes its
-            # statistics inside the kernel over the data-parallel ranks only.)
+        if c.tp * c.pp > 1 and isinstance(self.opt, FusedAdam):
             self.opt.stats_sync = ModelParallelStats(ctx, self.opt, self.n_rep)
         act_dtype = torch.bfloat16 if cuda else torch.float32
         if V == 1:
@@ -276,5 +281,8 @@ class Trainer3D:
         loss = self.pipe.run(chunk_fn(0), first_inputs=first) if self.V == 1 else self.pipe.run([chunk_fn(ch) for ch in range(self.V)], first)
         if self.ctx.coords.tp > 1 and self.n_rep:
             dist.all_reduce(self.opt.grad[:self.n_rep], group=self.ctx.tp_group)
+        if self._dp_allreduce:
+            dist.all_reduce(self.opt.grad, group=self.ctx.dp_group)
+            self.opt.grad.mul_(1.0 / self.ctx.coords.dp)
         self.opt.step()           # overflow flag and gradient norm are those of the whole replica (stats_sync)
         return loss
