@@ -70,6 +70,8 @@ def main():
     elif mode == "3d":
         dp, tp, pp = (int(a) for a in sys.argv[2:5])
         virtual = int(sys.argv[5]) if len(sys.argv) > 5 else 1      # chunks per pipeline rank (interleaved 1F1B)
+        scaled = len(sys.argv) > 6 and sys.argv[6] == "scaled"       # loss scaling and clipping on: replica-wide statistics
+        from cogito_b200.optim.fused import GradScaler
         from cogito_b200.models.llama import Llama, LlamaConfig
         from cogito_b200.parallel.groups import init_parallel
         from cogito_b200.parallel.llama_parallel import Trainer3D, shard_llama_state
@@ -77,12 +79,14 @@ def main():
         full = Llama(cfg, device=dev, dtype=torch.bfloat16)
         ctx = init_parallel(dp, tp, pp)
         M, mb, T = 4, 1, 256
-        t3 = Trainer3D(cfg, ctx, dev, num_microbatches=M, micro_batch=mb, seq_len=T, lr=1e-3, loss_scale=None, max_grad_norm=0.0,
-                       virtual_stages=virtual)
+        t3 = Trainer3D(cfg, ctx, dev, num_microbatches=M, micro_batch=mb, seq_len=T, lr=1e-3, loss_scale=1024.0 if scaled else None,
+                       max_grad_norm=1.0 if scaled else 0.0, virtual_stages=virtual)
         t3.load_from(full)
         ids = torch.randint(0, 2048, (dp * M * mb, T), generator=g).to(dev)
         tg = torch.randint(0, 2048, (dp * M * mb, T), generator=g).to(dev)
-        tf = Trainer(full, FusedAdam(full.parameters(), lr=1e-3), micro_batch=mb)
+        ref_opt = FusedAdam(full.parameters(), lr=1e-3, scaler=GradScaler(dev, init_scale=1024.0), max_grad_norm=1.0) if scaled \
+            else FusedAdam(full.parameters(), lr=1e-3)
+        tf = Trainer(full, ref_opt, micro_batch=mb)
         out["ref"] = [float(tf.step(ids, tg)) for _ in range(3)]
         d = ctx.coords.dp_rank
         got = []

@@ -74,3 +74,8 @@ def test_3d_llama_interleaved_schedule():
     res = _run(2, "3d", 1, 1, 2, 2)
     _close(res, 0.05)
     assert max(r["p2p_bytes"] for r in res) > 0
+
+
+def test_3d_llama_with_loss_scaling_and_clipping():
+    """tp 2: the overflow flag and the clipping norm are those of the whole replica (all-reduced over its ranks)."""
+    _close(_run(2, "3d", 1, 2, 1, 1, "scaled"), 0.05)
