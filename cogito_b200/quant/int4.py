@@ -90,6 +90,23 @@ class Int4Linear(torch.nn.Module):
         self._tiles = {}                      # kernel kind -> tile-major weights
 
     @classmethod
+    def from_packed(cls, packed: torch.Tensor, scales: torch.Tensor, in_features: int, out_features: int, group: int = 128,
+                    bias: torch.Tensor | None = None) -> "Int4Linear":
+        """Wraps already quantised values (of W^T, [in, out] row-major, as ``quantize_int4`` returns them),
+        e.g. read from a checkpoint; nothing is re-quantised."""
+        if packed.numel() != (in_features * out_features + 1) // 2 or scales.numel() != (in_features * out_features + group - 1) // group:
+            raise ValueError("packed / scales do not match the layer shape and group size")
+        self = cls.__new__(cls)
+        torch.nn.Module.__init__(self)
+        self.in_features, self.out_features, self.group = in_features, out_features, group
+        self.register_buffer("packed", packed.to(torch.uint8).contiguous())
+        self.register_buffer("scales", scales.to(torch.float32).contiguous())
+        self.register_buffer("bias", None if bias is None else bias.detach().to(torch.bfloat16))
+        self._acc = None
+        self._tiles = {}
+        return self
+
+    @classmethod
     def from_linear(cls, lin, group: int = 128) -> "Int4Linear":
         return cls(lin.weight.data, getattr(lin, "bias", None), group)
 

@@ -93,6 +93,57 @@ class LlamaInt4Engine:
             self.ar = ServeAllReduce(tp_group, dev, max_rows=batch * ar_tokens, cols=d)
         self._fresh = True                     # nothing committed since the last reset
 
+    # ------------------------------------------------------------ quantised checkpoints
+    _LINEARS = ("qkv", "proj", "gate_up", "down")
+
+    def save(self, path: str) -> int:
+        """Writes this rank's engine (embedding and norms in bf16 / fp32, every projection as a packed
+        INT4 entry followed by its ``.scales`` entry) as one COG1 file; ``load`` reads it back without
+        the full-precision model.  A tensor-parallel engine writes its own slices: one file per rank."""
+        from ..io.checkpoint import save_tensors
+        t, shapes = {"wte": self.wte, "norm_f": self.norm_f}, {}
+
+        def put(name, lin):
+            t[name], t[name + ".scales"] = lin.packed, lin.scales
+            shapes[name] = (lin.in_features, lin.out_features)
+
+        for i, l in enumerate(self.layers):
+            t[f"layers.{i}.norm1"], t[f"layers.{i}.norm2"] = l["norm1"], l["norm2"]
+            for k in self._LINEARS:
+                put(f"layers.{i}.{k}", l[k])
+        put("lm_head", self.lm_head)
+        return save_tensors(path, {k: v.detach().cpu() for k, v in t.items()}, int4_shapes=shapes)
+
+    @classmethod
+    def load(cls, path: str, cfg: LlamaConfig, batch: int, device="cpu", max_seq_len: int | None = None, weight_group: int = 128,
+             kv_group: int = 32, page_size: int = 64) -> "LlamaInt4Engine":
+        """An unsplit engine from a file written by ``save`` (same configuration and weight group)."""
+        from ..io.checkpoint import load_tensors
+        st = load_tensors(path)
+        dev = torch.device(device)
+        self = cls.__new__(cls)
+        self.cfg, self.device = cfg, dev
+        self.dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+        self.tp_group, self.tp, self.tp_rank = None, 1, 0
+        self.Hq, self.Hk = cfg.n_head, cfg.n_kv_head
+        D, d, ff = cfg.head_dim, cfg.d_model, cfg.d_ff
+        shape = {"qkv": (d, (cfg.n_head + 2 * cfg.n_kv_head) * D), "proj": (cfg.n_head * D, d), "gate_up": (d, 2 * ff), "down": (ff, d)}
+
+        def lin(name, in_f, out_f):
+            return Int4Linear.from_packed(st[name], st[name + ".scales"], in_f, out_f, weight_group).to(dev)
+
+        self.wte = st["wte"].to(dev, self.dtype)
+        self.norm_f = st["norm_f"].to(dev, self.dtype)
+        self.layers = [dict(norm1=st[f"layers.{i}.norm1"].to(dev, self.dtype), norm2=st[f"layers.{i}.norm2"].to(dev, self.dtype),
+                            **{k: lin(f"layers.{i}.{k}", *shape[k]) for k in cls._LINEARS}) for i in range(cfg.n_layer)]
+        self.lm_head = lin("lm_head", d, cfg.vocab_size)
+        self.max_seq_len = max_seq_len or cfg.max_seq_len
+        self.cache = PagedKVCacheInt4(cfg.n_layer, batch, self.max_seq_len, self.Hk, D, kv_group, page_size, dev)
+        self.rope = M.rope_tables(self.max_seq_len, D, cfg.rope_theta, dev)
+        self.batch = batch
+        self._fresh = True
+        return self
+
     def weight_bytes(self) -> int:
         n = 0
         for l in self.layers:

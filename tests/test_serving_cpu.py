@@ -117,3 +117,20 @@ def test_speculative_decoding_reproduces_target_greedy_and_accepts_its_own_draft
     logits = te.forward(prompts, commit=True)
     ref = target(prompts).float()
     assert torch.nn.functional.cosine_similarity(logits.flatten(), ref.flatten(), dim=0) > 0.9
+
+
+def test_engine_round_trips_through_a_quantised_checkpoint(tmp_path):
+    from cogito_b200.io.checkpoint import load_tensors
+    rng.manual_seed(2)
+    cfg = LlamaConfig(vocab_size=256, n_layer=2, d_model=128, n_head=4, n_kv_head=2, d_ff=256, max_seq_len=64)
+    eng = LlamaInt4Engine(Llama(cfg), batch=2, weight_group=64, kv_group=16, page_size=8)
+    path = str(tmp_path / "engine.cog")
+    nbytes = eng.save(path)
+    st = load_tensors(path)
+    assert st["layers.0.qkv"].dtype == torch.uint8 and st["layers.0.qkv.scales"].dtype == torch.float32
+    assert nbytes < sum(p.numel() for p in Llama(cfg).parameters()) * 4 * 0.5      # nibbles + scales + bf16/fp32 embedding
+    back = LlamaInt4Engine.load(path, cfg, batch=2, weight_group=64, kv_group=16, page_size=8)
+    ids = torch.randint(0, 256, (2, 7))
+    assert torch.equal(eng.forward(ids, commit=True), back.forward(ids, commit=True))
+    nxt = torch.randint(0, 256, (2, 1))
+    assert torch.equal(eng.forward(nxt), back.forward(nxt))
