@@ -22,7 +22,10 @@ template <class T> inline T fail(cg_error e, T v) { set_error(e); return v; }
 // ---- tensors
 cg_tensor* make(const int* shape, int ndim, bool requires_grad);          // zero-filled
 cg_tensor* make_like(const cg_tensor* t, bool requires_grad);
+cg_tensor* make_header(const int* shape, int ndim, bool requires_grad);  // counted, data / grad left null
 void ensure_grad(cg_tensor* t);
+// Frees tensor storage: std::free, or the device layer's free when p is device memory.
+void free_storage(void* p);
 inline bool wants_grad(const cg_tensor* t) { return t && t->requires_grad; }
 inline int rows_of(const cg_tensor* t) { return t->ndim ? t->size / t->shape[t->ndim - 1] : 1; }
 inline int cols_of(const cg_tensor* t) { return t->ndim ? t->shape[t->ndim - 1] : 1; }

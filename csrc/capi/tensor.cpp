@@ -37,6 +37,7 @@ namespace cgi {
 void set_error(cg_error e) { g_err = e; }
 uint64_t next_layer_seed() { return g_seed.load() * 0x100000001B3ull + 0x9E37ull * (g_layer_counter.fetch_add(1) + 1); }
 
+cg_tensor* make_header(const int* shape, int ndim, bool rg) { return header(shape, ndim, rg); }
 cg_tensor* make(const int* shape, int ndim, bool rg) {
   cg_tensor* t = header(shape, ndim, rg);
   if (!t) return nullptr;
@@ -220,8 +221,8 @@ CG_EXPORT void cg_tensor_release(cg_tensor* t) {
       delete c;
     }
     if (x->arena) continue;                        // storage belongs to the arena
-    if (!x->is_view) std::free(x->data);
-    std::free(x->grad);
+    if (!x->is_view) free_storage(x->data);      // host or device memory
+    free_storage(x->grad);
     std::free(x);
     g_live.fetch_sub(1);
   }

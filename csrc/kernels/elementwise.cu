@@ -143,6 +143,18 @@ __global__ void cast_kernel(const TI* __restrict__ x, TO* out, long long n) {
     stf<TO>(out, i, ldf<TI>(x, i));
 }
 
+// x = hi + lo with both halves in bf16: the two-term split that lets three bf16 tensor-core
+// products (hi*hi + hi*lo + lo*hi) stand in for an fp32 product.
+__global__ void split_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* hi, __nv_bfloat16* lo, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float v = x[i];
+    const __nv_bfloat16 h = __float2bfloat16(v);
+    hi[i] = h;
+    lo[i] = __float2bfloat16(v - __bfloat162float(h));
+  }
+}
+
 // ---- reductions ---------------------------------------------------------
 enum { RED_SUM = 0, RED_MEAN = 1, RED_MAX = 2, RED_MIN = 3 };
 __device__ __forceinline__ float red_identity(int op) {
@@ -549,6 +561,15 @@ CGK_API int cgk_cast(const void* x, void* out, long long n, int to_bf16, void* s
   if (n == 0) return 0;
   if (to_bf16) cast_kernel<float, __nv_bfloat16><<<ew_grid(n), 256, 0, ST(stream)>>>((const float*)x, (__nv_bfloat16*)out, n);
   else cast_kernel<__nv_bfloat16, float><<<ew_grid(n), 256, 0, ST(stream)>>>((const __nv_bfloat16*)x, (float*)out, n);
+  CGK_LAUNCH_CHECK();
+  return 0;
+}
+
+// hi[i] = bf16(x[i]), lo[i] = bf16(x[i] - hi[i])
+CGK_API int cgk_split_bf16(const float* x, void* hi, void* lo, long long n, void* stream) {
+  CGK_REQUIRE(x && hi && lo, "cgk_split_bf16: null pointer");
+  if (n == 0) return 0;
+  split_bf16_kernel<<<ew_grid(n), 256, 0, ST(stream)>>>(x, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo, n);
   CGK_LAUNCH_CHECK();
   return 0;
 }

@@ -243,5 +243,6 @@ bool cg_optimizer_update_scale(cg_optimizer* opt, float grad_norm);   /* true: s
 #endif
 
 #include "cogito_ext.h"
+#include "cogito_cuda.h"
 
 #endif /* COGITO_H */
