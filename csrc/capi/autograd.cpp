@@ -109,6 +109,7 @@ CG_EXPORT cg_tensor* cg_matmul(cg_tensor* a, cg_tensor* b) {
   shape[a->ndim - 1] = b->shape[b->ndim - 1];
   cg_tensor* o = make(shape, a->ndim, false);
   if (!o) return nullptr;
+  (void)cg_last_error();                    // an error left by an earlier call must not fail this one
   cg_tensor_matmul(a, b, o);
   if (cg_last_error() != CG_SUCCESS) { cg_tensor_release(o); return fail(CG_ERROR_SHAPE_MISMATCH, (cg_tensor*)nullptr); }
   attach(o, {a, b}, [a, b](cg_tensor* self) {

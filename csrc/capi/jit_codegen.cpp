@@ -117,6 +117,18 @@ bool emit_c_node(const cg_ir_graph* g, const cg_ir_node* n, std::ostringstream& 
     case OP_RESHAPE: case OP_NOOP:
       s << "  memcpy(t[" << out << "], t[" << n->input_ids[0] << "], sizeof(float) * " << o->size << ");\n";
       return true;
+    case OP_BROADCAST: {
+      cg_tensor* a = T(0);
+      int st[CG_MAX_DIMS];
+      cg_broadcast_strides(a->shape, a->ndim, const_cast<int*>(o->shape), o->ndim, st);
+      s << "  for (long i = 0; i < " << o->size << "; ++i) {\n    long r = i, off = 0;\n";
+      for (int d = o->ndim - 1; d >= 0; --d) {
+        if (st[d]) s << "    off += (r % " << o->shape[d] << ") * " << st[d] << ";";
+        s << "    r /= " << o->shape[d] << ";\n";
+      }
+      s << "    t[" << out << "][i] = t[" << n->input_ids[0] << "][off];\n  }\n";
+      return true;
+    }
     default: return false;
   }
 }

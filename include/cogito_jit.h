@@ -150,6 +150,28 @@ char* cg_fusion_generate_kernel(cg_fusion_group* group);
 void cg_fusion_apply(cg_fusion_pass* pass);
 void cg_fusion_group_free(cg_fusion_group* group);
 void cg_fusion_pass_free(cg_fusion_pass* pass);
+/* Pattern matchers anchored at one node (start_idx = index into graph->nodes): LayerNorm spelled
+ * as MEAN, SUB, MUL, MEAN, [ADD], RSQRT+MUL or SQRT+DIV, [MUL], [ADD]; attention spelled as
+ * [TRANSPOSE], MATMUL, [MUL | DIV], [ADD], SOFTMAX, MATMUL.  On a match *out_group (may be NULL)
+ * receives a new group (FUSION_LAYERNORM / FUSION_ATTENTION) that the caller frees. */
+bool cg_fusion_match_layernorm(cg_ir_graph* graph, int start_idx, cg_fusion_group** out_group);
+bool cg_fusion_match_attention(cg_ir_graph* graph, int start_idx, cg_fusion_group** out_group);
+
+/* ---- the reference's names for entry points that this library also has under other names ---- */
+const char* cg_opcode_name(cg_ir_opcode op);                      /* = cg_ir_opcode_name */
+/* Allocates the result of `op` (shape inferred), records the node when a trace is open, returns it. */
+cg_tensor* cg_jit_record_op(cg_ir_opcode op, cg_tensor** inputs, int num_inputs, void* attributes, size_t attr_size);
+/* Copies inputs into the graph's inputs, runs the compiled module (or the interpreter), copies the
+ * graph's outputs out. */
+void cg_jit_execute(cg_jit_compiler* compiler, cg_tensor** inputs, int num_inputs, cg_tensor** outputs, int num_outputs);
+/* Linear-scan register assignment over the live nodes; results via the three readers below. */
+void cg_ir_allocate_registers(cg_ir_graph* graph, int max_regs);
+int cg_ir_register_of(cg_ir_graph* graph, int tensor_id);         /* >= 0, -1 spilled, -2 not planned */
+int cg_ir_spill_count(cg_ir_graph* graph);
+int cg_ir_registers_used(cg_ir_graph* graph);
+void cg_symbolic_report_mismatch(cg_symbolic_shape* a, cg_symbolic_shape* b, const char* context);   /* to stderr */
+/* Attention of [batch, seq, heads, d_head] tensors; the caller frees the result. */
+cg_tensor* cg_flash_attn_forward(cg_tensor* q, cg_tensor* k, cg_tensor* v, float dropout_prob, float softmax_scale, bool causal);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,182 @@
+"""Entry points that carry the reference's own names (cg_jit_record_op, cg_jit_execute,
+cg_opcode_name, cg_ir_allocate_registers, cg_fusion_match_layernorm / _attention,
+cg_symbolic_report_mismatch, cg_flash_attn_forward): built by hand graphs, checked against numpy."""
+import ctypes
+from ctypes import POINTER, c_bool, c_char_p, c_float, c_int, c_size_t, c_void_p
+
+import numpy as np
+
+from capi_defs import FusionGroup, IrGraph, JitCompiler, L, T, TensorP, borrowed
+
+OP = dict(ADD=1, SUB=2, MUL=3, DIV=4, SQRT=8, RSQRT=9, RELU=10, SOFTMAX=14, MATMUL=15, TRANSPOSE=16, SUM=19, MEAN=20,
+          FUSED_ATTENTION=26, FUSED_LAYERNORM=27)
+
+
+def _lib():
+    lib = L()
+    GP = POINTER(IrGraph)
+    lib.cg_jit_record_op.restype, lib.cg_jit_record_op.argtypes = TensorP, [c_int, POINTER(TensorP), c_int, c_void_p, c_size_t]
+    lib.cg_jit_execute.restype, lib.cg_jit_execute.argtypes = None, [POINTER(JitCompiler), POINTER(TensorP), c_int, POINTER(TensorP), c_int]
+    lib.cg_opcode_name.restype, lib.cg_opcode_name.argtypes = c_char_p, [c_int]
+    lib.cg_ir_allocate_registers.restype, lib.cg_ir_allocate_registers.argtypes = None, [GP, c_int]
+    for name in ("cg_ir_spill_count", "cg_ir_registers_used"):
+        getattr(lib, name).restype, getattr(lib, name).argtypes = c_int, [GP]
+    lib.cg_ir_register_of.restype, lib.cg_ir_register_of.argtypes = c_int, [GP, c_int]
+    for name in ("cg_fusion_match_layernorm", "cg_fusion_match_attention"):
+        getattr(lib, name).restype, getattr(lib, name).argtypes = c_bool, [GP, c_int, POINTER(POINTER(FusionGroup))]
+    lib.cg_flash_attn_forward.restype = TensorP
+    lib.cg_flash_attn_forward.argtypes = [TensorP, TensorP, TensorP, c_float, c_float, c_bool]
+    lib.cg_jit_begin_trace.restype = None
+    lib.cg_jit_end_trace.restype = GP
+    lib.cg_jit_compiler_new.restype, lib.cg_jit_compiler_new.argtypes = POINTER(JitCompiler), [GP, c_int]
+    lib.cg_jit_compile.restype, lib.cg_jit_compile.argtypes = c_bool, [POINTER(JitCompiler)]
+    lib.cg_jit_compiler_free.argtypes = [POINTER(JitCompiler)]
+    lib.cg_ir_graph_free.argtypes = [GP]
+    lib.cg_fusion_group_free.argtypes = [POINTER(FusionGroup)]
+    lib.cg_tensor_release.argtypes = [TensorP]
+    return lib
+
+
+def _rec(lib, made, op, *inputs, axis=None):
+    arr = (TensorP * len(inputs))(*inputs)
+    attr, size = (None, 0) if axis is None else (ctypes.byref(c_int(axis)), 4)
+    out = lib.cg_jit_record_op(OP[op], arr, len(inputs), ctypes.cast(attr, c_void_p) if attr is not None else None, size)
+    assert out
+    made.append(out)
+    return out
+
+
+def test_opcode_names():
+    lib = _lib()
+    assert lib.cg_opcode_name(OP["MATMUL"]).lower().find(b"matmul") >= 0
+    assert lib.cg_opcode_name(OP["ADD"]) != lib.cg_opcode_name(OP["SUB"])
+
+
+def test_record_op_infers_shapes_and_execute_runs_the_graph():
+    lib = _lib()
+    rng = np.random.default_rng(0)
+    a, b, c = (rng.standard_normal(s).astype(np.float32) for s in ((4, 6), (6, 5), (5,)))
+    ta, tb, tc = T(a), T(b), T(c)
+    made = []
+    lib.cg_jit_begin_trace()
+    mm = _rec(lib, made, "MATMUL", ta._ptr, tb._ptr)
+    assert borrowed(mm).shape == (4, 5)
+    ad = _rec(lib, made, "ADD", mm, tc._ptr)                     # [5] over [4,5]: an OP_BROADCAST node is put in front
+    re = _rec(lib, made, "RELU", ad)
+    sm = _rec(lib, made, "SUM", re, axis=1)
+    assert borrowed(sm).shape == (4,)
+    tr = _rec(lib, made, "TRANSPOSE", re)
+    assert borrowed(tr).shape == (5, 4)
+    g = lib.cg_jit_end_trace()
+    assert g and g.contents.num_nodes == 6 and g.contents.num_inputs == 3 and g.contents.num_outputs == 2
+    # new values for the inputs, through the compiled module and through the interpreter
+    a2, b2, c2 = (rng.standard_normal(s).astype(np.float32) for s in ((4, 6), (6, 5), (5,)))
+    ref = np.maximum(a2 @ b2 + c2, 0)
+    order = [g.contents.input_node_ids[i] for i in range(3)]
+    by_id = {}
+    for t, arr in ((ta, a2), (tb, b2), (tc, c2)):
+        for i in range(g.contents.num_tensors):
+            if ctypes.addressof(g.contents.tensors[i].contents) == ctypes.addressof(t._ptr.contents):
+                by_id[i] = T(arr)
+    ins = (TensorP * 3)(*[by_id[i]._ptr for i in order])
+    out_ids = [g.contents.output_node_ids[j] for j in range(2)]
+    outs_np = {}
+    for compile_it in (False, True):
+        comp = lib.cg_jit_compiler_new(g, 0)
+        if compile_it:
+            assert lib.cg_jit_compile(comp)
+        o = [T(np.zeros(borrowed(g.contents.tensors[i]).shape, np.float32)) for i in out_ids]
+        outs = (TensorP * 2)(*[t._ptr for t in o])
+        lib.cg_jit_execute(comp, ins, 3, outs, 2)
+        got = {tuple(borrowed(t._ptr).shape): borrowed(t._ptr) for t in o}
+        np.testing.assert_allclose(got[(4,)], ref.sum(1), rtol=1e-5, atol=1e-5)
+        np.testing.assert_allclose(got[(5, 4)], ref.T, rtol=1e-5, atol=1e-5)
+        outs_np[compile_it] = got
+        comp.contents.graph = None                               # the graph is freed once, below
+        lib.cg_jit_compiler_free(comp)
+    # register plan: 6 values, the relu result is read twice
+    lib.cg_ir_allocate_registers(g, 8)
+    assert lib.cg_ir_spill_count(g) == 0 and 2 <= lib.cg_ir_registers_used(g) <= 6
+    regs = [lib.cg_ir_register_of(g, g.contents.nodes[i].contents.output_id) for i in range(6)]
+    assert all(r >= 0 for r in regs) and regs[4] != regs[3]      # sum may not overwrite relu, transpose still reads it
+    lib.cg_ir_allocate_registers(g, 1)
+    assert lib.cg_ir_spill_count(g) >= 1
+    lib.cg_ir_graph_free(g)
+    for t in made:
+        lib.cg_tensor_release(t)
+
+
+def _layernorm_graph(lib, made, x, gamma, beta, eps, use_sqrt):
+    mu = _rec(lib, made, "MEAN", x, axis=1)
+    mu2 = mu                                                     # [rows] broadcasts against [rows, D] only as a column
+    c = _rec(lib, made, "SUB", x, mu2)
+    sq = _rec(lib, made, "MUL", c, c)
+    var = _rec(lib, made, "MEAN", sq, axis=1)
+    ve = _rec(lib, made, "ADD", var, eps)
+    if use_sqrt:
+        y = _rec(lib, made, "DIV", c, _rec(lib, made, "SQRT", ve))
+    else:
+        y = _rec(lib, made, "MUL", c, _rec(lib, made, "RSQRT", ve))
+    return _rec(lib, made, "ADD", _rec(lib, made, "MUL", y, gamma), beta)
+
+
+def test_layernorm_and_attention_matchers():
+    lib = _lib()
+    rng = np.random.default_rng(1)
+    # square [8, 8] so that the per-row statistics [8] broadcast shape-wise in this hand-built graph
+    x, gamma, beta, eps = T(rng.standard_normal((8, 8))), T(rng.standard_normal(8)), T(rng.standard_normal(8)), T(np.full(8, 1e-5))
+    for use_sqrt in (False, True):
+        made = []
+        lib.cg_jit_begin_trace()
+        _layernorm_graph(lib, made, x._ptr, gamma._ptr, beta._ptr, eps._ptr, use_sqrt)
+        g = lib.cg_jit_end_trace()
+        grp = POINTER(FusionGroup)()
+        assert lib.cg_fusion_match_layernorm(g, 0, ctypes.byref(grp))
+        assert grp.contents.num_nodes == 11 and grp.contents.fusion_type == 5 and grp.contents.kernel_name == b"fused_layernorm"
+        lib.cg_fusion_group_free(grp)
+        assert not lib.cg_fusion_match_layernorm(g, 1, None)     # anchored at the SUB: no match
+        assert not lib.cg_fusion_match_attention(g, 0, None)
+        lib.cg_ir_graph_free(g)
+        for t in made:
+            lib.cg_tensor_release(t)
+    q, k, v, scale = T(rng.standard_normal((16, 8))), T(rng.standard_normal((16, 8))), T(rng.standard_normal((16, 8))), T(np.full(16, 0.35))
+    made = []
+    lib.cg_jit_begin_trace()
+    kt = _rec(lib, made, "TRANSPOSE", k._ptr)
+    s = _rec(lib, made, "MUL", _rec(lib, made, "MATMUL", q._ptr, kt), scale._ptr)
+    o = _rec(lib, made, "MATMUL", _rec(lib, made, "SOFTMAX", s), v._ptr)
+    assert borrowed(o).shape == (16, 8)
+    g = lib.cg_jit_end_trace()
+    grp = POINTER(FusionGroup)()
+    assert lib.cg_fusion_match_attention(g, 1, ctypes.byref(grp))
+    assert grp.contents.num_nodes == 5 and grp.contents.fusion_type == 4
+    lib.cg_fusion_group_free(grp)
+    assert not lib.cg_fusion_match_attention(g, 5, None) and not lib.cg_fusion_match_layernorm(g, 1, None)
+    lib.cg_ir_graph_free(g)
+    for t in made:
+        lib.cg_tensor_release(t)
+
+
+def test_flash_attn_forward_by_the_transformers_name(capfd):
+    lib = _lib()
+    rng = np.random.default_rng(2)
+    q, k, v = (rng.standard_normal((2, 10, 4, 8)).astype(np.float32) for _ in range(3))
+    tq, tk, tv = T(q), T(k), T(v)
+    out = lib.cg_flash_attn_forward(tq._ptr, tk._ptr, tv._ptr, 0.0, 0.0, True)
+    assert out
+    s = np.einsum("bqhd,bkhd->bhqk", q, k).astype(np.float64) / np.sqrt(8)
+    s = np.where(np.arange(10)[None, :] > np.arange(10)[:, None], -np.inf, s)
+    p = np.exp(s - s.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    np.testing.assert_allclose(borrowed(out), np.einsum("bhqk,bkhd->bqhd", p, v), rtol=1e-4, atol=1e-5)
+    lib.cg_tensor_release(out)
+    # the mismatch report names the offending dimension
+    lib.cg_shape_from_ints.restype, lib.cg_shape_from_ints.argtypes = c_void_p, [POINTER(c_int), c_int]
+    lib.cg_symbolic_report_mismatch.restype, lib.cg_symbolic_report_mismatch.argtypes = None, [c_void_p, c_void_p, c_char_p]
+    lib.cg_shape_free.argtypes = [c_void_p]
+    a, b = lib.cg_shape_from_ints((c_int * 3)(2, 3, 4), 3), lib.cg_shape_from_ints((c_int * 2)(5, 4), 2)
+    lib.cg_symbolic_report_mismatch(a, b, b"matmul of test")
+    lib.cg_shape_free(a)
+    lib.cg_shape_free(b)
+    err = capfd.readouterr().err
+    assert "matmul of test" in err and "dimension -2" in err and "3" in err and "5" in err
