@@ -138,6 +138,41 @@ CG_EXPORT bool cg_fusion_match_attention(cg_ir_graph* g, int start_idx, cg_fusio
   return emit(nodes, FUSION_ATTENTION, "fused_attention", out_group);
 }
 
+// MATMUL -> [ADD bias (through an optional OP_BROADCAST of the bias)] -> activation
+// (RELU, SIGMOID, TANH or GELU), each result read only by the next node: the shape the tcgen05
+// GEMM's epilogue covers (bias, activation).  A product followed by the bias alone matches too.
+// Group type FUSION_EPILOGUE.  (Declared at include/cg_fusion.h:128 in the reference.)
+CG_EXPORT bool cg_fusion_match_matmul_epilogue(cg_ir_graph* g, int start_idx, cg_fusion_group** out_group) {
+  if (out_group) *out_group = nullptr;
+  if (!g) { set_error(CG_ERROR_NULL_POINTER); return false; }
+  Walk w(g);
+  cg_ir_node* mm = w.node(start_idx);
+  if (!mm || mm->opcode != OP_MATMUL) return false;
+  std::vector<cg_ir_node*> nodes{mm};
+  int t = mm->output_id;
+  if (cg_ir_node* bias = w.sole(t, OP_ADD)) { nodes.push_back(bias); t = bias->output_id; }
+  cg_ir_node* act = nullptr;
+  for (cg_ir_opcode op : {OP_RELU, OP_SIGMOID, OP_TANH, OP_GELU}) if (!act) act = w.sole(t, op);
+  if (act) nodes.push_back(act);
+  if (nodes.size() < 2) return false;
+  return emit(nodes, FUSION_EPILOGUE, "fused_matmul_epilogue", out_group);
+}
+
+// RELU -> elementwise MUL (the dropout mask, already scaled) -> ADD (the residual), each result
+// read only by the next node.  Group type FUSION_ELEMENTWISE.  (include/cg_fusion.h:134.)
+CG_EXPORT bool cg_fusion_match_relu_dropout_add(cg_ir_graph* g, int start_idx, cg_fusion_group** out_group) {
+  if (out_group) *out_group = nullptr;
+  if (!g) { set_error(CG_ERROR_NULL_POINTER); return false; }
+  Walk w(g);
+  cg_ir_node* relu = w.node(start_idx);
+  if (!relu || relu->opcode != OP_RELU) return false;
+  cg_ir_node* drop = w.sole(relu->output_id, OP_MUL);
+  cg_ir_node* add = drop ? w.sole(drop->output_id, OP_ADD) : nullptr;
+  if (!add) return false;
+  std::vector<cg_ir_node*> nodes{relu, drop, add};
+  return emit(nodes, FUSION_ELEMENTWISE, "fused_relu_dropout_add", out_group);
+}
+
 // Prints both shapes and names the first dimension at which they cannot be unified (or the rank
 // difference) to stderr, prefixed with the caller's context.
 CG_EXPORT void cg_symbolic_report_mismatch(cg_symbolic_shape* a, cg_symbolic_shape* b, const char* context) {

@@ -204,6 +204,32 @@ CG_EXPORT cg_symbolic_shape* cg_shape_matmul(cg_symbolic_shape* a, cg_symbolic_s
   out[n] = dim_clone(a->dims[a->ndim - 2]); out[n + 1] = dim_clone(b->dims[b->ndim - 1]);
   return cg_shape_new(out, n + 2);
 }
+// [N, C, H, W] -> [N, out_channels, (H + 2p - k) / s + 1, (W + 2p - k) / s + 1] for a square kernel;
+// a symbolic extent gives an inferred dimension carrying that expression
+// (include/cg_symbolic.h:161 in the reference, where it is declared and never defined).
+CG_EXPORT cg_symbolic_shape* cg_shape_conv2d(cg_symbolic_shape* in, int out_channels, int kernel_size, int stride, int padding) {
+  if (!in) return fail(CG_ERROR_NULL_POINTER, (cg_symbolic_shape*)nullptr);
+  if (in->ndim != 4 || out_channels <= 0 || kernel_size <= 0 || stride <= 0 || padding < 0) return fail(CG_ERROR_INVALID_ARGUMENT, (cg_symbolic_shape*)nullptr);
+  auto spatial = [&](cg_symbolic_dim* d) -> cg_symbolic_dim* {
+    const int64_t off = 2 * (int64_t)padding - kernel_size;
+    if (d->type == DIM_CONSTANT) {
+      const int64_t v = d->value + off;
+      return v < 0 ? nullptr : cg_dim_const(v / stride + 1);
+    }
+    cg_symbolic_expr* base = d->expr ? expr_clone(d->expr) : cg_expr_var(d->name ? d->name : "?");
+    cg_symbolic_expr* e = cg_expr_add(cg_expr_floordiv(cg_expr_add(base, cg_expr_const(off)), cg_expr_const(stride)), cg_expr_const(1));
+    cg_symbolic_dim* out = cg_dim_inferred(e);
+    if (out && d->min_value > 0 && d->min_value + off >= 0) out->min_value = (d->min_value + off) / stride + 1;
+    if (out && d->max_value > 0 && d->max_value < INT64_MAX / 2 && d->max_value + off >= 0) out->max_value = (d->max_value + off) / stride + 1;
+    return out;
+  };
+  cg_symbolic_dim* out[4] = {dim_clone(in->dims[0]), cg_dim_const(out_channels), spatial(in->dims[2]), spatial(in->dims[3])};
+  if (!out[0] || !out[2] || !out[3]) {
+    for (cg_symbolic_dim* d : out) if (d) cg_dim_free(d);
+    return fail(CG_ERROR_SHAPE_MISMATCH, (cg_symbolic_shape*)nullptr);
+  }
+  return cg_shape_new(out, 4);
+}
 CG_EXPORT bool cg_shape_is_dynamic(cg_symbolic_shape* s) {
   if (s) for (int i = 0; i < s->ndim; ++i) if (s->dims[i]->type != DIM_CONSTANT) return true;
   return false;
@@ -268,6 +294,8 @@ CG_EXPORT bool cg_shape_guards_hold(cg_shape_specialization* sp, int64_t* vals, 
   }
   return true;
 }
+// The reference's name for the same check (include/cg_symbolic.h:200).
+CG_EXPORT bool cg_guards_check(cg_shape_specialization* sp, int64_t* vals, const char** names, int n) { return cg_shape_guards_hold(sp, vals, names, n); }
 CG_EXPORT void cg_shape_specialization_free(cg_shape_specialization* sp) {
   if (!sp) return;
   for (int i = 0; i < sp->num_guards; ++i) std::free(sp->guards[i].dim_name);

@@ -14,6 +14,9 @@ typedef uint8_t cg_fp8_e4m3;
 typedef uint8_t cg_fp8_e5m2;
 cg_bf16 cg_fp32_to_bf16(float f);          /* round to nearest even */
 float cg_bf16_to_fp32(cg_bf16 h);
+/* the reference's spellings (static inline there, include/cg_bf16.h:22-32) */
+static inline cg_bf16 cg_float_to_bf16(float f) { return cg_fp32_to_bf16(f); }
+static inline float cg_bf16_to_float(cg_bf16 b) { return cg_bf16_to_fp32(b); }
 typedef struct {
   cg_bf16* data; float* master; float* grad;
   int shape[CG_MAX_DIMS]; int ndim; int size; bool requires_grad;

@@ -54,6 +54,8 @@ cg_symbolic_shape* cg_shape_new(cg_symbolic_dim** dims, int ndim);   /* takes ow
 cg_symbolic_shape* cg_shape_from_ints(int* dims, int ndim);
 cg_symbolic_shape* cg_shape_broadcast(cg_symbolic_shape* a, cg_symbolic_shape* b);
 cg_symbolic_shape* cg_shape_matmul(cg_symbolic_shape* a, cg_symbolic_shape* b);
+/* [N, C, H, W] -> [N, out_channels, (H + 2p - k) / s + 1, (W + 2p - k) / s + 1], square kernel */
+cg_symbolic_shape* cg_shape_conv2d(cg_symbolic_shape* input, int out_channels, int kernel_size, int stride, int padding);
 bool cg_shape_is_dynamic(cg_symbolic_shape* shape);
 uint64_t cg_shape_hash(cg_symbolic_shape* shape);
 bool cg_shape_to_ints(cg_symbolic_shape* shape, int* out_dims, int* out_ndim);
@@ -62,6 +64,7 @@ void cg_shape_free(cg_symbolic_shape* shape);
 void cg_shape_print(cg_symbolic_shape* shape);
 cg_shape_specialization* cg_shape_specialize(cg_symbolic_shape* shape, int64_t* bindings, const char** binding_names, int num_bindings);
 bool cg_shape_guards_hold(cg_shape_specialization* spec, int64_t* bindings, const char** binding_names, int num_bindings);
+bool cg_guards_check(cg_shape_specialization* spec, int64_t* bindings, const char** binding_names, int num_bindings);   /* same check, the reference's name */
 void cg_shape_specialization_free(cg_shape_specialization* spec);
 
 /* ----------------------------------------------------------------- JIT */
@@ -156,6 +159,9 @@ void cg_fusion_pass_free(cg_fusion_pass* pass);
  * receives a new group (FUSION_LAYERNORM / FUSION_ATTENTION) that the caller frees. */
 bool cg_fusion_match_layernorm(cg_ir_graph* graph, int start_idx, cg_fusion_group** out_group);
 bool cg_fusion_match_attention(cg_ir_graph* graph, int start_idx, cg_fusion_group** out_group);
+/* MATMUL, [ADD bias], [RELU | SIGMOID | TANH | GELU] (FUSION_EPILOGUE); RELU, MUL mask, ADD (FUSION_ELEMENTWISE) */
+bool cg_fusion_match_matmul_epilogue(cg_ir_graph* graph, int start_idx, cg_fusion_group** out_group);
+bool cg_fusion_match_relu_dropout_add(cg_ir_graph* graph, int start_idx, cg_fusion_group** out_group);
 
 /* ---- the reference's names for entry points that this library also has under other names ---- */
 const char* cg_opcode_name(cg_ir_opcode op);                      /* = cg_ir_opcode_name */

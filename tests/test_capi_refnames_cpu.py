@@ -180,3 +180,71 @@ def test_flash_attn_forward_by_the_transformers_name(capfd):
     lib.cg_shape_free(b)
     err = capfd.readouterr().err
     assert "matmul of test" in err and "dimension -2" in err and "3" in err and "5" in err
+
+
+def test_epilogue_and_relu_dropout_add_matchers():
+    lib = _lib()
+    for name in ("cg_fusion_match_matmul_epilogue", "cg_fusion_match_relu_dropout_add"):
+        getattr(lib, name).restype, getattr(lib, name).argtypes = c_bool, [POINTER(IrGraph), c_int, POINTER(POINTER(FusionGroup))]
+    rng = np.random.default_rng(3)
+    x, wgt, bias = T(rng.standard_normal((4, 6))), T(rng.standard_normal((6, 6))), T(rng.standard_normal((4, 6)))
+    mask, res = T(rng.integers(0, 2, (4, 6)) * 2.0), T(rng.standard_normal((4, 6)))
+    made = []
+    OP["GELU"] = 13
+    lib.cg_jit_begin_trace()
+    h = _rec(lib, made, "GELU", _rec(lib, made, "ADD", _rec(lib, made, "MATMUL", x._ptr, wgt._ptr), bias._ptr))
+    _rec(lib, made, "ADD", _rec(lib, made, "MUL", _rec(lib, made, "RELU", h), mask._ptr), res._ptr)
+    g = lib.cg_jit_end_trace()
+    grp = POINTER(FusionGroup)()
+    assert lib.cg_fusion_match_matmul_epilogue(g, 0, ctypes.byref(grp))
+    assert grp.contents.num_nodes == 3 and grp.contents.fusion_type == 3 and grp.contents.kernel_name == b"fused_matmul_epilogue"
+    lib.cg_fusion_group_free(grp)
+    assert lib.cg_fusion_match_relu_dropout_add(g, 3, ctypes.byref(grp))
+    assert grp.contents.num_nodes == 3 and grp.contents.fusion_type == 1
+    lib.cg_fusion_group_free(grp)
+    assert not lib.cg_fusion_match_matmul_epilogue(g, 3, None) and not lib.cg_fusion_match_relu_dropout_add(g, 0, None)
+    lib.cg_ir_graph_free(g)
+    for t in made:
+        lib.cg_tensor_release(t)
+
+
+def test_conv2d_shape_inference_and_guards_check():
+    lib = _lib()
+    from ctypes import Structure, c_int64
+
+    class Dim(Structure):
+        _fields_ = [("type", c_int), ("value", c_int64), ("name", c_char_p), ("expr", c_void_p), ("min_value", c_int64),
+                    ("max_value", c_int64), ("divisible_by", c_bool), ("divisor", c_int64)]
+
+    class Shape(Structure):
+        _fields_ = [("dims", POINTER(POINTER(Dim))), ("ndim", c_int), ("hash", ctypes.c_uint64)]
+
+    SP = POINTER(Shape)
+    lib.cg_dim_const.restype, lib.cg_dim_const.argtypes = POINTER(Dim), [c_int64]
+    lib.cg_dim_var.restype, lib.cg_dim_var.argtypes = POINTER(Dim), [c_char_p]
+    lib.cg_shape_new.restype, lib.cg_shape_new.argtypes = SP, [POINTER(POINTER(Dim)), c_int]
+    lib.cg_shape_conv2d.restype, lib.cg_shape_conv2d.argtypes = SP, [SP, c_int, c_int, c_int, c_int]
+    lib.cg_shape_resolve.restype = c_bool
+    lib.cg_shape_resolve.argtypes = [SP, POINTER(c_int64), POINTER(c_char_p), c_int, POINTER(c_int)]
+    lib.cg_shape_free.argtypes = [SP]
+    dims = (POINTER(Dim) * 4)(lib.cg_dim_var(b"N"), lib.cg_dim_const(3), lib.cg_dim_const(32), lib.cg_dim_var(b"W"))
+    s = lib.cg_shape_new(dims, 4)
+    o = lib.cg_shape_conv2d(s, 16, 3, 2, 1)
+    assert o and o.contents.ndim == 4
+    assert o.contents.dims[1].contents.value == 16 and o.contents.dims[2].contents.value == (32 + 2 - 3) // 2 + 1
+    out = (c_int * 4)()
+    vals, names = (c_int64 * 2)(5, 65), (c_char_p * 2)(b"N", b"W")
+    assert lib.cg_shape_resolve(o, vals, names, 2, out)
+    assert list(out) == [5, 16, 16, (65 + 2 - 3) // 2 + 1]
+    assert not lib.cg_shape_conv2d(s, 16, 64, 1, 0)              # the kernel does not fit the constant extent
+    lib.cg_last_error()
+    # guards under the reference's name
+    lib.cg_shape_specialize.restype, lib.cg_shape_specialize.argtypes = c_void_p, [SP, POINTER(c_int64), POINTER(c_char_p), c_int]
+    lib.cg_guards_check.restype, lib.cg_guards_check.argtypes = c_bool, [c_void_p, POINTER(c_int64), POINTER(c_char_p), c_int]
+    lib.cg_shape_specialization_free.argtypes = [c_void_p]
+    spec = lib.cg_shape_specialize(s, vals, names, 2)
+    assert lib.cg_guards_check(spec, vals, names, 2)
+    assert not lib.cg_guards_check(spec, (c_int64 * 2)(5, 66), names, 2)
+    lib.cg_shape_specialization_free(spec)
+    lib.cg_shape_free(o)
+    lib.cg_shape_free(s)
