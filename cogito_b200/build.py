@@ -122,6 +122,30 @@ def build_capi(verbose: bool = False) -> Path:
     return out
 
 
+def build_capi_sanitized(verbose: bool = False) -> Path:
+    """The host runtime compiled with AddressSanitizer + UndefinedBehaviorSanitizer, as
+    ``build/libcogito_asan.so`` (not shipped; the memory-safety tests link C programs against it)."""
+    srcs = sorted((ROOT / "csrc" / "capi").glob("*.cpp"))
+    hdrs = list((ROOT / "include").glob("*.h")) + list((ROOT / "csrc" / "capi").glob("*.h*"))
+    out = BUILD_DIR / "libcogito_asan.so"
+    # the first compiler whose installation carries the sanitizer runtime
+    cxx = None
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), "/usr/bin/g++"):
+        if not cand:
+            continue
+        probe = subprocess.run([cand, "-print-file-name=libasan.so"], capture_output=True, text=True)
+        if probe.returncode == 0 and Path(probe.stdout.strip()).is_absolute() and Path(probe.stdout.strip()).exists():
+            cxx = cand
+            break
+    if cxx is None:
+        raise RuntimeError("no C++ compiler with an AddressSanitizer runtime found")
+    san = ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined", "-fno-omit-frame-pointer", "-g"]
+    flags = [f for f in CXX_FLAGS if f != "-O2"] + ["-O1"] + san
+    _build(srcs, hdrs, out, [cxx] + flags + ["-I", str(ROOT / "include")],
+           [cxx, "-shared", "-fPIC"] + san + ["-lpthread", "-ldl"], "capi_asan", verbose)
+    return out
+
+
 def build_all(verbose: bool = False) -> None:
     build_kernels(verbose)
     build_capi(verbose)
@@ -131,8 +155,12 @@ def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--kernels", action="store_true")
     ap.add_argument("--capi", action="store_true")
+    ap.add_argument("--sanitize", action="store_true", help="only build the ASan + UBSan copy of the host runtime")
     ap.add_argument("-v", "--verbose", action="store_true")
     args = ap.parse_args()
+    if args.sanitize:
+        print(build_capi_sanitized(args.verbose))
+        return
     if args.kernels or not args.capi:
         print(build_kernels(args.verbose))
     if args.capi or not args.kernels:
