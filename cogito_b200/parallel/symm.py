@@ -13,13 +13,29 @@ ever receive the peer addresses; no library kernel is given one.
 from __future__ import annotations
 
 import os
+import weakref
 
 import torch
 import torch.distributed as dist
 
 
+GUARD_BYTES = 256
+GUARD_PATTERN = 0xA5
+_LIVE = weakref.WeakSet()     # every buffer of this process (for check_all_canaries)
+
+
+def check_all_canaries() -> bool:
+    """True when no live symmetric buffer of this process has a damaged guard region."""
+    return all(b.check_canaries() for b in list(_LIVE))
+
+
 class SymmetricBuffer:
-    def __init__(self, nbytes: int, device, group=None):
+    """``canary=True`` (or ``COGITO_SYMM_CANARY=1``) brackets the buffer with two 256-byte guard
+    regions holding a fixed pattern; :meth:`check_canaries` tells whether any rank's kernel stored
+    outside the usable range (peers write into this memory by address, so nothing else would
+    notice).  ``local`` / ``ptrs`` always describe the usable range."""
+
+    def __init__(self, nbytes: int, device, group=None, canary: bool | None = None):
         self.device = torch.device(device)
         self.nbytes = (int(nbytes) + 255) // 256 * 256
         self.group = group
@@ -27,6 +43,35 @@ class SymmetricBuffer:
         self.rank = 0 if group is None else dist.get_rank(group)
         self._keep = []          # objects that keep peer mappings alive
         self.provider = "local"
+        if canary is None:
+            canary = os.environ.get("COGITO_SYMM_CANARY", "0") not in ("", "0")
+        self.guard = GUARD_BYTES if canary else 0
+        usable, self.nbytes = self.nbytes, self.nbytes + 2 * self.guard     # providers allocate guards too
+        try:
+            self._allocate()
+        finally:
+            self.nbytes = usable
+        self._raw = self.local
+        _LIVE.add(self)
+        if self.guard:
+            self._raw[:self.guard] = GUARD_PATTERN
+            self._raw[self.guard + usable:] = GUARD_PATTERN
+            self.local = self._raw[self.guard:self.guard + usable]
+            self.ptrs = [p + self.guard for p in self.ptrs]
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            if self.world > 1:
+                dist.barrier(self.group)
+
+    def check_canaries(self) -> bool:
+        """True when both guard regions of the LOCAL copy still hold the pattern (always True
+        without guards).  Call it after the kernels that use the buffer have finished."""
+        if not self.guard:
+            return True
+        lo, hi = self._raw[:self.guard], self._raw[self.guard + self.nbytes:]
+        return bool((lo == GUARD_PATTERN).all()) and bool((hi == GUARD_PATTERN).all())
+
+    def _allocate(self):
         if self.world == 1:
             self.local = torch.zeros(self.nbytes, dtype=torch.uint8, device=self.device)
             self.ptrs = [self.local.data_ptr()]

@@ -131,6 +131,11 @@ def main():
     else:
         raise SystemExit(f"unknown mode {mode}")
     out["status"] = list(_lib.read_status())
+    # guard regions around every symmetric buffer (COGITO_SYMM_CANARY=1): no peer stored out of range
+    torch.cuda.synchronize()
+    dist.barrier()
+    from cogito_b200.parallel.symm import check_all_canaries
+    out["canaries_ok"] = check_all_canaries()
     print("RESULT " + json.dumps(out), flush=True)
     dist.barrier()
     dist.destroy_process_group()

@@ -27,12 +27,15 @@ def _run(n, *args, timeout=600):
         pytest.skip(f"needs {n} GPUs")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), os.path.join(HERE, "mgpu_worker.py"), *map(str, args)]
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    # guard regions around every symmetric buffer: a peer store outside its range fails the test
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", COGITO_SYMM_CANARY="1")
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     found = re.findall(r"RESULT (\{[^{}]*\})", r.stdout)      # ranks may interleave their lines
     assert len(found) == n, r.stdout[-2000:]
-    return [json.loads(s) for s in found]
+    res = [json.loads(s) for s in found]
+    assert all(o["canaries_ok"] for o in res), res
+    return res
 
 
 def _close(res, tol):

@@ -116,6 +116,21 @@ def test_last_arriver_finishes_and_leaves_the_scratch_clean():
     assert results == {(0, 0, sum(range(1, W + 1)))}             # one finisher, complete sum, clean scratch
 
 
+def test_symmetric_buffer_canaries_catch_a_store_outside_the_usable_range():
+    import torch
+    from cogito_b200.parallel.symm import GUARD_BYTES, SymmetricBuffer
+    buf = SymmetricBuffer(1000, "cpu", canary=True)
+    assert buf.nbytes == 1024 and buf.local.numel() == 1024 and buf.ptrs[0] == buf.local.data_ptr()
+    v = buf.view(512, (64,), torch.float32)
+    v.fill_(3.0)
+    buf.view(0, (256,), torch.int32).fill_(-1)
+    assert buf.check_canaries()
+    buf._raw[GUARD_BYTES + 1024] = 0                             # one byte past the end, as a bad peer store would
+    assert not buf.check_canaries()
+    plain = SymmetricBuffer(1000, "cpu", canary=False)
+    assert plain.guard == 0 and plain.check_canaries()
+
+
 def test_all_reduce_protocol_with_real_threads_and_random_delays():
     P, E = 4, 25
     slots = [[None, None] for _ in range(P)]
