@@ -149,6 +149,45 @@ def load_training_state(base: str, model, opt) -> dict:
     return meta
 
 
+def dp_shard_path(base: str, rank: int, ranks: int) -> str:
+    return f"{base}.opt.dp{rank:02d}of{ranks:02d}.state"
+
+
+def save_dp_optimizer_shard(base: str, opt) -> str:
+    """Write this data-parallel rank's optimizer shard (``DPFusedAdam.shard_state``): Adam moments,
+    fp32 master slice, position in the flat vector, step and loss-scale state."""
+    sh = opt.shard_state()
+    tensors = {k: sh[k] for k in ("m", "v", "master") if sh.get(k) is not None}
+    meta = {k: sh[k] for k in ("begin", "count", "n", "ranks")}
+    meta["scaler"] = sh["scaler"]
+    tensors["meta.json"] = torch.from_numpy(np.frombuffer(json.dumps(meta).encode(), dtype=np.uint8).astype(np.float32))
+    path = dp_shard_path(base, opt.rank, opt.ranks)
+    save_tensors(path, tensors)
+    return path
+
+
+def load_dp_optimizer_resharded(base: str, opt) -> int:
+    """Restore ``opt`` (a ``DPFusedAdam`` of the CURRENT group, whatever its size) from the shard
+    files a previous run wrote under ``base``; returns the data-parallel size of that run.  The
+    parameters must have been loaded before (``load_model``)."""
+    import glob
+    import re
+    files = sorted(glob.glob(glob.escape(base) + ".opt.dp*of*.state"))
+    if not files:
+        raise FileNotFoundError(f"no optimizer shards under {base}")
+    old = {int(re.search(r"of(\d+)\.state$", f).group(1)) for f in files}
+    if len(old) != 1 or len(files) != next(iter(old)):
+        raise ValueError(f"incomplete or mixed shard set under {base}: {files}")
+    shards = []
+    for f in files:
+        state = load_tensors(f)
+        meta = json.loads(bytes(state.pop("meta.json").to(torch.uint8).tolist()).decode())
+        meta.update(state)
+        shards.append(meta)
+    opt.load_resharded(shards)
+    return next(iter(old))
+
+
 def gather_shards(base: str, dp: int, tp: int, pp: int) -> dict[str, torch.Tensor]:
     """Read every (tp, pp) shard of data-parallel replica 0 into one name -> tensor map with the
     coordinates prefixed (``tp0.pp1.<name>``); a model-specific merge turns it into full weights."""

@@ -104,6 +104,43 @@ class DPFusedAdam:
         if self.master is not None:
             self.master.copy_(self.fp.flat[self.begin:self.begin + self.count].float())
 
+    # -- checkpoint / elastic restart ------------------------------------------------------
+    def state_tensors(self):
+        """This rank's shard of the optimizer state."""
+        d = {"m": self.m, "v": self.v}
+        if self.master is not None:
+            d["master"] = self.master
+        return d
+
+    def shard_state(self) -> dict:
+        """Everything a restart needs from this rank: its shard, where the shard sits in the flat
+        parameter vector, and the step / loss-scale state (host copies)."""
+        d = {k: v.detach().cpu().clone() for k, v in self.state_tensors().items()}
+        d.update(begin=self.begin, count=self.count, n=self.n, ranks=self.ranks, scaler=self.scaler.state_dict())
+        return d
+
+    def load_resharded(self, shards) -> None:
+        """Restore from the shards of a run with ANY data-parallel size (a rank was lost, or ranks
+        were added).  Parameters start at the same offsets of the flat vector whatever the group
+        size (only the padding at its end depends on it), so this rank's slice is filled from the
+        overlap with each old shard; positions no old shard covers are padding and stay zero.
+        The parameters themselves must already hold the checkpointed weights."""
+        lo, hi = self.begin, self.begin + self.count
+        self.m.zero_()
+        self.v.zero_()
+        self.refresh_master()
+        for sh in shards:
+            a, b = max(lo, sh["begin"]), min(hi, sh["begin"] + sh["count"])
+            if a >= b:
+                continue
+            src, dst = slice(a - sh["begin"], b - sh["begin"]), slice(a - lo, b - lo)
+            self.m[dst].copy_(sh["m"][src])
+            self.v[dst].copy_(sh["v"][src])
+            if self.master is not None and sh.get("master") is not None:
+                self.master[dst].copy_(sh["master"][src])
+        if shards and shards[0].get("scaler"):
+            self.scaler.load_state_dict(shards[0]["scaler"])
+
     def _fold_autograd_grads(self):
         for p in self.fp.params:
             if p.grad is not None:
