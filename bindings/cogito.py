@@ -79,6 +79,33 @@ def lib() -> ctypes.CDLL:
     return _LIB
 
 
+_DEVICE_READY = False
+
+
+def _device_lib() -> ctypes.CDLL:
+    """The library with the device layer declared and brought up (``cg_cuda_init``: device mode on
+    a machine with a GPU and the kernel library beside libcogito.so, host mode otherwise)."""
+    global _DEVICE_READY
+    L = lib()
+    if not _DEVICE_READY:
+        for name in ("cg_tensor_to_cuda", "cg_tensor_to_cpu"):
+            getattr(L, name).restype, getattr(L, name).argtypes = TensorP, [TensorP]
+        L.cg_tensor_cuda_zeros.restype, L.cg_tensor_cuda_zeros.argtypes = TensorP, [POINTER(c_int), c_int, c_bool]
+        L.cg_tensor_is_cuda.restype, L.cg_tensor_is_cuda.argtypes = c_bool, [TensorP]
+        L.cg_cuda_tensor_matmul.restype, L.cg_cuda_tensor_matmul.argtypes = None, [TensorP, TensorP, TensorP]
+        L.cg_cuda_init.restype = c_bool
+        L.cg_cuda_device_mode.restype = c_bool
+        L.cg_cuda_get_last_error.restype = c_char_p
+        L.cg_cuda_init()
+        _DEVICE_READY = True
+    return L
+
+
+def device_mode() -> bool:
+    """True when ``cg_cuda_*`` calls execute on a GPU, False when they compute on the host."""
+    return bool(_device_lib().cg_cuda_device_mode())
+
+
 def _check(ptr, what: str):
     if not ptr:
         L = lib()
@@ -147,6 +174,31 @@ class Tensor:
         if not c.grad:
             return None
         return np.ctypeslib.as_array(c.grad, shape=(c.size,)).reshape(self.shape)
+
+    # -- device layer (cg_cuda_*): device memory on a machine with a GPU, host memory otherwise
+    def cuda(self) -> "Tensor":
+        """A copy in device memory (``numpy()`` of it is invalid; bring it back with ``cpu()``)."""
+        L = _device_lib()
+        return Tensor(_ptr=_check(L.cg_tensor_to_cuda(self._ptr), "cg_tensor_to_cuda"))
+
+    def cpu(self) -> "Tensor":
+        L = _device_lib()
+        return Tensor(_ptr=_check(L.cg_tensor_to_cpu(self._ptr), "cg_tensor_to_cpu"))
+
+    @property
+    def is_cuda(self) -> bool:
+        return bool(_device_lib().cg_tensor_is_cuda(self._ptr))
+
+    def device_matmul(self, other: "Tensor") -> "Tensor":
+        """``cg_cuda_tensor_matmul`` of two device tensors ([M,K] x [K,N]): the tcgen05 GEMM on a B200."""
+        L = _device_lib()
+        arr, n = _shape_arg((self.shape[0], other.shape[1]))
+        out = Tensor(_ptr=_check(L.cg_tensor_cuda_zeros(arr, n, False), "cg_tensor_cuda_zeros"))
+        L.cg_cuda_tensor_matmul(self._ptr, other._ptr, out._ptr)
+        err = L.cg_last_error()
+        if err:
+            raise RuntimeError(f"cg_cuda_tensor_matmul: {L.cg_error_string(err).decode()}: {L.cg_cuda_get_last_error().decode()}")
+        return out
 
     def zero_grad(self):
         lib().cg_tensor_zero_grad(self._ptr)

@@ -58,6 +58,17 @@ def test_rope_and_tile_helpers(lib):
     c2.case_rope(lib)
 
 
+def test_python_binding_of_the_device_layer(lib):
+    import numpy as np
+    from capi_defs import cg
+    a = cg.Tensor.from_numpy(np.arange(6, dtype=np.float32).reshape(2, 3))
+    b = cg.Tensor.from_numpy(np.ones((3, 4), dtype=np.float32))
+    da, db = a.cuda(), b.cuda()
+    assert not cg.device_mode() and not da.is_cuda               # host mode in this test
+    out = da.device_matmul(db).cpu()
+    np.testing.assert_allclose(out.numpy(), a.numpy() @ b.numpy())
+
+
 def test_shutdown_and_reinit(lib):
     lib.cg_cuda_shutdown()
     assert not lib.cg_cuda_is_available()

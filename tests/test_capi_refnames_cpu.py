@@ -6,14 +6,23 @@ from ctypes import POINTER, c_bool, c_char_p, c_float, c_int, c_size_t, c_void_p
 
 import numpy as np
 
-from capi_defs import FusionGroup, IrGraph, JitCompiler, L, T, TensorP, borrowed
+from capi_defs import FusionGroup, IrGraph, JitCompiler, L, T, TensorP, borrowed, cg
 
 OP = dict(ADD=1, SUB=2, MUL=3, DIV=4, SQRT=8, RSQRT=9, RELU=10, SOFTMAX=14, MATMUL=15, TRANSPOSE=16, SUM=19, MEAN=20,
           FUSED_ATTENTION=26, FUSED_LAYERNORM=27)
 
 
+_PRIVATE = None
+
+
 def _lib():
-    lib = L()
+    # a handle of its own: the prototypes set here must not replace those other test modules set
+    # on the shared handle (same library instance underneath)
+    global _PRIVATE
+    L()
+    if _PRIVATE is None:
+        _PRIVATE = ctypes.CDLL(cg._find_library())
+    lib = _PRIVATE
     GP = POINTER(IrGraph)
     lib.cg_jit_record_op.restype, lib.cg_jit_record_op.argtypes = TensorP, [c_int, POINTER(TensorP), c_int, c_void_p, c_size_t]
     lib.cg_jit_execute.restype, lib.cg_jit_execute.argtypes = None, [POINTER(JitCompiler), POINTER(TensorP), c_int, POINTER(TensorP), c_int]
