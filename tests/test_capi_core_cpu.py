@@ -115,6 +115,19 @@ def test_mnist_example_trains_with_the_library_layers_loader_and_adam(tmp_path):
     assert "epoch 5" in r.stdout
 
 
+def test_device_example_runs_in_host_mode_without_a_gpu(tmp_path):
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if not cc:
+        pytest.skip("no C compiler")
+    exe = tmp_path / "device"
+    subprocess.check_call([cc, "-std=c11", "-Wall", "-Werror", "-I", str(ROOT / "include"), str(ROOT / "examples" / "device.c"),
+                           "-L", str(ROOT / "cogito_b200" / "lib"), "-lcogito", "-lm", "-o", str(exe)])
+    env = {"LD_LIBRARY_PATH": str(ROOT / "cogito_b200" / "lib"), "COGITO_FORCE_HOST": "1"}
+    r = subprocess.run([str(exe)], env=env, capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "mode: host" in r.stdout and "matches the host computation" in r.stdout
+
+
 def test_layers_match_torch_forward_and_backward():
     lib = L()
     # conv -> batchnorm -> relu -> maxpool -> flatten -> linear, loss = sum(out * w)
