@@ -48,6 +48,8 @@ def parse():
     ap.add_argument("--layers", type=int, default=12)
     ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"])
     ap.add_argument("--no-alt", action="store_true", help="with several GPUs, skip the extra data-parallel measurement")
+    ap.add_argument("--timeline", default="", help="after the timed regions, trace two more steps and write the device "
+                    "time per kernel name (rank 0) to this JSON file; not part of any reported number")
     args = ap.parse_args()
     if args.micro_batch <= 0:
         dp = args.gpus if (args.parallelism == "dp" or args.impl != "cogito") else 1
@@ -106,6 +108,30 @@ class ClockSampler:
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def kernel_timeline(step, path, rank, barrier, steps=2):
+    """Device time per kernel name over `steps` steps (kineto trace; shares, not a benchmark)."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    barrier()
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        for _ in range(steps):
+            step()
+        torch.cuda.synchronize()
+    barrier()
+    if rank != 0:
+        return
+    rows = []
+    for ev in prof.key_averages():
+        t = getattr(ev, "device_time_total", None)
+        if t is None:
+            t = getattr(ev, "cuda_time_total", 0.0)
+        if getattr(ev, "device_type", None) is not None and "CUDA" in str(ev.device_type) and t > 0:
+            rows.append({"kernel": ev.key[:120], "calls_per_step": ev.count / steps, "ms_per_step": t / 1e3 / steps})
+    rows.sort(key=lambda r: -r["ms_per_step"])
+    with open(path, "w") as f:
+        json.dump({"steps": steps, "total_ms_per_step": sum(r["ms_per_step"] for r in rows), "kernels": rows}, f, indent=1)
 
 
 def main():
@@ -181,6 +207,8 @@ def main():
     step_e2e()
     ms_e2e = timed(step_e2e, args.steps)
     final_loss = float(loss_box[0])
+    if args.timeline:
+        kernel_timeline(step_device, args.timeline, rank, barrier)
 
     # The named configuration is tensor parallel; the same model and batch under data parallelism (the
     # fused all-reduce + Adam kernel) is measured as well and reported beside it under "alt".

@@ -36,7 +36,7 @@ class GemmArgs(Structure):
         ("residual", c_void_p), ("ldr", c_int64),
         ("aux_out", c_void_p), ("ldaux", c_int64),
         ("aux_in", c_void_p), ("ldauxin", c_int64),
-        ("dact", c_int32), ("force_simt", c_int32), ("max_ctas", c_int32),
+        ("dact", c_int32), ("force_simt", c_int32), ("max_ctas", c_int32), ("split_k", c_int32),
     ]
 
 

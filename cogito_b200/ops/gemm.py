@@ -74,12 +74,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          residual: torch.Tensor | None = None, aux_out: torch.Tensor | None = None,
          aux_in: torch.Tensor | None = None, dact: str | None = None,
          accumulate: bool = False, alpha: float = 1.0, force_simt: bool = False,
-         max_ctas: int = 0) -> torch.Tensor:
+         max_ctas: int = 0, split_k: int = 0) -> torch.Tensor:
     """``a``: [.., M, K] (or [.., K, M] when ``a_mn``); ``b``: [.., N, K] (or [.., K, N] when ``b_mn``).
 
     ``out`` may be given (bf16 or fp32; required for ``accumulate``).  ``aux_out``
     receives the pre-activation value in bf16.  ``aux_in`` / ``dact`` multiply the
-    result by the activation derivative at ``aux_in``.
+    result by the activation derivative at ``aux_in``.  ``split_k`` (fp32 ``accumulate`` outputs
+    only): 0 lets the launcher slice a long K range over idle SMs, 1 forbids it, n forces n slices.
     """
     if a_mn:
         K, M = a.shape[-2], a.shape[-1]
@@ -167,6 +168,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         g.dact = ACT[dact]
     g.force_simt = int(force_simt)
     g.max_ctas = int(max_ctas)
+    g.split_k = int(split_k)
     _lib.check(_lib.lib().cgk_gemm_bf16(ctypes.byref(g), _lib.stream_ptr()), "cgk_gemm_bf16")
     _lib.count_launch()
     return out

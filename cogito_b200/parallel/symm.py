@@ -43,6 +43,7 @@ class SymmetricBuffer:
         self.rank = 0 if group is None else dist.get_rank(group)
         self._keep = []          # objects that keep peer mappings alive
         self.provider = "local"
+        self.multicast_ptr = 0   # NVSwitch multicast address of the buffer, when the provider bound one
         if canary is None:
             canary = os.environ.get("COGITO_SYMM_CANARY", "0") not in ("", "0")
         self.guard = GUARD_BYTES if canary else 0
@@ -58,6 +59,8 @@ class SymmetricBuffer:
             self._raw[self.guard + usable:] = GUARD_PATTERN
             self.local = self._raw[self.guard:self.guard + usable]
             self.ptrs = [p + self.guard for p in self.ptrs]
+            if self.multicast_ptr:
+                self.multicast_ptr += self.guard
             if self.device.type == "cuda":
                 torch.cuda.synchronize(self.device)
             if self.world > 1:
@@ -96,6 +99,10 @@ class SymmetricBuffer:
         t.zero_()
         self.local = t
         self.ptrs = [int(p) for p in hdl.buffer_ptrs]
+        try:
+            self.multicast_ptr = int(getattr(hdl, "multicast_ptr", 0) or 0)
+        except Exception:
+            self.multicast_ptr = 0
         self._keep.append(hdl)
         self.provider = "symm_mem"
         torch.cuda.synchronize(self.device)

@@ -92,14 +92,9 @@ class _ColumnRow(torch.autograd.Function):
 
 
 def _ag_gemm_bwd(ws, dy_shard, w, aux_in=None, dact=None):
-    """(AG(dy_shard) @ W) [* act'(aux_in)] for a row-sharded W [N, K_local]; returns (dx, gathered dy)."""
-    if aux_in is None or not dy_shard.is_cuda:
-        out, g = ag_gemm(ws, dy_shard, w, b_mn=True)
-        if aux_in is not None:
-            out = F.unary_backward(dact, aux_in, out)
-        return out, g
-    out, g = ag_gemm(ws, dy_shard, w, b_mn=True)
-    return F.unary_backward(dact, aux_in, out), g
+    """(AG(dy_shard) @ W) [* act'(aux_in)] for a row-sharded W [N, K_local]; returns (dx, gathered dy).
+    The activation derivative is applied in the GEMM's epilogue."""
+    return ag_gemm(ws, dy_shard, w, b_mn=True, aux_in=aux_in, dact=dact, keep=False)
 
 
 def head_span(n_head: int, ranks: int, rank: int):
@@ -326,6 +321,7 @@ class TPGPT2(nn.Module):
 
     def forward(self, ids, targets=None, grad_scale=1.0):
         B, T = ids.shape
+        self.ws.begin_step()         # the gathered activations of the previous pass are dead
         x = _VocabParallelEmbedding.apply(ids, self.wte, self.wpe, self.ws)
         for blk in self.blocks:
             x = blk(x, (B, T))
@@ -367,7 +363,10 @@ class TPGradSync:
 def build_tp_gpt2(cfg, rank, world, dev, group=None, micro_tokens=16384):
     if group is None and world > 1:
         group = dist.group.WORLD
-    ws = TPWorkspace(dev, group, max_rows=micro_tokens, max_cols=cfg.d_model)
+    # room for the gathered input of every column-parallel GEMM of one pass (two per block and
+    # the output head), which the backward pass reads again
+    arena = (2 * cfg.n_layer + 1) * ((micro_tokens * cfg.d_model * 2 + 255) // 256 * 256)
+    ws = TPWorkspace(dev, group, max_rows=micro_tokens, max_cols=cfg.d_model, arena_bytes=arena)
     model = TPGPT2(cfg, ws, device=dev, dtype=torch.bfloat16 if torch.device(dev).type == "cuda" else None)
     rep, shd = model.ordered_parameters()
     model._ordered = rep + shd

@@ -1,7 +1,8 @@
-// Device helpers of the fused compute + collective kernels: untiled bulk copies
-// (never the cluster-broadcast form), a one-thread relay that moves a byte range from
-// a peer GPU into local memory through a shared-memory ring, and bounded waits on
-// flags that another GPU writes.
+// Device helpers of the fused compute + collective kernels: whole-CTA copies from a
+// peer GPU's memory into local memory with plain 16-byte loads (many in flight per
+// thread, because a load over NVLink takes a microsecond or more to come back), and
+// bounded waits on flags that another GPU writes.  No bulk / TMA load ever names
+// peer memory here, and none carries a cluster-broadcast qualifier.
 #pragma once
 #include "../kernels/sm100.cuh"
 
@@ -13,73 +14,104 @@ namespace cgk {
 #define CGK_PEER_WAIT_BUDGET_NS 10000000000ull
 #endif
 
-__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes,
-                                          uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
+// 16-byte load that bypasses the L1 (the line belongs to another GPU or was written by
+// other CTAs of this launch).
+__device__ __forceinline__ uint4 ld_cg_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
 }
-__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
-               "r"(src_smem), "r"(bytes)
+
+// Depth of the software pipeline of cta_copy: loads in flight per thread.
+constexpr int COPY_UNROLL = 16;
+
+// All threads of the CTA copy `bytes` (a multiple of 16; both pointers 16-byte aligned)
+// from src (possibly a peer GPU's memory) to dst (local).  Each thread keeps COPY_UNROLL
+// 16-byte loads in flight before it stores: 64 KiB per 256-thread CTA, which is what it
+// takes to cover the NVLink round trip.  The stores are plain generic-proxy stores; the
+// caller publishes them (barrier + release).
+__device__ __forceinline__ void cta_copy(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                         long long bytes) {
+  const long long nvec = bytes >> 4;
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+  uint4* d = reinterpret_cast<uint4*>(dst);
+  const long long step = (long long)blockDim.x * COPY_UNROLL;
+  for (long long v0 = threadIdx.x; v0 < nvec; v0 += step) {
+    uint4 r[COPY_UNROLL];
+    if (v0 + (long long)(COPY_UNROLL - 1) * blockDim.x < nvec) {
+#pragma unroll
+      for (int u = 0; u < COPY_UNROLL; ++u) r[u] = ld_cg_u4(s + v0 + (long long)u * blockDim.x);
+#pragma unroll
+      for (int u = 0; u < COPY_UNROLL; ++u) d[v0 + (long long)u * blockDim.x] = r[u];
+    } else {
+#pragma unroll
+      for (int u = 0; u < COPY_UNROLL; ++u) {
+        const long long v = v0 + (long long)u * blockDim.x;
+        if (v < nvec) r[u] = ld_cg_u4(s + v);
+      }
+#pragma unroll
+      for (int u = 0; u < COPY_UNROLL; ++u) {
+        const long long v = v0 + (long long)u * blockDim.x;
+        if (v < nvec) d[v] = r[u];
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// NVSwitch multicast ("multimem") accesses.  `mc` is an address inside a multicast
+// mapping that every GPU of the group has bound its copy of a symmetric buffer to.
+// A store is replicated by the switch into every GPU's copy (the writer's included);
+// a load-reduce returns the sum of all copies, accumulated in fp32 inside the switch.
+// These are ordinary memory instructions on a multicast address: nothing here is a TMA
+// or bulk copy.
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ void multimem_st_u4(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");
 }
-
-// Relay state of one thread: a ring of RELAY_STAGES pieces in shared memory.
-constexpr int RELAY_STAGES = 8;
-constexpr uint32_t RELAY_PIECE = 16384;
-
-struct Relay {
-  uint32_t smem;      // ring base (RELAY_STAGES * RELAY_PIECE bytes, 128-byte aligned)
-  uint32_t bars;      // RELAY_STAGES mbarriers
-  uint32_t count;     // pieces issued so far
-};
-
-__device__ __forceinline__ void relay_init(Relay& r, uint32_t smem, uint32_t bars) {
-  r.smem = smem;
-  r.bars = bars;
-  r.count = 0;
-  for (int s = 0; s < RELAY_STAGES; ++s) mbar_init(bars + 8u * s, 1);
-  mbar_fence_init();
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
 }
 
-// Copies `bytes` (a multiple of 16) from src (possibly peer memory) to dst (local).
-// Returns false if a wait ran out.  All copies have completed when it returns.
-__device__ __forceinline__ bool relay_copy(Relay& r, const uint8_t* src, uint8_t* dst,
-                                           long long bytes, volatile int* dead, int* status) {
-  const long long pieces = (bytes + RELAY_PIECE - 1) / RELAY_PIECE;
-  // Software pipeline: loads run up to RELAY_AHEAD pieces ahead of the stores.  Piece
-  // idx reuses the stage of piece idx - RELAY_STAGES, whose store must have finished
-  // reading shared memory; since at least idx - RELAY_AHEAD + 1 stores are committed
-  // when piece idx is loaded, "at most RELAY_STAGES - RELAY_AHEAD stores still
-  // reading" implies that.
-  constexpr int RELAY_AHEAD = 6;
-  long long issued = 0, stored = 0;
-  const uint32_t base = r.count;
-  while (stored < pieces) {
-    while (issued < pieces && issued - stored < RELAY_AHEAD) {
-      const uint32_t idx = base + (uint32_t)issued;
-      const int s = idx % RELAY_STAGES;
-      if (idx >= (uint32_t)RELAY_STAGES) tma_store_wait_read<RELAY_STAGES - RELAY_AHEAD>();
-      const long long o = issued * RELAY_PIECE;
-      const uint32_t n = (uint32_t)((bytes - o) < (long long)RELAY_PIECE ? (bytes - o) : RELAY_PIECE);
-      mbar_expect_tx(r.bars + 8u * s, n);
-      bulk_load(r.smem + s * RELAY_PIECE, src + o, n, r.bars + 8u * s);
-      ++issued;
+// All threads of the CTA broadcast `bytes` (multiple of 16) from local src to the
+// multicast address mc_dst: local loads (COPY_UNROLL in flight), multicast stores.
+__device__ __forceinline__ void cta_multicast(const uint8_t* __restrict__ src, uint8_t* mc_dst,
+                                              long long bytes) {
+  const long long nvec = bytes >> 4;
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+  uint4* d = reinterpret_cast<uint4*>(mc_dst);
+  const long long step = (long long)blockDim.x * COPY_UNROLL;
+  for (long long v0 = threadIdx.x; v0 < nvec; v0 += step) {
+    uint4 r[COPY_UNROLL];
+#pragma unroll
+    for (int u = 0; u < COPY_UNROLL; ++u) {
+      const long long v = v0 + (long long)u * blockDim.x;
+      if (v < nvec) r[u] = ld_cg_u4(s + v);
     }
-    const uint32_t idx = base + (uint32_t)stored;
-    const int s = idx % RELAY_STAGES;
-    if (!mbar_wait(r.bars + 8u * s, (idx / RELAY_STAGES) & 1u, dead, status, 3100)) return false;
-    const long long o = stored * RELAY_PIECE;
-    const uint32_t n = (uint32_t)((bytes - o) < (long long)RELAY_PIECE ? (bytes - o) : RELAY_PIECE);
-    bulk_store(dst + o, r.smem + s * RELAY_PIECE, n);
-    tma_store_commit();
-    ++stored;
+#pragma unroll
+    for (int u = 0; u < COPY_UNROLL; ++u) {
+      const long long v = v0 + (long long)u * blockDim.x;
+      if (v < nvec) multimem_st_u4(d + v, r[u]);
+    }
   }
-  r.count = base + (uint32_t)pieces;
-  tma_store_wait_all<0>();
-  return true;
+}
+
+__device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4& u) {
+  float2 f;
+  f = unpack_bf16x2(u.x); acc[0] += f.x; acc[1] += f.y;
+  f = unpack_bf16x2(u.y); acc[2] += f.x; acc[3] += f.y;
+  f = unpack_bf16x2(u.z); acc[4] += f.x; acc[5] += f.y;
+  f = unpack_bf16x2(u.w); acc[6] += f.x; acc[7] += f.y;
 }
 
 }  // namespace cgk

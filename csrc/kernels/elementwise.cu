@@ -56,7 +56,7 @@ __device__ __forceinline__ float un_apply(int op, float x, float s) {
     case UN_RELU: return fmaxf(x, 0.0f);
     case UN_SIGMOID: return 1.0f / (1.0f + expf(-x));
     case UN_TANH: return tanhf(x);
-    case UN_GELU: return gelu_tanh(x);
+    case UN_GELU: return gelu_tanh_precise(x);
     case UN_SILU: return silu_f(x);
     case UN_POW: return powf(x, s);
     case UN_SCALE: return x * s;
@@ -78,7 +78,7 @@ __device__ __forceinline__ float un_grad(int op, float x, float s) {
     case UN_RELU: return x > 0.0f ? 1.0f : 0.0f;
     case UN_SIGMOID: { float y = 1.0f / (1.0f + expf(-x)); return y * (1.0f - y); }
     case UN_TANH: { float y = tanhf(x); return 1.0f - y * y; }
-    case UN_GELU: return dgelu_tanh(x);
+    case UN_GELU: return dgelu_tanh_precise(x);
     case UN_SILU: return dsilu_f(x);
     case UN_POW: return s * powf(x, s - 1.0f);
     case UN_SCALE: return s;

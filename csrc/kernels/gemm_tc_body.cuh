@@ -28,17 +28,25 @@ struct GemmDev {
   long long ldauxin;
   int dact;
   int* status;
+  // Split-K: every output tile is computed by split_k work units, each over kb_per_split
+  // k-blocks, that add their part into the fp32 output with vector reductions (only with
+  // out_fp32 && accumulate and no other epilogue term).  For weight gradients: a small
+  // output with a very long reduction dimension gives too few tiles for the SMs otherwise.
+  int split_k, kb_per_split;
   // ---- hooks used by the fused kernels (all off when zero / null) ----
   // A-operand readiness: before loading rows [m0, m0+128) of A the producer waits
   // until a_ready[m0 / a_ready_rows] >= a_ready_target (flags set by the copy CTAs
-  // of the same kernel).
+  // of the same kernel, or by the GPU that multicast the rows: system scope).
   const int* a_ready;
   int a_ready_rows;
   int a_ready_target;
-  int a_ready_skip_first, a_ready_skip_count;   // chunks that are in place before the launch
   // m-tile rotation: tile index tm is processed as (tm + m_rot) % tiles_m, so each
   // rank starts with the rows that are available / needed first.
   int m_rot;
+  // m-tile interleave: with m_inter = P the i-th row of tiles walked is block i / P of
+  // shard (i % P + m_src0) % P, so that the shards of all ranks are consumed (all-gather
+  // by multicast) or filled (reduce-scatter) at the same pace.
+  int m_inter, m_src0;
   // Reduce-scatter epilogue: rows [o*rs_rows, (o+1)*rs_rows) of the result belong to
   // rank o and are stored (bf16) at rs_dst[o] + (row - o*rs_rows)*ldc + col; after a
   // tile is stored, rs_flag[o][(row - o*rs_rows) / 128] is incremented (system scope).
@@ -108,6 +116,8 @@ __device__ __forceinline__ void epilogue_scalar(const GemmDev& g, int b, int m, 
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int GROUP_M = 8;
+constexpr int GEMM_THREADS = 384;       // TMA warp, MMA warp, TMEM warp, one spare, eight epilogue warps
+constexpr int RS_SIGNAL_BATCH = 4;      // reduce-scatter tiles published per system-scope fence
 
 template <int BN, int STAGES>
 struct GemmSmem {
@@ -115,10 +125,11 @@ struct GemmSmem {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int NUM_BARS = 2 * STAGES + 4;
-  // per-warp transposition area of the reduce-scatter epilogue (4 warps x 4 KiB)
+  static constexpr int NUM_BARS = 2 * STAGES + 6;
+  // per-warp transposition area of the reduce-scatter epilogue (8 warps x 4 KiB); the plain
+  // epilogue keeps the tile's bias slice there (2 x BN floats)
   static constexpr int EPI_OFFSET = (BAR_OFFSET + NUM_BARS * 8 + 16 + 127) / 128 * 128;
-  static constexpr int TOTAL = EPI_OFFSET + 4 * 4096 + 1024;  // + alignment slack
+  static constexpr int TOTAL = EPI_OFFSET + 8 * 4096 + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ void tile_coords(const GemmDev& g, int t, int& b, int& tm, int& tn) {
@@ -139,11 +150,12 @@ __device__ __forceinline__ void tile_coords(const GemmDev& g, int t, int& b, int
     tm = first_m + rr % rows_in_group;
     tn = rr / rows_in_group;
   }
+  if (g.m_inter > 1) tm = ((tm % g.m_inter + g.m_src0) % g.m_inter) * (g.tiles_m / g.m_inter) + tm / g.m_inter;
   if (g.m_rot) tm = (tm + g.m_rot) % g.tiles_m;
 }
 
 // cta / nctas: index and count of the CTAs that run this body (the fused kernels
-// give some CTAs of the grid other roles).  256 threads.
+// give some CTAs of the grid other roles).  GEMM_THREADS threads.
 template <int BN, int STAGES>
 __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUtensorMap& tmB,
                                              const GemmDev& g, int cta, int nctas,
@@ -157,6 +169,9 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUten
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  // meeting points of the 256 epilogue threads, alternating by tile parity (bounded waits,
+  // unlike a named barrier)
+  auto epi_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 4 + a); };
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + L::BAR_OFFSET + L::NUM_BARS * 8);
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
@@ -171,7 +186,8 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUten
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 128);
+      mbar_init(tempty_bar(a), 256);
+      mbar_init(epi_bar(a), 256);
     }
     *dead = 0;
     mbar_fence_init();
@@ -185,8 +201,18 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUten
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  const int total_tiles = g.batch * g.tiles_m * g.tiles_n;
-  const int kblocks = (g.K + BK - 1) / BK;
+  const int out_tiles = g.batch * g.tiles_m * g.tiles_n;
+  const int total_tiles = out_tiles * g.split_k;       // work units: unit u = (split u / out_tiles, tile u % out_tiles)
+  const int kblocks_all = (g.K + BK - 1) / BK;
+  auto k_range = [&](int u, int& kb0, int& kb1) {
+    if (g.split_k > 1) {
+      kb0 = (u / out_tiles) * g.kb_per_split;
+      kb1 = min(kblocks_all, kb0 + g.kb_per_split);
+    } else {
+      kb0 = 0;
+      kb1 = kblocks_all;
+    }
+  };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -196,23 +222,23 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUten
       bool ok = true;
       int last_ready_chunk = -1;
       for (int t = cta; t < total_tiles && ok; t += nctas) {
-        int b, tm, tn;
-        tile_coords(g, t, b, tm, tn);
+        int b, tm, tn, kb0, kb1;
+        tile_coords(g, t % out_tiles, b, tm, tn);
+        k_range(t, kb0, kb1);
         const int m0 = tm * BM, n0 = tn * BN;
         if (g.a_ready) {
           // rows of this tile may span two chunks when a_ready_rows < 128: wait for the last one
           const int last_row = min(m0 + BM, g.M) - 1;
           for (int ch = m0 / g.a_ready_rows; ch <= last_row / g.a_ready_rows && ok; ++ch) {
             if (ch == last_ready_chunk) continue;
-            if (ch >= g.a_ready_skip_first && ch < g.a_ready_skip_first + g.a_ready_skip_count) continue;
-            if (!flag_wait_ge_gpu(g.a_ready + ch, g.a_ready_target, dead, g.status, 110)) ok = false;
+            if (!flag_wait_ge_sys_cta(g.a_ready + ch, g.a_ready_target, dead, g.status, 110)) ok = false;
             last_ready_chunk = ch;
           }
           if (!ok) break;
           // the rows were written through the generic proxy by other CTAs
           asm volatile("fence.proxy.async;" ::: "memory");
         }
-        for (int kb = 0; kb < kblocks; ++kb, ++kit) {
+        for (int kb = kb0; kb < kb1; ++kb, ++kit) {
           const int s = kit % STAGES;
           const uint32_t ph = (kit / STAGES) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, dead, g.status, 100)) { ok = false; break; }
@@ -252,7 +278,9 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUten
         if (!mbar_wait(tempty_bar(acc), aph ^ 1u, dead, g.status, 200)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < kblocks; ++kb, ++kit) {
+        int kb0, kb1;
+        k_range(t, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb, ++kit) {
           const int s = kit % STAGES;
           const uint32_t ph = (kit / STAGES) & 1u;
           if (!mbar_wait(full_bar(s), ph, dead, g.status, 201)) { ok = false; break; }
@@ -263,7 +291,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUten
           for (int kk = 0; kk < BK / 16; ++kk) {
             const uint64_t ad = make_smem_desc_sw128(sA + kk * a_kstep, a_lbo, 1024u);
             const uint64_t bd = make_smem_desc_sw128(sB + kk * b_kstep, b_lbo, 1024u);
-            umma_f16(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
+            umma_f16(d_tmem, ad, bd, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
         }

@@ -1,11 +1,11 @@
 // bf16 GEMM on the 5th-generation tensor cores: TMA -> 128B-swizzled shared
 // memory -> tcgen05.mma (fp32 accumulators in TMEM) -> tcgen05.ld epilogue.
 //
-// One persistent CTA per SM, 256 threads, warp-specialised:
+// One persistent CTA per SM, 384 threads, warp-specialised:
 //   warp 0      TMA producer (one lane)
 //   warp 1      MMA issuer   (one lane)
 //   warp 2      TMEM allocator / deallocator
-//   warps 4..7  epilogue: each warp drains its 32-lane quadrant of TMEM
+//   warps 4..11 epilogue: warp w drains TMEM lane quadrant w % 4 for one half of the columns
 // Tile = 128 x BN x 64 with a STAGES-deep shared-memory ring and two TMEM
 // accumulators, so the epilogue of tile i overlaps the main loop of tile i+1.
 // The device code is in gemm_tc_body.cuh (shared with the fused collective kernels).
@@ -19,7 +19,7 @@
 namespace cgk {
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const GemmDev g) {
   extern __shared__ uint8_t smem_raw[];
@@ -114,6 +114,8 @@ int fill_gemm_dev(const cgk_gemm_args& a, GemmDev* pg) {
   g.aux_out = (__nv_bfloat16*)a.aux_out; g.ldaux = a.ldaux;
   g.aux_in = (const __nv_bfloat16*)a.aux_in; g.ldauxin = a.ldauxin;
   g.dact = a.dact;
+  g.split_k = 1;
+  g.kb_per_split = 0;
   g.status = device_status(dev);
   return 0;
 }
@@ -144,10 +146,10 @@ static int launch_tc(const cgk_gemm_args& a, const GemmDev& g0, int sms, cudaStr
   if (rc) return rc;
   CGK_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_tc_kernel<BN, STAGES>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-  int total = g.batch * g.tiles_m * g.tiles_n;
+  int total = g.batch * g.tiles_m * g.tiles_n * g.split_k;
   int cap = a.max_ctas > 0 ? a.max_ctas : sms;
   int grid = total < cap ? total : cap;
-  gemm_bf16_tc_kernel<BN, STAGES><<<grid, 256, L::TOTAL, stream>>>(tmA, tmB, g);
+  gemm_bf16_tc_kernel<BN, STAGES><<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tmA, tmB, g);
   CGK_LAUNCH_CHECK();
   return 0;
 }
@@ -178,6 +180,28 @@ CGK_API int cgk_gemm_bf16(const cgk_gemm_args* pa, void* stream_) {
     return 0;
   }
   const int sms = sm_count(dev);
+  const int ctas = a.max_ctas > 0 && a.max_ctas < sms ? a.max_ctas : sms;
+  // Split-K for accumulating fp32 outputs (weight gradients) whose tiles would leave SMs idle:
+  // the widest tile the output allows, and as many K slices as fill the machine.
+  const bool can_split = a.out_fp32 && a.accumulate && a.batch == 1 && !a.bias && a.act == 0 && !a.residual &&
+                         !a.aux_out && !a.aux_in && a.split_k != 1 && (a.ldc % 4) == 0 &&
+                         (((uintptr_t)a.out & 15) == 0) && (a.N % 32) == 0;
+  if (can_split) {
+    const int bn = a.N >= 192 ? 256 : (a.N >= 96 ? 128 : 64);
+    const long long tiles = (long long)((a.M + BM - 1) / BM) * ((a.N + bn - 1) / bn);
+    const int kblocks = (a.K + BK - 1) / BK;
+    int S = a.split_k > 1 ? a.split_k : (int)(ctas / tiles);
+    if (S > kblocks / 8) S = kblocks / 8;
+    if (S >= 2 && (a.split_k > 1 || tiles * 4 < (long long)ctas * 3)) {
+      g.kb_per_split = (kblocks + S - 1) / S;
+      g.split_k = (kblocks + g.kb_per_split - 1) / g.kb_per_split;     // no empty slice
+      switch (bn) {
+        case 256: return launch_tc<256, 4>(a, g, sms, stream);
+        case 128: return launch_tc<128, 6>(a, g, sms, stream);
+        default: return launch_tc<64, 8>(a, g, sms, stream);
+      }
+    }
+  }
   switch (pick_bn(a, a.max_ctas > 0 ? a.max_ctas : sms)) {
     case 256: return launch_tc<256, 4>(a, g, sms, stream);
     case 128: return launch_tc<128, 6>(a, g, sms, stream);

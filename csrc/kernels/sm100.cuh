@@ -165,6 +165,9 @@ __device__ __forceinline__ void st_release_gpu(int* p, int v) {
 __device__ __forceinline__ void red_release_sys_add(int* p, int v) {
   asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ void red_relaxed_sys_add(int* p, int v) {
+  asm volatile("red.relaxed.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
   asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -182,6 +185,24 @@ __device__ __forceinline__ bool flag_wait_ge_sys(const int* flag, int want, int*
       __nanosleep(64);
     }
   }
+  report_status(status, KST_FLAG_TIMEOUT, where, want);
+  return false;
+}
+// The same wait for a role of a CTA whose other roles must learn that it gave up.
+__device__ __forceinline__ bool flag_wait_ge_sys_cta(const int* flag, int want, volatile int* dead,
+                                                     int* status, int where) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0; it < CGK_WAIT_MAX_ITERS; ++it) {
+    if (ld_acquire_sys(flag) >= want) return true;
+    if ((it & 31u) == 31u) {
+      if (dead && *dead) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > CGK_WAIT_BUDGET_NS) break;
+      __nanosleep(32);
+    }
+  }
+  if (dead) *dead = 1;
   report_status(status, KST_FLAG_TIMEOUT, where, want);
   return false;
 }
@@ -432,12 +453,34 @@ __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t chunk) {
 // ---------------------------------------------------------------------------
 // small math helpers
 // ---------------------------------------------------------------------------
+// Hardware tanh (one MUFU instruction, relative error about 2^-11: below bf16 resolution).
+// tanhf() costs tens of instructions with a divergent slow path, which made the GELU
+// epilogue of a 128 x 256 tile several times longer than the tile's MMAs.
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float gelu_tanh(float x) {
+  const float c = 0.7978845608028654f;
+  float u = c * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.0f + tanh_fast(u));
+}
+__device__ __forceinline__ float dgelu_tanh(float x) {
+  const float c = 0.7978845608028654f;
+  float x2 = x * x;
+  float u = c * (x + 0.044715f * x * x2);
+  float t = tanh_fast(u);
+  float du = c * (1.0f + 3.0f * 0.044715f * x2);
+  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
+}
+// Full-precision forms for the fp32 elementwise kernels (memory-bound: tanhf costs nothing there).
+__device__ __forceinline__ float gelu_tanh_precise(float x) {
   const float c = 0.7978845608028654f;
   float u = c * (x + 0.044715f * x * x * x);
   return 0.5f * x * (1.0f + tanhf(u));
 }
-__device__ __forceinline__ float dgelu_tanh(float x) {
+__device__ __forceinline__ float dgelu_tanh_precise(float x) {
   const float c = 0.7978845608028654f;
   float x2 = x * x;
   float u = c * (x + 0.044715f * x * x2);
@@ -452,13 +495,9 @@ __device__ __forceinline__ float dsilu_f(float x) {
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {
-#ifdef CGK_EXPERIMENT_EXP_OFF
-  return x * 0.001f;
-#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-#endif
 }
 // Vector reduction into global memory (16-byte aligned).
 __device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, float c, float d) {
@@ -468,12 +507,8 @@ __device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, flo
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-#ifdef CGK_EXPERIMENT_PACK_TRUNC
-  return __byte_perm(__float_as_uint(lo), __float_as_uint(hi), 0x7632);
-#else
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
-#endif
 }
 __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
   __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);

@@ -56,6 +56,9 @@ typedef struct {
   int32_t dact;
   int32_t force_simt; /* testing: use the CUDA-core fallback */
   int32_t max_ctas;   /* 0 = one persistent CTA per SM */
+  int32_t split_k;    /* fp32 accumulating outputs only: 0 = split the K range over idle SMs when the
+                         output has few tiles (partial sums meet in the output through fp32 reductions,
+                         so their order, and the last bits, can differ between runs), 1 = never, n = n slices */
 } cgk_gemm_args;
 
 int cgk_gemm_bf16(const cgk_gemm_args* args, void* stream);
@@ -69,19 +72,22 @@ typedef struct {
   int32_t chunk_rows;       /* rows per readiness flag, a multiple of 128 */
   const void* shard_ptrs[8];   /* [M/ranks, K] bf16 activation shard of each rank */
   void* signal_ptrs[8];        /* int32[2*ranks] per rank: ready words, then done words */
-  int32_t* chunk_flags;        /* local int32[ranks * ceil(rows/chunk_rows)] */
+  void* chunk_flag_ptrs[8];    /* per rank: int32[ranks * ceil(rows/chunk_rows)] in symmetric memory */
   int32_t* done_count;         /* local int32[ranks], zero on entry, zero on exit */
   int32_t n_copy_ctas;         /* 0 = default */
+  void* mc_gathered;           /* NVSwitch multicast address of the gathered buffer (which then must
+                                  sit at the same offset of a symmetric buffer on every rank), or
+                                  null: the shards are pulled with peer loads.  In multicast mode
+                                  only shard_ptrs[rank] is read and it may be any local memory. */
 } cgk_ag_args;
 
 typedef struct {
   int32_t rank, ranks;
   int32_t queue_base;       /* value of *queue when the call starts: the sum over earlier calls
                                of (row blocks + CTAs of the launch); see cgk_gemm_rs_queue_step */
-  void* staging_ptrs[8];    /* per rank: bf16 [ranks][M/ranks][ld] partial slots */
+  void* partial_ptrs[8];    /* per rank: bf16 [M][ld] buffer that rank writes its partial product to */
   void* flag_ptrs[8];       /* per rank: int32[(M/ranks)/128] arrival counters, zero on entry and on exit */
-  int64_t ld;               /* leading dimension of a slot row */
-  int64_t slot_elems;       /* elements between slots */
+  int64_t ld;               /* leading dimension of a partial row */
   const void* bias;         /* bf16 [N] or null, added after the reduction */
   const void* residual;     /* bf16 [M/ranks, ldr] or null */
   int64_t ldr;
@@ -89,14 +95,15 @@ typedef struct {
   int64_t ldo;
   int32_t n_reduce_ctas;    /* 0 = default */
   int32_t* queue;           /* local int32 work counter, zero before the first call */
+  const void* mc_partial;   /* NVSwitch multicast address of the partial buffers (sum in the switch), or null */
 } cgk_rs_args;
 
 /* g->A is the LOCAL gathered buffer [M, K] (filled by the kernel, M = ranks * shard rows). */
 int cgk_ag_gemm(const cgk_gemm_args* g, const cgk_ag_args* x, void* stream);
-/* g describes this rank's partial product [M, N]; g->out is ignored. */
+/* g describes this rank's partial product [M, N]; g->out is ignored; g->max_ctas > 0 caps the grid. */
 int cgk_gemm_rs(const cgk_gemm_args* g, const cgk_rs_args* x, void* stream);
 /* By how much one cgk_gemm_rs call with M rows advances *queue on the current device. */
-int cgk_gemm_rs_queue_step(int M, int ranks);
+int cgk_gemm_rs_queue_step(int M, int ranks, int max_ctas);
 
 /* ---- Fused data-parallel optimizer step (csrc/comm/dp_adam.cu) ------------------ */
 /* Pointer tables are indexed by rank (peer mappings of symmetric memory).  This rank

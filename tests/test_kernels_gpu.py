@@ -39,6 +39,24 @@ def test_gemm_layouts(M, N, K, a_mn, b_mn):
     assert relerr(out, ref) < 1e-2
 
 
+@pytest.mark.parametrize("Mw,Nw,K,split", [(384, 768, 16384, 0), (768, 768, 8192, 4), (288, 768, 4096 + 64, 3),
+                                           (3072, 768, 2048, 0)])
+def test_gemm_split_k_weight_gradient(Mw, Nw, K, split):
+    """dW[Mw, Nw] += dy[K, Mw]^T x[K, Nw] in fp32: few output tiles, long reduction, sliced over the SMs."""
+    from cogito_b200.ops.gemm import gemm
+    torch.manual_seed(2)
+    dy = torch.randn(K, Mw, device=DEV, dtype=torch.bfloat16)
+    x = torch.randn(K, Nw, device=DEV, dtype=torch.bfloat16)
+    base = torch.randn(Mw, Nw, device=DEV, dtype=torch.float32)
+    out = base.clone()
+    gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=True, split_k=split)
+    ref = base + dy.float().T @ x.float()
+    assert relerr(out, ref) < 2e-3
+    one = base.clone()
+    gemm(dy, x, a_mn=True, b_mn=True, out=one, accumulate=True, split_k=1)      # unsliced
+    assert relerr(one, ref) < 2e-3
+
+
 def test_gemm_simt_fallback_unaligned():
     from cogito_b200.ops.gemm import gemm, gemm_reference
     torch.manual_seed(0)
