@@ -42,7 +42,7 @@ def parse():
     ap.add_argument("--impl", default="cogito", choices=["cogito", "reference", "torch"])
     ap.add_argument("--micro-batch", type=int, default=0,
                     help="sequences per micro-batch; 0 = the whole batch of the rank in one pass (no gradient "
-                         "accumulation: measured fastest, 500 K tok/s against 449 K with 8 on one GPU)")
+                         "accumulation)")
     ap.add_argument("--global-batch", type=int, default=64)
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=12)

@@ -56,7 +56,6 @@ class CogitoJob(_Job):
         self.dp = world if (world > 1 and args.parallelism == "dp") else 1
         self.rank = rank
         self.trainer = Trainer(self.model, self.opt, micro_batch=mb, parallel=parallel)
-        full = GPT2(cfg, device="meta") if False else None
         self.flops_per_token = _gpt2_flops_per_token(cfg, args.seq_len)
 
     def step(self, ids, targets):

@@ -6,7 +6,9 @@ total_size}; ``num_tensors`` directory entries of 120 bytes {name[64], ndim i32,
 dtype i32, offset u64, size_bytes u64}; then the payloads back to back.  The reference writes
 fp32 only (dtype 0) and leaves total_size 0; this writer also fills total_size and uses
 dtype 1 for bf16 payloads and dtype 2 for packed INT4 payloads (each followed by a
-``<name>.scales`` fp32 entry), which loaders that ignore those fields still skip over safely.
+``<name>.scales`` fp32 entry; ``cg_load_model`` dequantises such a pair into one fp32 tensor).
+Tensors of other types (integer counters, bool masks, fp64, fp16) keep their exact bytes under
+type codes of this library (16 and up), which a reader of the reference's format does not know.
 
 On top of the tensor file: a ``*.state`` sidecar (same format) with the optimizer moments, fp32
 master weights, step counters, loss-scale state and RNG seeds, so that a resumed run
@@ -26,21 +28,33 @@ MAGIC = 0x434F4731
 HEADER = struct.Struct("<IIIIQ")                     # magic, version, count, pad, total_size
 ENTRY = struct.Struct("<64si8iiQQ")                  # name, ndim, shape[8], dtype, offset, size
 DT_FP32, DT_BF16, DT_INT4 = 0, 1, 2
+# exact-byte payloads of this library (not part of the reference's enum)
+RAW_CODES = {torch.int64: 16, torch.int32: 17, torch.uint8: 18, torch.bool: 19, torch.float64: 20,
+             torch.float16: 21, torch.int16: 22, torch.int8: 23}
+RAW_NUMPY = {16: np.int64, 17: np.int32, 18: np.uint8, 19: np.bool_, 20: np.float64, 21: np.float16,
+             22: np.int16, 23: np.int8}
 assert HEADER.size == 24 and ENTRY.size == 120
 
 
-def _payload(t: torch.Tensor):
+def _payload(t: torch.Tensor, int4: bool):
     t = t.detach().cpu().contiguous()
+    if int4:
+        if t.dtype != torch.uint8:
+            raise TypeError("a packed INT4 payload must be a uint8 tensor")
+        return DT_INT4, t.numpy().tobytes()
     if t.dtype == torch.bfloat16:
         return DT_BF16, t.view(torch.int16).numpy().tobytes()
-    if t.dtype == torch.uint8:
-        return DT_INT4, t.numpy().tobytes()
-    return DT_FP32, t.float().numpy().tobytes()
+    if t.dtype == torch.float32:
+        return DT_FP32, t.numpy().tobytes()
+    if t.dtype in RAW_CODES:
+        return RAW_CODES[t.dtype], t.numpy().tobytes()
+    raise TypeError(f"cannot store a tensor of type {t.dtype} in a COG1 file")
 
 
 def save_tensors(path: str, tensors: dict[str, torch.Tensor], int4_shapes: dict[str, tuple] | None = None) -> int:
-    """Write a COG1 file.  uint8 tensors are stored as packed INT4 payloads whose logical shape
-    comes from ``int4_shapes[name]``.  Returns the number of bytes written."""
+    """Write a COG1 file.  The uint8 tensors named in ``int4_shapes`` are packed INT4 payloads whose
+    logical shape is ``int4_shapes[name]``; every other tensor keeps its type.  Returns the number
+    of bytes written."""
     names = list(tensors)
     entries, blobs = [], []
     off = HEADER.size + ENTRY.size * len(names)
@@ -49,8 +63,9 @@ def save_tensors(path: str, tensors: dict[str, torch.Tensor], int4_shapes: dict[
         if len(raw) > 63:
             raise ValueError(f"tensor name longer than 63 bytes: {name}")
         t = tensors[name]
-        dtype, blob = _payload(t)
-        shape = tuple(int4_shapes[name]) if (dtype == DT_INT4 and int4_shapes and name in int4_shapes) else tuple(t.shape)
+        is_int4 = bool(int4_shapes) and name in int4_shapes
+        dtype, blob = _payload(t, is_int4)
+        shape = tuple(int4_shapes[name]) if is_int4 else tuple(t.shape)
         if len(shape) > 8:
             raise ValueError("at most 8 dimensions")
         entries.append(ENTRY.pack(raw, len(shape), *(list(shape) + [0] * (8 - len(shape))), dtype, off, len(blob)))
@@ -85,13 +100,17 @@ def load_tensors(path: str, device="cpu", use_mmap: bool = True) -> dict[str, to
         name = raw.split(b"\0", 1)[0].decode()
         if offset + size > len(buf):
             raise ValueError(f"entry {name} points past the end of the file")
+        shape = tuple(shape)
         if dtype == DT_FP32:
-            t = torch.from_numpy(np.frombuffer(buf, np.float32, size // 4, offset).copy()).view(*shape)
+            t = torch.from_numpy(np.frombuffer(buf, np.float32, size // 4, offset).copy()).reshape(shape)
         elif dtype == DT_BF16:
-            t = torch.from_numpy(np.frombuffer(buf, np.int16, size // 2, offset).copy()).view(torch.bfloat16).view(*shape)
+            t = torch.from_numpy(np.frombuffer(buf, np.int16, size // 2, offset).copy()).view(torch.bfloat16).reshape(shape)
         elif dtype == DT_INT4:
             t = torch.from_numpy(np.frombuffer(buf, np.uint8, size, offset).copy())
-            t.logical_shape = tuple(shape)
+            t.logical_shape = shape
+        elif dtype in RAW_NUMPY:
+            npdt = np.dtype(RAW_NUMPY[dtype])
+            t = torch.from_numpy(np.frombuffer(buf, npdt, size // npdt.itemsize, offset).copy()).reshape(shape)
         else:
             raise ValueError(f"entry {name}: unknown dtype {dtype}")
         out[name] = t.to(device)

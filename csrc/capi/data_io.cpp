@@ -220,20 +220,95 @@ CG_EXPORT void cg_load_model(const char* filename, cg_tensor*** out_t, char*** o
   cg_tensor** ts = (cg_tensor**)std::calloc(n ? n : 1, sizeof(cg_tensor*));
   char** ns = (char**)std::calloc(n ? n : 1, sizeof(char*));
   bool ok = true;
+  // Payload types: 0 fp32, 1 bf16 (widened), 2 packed INT4 (flat groups, low nibble first, as
+  // cg_quantize_int4 writes them) dequantised with the "<name>.scales" entry that follows it,
+  // 16-23 exact-byte integer / bool / fp64 / fp16 payloads of the Python writer, converted to
+  // fp32 values.  An entry of any other type becomes a 1-D tensor of its byte values, so that one
+  // unknown entry does not make the rest of the file unreadable.
+  auto read_raw = [&](const cg_tensor_entry& e, std::vector<unsigned char>& raw) {
+    raw.resize((size_t)e.size_bytes);
+    return std::fseek(f, (long)e.offset, SEEK_SET) == 0 && (raw.empty() || std::fread(raw.data(), 1, raw.size(), f) == raw.size());
+  };
   for (int i = 0; ok && i < n; ++i) {
     cg_tensor_entry& e = dir[i];
     e.name[63] = 0;
-    ok = e.ndim >= 0 && e.ndim <= CG_MAX_DIMS && (e.dtype == 0 || e.dtype == 1);
+    ok = e.ndim >= 0 && e.ndim <= CG_MAX_DIMS && e.size_bytes <= ((uint64_t)1 << 40);
     if (!ok) break;
-    ts[i] = make(e.shape, e.ndim, false);
     ns[i] = strdup(e.name);
-    ok = ts[i] && std::fseek(f, (long)e.offset, SEEK_SET) == 0;
-    if (!ok) break;
-    if (e.dtype == 0) ok = e.size_bytes == (uint64_t)ts[i]->size * 4 && (ts[i]->size == 0 || std::fread(ts[i]->data, 4, ts[i]->size, f) == (size_t)ts[i]->size);
-    else {
-      std::vector<uint16_t> raw(ts[i]->size);
-      ok = e.size_bytes == (uint64_t)ts[i]->size * 2 && (ts[i]->size == 0 || std::fread(raw.data(), 2, raw.size(), f) == raw.size());
-      for (int j = 0; ok && j < ts[i]->size; ++j) ts[i]->data[j] = cg_bf16_to_fp32(raw[j]);
+    std::vector<unsigned char> raw;
+    if (e.dtype == 0 || e.dtype == 1) {
+      ts[i] = make(e.shape, e.ndim, false);
+      ok = ts[i] && std::fseek(f, (long)e.offset, SEEK_SET) == 0;
+      if (!ok) break;
+      if (e.dtype == 0) ok = e.size_bytes == (uint64_t)ts[i]->size * 4 && (ts[i]->size == 0 || std::fread(ts[i]->data, 4, ts[i]->size, f) == (size_t)ts[i]->size);
+      else {
+        std::vector<uint16_t> half(ts[i]->size);
+        ok = e.size_bytes == (uint64_t)ts[i]->size * 2 && (ts[i]->size == 0 || std::fread(half.data(), 2, half.size(), f) == half.size());
+        for (int j = 0; ok && j < ts[i]->size; ++j) ts[i]->data[j] = cg_bf16_to_fp32(half[j]);
+      }
+    } else if (e.dtype == 2) {
+      ts[i] = make(e.shape, e.ndim, false);
+      ok = ts[i] && read_raw(e, raw) && raw.size() * 2 >= (size_t)ts[i]->size;
+      if (!ok) break;
+      // the scales: next entry, named "<name>.scales", fp32 or bf16
+      std::vector<float> scales;
+      const std::string want = std::string(e.name) + ".scales";
+      if (i + 1 < n) {
+        cg_tensor_entry& se = dir[i + 1];
+        se.name[63] = 0;
+        std::vector<unsigned char> sraw;
+        if (want == se.name && (se.dtype == 0 || se.dtype == 1) && read_raw(se, sraw)) {
+          const size_t cnt = sraw.size() / (se.dtype == 0 ? 4 : 2);
+          scales.resize(cnt);
+          for (size_t j = 0; j < cnt; ++j) {
+            if (se.dtype == 0) std::memcpy(&scales[j], sraw.data() + 4 * j, 4);
+            else { uint16_t h16; std::memcpy(&h16, sraw.data() + 2 * j, 2); scales[j] = cg_bf16_to_fp32(h16); }
+          }
+        }
+      }
+      const long long cnt = ts[i]->size;
+      ok = !scales.empty() || cnt == 0;
+      if (!ok) break;
+      const long long group = cnt == 0 ? 1 : (cnt + (long long)scales.size() - 1) / (long long)scales.size();
+      for (long long j = 0; j < cnt; ++j) {
+        const unsigned char byte = raw[(size_t)(j >> 1)];
+        int q = (j & 1) ? (byte >> 4) : (byte & 0xF);
+        if (q >= 8) q -= 16;
+        ts[i]->data[j] = (float)q * scales[(size_t)(j / group)];
+      }
+    } else if (e.dtype >= 16 && e.dtype <= 23) {
+      static const int width[8] = {8, 4, 1, 1, 8, 2, 2, 1};
+      const int w = width[e.dtype - 16];
+      ts[i] = make(e.shape, e.ndim, false);
+      ok = ts[i] && read_raw(e, raw) && raw.size() == (size_t)ts[i]->size * w;
+      for (int j = 0; ok && j < ts[i]->size; ++j) {
+        const unsigned char* p = raw.data() + (size_t)j * w;
+        float v = 0.0f;
+        switch (e.dtype) {
+          case 16: { int64_t x; std::memcpy(&x, p, 8); v = (float)x; break; }
+          case 17: { int32_t x; std::memcpy(&x, p, 4); v = (float)x; break; }
+          case 18: v = (float)*p; break;
+          case 19: v = *p ? 1.0f : 0.0f; break;
+          case 20: { double x; std::memcpy(&x, p, 8); v = (float)x; break; }
+          case 21: {   // IEEE half
+            uint16_t h16; std::memcpy(&h16, p, 2);
+            const int sgn = h16 >> 15, ex = (h16 >> 10) & 31, man = h16 & 1023;
+            if (ex == 0) v = std::ldexp((float)man, -24);
+            else if (ex == 31) v = man ? NAN : INFINITY;
+            else v = std::ldexp((float)(man | 1024), ex - 25);
+            if (sgn) v = -v;
+            break;
+          }
+          case 22: { int16_t x; std::memcpy(&x, p, 2); v = (float)x; break; }
+          default: v = (float)(signed char)*p; break;
+        }
+        ts[i]->data[j] = v;
+      }
+    } else {
+      int shape1[1] = {(int)e.size_bytes};
+      ts[i] = make(shape1, 1, false);
+      ok = ts[i] && read_raw(e, raw);
+      for (size_t j = 0; ok && j < raw.size(); ++j) ts[i]->data[j] = (float)raw[j];
     }
   }
   std::fclose(f);

@@ -337,8 +337,16 @@ CGK_API int cgk_ag_gemm(const cgk_gemm_args* pg, const cgk_ag_args* px, void* st
   if (x.n_copy_ctas > 0) {
     a.n_copy = x.n_copy_ctas;
   } else if (a.mc_gathered != nullptr) {
-    // each rank only reads its own shard (local) and issues one multicast store per 16 bytes
-    a.n_copy = 8;
+    // Each rank only reads its own shard (local) and issues one multicast store per 16 bytes;
+    // a CTA moves 15-20 GB/s that way.  Enough of them to finish in the longer of (the time
+    // the other ranks' shards need to come in at NVLink rate) and (half of the GEMM's time).
+    const double t_link = (double)(x.ranks - 1) * (double)a.shard_bytes / 700e9;
+    const double t_gemm = 2.0 * ga.M * (double)ga.N * ga.K / 1.0e15 +
+                          2.0 * ((double)ga.M * ga.N + (double)ga.M * ga.K) / 5.0e12;
+    const double t = t_link > 0.5 * t_gemm ? t_link : 0.5 * t_gemm;
+    a.n_copy = (int)((double)a.shard_bytes / (t * 15e9) + 0.999);
+    if (a.n_copy < 4) a.n_copy = 4;
+    if (a.n_copy > 24) a.n_copy = 24;
   } else if (x.ranks == 1) {
     a.n_copy = 8;
   } else {

@@ -1,11 +1,11 @@
-// Column sums without any allocation: see colsum_noalloc.h for who needs this.
+// Column sums without any allocation: see include/cogito_noalloc.h for who needs this.
 //
 // The partial sums that cgk_colsum_bf16 keeps in caller-provided scratch live here
 // in a fixed array in device memory that is part of the library image.  Host code
 // cannot use the array's name as an address (on the host the name is only a
 // stand-in for the symbol), so the address is looked up once per device with
 // cudaGetSymbolAddress and that pointer is what the kernels receive.
-#include "colsum_noalloc.h"
+#include "../../include/cogito_noalloc.h"
 
 #include <mutex>
 

@@ -107,11 +107,6 @@ static int launch_bwd(const cgk_flash_args& a, const FlashBwdDev& p, cudaStream_
 
 using namespace cgk;
 
-#ifdef CGK_FLASH_TIMING
-CGK_API int cgk_flash_bwd_times(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, cgk::g_flash_bwd_times, 64);
-}
-#endif
 
 // Needs args->delta (fp32 [B,Hq,Tq]) and args->dq_accum (fp32 [B,Tq,Hq,D]) as
 // scratch; dq_accum is zeroed here.  d_o must have the strides of o.

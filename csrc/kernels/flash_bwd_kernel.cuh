@@ -5,20 +5,6 @@
 
 namespace cgk {
 
-// Optional phase timers (build with -DCGK_FLASH_TIMING), first compute thread of CTA (0,0,0).
-#ifdef CGK_FLASH_TIMING
-__device__ long long g_flash_bwd_times[8];
-#define BT_DECL long long bt_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long bt_last = clock64();
-#define BT_COUNT(i) bt_[i] += 1;
-#define BT_MARK(i) { long long bt_now = clock64(); bt_[i] += bt_now - bt_last; bt_last = bt_now; }
-#define BT_FLUSH() if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 128) \
-  { for (int bt_i = 0; bt_i < 8; ++bt_i) g_flash_bwd_times[bt_i] = bt_[bt_i]; }
-#else
-#define BT_DECL
-#define BT_MARK(i)
-#define BT_COUNT(i)
-#define BT_FLUSH()
-#endif
 
 struct FlashBwdDev {
   int B, Hq, Hk, Tq, Tk;

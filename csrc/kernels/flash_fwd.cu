@@ -28,19 +28,6 @@
 
 namespace cgk {
 
-// Optional phase timers (build with -DCGK_FLASH_TIMING): the first softmax thread
-// of CTA (0,0,0) accumulates the cycles spent in each phase of the key loop.
-#ifdef CGK_FLASH_TIMING
-__device__ long long g_flash_fwd_times[8];
-#define FT_DECL long long ft_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long ft_last = clock64();
-#define FT_MARK(i) { long long ft_now = clock64(); ft_[i] += ft_now - ft_last; ft_last = ft_now; }
-#define FT_FLUSH() if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 128) \
-  { for (int ft_i = 0; ft_i < 8; ++ft_i) g_flash_fwd_times[ft_i] = ft_[ft_i]; }
-#else
-#define FT_DECL
-#define FT_MARK(i)
-#define FT_FLUSH()
-#endif
 
 struct FlashFwdDev {
   int B, Hq, Hk, Tq, Tk;
@@ -292,13 +279,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const float slope = p.alibi ? p.alibi[h] * 1.4426950408889634f : 0.0f;
     const int qk = qpos + off;                 // last visible key under the causal mask
     float m = -INFINITY, l = 0.0f;
-    FT_DECL
     bool ok = true;
     uint32_t it = 0;
     for (int j = lo; j < my_hi && ok; ++j, ++it) {
-      FT_MARK(7)
       if (!mbar_wait(s_full(t), it & 1u, dead, p.status, 1300 + t)) { ok = false; break; }
-      FT_MARK(0)
       tc_fence_after();
       const int k0 = j * C::BN;
       // does any element of this tile need masking?  (warp-uniform)
@@ -356,7 +340,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         mx = m0;
       }
-      FT_MARK(1)
       // keep a stale maximum unless it grew by more than 2^8
       float m_use = (mx > m + 8.0f) ? mx : m;
       if (m == -INFINITY) m_use = mx;
@@ -381,7 +364,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_st_wait();
         }
       }
-      FT_MARK(2)
       l *= alpha;
       m = m_use;
       const float m_sub = (m == -INFINITY) ? 0.0f : m;
@@ -408,11 +390,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       l += (s0 + s1) + (s2 + s3);
       fence_proxy_async_smem();
       tc_fence_before();
-      FT_MARK(3)
       mbar_arrive(p_ready(t));
-      FT_MARK(4)
     }
-    FT_FLUSH()
     // epilogue: O / l -> global, LSE
     const bool have = my_hi > lo;
     if (have && ok) {
@@ -490,11 +469,6 @@ static int launch_fwd(const cgk_flash_args& a, const FlashFwdDev& p, cudaStream_
 
 using namespace cgk;
 
-#ifdef CGK_FLASH_TIMING
-CGK_API int cgk_flash_fwd_times(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, cgk::g_flash_fwd_times, 64);
-}
-#endif
 
 CGK_API int cgk_flash_forward(const cgk_flash_args* pa, void* stream) {
   CGK_REQUIRE(pa, "cgk_flash_forward: null args");

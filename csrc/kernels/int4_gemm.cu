@@ -55,12 +55,6 @@ struct Int4Dev {
   int* status;
 };
 
-#ifdef CGK_INT4_TIMING
-__device__ unsigned long long int4_t[16];
-#define IT_STAMP(i) if (blockIdx.x == 0 && blockIdx.y == 0) int4_t[i] = globaltimer_ns();
-#else
-#define IT_STAMP(i)
-#endif
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -96,7 +90,6 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const Int4Dev g) {
   const uint32_t a_bytes = (uint32_t)g.a_rows * 128u;
 
   if (threadIdx.x == 0) {
-    IT_STAMP(0)
     for (int s = 0; s < MAX_A_STAGES; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), 1); }
     for (int s = 0; s < B_STAGES; ++s) { mbar_init(b_full(s), CONVERT_WARPS); mbar_init(b_empty(s), 1); }
     for (int s = 0; s < MAX_RAW_STAGES; ++s) { mbar_init(raw_full(s), 1); mbar_init(raw_empty(s), CONVERT_WARPS); }
@@ -110,7 +103,6 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const Int4Dev g) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  if (threadIdx.x == 0) { IT_STAMP(1) }
 
   if (warp == 0) {
     // A thread's bulk copies run one after the other (measured: ~0.43 us each, whatever the ring
@@ -149,8 +141,6 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const Int4Dev g) {
         if (!mbar_wait(a_full(sa), (i / a_stages) & 1, dead, g.status, 302) ||
             !mbar_wait(b_full(sb), (i / B_STAGES) & 1, dead, g.status, 303)) { ok = false; break; }
         tc_fence_after();
-        if (i == 0) { IT_STAMP(2) }
-        if (i == ksteps / 2) { IT_STAMP(3) }
 #pragma unroll
         for (int sub = 0; sub < SUB; ++sub) {
           const uint32_t a_addr = sA + (sa * SUB + sub) * a_bytes, b_addr = sB + (sb * SUB + sub) * B_BYTES;
@@ -163,7 +153,6 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const Int4Dev g) {
         umma_commit(b_empty(sb));
       }
       if (ok) umma_commit(acc_full);
-      IT_STAMP(4)
     }
   } else if (warp >= 4) {
     const int tid = threadIdx.x - 128;                 // 0 .. 32*CONVERT_WARPS-1
@@ -208,7 +197,6 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const Int4Dev g) {
     // Accumulator positions j..j+7 of a group of 8 are columns j + {0,4,1,5,2,6,3,7}.
     if (warp < 8 && ok && mbar_wait(acc_full, 0, dead, g.status, 306)) {
       tc_fence_after();
-      if (tid == 0) { IT_STAMP(5) }
       const int row = m0 + (warp & 3) * 32 + lane;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
@@ -243,7 +231,6 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const Int4Dev g) {
   }
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) { IT_STAMP(6) }
   if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem, BN); }
   if (g.splits > 1) {
     // the split that arrives last at the tile's counter turns the fp32 sums into the output
@@ -266,7 +253,6 @@ int4_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const Int4Dev g) {
       if (threadIdx.x == 0) g.counters[mt * n_tiles + nt] = 0;
     }
   }
-  if (threadIdx.x == 0) { IT_STAMP(7) }
 }
 
 // packed [K][N/2] bytes + scales (flat groups) -> tiles [N/128][K/64][4608]
@@ -289,14 +275,6 @@ __global__ void int4_tile_kernel(const uint8_t* __restrict__ packed, const float
 }
 }  // namespace
 
-#ifdef CGK_INT4_TIMING
-CGK_API int cgk_int4_times(long long* out, int reset) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, int4_t, sizeof(long long) * 16);
-  if (reset) { long long z[16] = {}; cudaMemcpyToSymbol(int4_t, z, sizeof(z)); }
-  return 0;
-}
-#endif
 CGK_API long long cgk_int4_tiles_bytes(int K, int N) { return (long long)(N / BN) * (K / BK) * RAW_BYTES; }
 // Reorders reference-format weights (packed [K, N/2] bytes, fp32 scales per flat group) into the
 // tile-major stream the GEMM reads.  group: a multiple of 64 with N % group == 0.

@@ -64,18 +64,6 @@ struct WaDev {
   int* status;
 };
 
-// Profiling build (-DCGK_WA_TIMING): thread 0 of CTA (0,0) sums the cycles between the marked points of
-// a step; cgk_int4_wa_times copies the sums out.
-#ifdef CGK_WA_TIMING
-__device__ long long wa_t[8];
-#define WT_DECL long long wt_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long wt0_ = clock64();
-#define WT_LAP(i) { const long long n_ = clock64(); wt_[i] += n_ - wt0_; wt0_ = n_; }
-#define WT_STORE if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) { for (int q_ = 0; q_ < 8; ++q_) wa_t[q_] = wt_[q_]; }
-#else
-#define WT_DECL
-#define WT_LAP(i)
-#define WT_STORE
-#endif
 
 __device__ __forceinline__ uint4 ldg_stream_16(const void* p) {     // read once: do not keep in L1
   uint4 v;
@@ -192,7 +180,6 @@ int4_wa_kernel(const WaDev g) {
     const uint32_t t_st = tmem_a + ((uint32_t)(quad * 32) << 16) + sub * 32;      // + stage * W_ACOLS + half * 16
     int s = 0;                                                       // stage of the step, and the parity its a_empty wait needs
     uint32_t par = 1;
-    WT_DECL
     for (int i0 = 0; i0 < ksteps && ok; i0 += W_PREFETCH) {
 #pragma unroll
       for (int d = 0; d < W_PREFETCH; ++d) {
@@ -201,9 +188,7 @@ int4_wa_kernel(const WaDev g) {
         // stage s (TMEM operand columns and the X' tile) was last read by the MMAs of step i - W_STAGES;
         // one thread polls, a hardware barrier releases the rest
         if (tid == 0) go_s[d & 1] = (int)mbar_wait(a_empty(s), par, dead, g.status, 330);
-        WT_LAP(0)
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        WT_LAP(1)
         if (!go_s[d & 1]) { ok = false; break; }
         tc_fence_after();
         // nibbles -> bf16 pairs -> 32 TMEM columns of this feature's lane
@@ -221,7 +206,6 @@ int4_wa_kernel(const WaDev g) {
           }
           tmem_st16(t_st + s * W_ACOLS + hh * 16, t);
         }
-        WT_LAP(2)
         if (i + W_PREFETCH < ksteps) load_w(d, i + W_PREFETCH);
         // X chunks: times the scale of their k, rounded to bf16, summed for the offset correction, stored swizzled
         uint8_t* xstage = gen + s * (WSUB * x_bytes);
@@ -239,19 +223,15 @@ int4_wa_kernel(const WaDev g) {
             *reinterpret_cast<uint4*>(xstage + xdst[j]) = o;
           }
         }
-        WT_LAP(3)
         if (i + 2 < ksteps) load_x(d & 1, i + 2);
         tmem_st_wait();
-        WT_LAP(4)
         fence_proxy_async_smem();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(a_full(s));
-        WT_LAP(5)
         if (++s == W_STAGES) { s = 0; par ^= 1; }
       }
     }
-    WT_STORE
   }
   // ---- row sums of x': a chunk's row is fixed per (thread, j); sum the 8 pieces of a row, then over the blocks
 #pragma unroll
@@ -352,12 +332,6 @@ int launch_wa(const WaDev& g, dim3 grid, int smem, cudaStream_t st) {
 }
 }  // namespace
 
-#ifdef CGK_WA_TIMING
-CGK_API int cgk_int4_wa_times(long long* out) {
-  cudaDeviceSynchronize();
-  return (int)cudaMemcpyFromSymbol(out, wa_t, sizeof(long long) * 8);
-}
-#endif
 CGK_API long long cgk_int4_wa_tiles_bytes(int K, int N) { return (long long)(N / WF) * (K / WK) * W_RAW; }
 // Reorders reference-format weights (packed [K, N/2] bytes, fp32 scales per flat group) into the
 // stream cgk_int4_wa_gemm reads.  group: a multiple of 128 that divides N.

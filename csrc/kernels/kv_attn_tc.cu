@@ -58,18 +58,6 @@ __device__ __forceinline__ uint4 kvt_convert(uint32_t w, __nv_bfloat162 s2) {
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-// Profiling build (-DCGK_KVT_TIMING): thread 0 of CTA (0,0,0) sums the cycles between the marked points
-// of a key block; cgk_kvt_times copies the sums out.
-#ifdef CGK_KVT_TIMING
-__device__ long long kvt_t[16];
-#define KT_DECL long long kt_[16] = {}; long long kt0_ = clock64();
-#define KT_LAP(i) { const long long n_ = clock64(); kt_[i] += n_ - kt0_; kt0_ = n_; }
-#define KT_STORE if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) { for (int q_ = 0; q_ < 16; ++q_) kvt_t[q_] = kt_[q_]; }
-#else
-#define KT_DECL
-#define KT_LAP(i)
-#define KT_STORE
-#endif
 
 template <int N>
 __device__ __forceinline__ void kvt_tmem_ld(uint32_t taddr, uint32_t (&r)[N]) {
@@ -165,14 +153,11 @@ kv_attention_tc_kernel(KvDev c, const __nv_bfloat16* __restrict__ q, int Tq, int
   uint32_t phase = 0;
   bool ok = true;
   if (k_begin < k_end) fetch(k_begin);
-  KT_DECL
   for (int kb = k_begin; kb < k_end && ok; kb += KVT_KB) {
     convert();
-    KT_LAP(0)
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
-    KT_LAP(1)
     if (tid == 0) {
       tc_fence_after();
 #pragma unroll
@@ -181,14 +166,11 @@ kv_attention_tc_kernel(KvDev c, const __nv_bfloat16* __restrict__ q, int Tq, int
                  make_smem_desc_sw128(sb + S::OFF_Q + (kk >> 2) * (NP * 128) + (kk & 3) * 32, 16, 1024), idesc_s, kk != 0);
       umma_commit(bar_s);
     }
-    KT_LAP(2)
     if (kb + KVT_KB < k_end) fetch(kb + KVT_KB);
-    KT_LAP(3)
     // one thread polls (a poll is a shared-memory access; 256 pollers would crowd out the work), a
     // block barrier releases the rest, who read that thread's verdict
     if (tid == 0) go[0] = mbar_wait(bar_s, phase, dead, status, 610);
     __syncthreads();
-    KT_LAP(4)
     ok = go[0] != 0;
     if (!ok) break;
     tc_fence_after();
@@ -203,7 +185,6 @@ kv_attention_tc_kernel(KvDev c, const __nv_bfloat16* __restrict__ q, int Tq, int
       s[j] = (key >= k_end || key > len - Tq + t) ? -INFINITY : __uint_as_float(sr[j]) * scale_log2;   // causal among the new tokens
       tsc[(half * CPT + j) * TS + kin] = s[j];                      // row-major copy: the keys of a row lie on the lanes here
     }
-    KT_LAP(5)
     __syncthreads();
     {
       // row maximum over the block's 128 keys by TPR threads (a warp-wide redux per row and thread cost
@@ -225,7 +206,6 @@ kv_attention_tc_kernel(KvDev c, const __nv_bfloat16* __restrict__ q, int Tq, int
       }
     }
     __syncthreads();
-    KT_LAP(6)
     float corr[CPT];
 #pragma unroll
     for (int j = 0; j < CPT; ++j) {
@@ -237,11 +217,9 @@ kv_attention_tc_kernel(KvDev c, const __nv_bfloat16* __restrict__ q, int Tq, int
       l_part[j] = l_part[j] * corr[j] + __bfloat162float(pb);
       *reinterpret_cast<__nv_bfloat16*>(sm + S::OFF_P + (kin >> 6) * (NP * 128) + sw128_offset(r, (kin & 63) >> 3) + (kin & 7) * 2) = pb;
     }
-    KT_LAP(7)
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
-    KT_LAP(8)
     if (tid == 0) {
       tc_fence_after();
 #pragma unroll
@@ -250,10 +228,8 @@ kv_attention_tc_kernel(KvDev c, const __nv_bfloat16* __restrict__ q, int Tq, int
                  make_smem_desc_sw128(sb + S::OFF_P + (kk >> 2) * (NP * 128) + (kk & 3) * 32, 16, 1024), idesc_o, kk != 0);
       umma_commit(bar_o);
     }
-    KT_LAP(9)
     if (tid == 0) go[1] = mbar_wait(bar_o, phase, dead, status, 611);
     __syncthreads();
-    KT_LAP(10)
     ok = go[1] != 0;
     if (!ok) break;
     tc_fence_after();
@@ -263,9 +239,7 @@ kv_attention_tc_kernel(KvDev c, const __nv_bfloat16* __restrict__ q, int Tq, int
 #pragma unroll
     for (int j = 0; j < CPT; ++j) acc[j] = acc[j] * corr[j] + __uint_as_float(orr[j]);
     phase ^= 1;
-    KT_LAP(11)
   }
-  KT_STORE
   // row sums across the 128 keys of every block, then this split's partial
 #pragma unroll
   for (int j = 0; j < CPT; ++j) {
@@ -303,12 +277,6 @@ cudaError_t launch_np(const KvDev& c, const __nv_bfloat16* q, int Tq, int Hq, fl
 }
 }  // namespace
 
-#ifdef CGK_KVT_TIMING
-extern "C" int cgk_kvt_times(long long* out) {
-  cudaDeviceSynchronize();
-  return (int)cudaMemcpyFromSymbol(out, kvt_t, sizeof(long long) * 16);
-}
-#endif
 cudaError_t launch_kv_attention_tc(const KvDev& c, const __nv_bfloat16* q, int Tq, int Hq, float scale, int splits,
                                    float* part_acc, float* part_ml, int* status, cudaStream_t stream) {
   const int R = Tq * (Hq / c.heads);

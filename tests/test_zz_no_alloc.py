@@ -5,9 +5,7 @@ Some users of the kernel library cannot allocate device memory when they call it
 must not enter the allocator), so ``cgk_colsum_bf16_noalloc`` keeps its scratch
 inside the library.  This test calls it through its exported C symbol, twice in a
 row, and checks each result against the ordinary entry point (which takes
-caller-provided scratch) within the tolerance used for the other reductions.
-It is collected last so that a run stopping at the first failure has already run
-everything else."""
+caller-provided scratch) within the tolerance used for the other reductions."""
 import ctypes
 
 import pytest
