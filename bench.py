@@ -18,7 +18,13 @@ host->device copy of the batch from pinned memory and a device->host read of the
 with no Python packaging and no runnable transformer path) cannot be installed, so
 that arm prints its `unavailable` line.  `--impl torch` runs the same model with
 PyTorch library kernels (cuBLAS + SDPA + NCCL), the comparison point named for the
-configs the reference cannot run.
+configs the reference cannot run: tensor parallel over the N ranks as all-gather ->
+GEMM and GEMM -> reduce-scatter with NCCL collectives, the reference's unfused design.
+
+The default arm measures that baseline too, in the same process right after its own
+timed regions (same N, same batch, same warm-up; `--baseline-steps` timed steps), and
+reports `vs_baseline` = value / baseline value, with the baseline's own numbers under
+`baseline`.
 """
 from __future__ import annotations
 
@@ -48,6 +54,9 @@ def parse():
     ap.add_argument("--layers", type=int, default=12)
     ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"])
     ap.add_argument("--no-alt", action="store_true", help="with several GPUs, skip the extra data-parallel measurement")
+    ap.add_argument("--baseline-steps", type=int, default=-1,
+                    help="timed steps of the PyTorch-library baseline measured in the same run (-1 = min(steps, 5), "
+                         "0 = skip it and leave vs_baseline null)")
     ap.add_argument("--timeline", default="", help="after the timed regions, trace two more steps and write the device "
                     "time per kernel name (rank 0) to this JSON file; not part of any reported number")
     args = ap.parse_args()
@@ -210,6 +219,40 @@ def main():
     if args.timeline:
         kernel_timeline(step_device, args.timeline, rank, barrier)
 
+    # The comparison point: the identical configuration on PyTorch library kernels (NCCL + cuBLAS +
+    # SDPA + fused AdamW), measured here and now so that both numbers come from the same GPUs.
+    baseline = None
+    nb = min(args.steps, 5) if args.baseline_steps < 0 else args.baseline_steps
+    if args.impl == "cogito" and nb > 0:
+        try:
+            import copy
+            import gc
+            job = None
+            loss_box[0] = None
+            gc.collect()
+            torch.cuda.empty_cache()
+            ab = copy.copy(args)
+            ab.impl = "torch"
+            if ab.parallelism == "dp":
+                ab.micro_batch = max(1, B // world)
+            jobb = build_job(ab, rank, world, dev)
+
+            def step_base():
+                loss_box[0] = jobb.step(dev_ids, dev_tg)
+
+            for _ in range(3):
+                step_base()
+            msb = timed(step_base, nb) / nb
+            baseline = {"impl": "torch: NCCL collectives + cuBLAS + SDPA + fused AdamW, " + f"{args.parallelism}{world}",
+                        "value": tokens_per_step / (msb * 1e-3), "unit": "tokens/s", "ms_per_step": msb, "steps": nb,
+                        "warmup": 3, "final_loss": float(loss_box[0])}
+            jobb = None
+            loss_box[0] = None
+            gc.collect()
+            torch.cuda.empty_cache()
+        except Exception as e:
+            baseline = {"error": repr(e)[:300]}
+
     # The named configuration is tensor parallel; the same model and batch under data parallelism (the
     # fused all-reduce + Adam kernel) is measured as well and reported beside it under "alt".
     alt = None
@@ -243,7 +286,8 @@ def main():
         out = {
             "metric": "train tok/s/box (GPT-2-small, whole job)", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": (value / baseline["value"]) if baseline and "value" in baseline else None, "dtype": "bf16",
             "data": "synthetic (uniform token ids, N(0,0.02) weights)", "impl": args.impl,
             "config": {"model": "gpt2-small", "layers": args.layers, "d_model": 768, "heads": 12, "mlp": 3072,
                        "vocab": 50304, "global_batch": B, "seq_len": T, "micro_batch": args.micro_batch,
@@ -251,10 +295,14 @@ def main():
                        "l2": "inputs larger than L2: each step streams >10 GB of activations and weights"},
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+                    # every rank copies the whole global batch (ids and targets, int64): under tensor
+                    # parallelism each rank needs all tokens; the figure is per rank
                     "h2d_bytes_per_step": host_ids.numel() * 8 + host_tg.numel() * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "final_loss": final_loss,
             "model_tflops_per_gpu": flops_per_token * value / world / 1e12,
         }
+        if baseline is not None:
+            out["baseline"] = baseline
         if alt is not None:
             out["alt"] = alt
         print(json.dumps(out))

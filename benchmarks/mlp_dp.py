@@ -9,7 +9,9 @@ uniform labels, 256 samples per GPU and step (weak scaling).  With several GPUs 
 fused gradient all-reduce + unscale + Adam kernel over NVLink peer memory.  The step is a dozen small
 kernels, so it is also timed as a CUDA-graph replay on one GPU (the multi-GPU step waits on peers inside
 the kernel and is launched directly).  One JSON line from rank 0: samples/s over all GPUs, device time,
-max over ranks.
+max over ranks.  The same configuration on PyTorch library code (DistributedDataParallel over NCCL,
+bf16 autocast, torch.amp.GradScaler from 2^16, torch.optim.Adam) is timed in the same run and reported
+under "baseline", with "vs_baseline" = value / baseline value.
 """
 from __future__ import annotations
 
@@ -94,6 +96,28 @@ def main():
             graph_ms = timed(graph.replay, args.steps)
         except Exception as e:                          # the eager number above stands
             print(f"step not captured: {e!r}", file=sys.stderr)
+    # ---- the same job on PyTorch library code ----
+    base_ms = None
+    try:
+        tm = torch.nn.Sequential(torch.nn.Linear(784, 512), torch.nn.ReLU(), torch.nn.Linear(512, 512), torch.nn.ReLU(),
+                                 torch.nn.Linear(512, 10)).to(dev)
+        ddp = torch.nn.parallel.DistributedDataParallel(tm, device_ids=[dev.index]) if world > 1 else tm
+        topt = torch.optim.Adam(tm.parameters(), lr=1e-3, fused=True)
+        tscaler = torch.amp.GradScaler("cuda", init_scale=65536.0)
+
+        def tstep():
+            topt.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                l = torch.nn.functional.cross_entropy(ddp(x).float(), y)
+            tscaler.scale(l).backward()
+            tscaler.step(topt)
+            tscaler.update()
+
+        for _ in range(max(3, args.warmup)):
+            tstep()
+        base_ms = timed(tstep, args.steps)
+    except Exception as e:
+        print(f"baseline failed: {e!r}", file=sys.stderr)
     if rank == 0:
         best = min(ms, graph_ms) if graph_ms else ms
         print(json.dumps({
@@ -101,6 +125,9 @@ def main():
             "unit": "samples/s", "n_gpus": world, "steps": args.steps, "ms_per_step": round(ms, 4),
             "ms_per_step_cuda_graph": None if graph_ms is None else round(graph_ms, 4), "scaling": "weak",
             "launches_per_step": launches, "loss": float(loss[0]), "loss_scale": scaler.sync()["scale"],
+            "baseline": None if base_ms is None else {"impl": "torch DDP (NCCL) + autocast bf16 + GradScaler + fused Adam",
+                                                      "value": round(world * args.batch / base_ms * 1e3, 1), "ms_per_step": round(base_ms, 4)},
+            "vs_baseline": None if base_ms is None else round(base_ms / best, 3),
             "config": {"model": "784-512-512-10", "batch_per_gpu": args.batch, "dtype": "bf16", "optimizer": "adam 1e-3",
                        "loss_scale_init": 65536, "parallelism": f"dp{world}", "data": "synthetic"}}), flush=True)
     if world > 1:

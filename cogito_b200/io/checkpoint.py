@@ -174,10 +174,10 @@ def dp_shard_path(base: str, rank: int, ranks: int) -> str:
 
 def save_dp_optimizer_shard(base: str, opt) -> str:
     """Write this data-parallel rank's optimizer shard (``DPFusedAdam.shard_state``): Adam moments,
-    fp32 master slice, position in the flat vector, step and loss-scale state."""
+    fp32 master weights, the parts of the flat vector they belong to, step and loss-scale state."""
     sh = opt.shard_state()
     tensors = {k: sh[k] for k in ("m", "v", "master") if sh.get(k) is not None}
-    meta = {k: sh[k] for k in ("begin", "count", "n", "ranks")}
+    meta = {k: sh[k] for k in ("segments", "n", "ranks")}
     meta["scaler"] = sh["scaler"]
     tensors["meta.json"] = torch.from_numpy(np.frombuffer(json.dumps(meta).encode(), dtype=np.uint8).astype(np.float32))
     path = dp_shard_path(base, opt.rank, opt.ranks)

@@ -201,6 +201,28 @@ class ModelParallelStats:
         dist.all_reduce(norm_sq, op=dist.ReduceOp.SUM, group=self.ctx.mp_group)
 
 
+class ReplicaStatsDP:
+    """The same for the fused data-parallel optimizer: its bucket kernels leave (sum of squares,
+    overflow) of the parts of the DATA-PARALLEL-SUMMED gradient that this rank owns; the sum over
+    every rank of the job (data-, tensor- and pipeline-parallel) is what the whole model sees.
+    Replicated parameters (flat positions below ``n_rep``) are counted on tensor-parallel rank 0 only."""
+
+    def __init__(self, ctx, opt, n_rep: int):
+        self.ctx, self.opt, self.n_rep = ctx, opt, n_rep
+
+    def __call__(self, local: torch.Tensor) -> torch.Tensor:
+        st = local.clone()
+        c = self.ctx.coords
+        if c.tp > 1 and self.n_rep and c.tp_rank != 0:
+            for b, cnt, off in self.opt.segments:
+                hi = min(b + cnt, self.n_rep)
+                if hi > b:
+                    g = torch.nan_to_num(self.opt.gsum[off:off + hi - b], nan=0.0, posinf=0.0, neginf=0.0)
+                    st[0] -= (g * g).sum()
+        dist.all_reduce(st)
+        return st.contiguous()
+
+
 class Trainer3D:
     """One rank of a DP x TP x PP job.  ``step(ids, targets)`` takes this data-parallel replica's
     batch [M * micro_batch, T] (every rank of the replica passes the same tensors) and runs M
@@ -234,19 +256,23 @@ class Trainer3D:
         kw = dict(lr=lr, scaler=self.scaler, max_grad_norm=max_grad_norm, weight_decay=weight_decay)
         # Loss scaling and norm clipping decide per step from statistics of the WHOLE replica (all tp x pp
         # ranks): an overflow seen on one pipeline stage must skip the step on every stage.  The fused
-        # all-reduce + Adam kernel takes its statistics inside the kernel, over the data-parallel ranks of
-        # one (tp, pp) coordinate only, so it is used when neither is on (or the replica is one rank);
-        # otherwise gradients are averaged over the data-parallel group with one all-reduce and FusedAdam
-        # steps with the replica-wide statistics.
+        # data-parallel optimizer computes its statistics over the data-parallel ranks of one (tp, pp)
+        # coordinate; with model parallelism on top they are summed over all ranks of the job between
+        # its reduce kernels and its update kernel (ReplicaStatsDP), on the GPU, and the update kernel
+        # takes the agreed pair instead of its own exchange.  CPU ranks (gloo) average the gradients with
+        # one all-reduce and step FusedAdam with the replica-wide statistics.
         need_replica_stats = c.tp * c.pp > 1 and (loss_scale is not None or max_grad_norm > 0)
-        self._dp_allreduce = c.dp > 1 and need_replica_stats
-        self.opt = DPFusedAdam(params, ctx.dp_group, **kw) if (c.dp > 1 and not need_replica_stats) else FusedAdam(params, **kw)
+        fused_dp = c.dp > 1 and (cuda or not need_replica_stats)
+        self._dp_allreduce = c.dp > 1 and not fused_dp
+        self.opt = DPFusedAdam(params, ctx.dp_group, **kw) if fused_dp else FusedAdam(params, **kw)
         self.n_rep = 0
         for p, o in zip(self.opt.fp.params, self.opt.fp.offsets):
             if getattr(p, "tp_replicated", False):
                 self.n_rep = o + (p.numel() + 7) // 8 * 8
         if c.tp * c.pp > 1 and isinstance(self.opt, FusedAdam):
             self.opt.stats_sync = ModelParallelStats(ctx, self.opt, self.n_rep)
+        if need_replica_stats and isinstance(self.opt, DPFusedAdam):
+            self.opt.ext_stats_fn = ReplicaStatsDP(ctx, self.opt, self.n_rep)
         act_dtype = torch.bfloat16 if cuda else torch.float32
         if V == 1:
             self.pipe = PipelineExecutor(c.pp_rank, c.pp, num_microbatches, ctx.prev_stage, ctx.next_stage,

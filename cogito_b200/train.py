@@ -57,6 +57,8 @@ class Trainer:
             else:
                 gs = 1.0 / n_micro
             loss = self.model(ids[sl], targets[sl], grad_scale=gs)
+            if i == n_micro - 1 and hasattr(self.opt, "arm"):
+                self.opt.arm()           # last backward pass of the step: gradient buckets may leave as they fill
             loss.backward()
             d = loss.detach()
             total = d if total is None else total + d

@@ -25,28 +25,54 @@
 
 namespace cgk {
 
-// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; one warp per row.
-__global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
-                                   float* __restrict__ delta, int B, int H, int T, int D,
-                                   long long o_bs, long long o_ts, long long o_hs, long long do_bs,
-                                   long long do_ts, long long do_hs) {
-  const long long total = (long long)B * H * T;
-  const int lane = threadIdx.x & 31;
-  for (long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < total;
-       w += ((long long)gridDim.x * blockDim.x) >> 5) {
-    const int t = (int)(w % T);
-    const int h = (int)((w / T) % H);
-    const int b = (int)(w / ((long long)T * H));
-    const __nv_bfloat16* o = O + b * o_bs + t * o_ts + h * o_hs;
-    const __nv_bfloat16* d = dO + b * do_bs + t * do_ts + h * do_hs;
-    float s = 0.0f;
-    for (int c = lane * 2; c < D; c += 64) {
-      float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(o + c));
-      float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(d + c));
-      s += a.x * g.x + a.y * g.y;
+// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d].  A row of D elements is shared by D / 8
+// lanes (one 16-byte load of each tensor per lane); every thread works on four rows at a time so
+// that eight loads are in flight, which is what a streaming kernel needs to approach HBM rate.
+template <int D>
+__global__ void __launch_bounds__(256)
+flash_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
+                   float* __restrict__ delta, int B, int H, int T,
+                   long long o_bs, long long o_ts, long long o_hs, long long do_bs,
+                   long long do_ts, long long do_hs) {
+  constexpr int LPR = D / 8;                 // lanes per row
+  constexpr int U = 4;
+  const long long rows = (long long)B * T * H;            // row r = (b * T + t) * H + h
+  const long long groups = (long long)gridDim.x * blockDim.x / LPR;
+  const long long g0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LPR;
+  const int c = ((int)threadIdx.x % LPR) * 8;
+  for (long long r0 = g0; r0 < rows; r0 += groups * U) {
+    uint4 a[U], g[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long r = r0 + u * groups;
+      if (r < rows) {
+        const int h = (int)(r % H);
+        const long long bt = r / H;
+        const int t = (int)(bt % T);
+        const long long b = bt / T;
+        a[u] = __ldg(reinterpret_cast<const uint4*>(O + b * o_bs + t * o_ts + h * o_hs + c));
+        g[u] = __ldg(reinterpret_cast<const uint4*>(dO + b * do_bs + t * do_ts + h * do_hs + c));
+      }
     }
-    s = warp_sum(s);
-    if (lane == 0) delta[((long long)b * H + h) * T + t] = s;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long r = r0 + u * groups;
+      float s = 0.0f;
+      if (r < rows) {
+        float2 x, y;
+        x = unpack_bf16x2(a[u].x); y = unpack_bf16x2(g[u].x); s += x.x * y.x + x.y * y.y;
+        x = unpack_bf16x2(a[u].y); y = unpack_bf16x2(g[u].y); s += x.x * y.x + x.y * y.y;
+        x = unpack_bf16x2(a[u].z); y = unpack_bf16x2(g[u].z); s += x.x * y.x + x.y * y.y;
+        x = unpack_bf16x2(a[u].w); y = unpack_bf16x2(g[u].w); s += x.x * y.x + x.y * y.y;
+      }
+#pragma unroll
+      for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (r < rows && (threadIdx.x % LPR) == 0) {
+        const int h = (int)(r % H);
+        const long long bt = r / H;
+        delta[((bt / T) * H + h) * T + (bt % T)] = s;
+      }
+    }
   }
 }
 
@@ -119,18 +145,26 @@ CGK_API int cgk_flash_backward(const cgk_flash_args* pa, void* stream) {
   CGK_REQUIRE(a.Hq % a.Hk == 0, "cgk_flash_backward: Hq must be a multiple of Hk");
   CGK_REQUIRE((a.dq_hs | a.dq_ts | a.dq_bs | a.dk_hs | a.dk_ts | a.dk_bs | a.dv_hs | a.dv_ts | a.dv_bs) % 8 == 0,
               "cgk_flash_backward: gradient strides must be multiples of 8 elements");
+  CGK_REQUIRE((a.o_hs | a.o_ts | a.o_bs) % 8 == 0 && (((uintptr_t)a.o | (uintptr_t)a.d_o) & 15) == 0,
+              "cgk_flash_backward: O and dO must be 16-byte aligned with strides that are multiples of 8 elements");
   if (a.B == 0 || a.Tq == 0 || a.Hq == 0 || a.Tk == 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   int dev = 0;
   CGK_CUDA_CHECK(cudaGetDevice(&dev));
   const long long rows = (long long)a.B * a.Hq * a.Tq;
   {
-    long long blocks = (rows * 32 + 255) / 256;
-    long long cap = (long long)sm_count(dev) * 16;
+    long long blocks = (rows * (a.D / 8) + 256 * 4 - 1) / (256 * 4);
+    long long cap = (long long)sm_count(dev) * 8;
     if (blocks > cap) blocks = cap;
-    flash_delta_kernel<<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)a.o, (const __nv_bfloat16*)a.d_o,
-                                                    a.delta, a.B, a.Hq, a.Tq, a.D, a.o_bs, a.o_ts, a.o_hs,
-                                                    a.o_bs, a.o_ts, a.o_hs);
+    if (blocks < 1) blocks = 1;
+    if (a.D == 64)
+      flash_delta_kernel<64><<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)a.o, (const __nv_bfloat16*)a.d_o,
+                                                          a.delta, a.B, a.Hq, a.Tq, a.o_bs, a.o_ts, a.o_hs,
+                                                          a.o_bs, a.o_ts, a.o_hs);
+    else
+      flash_delta_kernel<128><<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)a.o, (const __nv_bfloat16*)a.d_o,
+                                                           a.delta, a.B, a.Hq, a.Tq, a.o_bs, a.o_ts, a.o_hs,
+                                                           a.o_bs, a.o_ts, a.o_hs);
     CGK_LAUNCH_CHECK();
   }
   CGK_CUDA_CHECK(cudaMemsetAsync(a.dq_accum, 0, (size_t)rows * a.D * sizeof(float), st));

@@ -105,32 +105,52 @@ int cgk_gemm_rs(const cgk_gemm_args* g, const cgk_rs_args* x, void* stream);
 /* By how much one cgk_gemm_rs call with M rows advances *queue on the current device. */
 int cgk_gemm_rs_queue_step(int M, int ranks, int max_ctas);
 
-/* ---- Fused data-parallel optimizer step (csrc/comm/dp_adam.cu) ------------------ */
-/* Pointer tables are indexed by rank (peer mappings of symmetric memory).  This rank
- * owns elements [begin, begin + count) of the flat parameter space. */
+/* ---- Fused data-parallel optimizer step in buckets (csrc/comm/dp_adam.cu) --------- */
+/* The flat parameter space [0, n) is cut into buckets of bucket_len elements (the last may be
+ * shorter; n and bucket_len are multiples of 8 * ranks).  Inside bucket b of length len_b rank r
+ * owns [b * bucket_len + r * len_b / ranks, + len_b / ranks); its reduced gradients, Adam moments
+ * and fp32 master weights are stored bucket after bucket (n / ranks elements in all).  Pointer
+ * tables are indexed by rank (peer mappings of symmetric memory). */
+#define CGK_DP_MAX_BUCKETS 64
+#define CGK_DP_MAX_CTAS 1024
 typedef struct {
-  int32_t rank, ranks, epoch;      /* epoch > 0, +1 per call */
-  int32_t grid_ctas;               /* CTAs to launch, <= SM count (all must be resident) */
+  int32_t rank, ranks;
+  int32_t epoch;                   /* > 0, the same for all buckets of a step, +1 per step */
+  int32_t bucket;                  /* index of the bucket */
+  int32_t grid_ctas;               /* CTAs of this launch (a few: it runs beside the backward pass) */
   const void* grad_ptrs[8];        /* fp32 flat gradients of every rank */
+  void* signal_ptrs[8];            /* cgk_dp_signal_bytes(ranks) bytes per rank, zero before the first call */
+  float* gsum;                     /* local out: reduced gradients of the owned part of this bucket */
+  int64_t begin, count;            /* the owned part: flat offset and length */
+  float* block_part;               /* local scratch [2 * grid_ctas] for this bucket */
+  void* arrive;                    /* local uint32 counter for this bucket, zero before the first call */
+  float* stats;                    /* local out [2]: sum of squares and overflow flag of the owned part */
+} cgk_dp_bucket_args;
+
+typedef struct {
+  int32_t rank, ranks, epoch, nbuckets;
+  int32_t grid_ctas;               /* 0 = default */
   void* param_lp_ptrs[8];          /* bf16 flat parameters of every rank, or all null */
   void* param_fp_ptrs[8];          /* fp32 flat parameters of every rank (used when no bf16 copy) */
-  void* signal_ptrs[8];            /* int32[64] per rank, zero before the first call */
-  float* master;                   /* local fp32 master slice [count], or null */
-  float* m; float* v;              /* local Adam moments [count] */
-  float* gsum;                     /* local scratch [count] */
-  int64_t begin, count;
+  void* signal_ptrs[8];
+  float* master;                   /* local fp32 master weights of the owned parts [n / ranks], or null */
+  float* m; float* v;              /* local Adam moments [n / ranks] */
+  const float* gsum;               /* local reduced gradients [n / ranks] (from cgk_dp_bucket_reduce) */
+  int64_t n, bucket_len;
   float lr, beta1, beta2, eps, weight_decay, max_grad_norm;
   float grad_mul;                  /* multiplies the summed gradient (1/ranks = mean) */
   float growth, backoff, min_scale, max_scale;
   int32_t window;
   void* scaler;                    /* local scaler state (cgk_scaler_state_bytes) */
-  float* block_part;               /* local scratch [2 * grid_ctas] */
-  void* grid_bar;                  /* local uint32 counter, zero before the first call */
-  uint32_t grid_bar_base;          /* 2 * grid_ctas * (number of earlier calls) */
-} cgk_dp_adam_args;
+  const float* bucket_stats;       /* local [nbuckets][2], written by cgk_dp_bucket_reduce */
+  const float* ext_stats;          /* device {sum of squares, overflow} agreed by a larger group (tensor /
+                                      pipeline parallel replica), or null: the group of this call decides */
+  void* arrive;                    /* local uint32 counter, zero before the first call */
+} cgk_dp_finish_args;
 
-int cgk_dp_adam_step(const cgk_dp_adam_args* args, void* stream);
-int cgk_dp_adam_max_ctas(void);
+int cgk_dp_bucket_reduce(const cgk_dp_bucket_args* args, void* stream);
+int cgk_dp_adam_finish(const cgk_dp_finish_args* args, void* stream);
+int cgk_dp_signal_bytes(int ranks);
 
 /* Tensor-parallel serving: x[t,:] += sum over ranks of partial_p[t,:], then (w given)
  * h = rmsnorm(x) * w, in one launch over peer memory (one-shot all-reduce, sums in rank order).

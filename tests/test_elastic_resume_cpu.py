@@ -51,7 +51,8 @@ def _worker(rank, world, port, base, mode, q):
         xs, ys = _data()
         if mode == "resume":
             load_model(base + ".cog", model)
-        opt = DPFusedAdam(model.parameters(), group=dist.group.WORLD, lr=5e-2, weight_decay=0.01, max_grad_norm=1.0)
+        opt = DPFusedAdam(model.parameters(), group=dist.group.WORLD, lr=5e-2, weight_decay=0.01, max_grad_norm=1.0,
+                          bucket_elems=96 * world)          # bucket boundaries move with the group size
         if mode == "resume":
             old = load_dp_optimizer_resharded(base, opt)
             assert old == 3

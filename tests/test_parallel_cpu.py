@@ -102,7 +102,8 @@ def _dp_worker(rank, world, port, q):
         ref, dp = mk(), mk()
         dp.load_state_dict(ref.state_dict())
         o_ref = FusedAdam(ref.parameters(), lr=1e-2, master_weights=False)
-        o_dp = DPFusedAdam(dp.parameters(), dist.group.WORLD, lr=1e-2)
+        o_dp = DPFusedAdam(dp.parameters(), dist.group.WORLD, lr=1e-2, bucket_elems=64)    # several buckets, the last one short
+        assert o_dp.nbuckets > 2 and sum(c for _, c, _ in o_dp.segments) == o_dp.n // world
         g = torch.Generator().manual_seed(3)
         X = torch.randn(8, 12, generator=g)
         Y = torch.randint(0, 4, (8,), generator=g)
@@ -131,3 +132,56 @@ def test_dp_fused_adam_matches_full_batch_on_two_cpu_ranks():
         assert p.exitcode == 0
     for rank, diff in res:
         assert diff < 1e-5, (rank, diff)
+
+
+def _torch_tp_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import types
+        from cogito_b200 import bench_support as bs
+        from cogito_b200.models.gpt2 import GPT2Config
+        torch.manual_seed(0)
+        cfg = GPT2Config(vocab_size=64, n_layer=2, d_model=32, n_head=4, d_ff=64, max_seq_len=16)
+        # one unsplit model; every rank cuts its shard out of it
+        ref = bs._TorchTPGPT2(cfg, 0, 1, None)
+        tp = bs._TorchTPGPT2(cfg, rank, world, dist.group.WORLD)
+        hd, hl, fl, vl = 8, 4 // world, 64 // world, 64 // world
+        with torch.no_grad():
+            tp.wte.copy_(ref.wte[rank * vl:(rank + 1) * vl]); tp.wpe.copy_(ref.wpe)
+            for a, b in zip(ref.blocks, tp.blocks):
+                wq = a.qkv.weight.view(3, 4, hd, 32)[:, rank * hl:(rank + 1) * hl]
+                b.qkv.weight.copy_(wq.reshape(3 * hl * hd, 32))
+                b.qkv.bias.copy_(a.qkv.bias.view(3, 4, hd)[:, rank * hl:(rank + 1) * hl].reshape(-1))
+                b.proj.weight.copy_(a.proj.weight[:, rank * hl * hd:(rank + 1) * hl * hd])
+                b.up.weight.copy_(a.up.weight[rank * fl:(rank + 1) * fl]); b.up.bias.copy_(a.up.bias[rank * fl:(rank + 1) * fl])
+                b.down.weight.copy_(a.down.weight[:, rank * fl:(rank + 1) * fl])
+        g = torch.Generator().manual_seed(1)
+        ids = torch.randint(0, 64, (4, 16), generator=g)
+        tg = torch.randint(0, 64, (4, 16), generator=g)
+        l_ref, l_tp = ref(ids, tg), tp(ids, tg)
+        l_ref.backward(); l_tp.backward()
+        gq_ref = ref.blocks[0].qkv.weight.grad.view(3, 4, hd, 32)[:, rank * hl:(rank + 1) * hl].reshape(3 * hl * hd, 32)
+        q.put((rank, float(l_ref), float(l_tp), float((gq_ref - tp.blocks[0].qkv.weight.grad).abs().max()),
+               float(gq_ref.abs().max())))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_torch_tensor_parallel_baseline_of_the_bench_matches_its_unsplit_form():
+    """The comparison arm of bench.py (NCCL-style collectives + library GEMMs) computes the same
+    loss and gradients as the same model on one rank."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_torch_tp_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in range(world)]
+    for p in procs:
+        p.join(30)
+    for rank, l_ref, l_tp, gerr, gmax in res:
+        assert abs(l_ref - l_tp) < 1e-4 * max(1.0, abs(l_ref)), res
+        assert gerr < 1e-4 * max(gmax, 1e-3), res
