@@ -17,6 +17,7 @@ from ..ops import functional as F
 from ..ops import loss as L
 from ..ops import misc as M
 from ..utils import rng
+from ..utils.recompute import checkpoint
 
 
 @dataclass
@@ -28,6 +29,7 @@ class GPT2Config:
     d_ff: int = 3072
     max_seq_len: int = 2048
     init_std: float = 0.02
+    recompute: bool = False        # drop the activations inside every block and recompute them in backward
     norm_eps: float = 1e-5
 
     def block_config(self) -> TransformerConfig:
@@ -52,7 +54,7 @@ class GPT2(nn.Module):
     def hidden(self, ids: torch.Tensor) -> torch.Tensor:
         x = M.embedding(ids, self.wte, self.wpe)
         for blk in self.blocks:
-            x = blk(x)
+            x = checkpoint(blk, x) if self.cfg.recompute else blk(x)
         return self.ln_f(x)
 
     def forward(self, ids: torch.Tensor, targets: torch.Tensor | None = None, grad_scale: float = 1.0):

@@ -19,6 +19,7 @@ from ..nn.transformer import TransformerBlock, TransformerConfig
 from ..ops import loss as L
 from ..ops import misc as M
 from ..utils import rng
+from ..utils.recompute import checkpoint
 
 
 @dataclass
@@ -33,6 +34,7 @@ class LlamaConfig:
     rope_theta: float = 10000.0
     norm_eps: float = 1e-5
     init_std: float = 0.02
+    recompute: bool = False        # drop the activations inside every block and recompute them in backward
 
     @property
     def head_dim(self) -> int:
@@ -72,7 +74,7 @@ class Llama(nn.Module):
     def hidden(self, ids: torch.Tensor) -> torch.Tensor:
         x = M.embedding(ids, self.wte, None)
         for blk in self.blocks:
-            x = blk(x)
+            x = checkpoint(blk, x) if self.cfg.recompute else blk(x)
         return self.norm_f(x)
 
     def forward(self, ids: torch.Tensor, targets: torch.Tensor | None = None, grad_scale: float = 1.0):

@@ -54,6 +54,8 @@ def _declare(L: ctypes.CDLL) -> None:
         "cgk_ce_backward": [vp, vp, ll, vp, vp, i, i, ll, f, vp, ll, vp],
         "cgk_softmax_rows": [vp, vp, i, i, f, vp],
         "cgk_softmax_rows_backward": [vp, vp, vp, i, i, vp],
+        "cgk_softmax_dropout_residual": [i, vp, vp, vp, vp, i, i, f, c_ulonglong, vp],
+        "cgk_softmax_dropout_residual_backward": [i, vp, vp, vp, vp, i, i, f, c_ulonglong, vp],
         "cgk_scaler_init": [vp, f, vp],
         "cgk_grad_stats": [vp, ll, vp, vp, i, vp],
         "cgk_adam_step": [vp, vp, vp, vp, vp, ll, f, f, f, f, f, f, vp, vp],

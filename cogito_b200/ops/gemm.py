@@ -16,6 +16,20 @@ from . import _lib
 
 ACT = {"none": 0, None: 0, "gelu": 1, "relu": 2, "silu": 3, "sigmoid": 4, "tanh": 5}
 
+_default_max_ctas = 0
+
+
+def set_default_max_ctas(n: int) -> None:
+    """Caps the grid of every GEMM that does not name its own cap (0 = one CTA per SM).  A job whose
+    point-to-point transfers run beside the compute kernels (pipeline parallelism) leaves a few SMs
+    free this way: a persistent GEMM on every SM would keep the transfer kernels from starting."""
+    global _default_max_ctas
+    _default_max_ctas = max(0, int(n))
+
+
+def default_max_ctas() -> int:
+    return _default_max_ctas
+
 
 def _act_cpu(name, x):
     if name in (None, "none"):
@@ -167,7 +181,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         g.aux_in, g.ldauxin = aux_in.data_ptr(), _ld(aux_in)
         g.dact = ACT[dact]
     g.force_simt = int(force_simt)
-    g.max_ctas = int(max_ctas)
+    g.max_ctas = int(max_ctas) if max_ctas else _default_max_ctas
     g.split_k = int(split_k)
     _lib.check(_lib.lib().cgk_gemm_bf16(ctypes.byref(g), _lib.stream_ptr()), "cgk_gemm_bf16")
     _lib.count_launch()

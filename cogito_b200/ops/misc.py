@@ -161,6 +161,72 @@ def dropout(x, p: float, training: bool = True, seed: int | None = None):
     return _Dropout.apply(x, p, seed)
 
 
+class _SoftmaxDropoutResidual(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, mul, residual, p, seed):
+        V = x.shape[-1]
+        x2 = x.reshape(-1, V).contiguous()
+        ctx.p, ctx.seed, ctx.has_res = p, seed, residual is not None
+        ctx.save_for_backward(x2, mul.reshape(-1, V).contiguous() if mul is not None else torch.empty(0))
+        ctx.has_mul = mul is not None
+        ctx.shape = x.shape
+        if not x.is_cuda:
+            s = torch.softmax(x2.float(), -1)
+            w = mul.reshape(-1, V).float() if mul is not None else _keep_cpu(x2.shape, p, seed)
+            out = s * w
+            if residual is not None:
+                out = out + residual.reshape(-1, V).float()
+            return out.to(x.dtype).reshape(x.shape)
+        out = torch.empty_like(x2)
+        m2 = ctx.saved_tensors[1] if mul is not None else None
+        r2 = residual.reshape(-1, V).contiguous() if residual is not None else None
+        _lib.check(_lib.lib().cgk_softmax_dropout_residual(_dt(x2), x2.data_ptr(), _lib.ptr(m2), _lib.ptr(r2), out.data_ptr(),
+                                                           x2.shape[0], V, float(p), int(seed), _lib.stream_ptr()),
+                   "cgk_softmax_dropout_residual")
+        _lib.count_launch()
+        return out.reshape(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, m2 = ctx.saved_tensors
+        V = x2.shape[-1]
+        dy2 = dy.reshape(-1, V).contiguous()
+        mul = m2 if ctx.has_mul else None
+        if not x2.is_cuda:
+            s = torch.softmax(x2.float(), -1)
+            w = mul.float() if mul is not None else _keep_cpu(x2.shape, ctx.p, ctx.seed)
+            g = dy2.float() * w
+            dx = (s * (g - (g * s).sum(-1, keepdim=True))).to(x2.dtype)
+        else:
+            dx = torch.empty_like(x2)
+            _lib.check(_lib.lib().cgk_softmax_dropout_residual_backward(_dt(x2), x2.data_ptr(), _lib.ptr(mul), dy2.data_ptr(),
+                                                                        dx.data_ptr(), x2.shape[0], V, float(ctx.p), int(ctx.seed),
+                                                                        _lib.stream_ptr()), "cgk_softmax_dropout_residual_backward")
+            _lib.count_launch()
+        return dx.reshape(ctx.shape), None, (dy if ctx.has_res else None), None, None
+
+
+def _keep_cpu(shape, p, seed):
+    if p <= 0.0:
+        return torch.ones(shape)
+    g = torch.Generator().manual_seed(seed)
+    return (torch.rand(shape, generator=g) >= p).float() / (1.0 - p)
+
+
+def softmax_dropout_residual(x, residual=None, p: float = 0.0, training: bool = True, seed: int | None = None, mul=None):
+    """``dropout(softmax(x, -1), p) + residual`` as one pass over each row (fp32 or bf16).  With ``mul``
+    the softmax is multiplied by that tensor instead of a generated mask: the softmax -> mul -> add
+    chain that the fusion pass names ``fused_softmax_dropout_residual`` (src/jit/fusion.c:152-190 in
+    the reference, where it is a name only).  The backward pass recomputes the softmax from ``x`` and
+    regenerates the mask from the seed; ``mul`` itself gets no gradient."""
+    if not training:
+        p = 0.0
+    if seed is None:
+        _dropout_counter[0] += 1
+        seed = (torch.initial_seed() * 1000003 + _dropout_counter[0]) & 0x7FFFFFFFFFFFFFFF
+    return _SoftmaxDropoutResidual.apply(x, mul, residual, float(p), seed)
+
+
 # ---------------------------------------------------------------------------
 def rope_tables(max_seq: int, head_dim: int, theta: float = 10000.0, device=None):
     """cos / sin tables [max_seq, head_dim / 2], angle = pos * theta^(-2i/D)."""

@@ -74,6 +74,11 @@ class ParallelContext:
     pp_ranks: list = field(default_factory=list)
     dp_ranks: list = field(default_factory=list)
     mp_ranks: list = field(default_factory=list)
+    # one two-rank group per pipeline neighbour and direction: 'recv_fwd' (from the previous stage),
+    # 'send_fwd' (to the next), 'recv_bwd' (from the next), 'send_bwd' (to the previous).  Each carries
+    # the transfers of one direction between one pair of stages, in micro-batch order, on its own
+    # communicator, so that a receive posted early never sits in front of a send to the other neighbour.
+    pipeline_links: dict = field(default_factory=dict)
 
     @property
     def prev_stage(self) -> int | None:
@@ -86,8 +91,14 @@ class ParallelContext:
         return None if c.pp_rank == c.pp - 1 else rank_of(c.dp_rank, c.pp_rank + 1, c.tp_rank, c.tp, c.pp)
 
 
-def init_parallel(dp: int = 1, tp: int = 1, pp: int = 1) -> ParallelContext:
-    """Create the tp / pp / dp groups (collective: every rank of the world calls it)."""
+def init_parallel(dp: int = 1, tp: int = 1, pp: int = 1, pipeline_links: bool = True) -> ParallelContext:
+    """Create the tp / pp / dp groups (collective: every rank of the world calls it), and with
+    ``pipeline_links`` the per-neighbour, per-direction groups of the pipeline transfers."""
+    import os
+    if pp > 1:
+        # point-to-point kernels of the pipeline run beside compute kernels: keep them to a few CTAs
+        # (the executor leaves that many SMs free); must be set before the communicators exist
+        os.environ.setdefault("NCCL_MAX_P2P_NCHANNELS", "2")
     if not dist.is_initialized():
         if dp * tp * pp != 1:
             raise RuntimeError("torch.distributed is not initialised")
@@ -108,4 +119,13 @@ def init_parallel(dp: int = 1, tp: int = 1, pp: int = 1) -> ParallelContext:
         g = dist.new_group(ranks)
         if rank in ranks:
             ctx.mp_group, ctx.mp_ranks = g, ranks
+    if pp > 1 and pipeline_links:
+        for colour in sorted(ppg):
+            ranks = ppg[colour]                     # the stages of one pipeline, first to last
+            for a, b in zip(ranks[:-1], ranks[1:]):
+                fwd, bwd = dist.new_group([a, b]), dist.new_group([a, b])
+                if rank == a:
+                    ctx.pipeline_links["send_fwd"], ctx.pipeline_links["recv_bwd"] = fwd, bwd
+                if rank == b:
+                    ctx.pipeline_links["recv_fwd"], ctx.pipeline_links["send_bwd"] = fwd, bwd
     return ctx

@@ -28,6 +28,7 @@ from .interleaved import InterleavedExecutor
 from .pipeline import PipelineExecutor
 from .tensor_parallel import _ColumnRow, _LMHead, _VocabParallelCE
 from .tp_ops import TPWorkspace
+from ..utils.recompute import checkpoint
 
 
 class TPLlamaBlock(nn.Module):
@@ -117,6 +118,7 @@ class LlamaStage(nn.Module):
         if cfg.n_layer % num_stages:
             raise ValueError("layers must divide evenly over the pipeline stages")
         self.cfg, self.ws, self.stage, self.S = cfg, ws, stage, num_stages
+        self.recompute = False         # True: per-block activation recomputation
         per = cfg.n_layer // num_stages
         self.first, self.last = stage * per, (stage + 1) * per
         P = ws.ranks
@@ -141,7 +143,7 @@ class LlamaStage(nn.Module):
         if self.stage == 0:
             x = _SeqShardEmbedding.apply(x, self.wte, self.ws)
         for blk in self.blocks:
-            x = blk(x, batch_tokens)
+            x = checkpoint(blk, x, batch_tokens) if self.recompute else blk(x, batch_tokens)
         if self.stage != self.S - 1:
             return x
         logits = _LMHead.apply(self.norm_f(x), self.w_head, self.ws)
@@ -232,10 +234,17 @@ class Trainer3D:
 
     def __init__(self, cfg: LlamaConfig, ctx: ParallelContext, device, num_microbatches: int, micro_batch: int, seq_len: int,
                  lr: float = 1e-4, loss_scale: float | None = 65536.0, max_grad_norm: float = 1.0, weight_decay: float = 0.0,
-                 virtual_stages: int = 1):
+                 virtual_stages: int = 1, recompute: str | None = None, comm_sms: int = 8):
         """virtual_stages > 1: every pipeline rank holds that many model chunks (virtual stage = chunk * pp +
         pp_rank) and the step runs the interleaved 1F1B schedule (parallel/interleaved.py); the number of
-        micro-batches must then be a multiple of pp."""
+        micro-batches must then be a multiple of pp.
+        recompute: None keeps every activation; "block" drops the activations inside each transformer
+        block and recomputes them in backward (``utils.recompute.checkpoint``); "stage" keeps only each
+        in-flight micro-batch's stage input and runs the stage's forward pass a second time (1F1B
+        executor only).  comm_sms: SMs that persistent GEMM kernels leave free for the pipeline's
+        transfer kernels, which run on a side stream beside them."""
+        if recompute not in (None, "block", "stage"):
+            raise ValueError("recompute must be None, 'block' or 'stage'")
         self.cfg, self.ctx, self.device = cfg, ctx, torch.device(device)
         self.M, self.mb, self.T = num_microbatches, micro_batch, seq_len
         cuda = self.device.type == "cuda"
@@ -244,10 +253,17 @@ class Trainer3D:
         tokens = micro_batch * seq_len
         if tokens % c.tp:
             raise ValueError("micro_batch * seq_len must divide by the tensor-parallel size")
+        max_ctas = 0
+        if cuda and c.pp > 1 and comm_sms > 0:
+            from ..ops.gemm import set_default_max_ctas
+            max_ctas = max(8, torch.cuda.get_device_properties(self.device).multi_processor_count - comm_sms)
+            set_default_max_ctas(max_ctas)
         self.ws = TPWorkspace(self.device, ctx.tp_group if c.tp > 1 else None, max_rows=tokens,
-                              max_cols=max(cfg.d_model, 1))
+                              max_cols=max(cfg.d_model, 1), max_ctas=max_ctas)
         V = self.V = virtual_stages
         self.stages = [LlamaStage(cfg, self.ws, ch * c.pp + c.pp_rank, c.pp * V, self.device, dtype) for ch in range(V)]
+        for st in self.stages:
+            st.recompute = recompute == "block"
         self.stage = self.stages[0]
         self.scaler = GradScaler(self.device, enabled=loss_scale is not None, init_scale=loss_scale or 1.0)
         # replicated parameters of every chunk first: their gradients are one contiguous slice
@@ -276,7 +292,8 @@ class Trainer3D:
         act_dtype = torch.bfloat16 if cuda else torch.float32
         if V == 1:
             self.pipe = PipelineExecutor(c.pp_rank, c.pp, num_microbatches, ctx.prev_stage, ctx.next_stage,
-                                         (tokens // c.tp, cfg.d_model), act_dtype, self.device)
+                                         (tokens // c.tp, cfg.d_model), act_dtype, self.device,
+                                         links=ctx.pipeline_links, recompute=recompute == "stage")
         else:
             self.pipe = InterleavedExecutor(c.pp_rank, ctx.pp_ranks if c.pp > 1 else [0], V, num_microbatches,
                                             (tokens // c.tp, cfg.d_model), act_dtype, self.device)

@@ -295,13 +295,6 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ ids,
 }
 
 // ---- dropout (counter-based RNG) --------------------------------------------
-__device__ __forceinline__ uint32_t mix32(uint64_t z) {
-  z += 0x9E3779B97F4A7C15ull;
-  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
-  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
-  z = z ^ (z >> 31);
-  return (uint32_t)(z >> 32);
-}
 // y = x * keep / (1 - p) with keep decided by hash(seed, index); the backward
 // pass calls the same kernel on dy with the same seed, so no mask is stored.
 template <typename T>

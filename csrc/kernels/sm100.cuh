@@ -499,6 +499,18 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Counter-based random bits: a hash of (seed, element index).  The dropout kernels draw their
+// keep / drop decision from it, forward and backward alike, so no mask is ever stored.
+__device__ __forceinline__ uint32_t mix32(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z = z ^ (z >> 31);
+  return (uint32_t)(z >> 32);
+}
+__device__ __forceinline__ bool dropout_keep(unsigned long long seed, long long index, uint32_t thresh) {
+  return mix32(seed * 0x100000001B3ull + (uint64_t)index) >= thresh;
+}
 // Vector reduction into global memory (16-byte aligned).
 __device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),

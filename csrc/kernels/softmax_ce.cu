@@ -7,6 +7,10 @@
 //  * cgk_ce_stats + cgk_ce_backward: the same split in two so a vocabulary-
 //    parallel run can all-reduce (max, sum-exp, target-logit) between them.
 //  * cgk_softmax_rows / cgk_softmax_rows_backward: plain row softmax, fp32.
+//  * cgk_softmax_dropout_residual (+ backward): out = dropout(softmax(x)) + residual in one
+//    pass over the row, fp32 or bf16; the multiplier is either a tensor (the reference's
+//    softmax -> mul -> add pattern, src/jit/fusion.c:152-190) or a keep mask drawn from
+//    (seed, element index), which the backward pass regenerates.
 //
 // Reference counterparts: cg_cross_entropy_loss (src/layers/loss.c:44-78, always
 // applies softmax, clamps p at 1e-7), cg_cuda_softmax_forward/backward
@@ -208,6 +212,79 @@ softmax_rows_bwd_kernel(const float* __restrict__ y, const float* __restrict__ d
   }
 }
 
+template <typename T> __device__ __forceinline__ float ldv(const T* p, long long i);
+template <> __device__ __forceinline__ float ldv<float>(const float* p, long long i) { return p[i]; }
+template <> __device__ __forceinline__ float ldv<__nv_bfloat16>(const __nv_bfloat16* p, long long i) { return __bfloat162float(p[i]); }
+template <typename T> __device__ __forceinline__ void stv(T* p, long long i, float v);
+template <> __device__ __forceinline__ void stv<float>(float* p, long long i, float v) { p[i] = v; }
+template <> __device__ __forceinline__ void stv<__nv_bfloat16>(__nv_bfloat16* p, long long i, float v) { p[i] = __float2bfloat16(v); }
+
+// out[r, c] = softmax(x[r, :])[c] * w(r, c) + residual[r, c], with w = mul[r, c] when a multiplier
+// tensor is given, else keep(seed, r * V + c) / (1 - p) (1 when p == 0).  One CTA per row at a time.
+template <typename T>
+__global__ void __launch_bounds__(CE_THREADS)
+softmax_dropout_residual_kernel(const T* __restrict__ x, const T* __restrict__ mul, const T* __restrict__ residual,
+                                T* __restrict__ out, int R, int V, float p, unsigned long long seed) {
+  __shared__ MaxSum sh[CE_THREADS / 32];
+  const float keep_scale = 1.0f / (1.0f - p);
+  const uint32_t thresh = (uint32_t)(p * 4294967296.0);
+  for (int r = blockIdx.x; r < R; r += gridDim.x) {
+    const long long base = (long long)r * V;
+    MaxSum a;
+    a.m = -INFINITY;
+    a.s = 0.0f;
+    for (int c = threadIdx.x; c < V; c += blockDim.x) ms_push(a, ldv<T>(x, base + c));
+    const MaxSum ms = block_maxsum(a, sh);
+    const float inv = 1.0f / ms.s;
+    for (int c = threadIdx.x; c < V; c += blockDim.x) {
+      float v = __expf(ldv<T>(x, base + c) - ms.m) * inv;
+      if (mul) v *= ldv<T>(mul, base + c);
+      else if (p > 0.0f) v = dropout_keep(seed, base + c, thresh) ? v * keep_scale : 0.0f;
+      if (residual) v += ldv<T>(residual, base + c);
+      stv<T>(out, base + c, v);
+    }
+    __syncthreads();
+  }
+}
+
+// dx = s * (g - sum(g * s)) with s = softmax(x) recomputed from x and g = dy * w.
+template <typename T>
+__global__ void __launch_bounds__(CE_THREADS)
+softmax_dropout_residual_bwd_kernel(const T* __restrict__ x, const T* __restrict__ mul, const T* __restrict__ dy,
+                                    T* __restrict__ dx, int R, int V, float p, unsigned long long seed) {
+  __shared__ MaxSum sh[CE_THREADS / 32];
+  __shared__ float shf[CE_THREADS / 32];
+  const float keep_scale = 1.0f / (1.0f - p);
+  const uint32_t thresh = (uint32_t)(p * 4294967296.0);
+  for (int r = blockIdx.x; r < R; r += gridDim.x) {
+    const long long base = (long long)r * V;
+    MaxSum a;
+    a.m = -INFINITY;
+    a.s = 0.0f;
+    for (int c = threadIdx.x; c < V; c += blockDim.x) ms_push(a, ldv<T>(x, base + c));
+    const MaxSum ms = block_maxsum(a, sh);
+    const float inv = 1.0f / ms.s;
+    auto weight = [&](int c) {
+      if (mul) return ldv<T>(mul, base + c);
+      if (p > 0.0f) return dropout_keep(seed, base + c, thresh) ? keep_scale : 0.0f;
+      return 1.0f;
+    };
+    float dot = 0.0f;
+    for (int c = threadIdx.x; c < V; c += blockDim.x)
+      dot += ldv<T>(dy, base + c) * weight(c) * __expf(ldv<T>(x, base + c) - ms.m) * inv;
+    dot = warp_sum(dot);
+    if ((threadIdx.x & 31) == 0) shf[threadIdx.x >> 5] = dot;
+    __syncthreads();
+    float tot = 0.0f;
+    for (int w = 0; w < CE_THREADS / 32; ++w) tot += shf[w];
+    __syncthreads();
+    for (int c = threadIdx.x; c < V; c += blockDim.x) {
+      const float s = __expf(ldv<T>(x, base + c) - ms.m) * inv;
+      stv<T>(dx, base + c, s * (ldv<T>(dy, base + c) * weight(c) - tot));
+    }
+  }
+}
+
 }  // namespace cgk
 
 using namespace cgk;
@@ -271,6 +348,39 @@ CGK_API int cgk_softmax_rows_backward(const float* y, const float* dy, float* dx
   CGK_REQUIRE(y && dy && dx && V > 0, "cgk_softmax_rows_backward: bad argument");
   if (R == 0) return 0;
   softmax_rows_bwd_kernel<<<ce_grid(R), CE_THREADS, 0, (cudaStream_t)stream>>>(y, dy, dx, R, V);
+  CGK_LAUNCH_CHECK();
+  return 0;
+}
+
+// dtype: 0 fp32, 1 bf16 (all four tensors alike).  mul and residual may be null; with mul == null and
+// p > 0 the multiplier is the dropout mask of (seed, element index).  out may alias residual.
+CGK_API int cgk_softmax_dropout_residual(int dtype, const void* x, const void* mul, const void* residual, void* out,
+                                         int R, int V, float p, unsigned long long seed, void* stream) {
+  CGK_REQUIRE(x && out && V > 0 && R >= 0 && p >= 0.0f && p < 1.0f && (dtype == 0 || dtype == 1),
+              "cgk_softmax_dropout_residual: bad argument");
+  if (R == 0) return 0;
+  if (dtype == 0)
+    softmax_dropout_residual_kernel<float><<<ce_grid(R), CE_THREADS, 0, (cudaStream_t)stream>>>(
+        (const float*)x, (const float*)mul, (const float*)residual, (float*)out, R, V, p, seed);
+  else
+    softmax_dropout_residual_kernel<__nv_bfloat16><<<ce_grid(R), CE_THREADS, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)mul, (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, R, V, p, seed);
+  CGK_LAUNCH_CHECK();
+  return 0;
+}
+
+// dx for the call above (the gradient of the residual is dy itself; that of mul is not produced).
+CGK_API int cgk_softmax_dropout_residual_backward(int dtype, const void* x, const void* mul, const void* dy, void* dx,
+                                                  int R, int V, float p, unsigned long long seed, void* stream) {
+  CGK_REQUIRE(x && dy && dx && V > 0 && R >= 0 && p >= 0.0f && p < 1.0f && (dtype == 0 || dtype == 1),
+              "cgk_softmax_dropout_residual_backward: bad argument");
+  if (R == 0) return 0;
+  if (dtype == 0)
+    softmax_dropout_residual_bwd_kernel<float><<<ce_grid(R), CE_THREADS, 0, (cudaStream_t)stream>>>(
+        (const float*)x, (const float*)mul, (const float*)dy, (float*)dx, R, V, p, seed);
+  else
+    softmax_dropout_residual_bwd_kernel<__nv_bfloat16><<<ce_grid(R), CE_THREADS, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)mul, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, R, V, p, seed);
   CGK_LAUNCH_CHECK();
   return 0;
 }

@@ -254,6 +254,15 @@ int cgk_selftest_bounded_wait(const int* flag, int want, unsigned long long budg
 /* mask [(L+n), (L+n)], 0 or -1e9: causal prefix; tree node i sees the prefix, its ancestors, itself. */
 int cgk_tree_mask(const int* parents, int n, int L, float* mask_f32, void* mask_bf16, void* stream);
 
+/* ---- Fused row kernel of the fusion pass (csrc/kernels/softmax_ce.cu) --------------------- */
+/* out = softmax(x) * w + residual per row, w = mul (tensor) or the dropout mask of (seed, index)
+ * scaled by 1 / (1 - p); dtype 0 fp32, 1 bf16; mul / residual may be null.  This is the kernel
+ * behind the "fused_softmax_dropout_residual" group (softmax -> mul -> add). */
+int cgk_softmax_dropout_residual(int dtype, const void* x, const void* mul, const void* residual, void* out,
+                                 int R, int V, float p, unsigned long long seed, void* stream);
+int cgk_softmax_dropout_residual_backward(int dtype, const void* x, const void* mul, const void* dy, void* dx,
+                                          int R, int V, float p, unsigned long long seed, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -71,6 +71,7 @@ def main():
         dp, tp, pp = (int(a) for a in sys.argv[2:5])
         virtual = int(sys.argv[5]) if len(sys.argv) > 5 else 1      # chunks per pipeline rank (interleaved 1F1B)
         scaled = len(sys.argv) > 6 and sys.argv[6] == "scaled"       # loss scaling and clipping on: replica-wide statistics
+        recompute = sys.argv[7] if len(sys.argv) > 7 and sys.argv[7] in ("block", "stage") else None
         from cogito_b200.optim.fused import GradScaler
         from cogito_b200.models.llama import Llama, LlamaConfig
         from cogito_b200.parallel.groups import init_parallel
@@ -80,7 +81,7 @@ def main():
         ctx = init_parallel(dp, tp, pp)
         M, mb, T = 4, 1, 256
         t3 = Trainer3D(cfg, ctx, dev, num_microbatches=M, micro_batch=mb, seq_len=T, lr=1e-3, loss_scale=1024.0 if scaled else None,
-                       max_grad_norm=1.0 if scaled else 0.0, virtual_stages=virtual)
+                       max_grad_norm=1.0 if scaled else 0.0, virtual_stages=virtual, recompute=recompute)
         t3.load_from(full)
         ids = torch.randint(0, 2048, (dp * M * mb, T), generator=g).to(dev)
         tg = torch.randint(0, 2048, (dp * M * mb, T), generator=g).to(dev)
@@ -99,6 +100,8 @@ def main():
             got.append(float(v[0] / v[1]))
         out["got"] = got
         out["p2p_bytes"] = t3.pipe.p2p_bytes
+        out["peak_mem_mb"] = torch.cuda.max_memory_allocated(dev) / 2 ** 20
+        out["fused_dp"] = type(t3.opt).__name__
     elif mode == "serve":
         # tensor-parallel INT4 engine (fused all-reduce + residual + RMSNorm over peer memory) against
         # the unsplit engine on the same GPU; head_dim 128 keeps every slice on a weight-group boundary

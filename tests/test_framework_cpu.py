@@ -174,3 +174,43 @@ def test_gpt2_trains_on_cpu_and_trainer_accumulates_micro_batches():
     l2 = [float(t2.step(ids, tg)) for _ in range(8)]
     assert l1[-1] < l1[0] - 0.5
     assert all(abs(a - b) < 1e-3 for a, b in zip(l1, l2))      # micro-batching is exact
+
+
+def test_block_recompute_gives_the_same_loss_and_gradients():
+    import torch
+    from cogito_b200.models.gpt2 import GPT2, GPT2Config
+    from cogito_b200.utils.rng import manual_seed
+    g = torch.Generator().manual_seed(3)
+    ids, tg = torch.randint(0, 64, (2, 16), generator=g), torch.randint(0, 64, (2, 16), generator=g)
+    grads = []
+    for rc in (False, True):
+        manual_seed(0)
+        m = GPT2(GPT2Config(vocab_size=64, n_layer=2, d_model=32, n_head=2, d_ff=64, max_seq_len=16, recompute=rc))
+        loss = m(ids, tg)
+        loss.backward()
+        grads.append((float(loss), [p.grad.clone() for p in m.parameters()]))
+    assert abs(grads[0][0] - grads[1][0]) < 1e-6
+    for a, b in zip(grads[0][1], grads[1][1]):
+        assert torch.allclose(a, b, atol=1e-6, rtol=1e-5)
+
+
+def test_softmax_dropout_residual_matches_its_unfused_chain():
+    import torch
+    from cogito_b200.ops.misc import softmax_dropout_residual
+    torch.manual_seed(0)
+    x = torch.randn(5, 7, 33, requires_grad=True)
+    mul = (torch.rand(5, 7, 33) > 0.2).float() / 0.8
+    res = torch.randn(5, 7, 33, requires_grad=True)
+    out = softmax_dropout_residual(x, res, mul=mul)
+    ref = torch.softmax(x, -1) * mul + res
+    assert torch.allclose(out, ref, atol=1e-6)
+    g = torch.randn_like(out)
+    gx, gr = torch.autograd.grad(out, (x, res), g)
+    rx, rr = torch.autograd.grad(ref, (x, res), g)
+    assert torch.allclose(gx, rx, atol=1e-6) and torch.allclose(gr, rr)
+    # generated mask: every kept element is softmax / (1 - p), the rest is the residual alone
+    y = softmax_dropout_residual(x.detach(), None, p=0.25, seed=11)
+    s = torch.softmax(x.detach(), -1)
+    kept = y != 0
+    assert torch.allclose(y[kept], (s / 0.75)[kept], atol=1e-6) and 0.6 < kept.float().mean() < 0.9
+    assert torch.equal(softmax_dropout_residual(x.detach(), None, p=0.25, training=False), s)

@@ -82,3 +82,17 @@ def test_3d_llama_interleaved_schedule():
 def test_3d_llama_with_loss_scaling_and_clipping():
     """tp 2: the overflow flag and the clipping norm are those of the whole replica (all-reduced over its ranks)."""
     _close(_run(2, "3d", 1, 2, 1, 1, "scaled"), 0.05)
+
+
+@pytest.mark.parametrize("dp,tp,pp,recompute", [(1, 2, 1, "block"), (1, 1, 2, "stage"), (1, 2, 2, "block")])
+def test_3d_llama_activation_recompute(dp, tp, pp, recompute):
+    """Same losses with the activations of every block (or stage) dropped and recomputed in backward."""
+    _close(_run(dp * tp * pp, "3d", dp, tp, pp, 1, "plain", recompute), 0.05)
+
+
+def test_3d_llama_scaled_keeps_the_fused_data_parallel_optimizer():
+    """dp 2 x tp 2 with loss scaling and clipping: the bucketed all-reduce + Adam kernels run with statistics of
+    the whole job."""
+    res = _run(4, "3d", 2, 2, 1, 1, "scaled")
+    _close(res, 0.05)
+    assert all(r["fused_dp"] == "DPFusedAdam" for r in res)

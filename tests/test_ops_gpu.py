@@ -219,3 +219,32 @@ def test_fused_sgd_nesterov_matches_torch():
         o.zero_grad(); w.main_grad.copy_(g); o.step()
         wt.grad = g.clone(); ot.step()
     assert relerr(w, wt) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_softmax_dropout_residual_kernel(dtype):
+    """One row kernel for softmax -> multiply -> add, against the three separate steps."""
+    from cogito_b200.ops.misc import _dropout_apply, softmax_dropout_residual
+    torch.manual_seed(0)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    x = torch.randn(37, 4, 1000, device="cuda").to(dtype).requires_grad_(True)
+    res = torch.randn(37, 4, 1000, device="cuda").to(dtype).requires_grad_(True)
+    mul = ((torch.rand(37, 4, 1000, device="cuda") > 0.3).float() / 0.7).to(dtype)
+    out = softmax_dropout_residual(x, res, mul=mul)
+    ref = torch.softmax(x.float(), -1) * mul.float() + res.float()
+    assert (out.float() - ref).abs().max() < tol
+    g = torch.randn_like(out)
+    gx, gr = torch.autograd.grad(out, (x, res), g)
+    rx, rr = torch.autograd.grad(ref, (x, res), g.float())
+    assert (gx.float() - rx.float()).abs().max() < tol * max(1.0, float(rx.abs().max())) and torch.equal(gr, g)
+    # generated mask = the mask of the stand-alone dropout kernel for the same seed
+    y = softmax_dropout_residual(x.detach(), res.detach(), p=0.2, seed=77)
+    s = torch.softmax(x.detach().float(), -1)
+    sep = _dropout_apply(s, 0.2, 77) + res.detach().float()
+    assert (y.float() - sep).abs().max() < tol
+    x2 = x.detach().clone().requires_grad_(True)
+    y2 = softmax_dropout_residual(x2, None, p=0.2, seed=77)
+    (g2,) = torch.autograd.grad(y2, x2, g)
+    xs = x.detach().float().requires_grad_(True)
+    (r2,) = torch.autograd.grad(_dropout_apply(torch.softmax(xs, -1), 0.2, 77), xs, g.float())
+    assert (g2.float() - r2).abs().max() < tol * max(1.0, float(r2.abs().max()))
