@@ -8,7 +8,7 @@
 
 Objects are cached under ``build/`` and rebuilt when a source or any header is
 newer.  ``python -m cogito_b200.build`` builds both; ``--kernels`` / ``--capi``
-build one.
+build one; ``--debug-bounds`` builds the index-checking copy of the kernel library.
 """
 from __future__ import annotations
 
@@ -95,16 +95,22 @@ def _build(sources: list[Path], headers: list[Path], out: Path, compiler: list[s
     return True
 
 
-def build_kernels(verbose: bool = False) -> Path:
+def build_kernels(verbose: bool = False, debug_bounds: bool = False) -> Path:
+    """debug_bounds: the same sources with -DCGK_DEBUG_BOUNDS as ``libcogito_kernels_dbg.so``: indices
+    that come from data or from tile edges are checked, the first violation per source file is
+    recorded (never a trap) and the access redirected inside the array.  ``COGITO_KERNELS_DEBUG=1``
+    makes the package load that library, and ``ops._lib.assert_device_ok`` (which the GPU tests
+    call after every test) then fails on a recorded violation."""
     srcs = sorted((ROOT / "csrc" / "kernels").glob("*.cu")) + sorted((ROOT / "csrc" / "comm").glob("*.cu"))
     hdrs = (list((ROOT / "csrc").rglob("*.cuh")) + list((ROOT / "csrc").rglob("*.h")) + list((ROOT / "csrc").rglob("*.inc"))
             + list((ROOT / "include").glob("*.h")))
-    out = LIB_DIR / "libcogito_kernels.so"
+    out = LIB_DIR / ("libcogito_kernels_dbg.so" if debug_bounds else "libcogito_kernels.so")
     nvcc = _nvcc()
-    _build(srcs, hdrs, out, [nvcc] + NVCC_FLAGS + ["-I", str(ROOT / "include")],
+    flags = NVCC_FLAGS + (["-DCGK_DEBUG_BOUNDS"] if debug_bounds else [])
+    _build(srcs, hdrs, out, [nvcc] + flags + ["-I", str(ROOT / "include")],
            [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC",
             "-cudart", "shared"],
-           "kernels", verbose)
+           "kernels_dbg" if debug_bounds else "kernels", verbose)
     return out
 
 
@@ -156,10 +162,15 @@ def main() -> None:
     ap.add_argument("--kernels", action="store_true")
     ap.add_argument("--capi", action="store_true")
     ap.add_argument("--sanitize", action="store_true", help="only build the ASan + UBSan copy of the host runtime")
+    ap.add_argument("--debug-bounds", action="store_true",
+                    help="only build libcogito_kernels_dbg.so: every kernel with index checks that record the first violation")
     ap.add_argument("-v", "--verbose", action="store_true")
     args = ap.parse_args()
     if args.sanitize:
         print(build_capi_sanitized(args.verbose))
+        return
+    if args.debug_bounds:
+        print(build_kernels(args.verbose, debug_bounds=True))
         return
     if args.kernels or not args.capi:
         print(build_kernels(args.verbose))

@@ -13,8 +13,12 @@ from pathlib import Path
 
 import torch
 
-_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libcogito_kernels.so"
+# COGITO_KERNELS_DEBUG=1 selects the index-checking build (python -m cogito_b200.build --debug-bounds)
+_DEBUG = os.environ.get("COGITO_KERNELS_DEBUG", "0") not in ("", "0")
+_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / ("libcogito_kernels_dbg.so" if _DEBUG else "libcogito_kernels.so")
 _lib = None
+# source files that carry index checks in the debug build (one recorded violation each)
+_BOUNDS_FILES = ("gemm_tcgen05", "softmax_ce", "serving", "elementwise", "flash_fwd", "flash_bwd")
 
 
 class KernelError(RuntimeError):
@@ -155,10 +159,30 @@ def read_status() -> tuple[int, int, int, int]:
     return tuple(out)  # type: ignore[return-value]
 
 
+def read_bounds(reset: bool = True) -> list[tuple[str, int, int, int]]:
+    """Index violations recorded by the debug build: (source file, line, index, limit); empty with the
+    ordinary library.  Synchronises."""
+    if not _DEBUG:
+        return []
+    torch.cuda.synchronize()
+    out = []
+    for name in _BOUNDS_FILES:
+        fn = getattr(lib(), f"cgk_bounds_read_{name}", None)
+        if fn is None:
+            continue
+        word = (c_int * 4)()
+        if fn(word, int(reset)) == 0 and word[0] != 0:
+            out.append((name, word[1], word[2], word[3]))
+    return out
+
+
 def assert_device_ok() -> None:
     code, where, block, aux = read_status()
     if code != 0:
         raise KernelError(f"device status: code={code} where={where} block={block} aux={aux}")
+    bad = read_bounds()
+    if bad:
+        raise KernelError(f"index outside its range (file, line, index, limit): {bad}")
 
 
 _launches = 0

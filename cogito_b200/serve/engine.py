@@ -326,10 +326,19 @@ class SpeculativeDecoder:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             before = _lib.launches()
+            # The fused all-reduce alternates between two slots by the parity of a HOST call counter, and the
+            # choice is frozen into the captured launches; replays alternate correctly only if one step makes an
+            # even number of such calls per engine.  Check that, and put the counters back when capture fails.
+            reducers = [e.ar for e in (self.draft, self.target) if getattr(e, "ar", None) is not None]
+            epochs = [r.epoch for r in reducers]
             try:
                 with torch.cuda.graph(graph):
                     self._g_out = self.step_full(self._g_last)
+                if any((r.epoch - e0) % 2 for r, e0 in zip(reducers, epochs)):
+                    raise RuntimeError("an odd number of fused all-reduce calls per step cannot be replayed")
             except Exception as e:                               # something in the step cannot be captured here
+                for r, e0 in zip(reducers, epochs):
+                    r.epoch = e0
                 warnings.warn(f"decode step not captured ({e!r}); launching it from Python")
                 self.use_graph = False
                 return self.step_full(last)

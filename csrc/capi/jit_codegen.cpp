@@ -3,12 +3,19 @@
 // Reference surface: include/cg_jit.h (codegen, compiler), include/cg_fusion.h,
 // src/jit/graph_capture.c:383-660, src/jit/fusion.c.
 #include <dlfcn.h>
+#include <errno.h>
+#include <fcntl.h>
+#include <spawn.h>
+#include <sys/stat.h>
+#include <sys/wait.h>
 #include <unistd.h>
 
 #include <atomic>
 #include <set>
 #include <sstream>
 #include <string>
+
+extern char** environ;
 
 #include "internal.hpp"
 #include "jit_internal.hpp"
@@ -199,20 +206,40 @@ CG_EXPORT bool cg_jit_compile(cg_jit_compiler* c) {
   if (c->backend != JIT_BACKEND_CPU) { std::fprintf(stderr, "JIT: Unsupported backend\n"); return fail(CG_ERROR_INVALID_ARGUMENT, false); }
   c->source_code = cg_jit_codegen_c(c->graph);
   c->source_len = std::strlen(c->source_code);
+  // The source and the shared object live in a directory of their own that only this user can
+  // enter (mkdtemp, mode 0700), so nobody can plant a file or a link at the paths used here; the
+  // compiler is started directly with an argument vector (no shell: TMPDIR and CC are never parsed).
   const char* tmp = getenv("TMPDIR");
-  const std::string stem = std::string(tmp ? tmp : "/tmp") + "/cogito_jit_" + std::to_string((long)getpid()) + "_" + std::to_string(g_module_counter.fetch_add(1));
-  const std::string src = stem + ".c", lib = stem + ".so";
-  FILE* f = std::fopen(src.c_str(), "w");
-  if (!f) return fail(CG_ERROR_FILE_NOT_FOUND, false);
+  std::string dir = std::string(tmp && *tmp ? tmp : "/tmp") + "/cogito_jit_XXXXXX";
+  if (!mkdtemp(&dir[0])) return fail(CG_ERROR_FILE_NOT_FOUND, false);
+  const std::string src = dir + "/kernel.c", lib = dir + "/kernel.so";
+  auto cleanup = [&]() { unlink(src.c_str()); unlink(lib.c_str()); rmdir(dir.c_str()); };
+  const int fd = open(src.c_str(), O_WRONLY | O_CREAT | O_EXCL, 0600);
+  if (fd < 0) { cleanup(); return fail(CG_ERROR_FILE_NOT_FOUND, false); }
+  FILE* f = fdopen(fd, "w");
+  if (!f) { close(fd); cleanup(); return fail(CG_ERROR_FILE_NOT_FOUND, false); }
   std::fwrite(c->source_code, 1, c->source_len, f);
   std::fclose(f);
   const char* cc = getenv("CC");
-  const std::string cmd = std::string(cc ? cc : "cc") + " -O2 -shared -fPIC -o " + lib + " " + src + " -lm 2>/dev/null";
-  const int rc = std::system(cmd.c_str());
-  unlink(src.c_str());
-  if (rc != 0) return false;                         // no compiler here: cg_jit_run interprets instead
+  const std::string compiler = cc && *cc ? cc : "cc";
+  std::vector<std::string> args = {compiler, "-O2", "-shared", "-fPIC", "-o", lib, src, "-lm"};
+  std::vector<char*> argv;
+  for (auto& a : args) argv.push_back(&a[0]);
+  argv.push_back(nullptr);
+  posix_spawn_file_actions_t fa;
+  posix_spawn_file_actions_init(&fa);
+  posix_spawn_file_actions_addopen(&fa, 2, "/dev/null", O_WRONLY, 0);      // a missing compiler is not an error worth printing
+  pid_t pid = 0;
+  int rc = posix_spawnp(&pid, compiler.c_str(), &fa, nullptr, argv.data(), environ);
+  posix_spawn_file_actions_destroy(&fa);
+  if (rc == 0) {
+    int status = 0;
+    while (waitpid(pid, &status, 0) < 0 && errno == EINTR) {}
+    rc = (WIFEXITED(status) && WEXITSTATUS(status) == 0) ? 0 : 1;
+  }
+  if (rc != 0) { cleanup(); return false; }           // no compiler here: cg_jit_run interprets instead
   void* h = dlopen(lib.c_str(), RTLD_NOW | RTLD_LOCAL);
-  unlink(lib.c_str());
+  cleanup();
   if (!h) return false;
   c->compiled_module = h; c->compiled_kernel = dlsym(h, "jit_kernel"); c->is_compiled = c->compiled_kernel != nullptr;
   return c->is_compiled;

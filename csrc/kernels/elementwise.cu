@@ -742,3 +742,5 @@ CGK_API int cgk_maxpool_backward(const float* dy, const int* argmax, float* dx, 
   CGK_LAUNCH_CHECK();
   return 0;
 }
+
+CGK_BOUNDS_READER(elementwise)

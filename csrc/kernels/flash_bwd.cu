@@ -70,7 +70,7 @@ flash_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __r
       if (r < rows && (threadIdx.x % LPR) == 0) {
         const int h = (int)(r % H);
         const long long bt = r / H;
-        delta[((bt / T) * H + h) * T + (bt % T)] = s;
+        delta[CGK_IDX(((bt / T) * H + h) * T + (bt % T), rows)] = s;
       }
     }
   }
@@ -189,3 +189,5 @@ CGK_API int cgk_flash_backward(const cgk_flash_args* pa, void* stream) {
   }
   return 0;
 }
+
+CGK_BOUNDS_READER(flash_bwd)

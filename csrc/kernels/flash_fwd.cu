@@ -426,7 +426,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     if (row_ok && p.lse) {
       const float lse = (l > 0.0f) ? (m * 0.6931471805599453f + __logf(l)) : INFINITY;
-      p.lse[((long long)b * p.Hq + h) * p.Tq + qpos] = lse;
+      p.lse[((long long)b * p.Hq + h) * p.Tq + CGK_IDX(qpos, p.Tq)] = lse;
     }
   }
 
@@ -492,3 +492,5 @@ CGK_API int cgk_flash_forward(const cgk_flash_args* pa, void* stream) {
   if (a.D == 64) return launch_fwd<64>(a, p, (cudaStream_t)stream);
   return launch_fwd<128>(a, p, (cudaStream_t)stream);
 }
+
+CGK_BOUNDS_READER(flash_fwd)

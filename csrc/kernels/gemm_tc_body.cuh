@@ -85,6 +85,8 @@ __device__ __forceinline__ void* out_address(const GemmDev& g, int b, int m, int
     return g.rs_dst[o] + (long long)(m - o * g.rs_rows) * g.ldc + n;
   }
   fp32 = g.out_fp32 != 0;
+  m = (int)CGK_IDX(m, g.M);
+  n = (int)CGK_IDX(n, g.N);
   const long long off = (long long)b * g.strideC + (long long)m * g.ldc + n;
   return fp32 ? (void*)(reinterpret_cast<float*>(g.out) + off)
               : (void*)(reinterpret_cast<__nv_bfloat16*>(g.out) + off);

@@ -208,3 +208,5 @@ CGK_API int cgk_gemm_bf16(const cgk_gemm_args* pa, void* stream_) {
     default: return launch_tc<64, 8>(a, g, sms, stream);
   }
 }
+
+CGK_BOUNDS_READER(gemm_tcgen05)

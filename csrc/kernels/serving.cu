@@ -74,7 +74,7 @@ __global__ void kv_append_kernel(KvDev c, const __nv_bfloat16* __restrict__ k_ne
   const int h = wid % c.heads, t = (wid / c.heads) % T, b = wid / (c.heads * T);
   const int pos = c.lengths[b] + t, lp = pos / c.page_size;
   if (lp >= c.max_pages) { if (lane == 0) report_status(status, KST_BAD_ARG, 400, pos); return; }
-  const int page = c.page_table[b * c.max_pages + lp];
+  const int page = c.page_table[CGK_IDX(b * c.max_pages + lp, c.batch * c.max_pages)];
   const long long tok = ((long long)page * c.page_size + pos % c.page_size) * c.heads + h;
   const int G = c.D / c.group;
   for (int which = 0; which < 2; ++which) {
@@ -361,7 +361,7 @@ sample_kernel(const void* __restrict__ logits, int logits_bf16, long long ld, in
     const float u = u01(rnd.c[0]) * mass;
     float acc = 0.0f; int pick = keep - 1;
     for (int i = 0; i < keep; ++i) { acc += cand_v[i]; if (u < acc) { pick = i; break; } }
-    tokens[row] = cand_i[pick];
+    tokens[row] = cand_i[CGK_IDX(pick, keep)];
     if (probs_out) for (int i = 0; i < keep; ++i) probs_out[(long long)row * V + cand_i[i]] = cand_v[i] / mass;
   }
 }
@@ -385,7 +385,7 @@ spec_accept_kernel(const int* __restrict__ draft_tokens, const float* __restrict
   if (tid == 0) {
     int n = 0;
     for (; n < gamma; ++n) {
-      const int tok = draft_tokens[b * gamma + n];
+      const int tok = (int)CGK_IDX(draft_tokens[b * gamma + n], V);
       const float pd = q[((long long)b * gamma + n) * V + tok], pt = p[((long long)b * (gamma + 1) + n) * V + tok];
       const Philox r2 = philox(seed, 0x9747b28cull + (uint64_t)b, (step ? (uint64_t)*step : 0ull) * 64 + n);
       const float ratio = pd > 0.0f ? fminf(1.0f, pt / pd) : 1.0f;
@@ -441,7 +441,7 @@ __global__ void tree_mask_kernel(const int* __restrict__ parents, int n, int L, 
     bool vis;
     if (i < L) vis = j <= i;
     else if (j < L) vis = true;
-    else { vis = false; int a = i - L; for (int hop = 0; hop <= n && a >= 0; ++hop) { if (a == j - L) { vis = true; break; } a = parents[a]; } }
+    else { vis = false; int a = i - L; for (int hop = 0; hop <= n && a >= 0; ++hop) { if (a == j - L) { vis = true; break; } a = parents[CGK_IDX(a, n)]; if (a >= 0) (void)CGK_IDX(a, n); } }
     const float v = vis ? 0.0f : -1e9f;
     if (mask_f32) mask_f32[idx] = v;
     if (mask_bf16) mask_bf16[idx] = __float2bfloat16(v);
@@ -542,3 +542,5 @@ CGK_API int cgk_tree_mask(const int* parents, int n, int L, float* mask_f32, voi
   CGK_LAUNCH_CHECK();
   return 0;
 }
+
+CGK_BOUNDS_READER(serving)

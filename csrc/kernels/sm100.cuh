@@ -23,6 +23,7 @@ enum : int {
   KST_MBAR_TIMEOUT = 1,   // an mbarrier wait ran out
   KST_FLAG_TIMEOUT = 2,   // a wait on a global-memory flag ran out
   KST_BAD_ARG = 3,
+  KST_BOUNDS = 4,         // debug build: an index outside its range (where = source line)
 };
 
 __device__ __forceinline__ void report_status(int* status, int code, int where, int aux) {
@@ -34,6 +35,38 @@ __device__ __forceinline__ void report_status(int* status, int code, int where, 
     __threadfence_system();
   }
 }
+
+// ---------------------------------------------------------------------------
+// Index checks of the debug build (python -m cogito_b200.build --debug-bounds, which compiles every
+// kernel with -DCGK_DEBUG_BOUNDS into libcogito_kernels_dbg.so).  CGK_IDX(i, n) yields i; in the
+// debug build an i outside [0, n) is recorded once per source file (code KST_BOUNDS, source line,
+// index, limit) and replaced by 0, so the access that follows stays inside the array: the kernel
+// never traps and the test that ran it fails on the recorded word instead
+// (cgk_bounds_read_<file>, read by cogito_b200.ops._lib.assert_device_ok).
+// ---------------------------------------------------------------------------
+#ifdef CGK_DEBUG_BOUNDS
+static __device__ int cgk_bounds_word[4];
+__device__ __forceinline__ long long cgk_checked_index(long long i, long long n, int line) {
+  if (i >= 0 && i < n) return i;
+  if (atomicCAS(&cgk_bounds_word[0], 0, (int)KST_BOUNDS) == 0) {
+    cgk_bounds_word[1] = line;
+    cgk_bounds_word[2] = (int)i;
+    cgk_bounds_word[3] = (int)n;
+  }
+  return 0;
+}
+#define CGK_IDX(i, n) cgk_checked_index((long long)(i), (long long)(n), __LINE__)
+#define CGK_BOUNDS_READER(name)                                                               \
+  extern "C" __attribute__((visibility("default"))) int cgk_bounds_read_##name(int* out, int reset) { \
+    int z[4] = {0, 0, 0, 0};                                                                  \
+    if (cudaMemcpyFromSymbol(out, cgk::cgk_bounds_word, sizeof(z)) != cudaSuccess) return -2; \
+    if (reset && cudaMemcpyToSymbol(cgk::cgk_bounds_word, z, sizeof(z)) != cudaSuccess) return -2; \
+    return 0;                                                                                 \
+  }
+#else
+#define CGK_IDX(i, n) (i)
+#define CGK_BOUNDS_READER(name)
+#endif
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;

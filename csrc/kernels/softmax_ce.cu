@@ -130,6 +130,7 @@ softmax_ce_fused_kernel(const __nv_bfloat16* __restrict__ logits, const long lon
   for (int r = blockIdx.x; r < R; r += gridDim.x) {
     const __nv_bfloat16* row = logits + (long long)r * ld;
     const long long tgt = targets[r];
+    if (tgt != ignore_index) (void)CGK_IDX(tgt, V);        // debug build: a label outside the vocabulary is reported, not just skipped
     const bool ignored = (tgt == ignore_index) || tgt < 0 || tgt >= V;
     MaxSum ms = block_maxsum(row_maxsum_bf16(row, V), sh);
     const float lse = ms.m + __logf(ms.s);
@@ -384,3 +385,5 @@ CGK_API int cgk_softmax_dropout_residual_backward(int dtype, const void* x, cons
   CGK_LAUNCH_CHECK();
   return 0;
 }
+
+CGK_BOUNDS_READER(softmax_ce)
