@@ -91,14 +91,14 @@ def _qkv(B, T, H, Hk, D):
 
 def case_flash_fwd(t, small):
     from cogito_b200.ops.attention import flash_forward
-    for B, T, H, Hk, D in ([(2, 2048, 12, 12, 64)] if small else [(8, 2048, 12, 12, 64), (4, 4096, 32, 8, 128)]):
+    for B, T, H, Hk, D in ([(8, 2048, 12, 12, 64)] if small else [(8, 2048, 12, 12, 64), (4, 4096, 32, 8, 128)]):
         q, k, v = _qkv(B, T, H, Hk, D)
         emit("flash_fwd", t(lambda: flash_forward(q, k, v, causal=True)), flops=2.0 * B * H * T * T * D, B=B, T=T, H=H, Hk=Hk, D=D, causal=True)
 
 
 def case_flash_bwd(t, small):
     from cogito_b200.ops.attention import flash_backward, flash_forward
-    for B, T, H, Hk, D in ([(2, 2048, 12, 12, 64)] if small else [(8, 2048, 12, 12, 64), (4, 4096, 32, 8, 128)]):
+    for B, T, H, Hk, D in ([(8, 2048, 12, 12, 64)] if small else [(8, 2048, 12, 12, 64), (4, 4096, 32, 8, 128)]):
         q, k, v = _qkv(B, T, H, Hk, D)
         o, lse = flash_forward(q, k, v, causal=True)
         do = torch.randn_like(o)

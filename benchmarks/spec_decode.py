@@ -3,7 +3,7 @@
     python benchmarks/spec_decode.py [--layers 32] [--batch 16] [--prompt 512] [--new 256] [--gamma 4]
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 benchmarks/spec_decode.py   # TP=8
 
-Target: Llama-7B-shaped model (32 layers, d_model 4096, 32 heads, d_ff 11008, vocabulary 32000) with
+Target: Llama-7B-shaped model (32 layers, d_model 4096, 32 query / 8 KV heads, d_ff 11008, vocabulary 32000) with
 INT4 weights in groups of 128 and an INT4 KV cache; draft: 2 layers of the same width; random
 weights (N(0, 0.02)) and uniform random prompts.  gamma drafted tokens per step, temperature 0.8,
 top-k 50, top-p 0.9.  One JSON line from rank 0: decode tokens/s over all sequences (device time of
@@ -33,7 +33,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--new", type=int, default=256)
     ap.add_argument("--gamma", type=int, default=4)
-    ap.add_argument("--kv-heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8, help="KV heads of the target (grouped-query attention: 32 query heads share them)")
     ap.add_argument("--self-draft", action="store_true")
     ap.add_argument("--tp-graph", action="store_true", help="replay the step from a CUDA graph under tensor parallelism too")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
