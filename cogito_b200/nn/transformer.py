@@ -24,6 +24,7 @@ from torch import nn
 from ..ops import functional as F
 from ..ops import misc as M
 from ..ops.attention import alibi_slopes, flash_backward, flash_forward
+from ..ops.gemm import gemm
 from .modules import Dropout, LayerNorm, Linear, RMSNorm, _maybe_bf16
 
 
@@ -91,6 +92,50 @@ class _PackedAttention(torch.autograd.Function):
         return dx, None, None, None, None, None, None, None
 
 
+class _QKVRopeAttention(torch.autograd.Function):
+    """o = attention(rope(h W^T + b)): the QKV projection applies the rotary embedding to its q and
+    k columns in the GEMM's epilogue (no separate pass over the projection), attention runs on the
+    packed result, and the backward pass undoes the rotation on the gradient of the projection (in
+    place, on its own buffer) before the two backward GEMMs.
+    Reference: OP_FUSED_QKV_ROPE (include/cg_jit.h:59, src/jit/fusion.c:192-224, a name only there)
+    and cg_flash_attention_forward_rope_cuda (src/cuda/flash_attn_kernels.c:568)."""
+
+    @staticmethod
+    def forward(ctx, h, w, b, Hq, Hk, D, causal, window, scale, alibi, rope):
+        B, T, _ = h.shape
+        x2 = h.reshape(B * T, -1)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        spec = (rope[0], rope[1], (Hq + Hk) * D, D, T, 0, False)
+        qkv = gemm(x2, w, bias=b, rope=spec).view(B, T, Hq + 2 * Hk, D)
+        q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hk], qkv[:, :, Hq + Hk:]
+        o, lse = flash_forward(q, k, v, causal=causal, window=window, scale=scale, alibi=alibi)
+        ctx.save_for_backward(x2, w, qkv, o, lse, alibi if alibi is not None else torch.empty(0))
+        ctx.cfg = (Hq, Hk, D, causal, window, scale, alibi is not None)
+        ctx.rope, ctx.bias, ctx.hshape = rope, b, h.shape
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        x2, w, qkv, o, lse, alibi = ctx.saved_tensors
+        Hq, Hk, D, causal, window, scale, has_alibi = ctx.cfg
+        q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hk], qkv[:, :, Hq + Hk:]
+        dqkv = torch.empty_like(qkv)
+        kw = dict(causal=causal, window=window, scale=scale, alibi=alibi if has_alibi else None)
+        if qkv.is_cuda:
+            flash_backward(do.contiguous(), q, k, v, o, lse, dq=dqkv[:, :, :Hq], dk=dqkv[:, :, Hq:Hq + Hk],
+                           dv=dqkv[:, :, Hq + Hk:], **kw)
+        else:
+            dq, dk, dv = flash_backward(do, q, k, v, o, lse, **kw)
+            dqkv[:, :, :Hq], dqkv[:, :, Hq:Hq + Hk], dqkv[:, :, Hq + Hk:] = dq, dk, dv
+        M.rope_apply_(dqkv[:, :, :Hq + Hk], ctx.rope[0], ctx.rope[1], backward=True)
+        d2 = dqkv.view(x2.shape[0], -1)
+        dh = gemm(d2, w, b_mn=True).view(ctx.hshape) if ctx.needs_input_grad[0] else None
+        dw = F._weight_grad(d2, x2, w)
+        db = F._bias_grad(d2, ctx.bias) if ctx.bias is not None else None
+        return dh, dw, db, None, None, None, None, None, None, None, None
+
+
 def packed_attention(x, Hq, Hk, *, causal=True, window=-1, scale=None, alibi=None, rope=None):
     """rope: (cos, sin) tables or None; positions are 0..T-1."""
     return _PackedAttention.apply(x, Hq, Hk, causal, window, scale, alibi, rope)
@@ -119,6 +164,10 @@ class SelfAttention(nn.Module):
         B, T, _ = h.shape
         Hq, Hk, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
         self._tables(h.device)
+        if cfg.rope and h.is_cuda and D in (64, 128) and h.dtype == torch.bfloat16:
+            o = _QKVRopeAttention.apply(h, self.qkv.weight, self.qkv.bias, Hq, Hk, D, cfg.causal, cfg.window,
+                                        1.0 / math.sqrt(D), self._alibi, self._rope)
+            return self.proj(o.reshape(B, T, Hq * D), residual=residual)
         x = self.qkv(h).view(B, T, Hq + 2 * Hk, D)
         o = packed_attention(x, Hq, Hk, causal=cfg.causal, window=cfg.window,
                              scale=1.0 / math.sqrt(D), alibi=self._alibi,

@@ -40,7 +40,10 @@ class GemmArgs(Structure):
         ("residual", c_void_p), ("ldr", c_int64),
         ("aux_out", c_void_p), ("ldaux", c_int64),
         ("aux_in", c_void_p), ("ldauxin", c_int64),
-        ("dact", c_int32), ("force_simt", c_int32), ("max_ctas", c_int32), ("split_k", c_int32),
+        ("dact", c_int32), ("force_simt", c_int32), ("max_ctas", c_int32),
+        ("rope_cos", c_void_p), ("rope_sin", c_void_p),
+        ("rope_cols", c_int32), ("rope_D", c_int32), ("rope_T", c_int32), ("rope_pos0", c_int32), ("rope_inverse", c_int32),
+        ("split_k", c_int32),
     ]
 
 

@@ -55,15 +55,30 @@ def _dact_cpu(name, x):
     return g
 
 
+def rope_reference(v, rope):
+    """Rotary embedding of the first ``cols`` columns of v [M, N] (heads of D columns; row r is
+    position r % T + pos0): the restatement of the GEMM's rotary epilogue."""
+    cos, sin, cols, D, T, pos0, inverse = rope
+    M_ = v.shape[0]
+    pos = (torch.arange(M_, device=v.device) % T) + pos0
+    c, s = cos.to(v.device)[pos].float(), sin.to(v.device)[pos].float() * (-1.0 if inverse else 1.0)     # [M, D/2]
+    x = v[:, :cols].reshape(M_, cols // D, D)
+    a, b = x[..., :D // 2], x[..., D // 2:]
+    rot = torch.cat([a * c[:, None] - b * s[:, None], b * c[:, None] + a * s[:, None]], -1).reshape(M_, cols)
+    return torch.cat([rot, v[:, cols:]], 1)
+
+
 def gemm_reference(a, b, *, a_mn=False, b_mn=False, bias=None, act=None, residual=None,
                    aux_in=None, dact=None, alpha=1.0, accumulate_into=None, out_dtype=torch.bfloat16,
-                   want_aux=False):
+                   want_aux=False, rope=None):
     """fp32 restatement of the kernel's formula (any device)."""
     A = a.float().transpose(-1, -2) if a_mn else a.float()
     B = b.float() if b_mn else b.float().transpose(-1, -2)
     v = alpha * (A @ B)
     if bias is not None:
         v = v + bias.float()
+    if rope is not None:
+        v = rope_reference(v, rope)
     aux = v.to(a.dtype) if want_aux else None   # bf16 operands: the kernel stores the pre-activation in bf16
     v = _act_cpu(act, v)
     if aux_in is not None:
@@ -74,6 +89,17 @@ def gemm_reference(a, b, *, a_mn=False, b_mn=False, bias=None, act=None, residua
         v = v + accumulate_into.float()
     out = v.to(out_dtype)
     return (out, aux) if want_aux else out
+
+
+def fill_rope(g, rope, device) -> None:
+    """Copies a rotary specification into a GemmArgs block (the tables must be fp32 on the device)."""
+    cos, sin, cols, D, T, pos0, inverse = rope
+    if cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.device != device or not cos.is_contiguous() or not sin.is_contiguous():
+        raise TypeError("rotary tables must be contiguous fp32 tensors on the operands' device")
+    if cos.shape[-1] != D // 2 or cos.shape[0] < T + pos0:
+        raise ValueError("rotary tables do not cover the positions asked for")
+    g.rope_cos, g.rope_sin = cos.data_ptr(), sin.data_ptr()
+    g.rope_cols, g.rope_D, g.rope_T, g.rope_pos0, g.rope_inverse = int(cols), int(D), int(T), int(pos0), int(bool(inverse))
 
 
 def _ld(t: torch.Tensor) -> int:
@@ -88,13 +114,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          residual: torch.Tensor | None = None, aux_out: torch.Tensor | None = None,
          aux_in: torch.Tensor | None = None, dact: str | None = None,
          accumulate: bool = False, alpha: float = 1.0, force_simt: bool = False,
-         max_ctas: int = 0, split_k: int = 0) -> torch.Tensor:
+         max_ctas: int = 0, split_k: int = 0, rope=None) -> torch.Tensor:
     """``a``: [.., M, K] (or [.., K, M] when ``a_mn``); ``b``: [.., N, K] (or [.., K, N] when ``b_mn``).
 
     ``out`` may be given (bf16 or fp32; required for ``accumulate``).  ``aux_out``
     receives the pre-activation value in bf16.  ``aux_in`` / ``dact`` multiply the
     result by the activation derivative at ``aux_in``.  ``split_k`` (fp32 ``accumulate`` outputs
     only): 0 lets the launcher slice a long K range over idle SMs, 1 forbids it, n forces n slices.
+    ``rope``: (cos, sin, cols, head_dim, T, pos0, inverse) applies the rotary embedding to the first
+    ``cols`` output columns in the epilogue (2-D bf16 output, bias allowed, nothing else).
     """
     if a_mn:
         K, M = a.shape[-2], a.shape[-1]
@@ -119,7 +147,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
                              aux_in=aux_in, dact=dact, alpha=alpha,
                              accumulate_into=out if accumulate else None,
                              out_dtype=out.dtype if out is not None else cpu_dtype,
-                             want_aux=aux_out is not None)
+                             want_aux=aux_out is not None, rope=rope)
         if aux_out is not None:
             ref, aux = ref
             aux_out.copy_(aux)
@@ -183,6 +211,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     g.force_simt = int(force_simt)
     g.max_ctas = int(max_ctas) if max_ctas else _default_max_ctas
     g.split_k = int(split_k)
+    if rope is not None:
+        fill_rope(g, rope, a.device)
     _lib.check(_lib.lib().cgk_gemm_bf16(ctypes.byref(g), _lib.stream_ptr()), "cgk_gemm_bf16")
     _lib.count_launch()
     return out

@@ -62,12 +62,16 @@ class TPLlamaBlock(nn.Module):
         Hq, Hk, D = self.hq, self.hk, self.hd
         rope = self._tables(x_shard.device)
 
+        # on GPUs the QKV GEMM rotates the q and k heads in its epilogue; elsewhere attention does it
+        fused_rope = x_shard.is_cuda and D in (64, 128) and ((Hq + 2 * Hk) * D) % 32 == 0
+
         def attend(qkv):
             x = qkv.view(B, T, Hq + 2 * Hk, D)
-            o = packed_attention(x, Hq, Hk, causal=True, scale=1.0 / math.sqrt(D), rope=rope)
+            o = packed_attention(x, Hq, Hk, causal=True, scale=1.0 / math.sqrt(D), rope=None if fused_rope else rope)
             return o.reshape(B * T, Hq * D)
 
-        x_shard = _ColumnRow.apply(self.norm1(x_shard), self.w_qkv, None, self.w_proj, None, None, x_shard, self.ws, attend)
+        x_shard = _ColumnRow.apply(self.norm1(x_shard), self.w_qkv, None, self.w_proj, None, None, x_shard, self.ws, attend,
+                                   (rope[0], rope[1], (Hq + Hk) * D, D, T) if fused_rope else None)
         return _ColumnRow.apply(self.norm2(x_shard), self.w_gate_up, None, self.w_down, None, None, x_shard, self.ws, M.swiglu)
 
 

@@ -45,11 +45,16 @@ class _ColumnRow(torch.autograd.Function):
     W2 row-sharded: the tensor-parallel MLP, and (with `inner`) the attention block."""
 
     @staticmethod
-    def forward(ctx, x_shard, w1, b1, w2, b2, act, residual, ws, inner):
+    def forward(ctx, x_shard, w1, b1, w2, b2, act, residual, ws, inner, rope=None):
+        """rope: (cos, sin, cols, head_dim, T) applies the rotary embedding to the first ``cols`` columns
+        of the first GEMM's output in its epilogue (the q and k heads of a QKV projection); ``inner``
+        then sees rotated heads, and the backward pass undoes the rotation on the gradient."""
         z = None
         if act not in (None, "none"):
             z = torch.empty(x_shard.shape[0] * ws.ranks, w1.shape[0], device=x_shard.device, dtype=x_shard.dtype)
-        h, gathered = ag_gemm(ws, x_shard, w1, bias=b1, act=act, aux_out=z)
+        spec = None if rope is None else (rope[0], rope[1], rope[2], rope[3], rope[4], 0, False)
+        h, gathered = ag_gemm(ws, x_shard, w1, bias=b1, act=act, aux_out=z, rope=spec)
+        ctx.rope = rope
         if inner is not None:
             # differentiable function applied between the two GEMMs (attention); it runs
             # under its own small autograd graph, replayed in backward
@@ -83,12 +88,15 @@ class _ColumnRow(torch.autograd.Function):
             h_in, h_out = ctx.inner_io
             (dz,) = torch.autograd.grad(h_out, h_in, dz)
             dz = dz.contiguous()
+            if ctx.rope is not None:
+                cos, sin, cols, D, T = ctx.rope
+                M.rope_apply_(dz.view(-1, T, dz.shape[1] // D, D)[:, :, :cols // D], cos, sin, backward=True)
             if has_act:
                 dz = F.unary_backward(act, z, dz)
         dw1 = _wgrad(dz, gathered, w1)
         db1 = _bgrad(dz, ctx.b1)
         dx = gemm_rs(ws, dz, w1, b_mn=True)
-        return dx, dw1, db1, dw2, db2, None, (dy if ctx.has_res else None), None, None
+        return dx, dw1, db1, dw2, db2, None, (dy if ctx.has_res else None), None, None, None
 
 
 def _ag_gemm_bwd(ws, dy_shard, w, aux_in=None, dact=None):

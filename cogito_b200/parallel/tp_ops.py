@@ -18,7 +18,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import _lib
-from ..ops.gemm import _ld, gemm
+from ..ops.gemm import _ld, fill_rope, gemm
 from .symm import SymmetricBuffer
 
 
@@ -153,12 +153,13 @@ def _fill_gemm(g, a, b, out, M, N, K, b_mn):
 
 def ag_gemm(ws: TPWorkspace, x_shard: torch.Tensor, w: torch.Tensor, *, b_mn: bool = False,
             bias=None, act=None, aux_out=None, aux_in=None, dact=None, out_dtype=torch.bfloat16,
-            keep: bool = True):
+            keep: bool = True, rope=None):
     """Returns (out [M, N], gathered [M, K]) with M = ranks * x_shard.shape[0].
 
     out = act(gather(x_shard) @ W^T + bias) [* dact'(aux_in)]; ``w`` is [N, K] (or [K, N] with
     b_mn).  ``keep=False`` says that the gathered matrix is consumed before the next-but-one
-    gather (it may then sit in one of the two alternating multicast buffers)."""
+    gather (it may then sit in one of the two alternating multicast buffers).  ``rope``: rotary
+    specification for the GEMM's epilogue (see ``ops.gemm.gemm``)."""
     rows, K = x_shard.shape
     P = ws.ranks
     M = rows * P
@@ -171,12 +172,12 @@ def ag_gemm(ws: TPWorkspace, x_shard: torch.Tensor, w: torch.Tensor, *, b_mn: bo
         else:
             gathered = x_shard
         out = gemm(gathered, w, b_mn=b_mn, bias=bias, act=act, aux_out=aux_out, aux_in=aux_in, dact=dact,
-                   out_dtype=out_dtype)
+                   out_dtype=out_dtype, rope=rope)
         return out, gathered
     if P == 1:
         x_shard = x_shard.contiguous()
         return gemm(x_shard, w, b_mn=b_mn, bias=bias, act=act, aux_out=aux_out, aux_in=aux_in, dact=dact,
-                    out_dtype=out_dtype), x_shard
+                    out_dtype=out_dtype, rope=rope), x_shard
     if rows % 128 or K % 8:
         raise ValueError("ag_gemm: rows per rank must be a multiple of 128 and K of 8")
     x_shard = x_shard.contiguous()
@@ -204,6 +205,8 @@ def ag_gemm(ws: TPWorkspace, x_shard: torch.Tensor, w: torch.Tensor, *, b_mn: bo
         g.aux_in, g.ldauxin = aux_in.data_ptr(), _ld(aux_in)
         g.dact = {"none": 0, None: 0, "gelu": 1, "relu": 2, "silu": 3, "sigmoid": 4, "tanh": 5}[dact]
     g.max_ctas = ws.max_ctas
+    if rope is not None:
+        fill_rope(g, rope, x_shard.device)
     ws.epoch += 1
     a = AgArgs()
     a.rank, a.ranks, a.epoch = ws.rank, P, ws.epoch

@@ -314,6 +314,10 @@ CGK_API int cgk_ag_gemm(const cgk_gemm_args* pg, const cgk_ag_args* px, void* st
   CGK_REQUIRE(ga.M % x.ranks == 0 && (ga.M / x.ranks) % BM == 0, "cgk_ag_gemm: rows per rank must be a multiple of 128");
   CGK_REQUIRE(ga.lda == ga.K && gemm_tma_ok(ga), "cgk_ag_gemm: gathered buffer must be dense and TMA-addressable");
   CGK_REQUIRE(x.epoch > 0 && x.chunk_rows > 0 && x.chunk_rows % BM == 0, "cgk_ag_gemm: bad epoch / chunk_rows");
+  if (ga.rope_cos) {
+    int rc2 = gemm_rope_ok(ga);
+    if (rc2) return rc2;
+  }
   int dev = 0;
   CGK_CUDA_CHECK(cudaGetDevice(&dev));
   GemmDev g;
@@ -390,7 +394,7 @@ CGK_API int cgk_gemm_rs(const cgk_gemm_args* pg, const cgk_rs_args* px, void* st
   CGK_REQUIRE(ga.batch == 1 && gemm_tma_ok(ga), "cgk_gemm_rs: operands must be 2-D and TMA-addressable");
   CGK_REQUIRE(ga.M % x.ranks == 0 && (ga.M / x.ranks) % BM == 0, "cgk_gemm_rs: rows per rank must be a multiple of 128");
   CGK_REQUIRE(ga.N % 8 == 0 && x.ld % 8 == 0 && x.ldo % 8 == 0, "cgk_gemm_rs: N and leading dimensions must be multiples of 8");
-  CGK_REQUIRE(!ga.residual && !ga.aux_out && !ga.aux_in && !ga.bias && ga.act == 0,
+  CGK_REQUIRE(!ga.residual && !ga.aux_out && !ga.aux_in && !ga.bias && ga.act == 0 && !ga.rope_cos,
               "cgk_gemm_rs: epilogue terms are applied after the reduction (pass bias / residual in cgk_rs_args)");
   int dev = 0;
   CGK_CUDA_CHECK(cudaGetDevice(&dev));

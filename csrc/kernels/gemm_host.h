@@ -14,6 +14,8 @@ int make_gemm_tmaps(const cgk_gemm_args& a, int BN, CUtensorMap* tmA, CUtensorMa
 int fill_gemm_dev(const cgk_gemm_args& a, GemmDev* g);
 // True when both operands satisfy TMA's alignment rules.
 bool gemm_tma_ok(const cgk_gemm_args& a);
+// Checks the arguments of the rotary epilogue (0 or CGK_E_ARG).
+int gemm_rope_ok(const cgk_gemm_args& a);
 // Tile width (256 / 128 / 64) for a problem run by `ctas` persistent CTAs.
 int pick_bn(const cgk_gemm_args& a, int ctas);
 

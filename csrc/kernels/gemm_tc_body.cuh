@@ -28,6 +28,9 @@ struct GemmDev {
   long long ldauxin;
   int dact;
   int* status;
+  // Rotary embedding applied to output columns [0, rope_cols) (see cgk_gemm_args)
+  const float* rope_cos; const float* rope_sin;
+  int rope_cols, rope_D, rope_T, rope_pos0, rope_inverse;
   // Split-K: every output tile is computed by split_k work units, each over kb_per_split
   // k-blocks, that add their part into the fp32 output with vector reductions (only with
   // out_fp32 && accumulate and no other epilogue term).  For weight gradients: a small

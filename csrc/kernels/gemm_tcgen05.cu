@@ -114,6 +114,9 @@ int fill_gemm_dev(const cgk_gemm_args& a, GemmDev* pg) {
   g.aux_out = (__nv_bfloat16*)a.aux_out; g.ldaux = a.ldaux;
   g.aux_in = (const __nv_bfloat16*)a.aux_in; g.ldauxin = a.ldauxin;
   g.dact = a.dact;
+  g.rope_cos = a.rope_cos; g.rope_sin = a.rope_sin;
+  g.rope_cols = a.rope_cols; g.rope_D = a.rope_D; g.rope_T = a.rope_T; g.rope_pos0 = a.rope_pos0;
+  g.rope_inverse = a.rope_inverse;
   g.split_k = 1;
   g.kb_per_split = 0;
   g.status = device_status(dev);
@@ -126,7 +129,18 @@ bool gemm_tma_ok(const cgk_gemm_args& a) {
          (a.batch == 1 || (a.strideA % 8 == 0 && a.strideB % 8 == 0)) && a.K > 0;
 }
 
+int gemm_rope_ok(const cgk_gemm_args& a) {
+  CGK_REQUIRE(a.rope_sin && (a.rope_D == 64 || a.rope_D == 128) && a.rope_cols > 0 && a.rope_cols % a.rope_D == 0 &&
+                  a.rope_cols <= a.N && a.rope_T > 0 && a.rope_pos0 >= 0,
+              "gemm: rotary epilogue needs sin/cos tables, head_dim 64 or 128 and whole heads");
+  CGK_REQUIRE(a.batch == 1 && !a.out_fp32 && !a.accumulate && a.act == 0 && !a.residual && !a.aux_out && !a.aux_in &&
+                  a.N % 32 == 0 && a.ldc % 8 == 0 && (((uintptr_t)a.out) & 15) == 0 && !a.force_simt && gemm_tma_ok(a),
+              "gemm: the rotary epilogue takes a plain bf16 2-D output (bias allowed), N a multiple of 32");
+  return 0;
+}
+
 int pick_bn(const cgk_gemm_args& a, int ctas) {
+  if (a.rope_cos) return 256;       // both halves of a tile's columns must hold whole heads of up to 128 elements
   const long long tm = (a.M + BM - 1) / BM;
   auto tiles = [&](int bn) { return (long long)a.batch * tm * ((a.N + bn - 1) / bn); };
   // Widest tile that still gives every SM work; narrow tiles for small problems.
@@ -171,6 +185,10 @@ CGK_API int cgk_gemm_bf16(const cgk_gemm_args* pa, void* stream_) {
   if (rc) return rc;
   CGK_REQUIRE(a.batch == 1 || !(a.residual || a.aux_out || a.aux_in),
               "cgk_gemm_bf16: residual/aux epilogues are 2-D only");
+  if (a.rope_cos) {
+    int rc2 = gemm_rope_ok(a);
+    if (rc2) return rc2;
+  }
   if (a.force_simt || !gemm_tma_ok(a)) {
     dim3 grid((a.N + 31) / 32, (a.M + 31) / 32, a.batch);
     dim3 block(32, 32, 1);

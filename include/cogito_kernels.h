@@ -56,6 +56,12 @@ typedef struct {
   int32_t dact;
   int32_t force_simt; /* testing: use the CUDA-core fallback */
   int32_t max_ctas;   /* 0 = one persistent CTA per SM */
+  /* Rotary embedding in the epilogue (the QKV projection): output columns [0, rope_cols) are heads of
+   * rope_D (64 or 128) elements; element pairs (i, i + rope_D / 2) of a head are rotated by the angle
+   * of position (row % rope_T) + rope_pos0, taken from fp32 tables [positions][rope_D / 2]
+   * (rope_inverse: by the negative angle).  bf16 output only, no activation / residual / aux. */
+  const float* rope_cos; const float* rope_sin;
+  int32_t rope_cols, rope_D, rope_T, rope_pos0, rope_inverse;
   int32_t split_k;    /* fp32 accumulating outputs only: 0 = split the K range over idle SMs when the
                          output has few tiles (partial sums meet in the output through fp32 reductions,
                          so their order, and the last bits, can differ between runs), 1 = never, n = n slices */

@@ -57,6 +57,28 @@ def test_gemm_split_k_weight_gradient(Mw, Nw, K, split):
     assert relerr(one, ref) < 2e-3
 
 
+@pytest.mark.parametrize("D,heads_rot,heads_all,T", [(64, 6, 9, 128), (128, 5, 6, 96), (64, 3, 3, 64), (128, 2, 3, 50)])
+@pytest.mark.parametrize("inverse", [False, True])
+def test_gemm_rotary_epilogue(D, heads_rot, heads_all, T, inverse):
+    """QKV projection with the rotary embedding applied in the epilogue, against the fp32 restatement
+    (bias first, then the rotation of the first heads_rot heads; the remaining columns untouched)."""
+    from cogito_b200.ops.gemm import gemm, gemm_reference
+    from cogito_b200.ops.misc import rope_tables
+    torch.manual_seed(3)
+    M, K, N = 3 * T, 200, heads_all * D
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.1
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    cos, sin = rope_tables(T + 7, D, 10000.0, DEV)
+    spec = (cos, sin, heads_rot * D, D, T, 5, inverse)
+    out = gemm(a, w, bias=bias, rope=spec)
+    ref = gemm_reference(a, w, bias=bias, rope=spec, out_dtype=torch.float32)
+    assert relerr(out, ref) < 1e-2
+    # the columns behind the rotated heads are the plain projection
+    plain = gemm(a, w, bias=bias)
+    assert torch.equal(out[:, heads_rot * D:], plain[:, heads_rot * D:])
+
+
 def test_gemm_simt_fallback_unaligned():
     from cogito_b200.ops.gemm import gemm, gemm_reference
     torch.manual_seed(0)

@@ -112,3 +112,27 @@ def test_bounded_wait_times_out_with_a_status_and_the_context_survives():
     _lib.check(L.cgk_selftest_bounded_wait(flag.data_ptr(), 2, 200_000_000, reached.data_ptr(), _lib.stream_ptr()))
     assert _lib.read_status()[0] == 0 and int(reached) == 1
     assert torch.ones(4, device=DEV).sum().item() == 4       # the context is intact
+
+
+def test_attention_with_rotary_epilogue_matches_the_unfused_path():
+    """SelfAttention with RoPE: on the GPU the QKV GEMM rotates q and k in its epilogue; the CPU path
+    rotates the projection buffer in a pass of its own.  Same outputs and gradients."""
+    import copy
+    from cogito_b200.nn.transformer import SelfAttention, TransformerConfig
+    from cogito_b200.utils.rng import manual_seed
+    manual_seed(0)
+    for D, Hq, Hk in ((64, 4, 2), (128, 2, 1)):
+        cfg = TransformerConfig(hidden_size=Hq * D, num_heads=Hq, num_kv_heads=Hk, head_dim=D, bias=False, rope=True, max_seq_len=96)
+        cpu = SelfAttention(cfg)
+        gpu = copy.deepcopy(cpu).to("cuda", torch.bfloat16)
+        x = torch.randn(2, 96, Hq * D)
+        xc = x.clone().requires_grad_(True)
+        xg = x.to("cuda", torch.bfloat16).requires_grad_(True)
+        yc, yg = cpu(xc), gpu(xg)
+        g = torch.randn_like(yc)
+        yc.backward(g)
+        yg.backward(g.to("cuda", torch.bfloat16))
+        rel = lambda a, b: float((a.float().cpu() - b.float()).abs().max() / (b.float().abs().max() + 1e-6))
+        assert rel(yg, yc) < 3e-2
+        assert rel(xg.grad, xc.grad) < 4e-2
+        assert rel(gpu.qkv.weight.grad, cpu.qkv.weight.grad) < 4e-2
