@@ -113,8 +113,8 @@ class LayerNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(dim, device=device, dtype=dtype))
         self.bias = nn.Parameter(torch.zeros(dim, device=device, dtype=dtype)) if bias else None
 
-    def forward(self, x, residual=None):
-        return N.layer_norm(_maybe_bf16(x), self.weight, self.bias, self.eps, residual)
+    def forward(self, x, residual=None, passthrough=False):
+        return N.layer_norm(_maybe_bf16(x), self.weight, self.bias, self.eps, residual, passthrough)
 
 
 class RMSNorm(nn.Module):
@@ -123,8 +123,8 @@ class RMSNorm(nn.Module):
         self.eps = eps
         self.weight = nn.Parameter(torch.ones(dim, device=device, dtype=dtype))
 
-    def forward(self, x, residual=None):
-        return N.rms_norm(_maybe_bf16(x), self.weight, self.eps, residual)
+    def forward(self, x, residual=None, passthrough=False):
+        return N.rms_norm(_maybe_bf16(x), self.weight, self.eps, residual, passthrough)
 
 
 class BatchNorm1d(nn.Module):

@@ -214,8 +214,12 @@ class TransformerBlock(nn.Module):
             if cfg.dropout > 0 and self.training:
                 x = x + self.drop(self.attn(self.norm1(x)))
                 return x + self.drop(self.mlp(self.norm2(x)))
-            x = self.attn(self.norm1(x), residual=x)
-            return self.mlp(self.norm2(x), residual=x)
+            # the norm hands its input back as a second result for the residual branch, so that the
+            # two gradients of x are summed inside the norm's backward kernel
+            h, xr = self.norm1(x, passthrough=True)
+            x = self.attn(h, residual=xr)
+            h, xr = self.norm2(x, passthrough=True)
+            return self.mlp(h, residual=xr)
         # post-norm: x = norm(x + f(x))
         x = self.norm1(x + self.drop(self.attn(x)))
         return self.norm2(x + self.drop(self.mlp(x)))

@@ -93,7 +93,7 @@ def norm_backward_raw(dy2, s2, gamma, mean, rstd, rms, dres2=None, dgamma_out=No
 
 class _Norm(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, gamma, beta, residual, eps, rms):
+    def forward(ctx, x, gamma, beta, residual, eps, rms, passthrough=False):
         D = x.shape[-1]
         x2 = x.reshape(-1, D)
         if not x2.is_contiguous():
@@ -112,6 +112,10 @@ class _Norm(torch.autograd.Function):
         ctx.shape = x.shape
         if residual is not None:
             return y.reshape(x.shape), s.reshape(x.shape)
+        if passthrough:
+            # the input goes out again as a second result (the residual branch reads it); its gradient
+            # comes back as `dsum` and is added inside the backward kernel instead of by autograd
+            return y.reshape(x.shape), x.view_as(x)
         return y.reshape(x.shape)
 
     @staticmethod
@@ -133,12 +137,15 @@ class _Norm(torch.autograd.Function):
         dbeta = None
         if b is not None and not ctx.rms:
             dbeta = None if mg_b is not None else db.to(b.dtype)
-        return dx, dgamma, dbeta, (dx if ctx.has_res else None), None, None
+        return dx, dgamma, dbeta, (dx if ctx.has_res else None), None, None, None
 
 
-def layer_norm(x, gamma, beta=None, eps: float = 1e-5, residual=None):
-    return _Norm.apply(x, gamma, beta, residual, eps, False)
+def layer_norm(x, gamma, beta=None, eps: float = 1e-5, residual=None, passthrough: bool = False):
+    """``passthrough=True`` (without ``residual``) returns ``(y, x)``: use the second result wherever
+    the block reads ``x`` again (its residual branch); the two gradients then meet inside the norm's
+    backward kernel instead of in a separate addition."""
+    return _Norm.apply(x, gamma, beta, residual, eps, False, passthrough)
 
 
-def rms_norm(x, gamma, eps: float = 1e-6, residual=None):
-    return _Norm.apply(x, gamma, None, residual, eps, True)
+def rms_norm(x, gamma, eps: float = 1e-6, residual=None, passthrough: bool = False):
+    return _Norm.apply(x, gamma, None, residual, eps, True, passthrough)

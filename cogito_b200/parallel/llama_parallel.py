@@ -70,9 +70,11 @@ class TPLlamaBlock(nn.Module):
             o = packed_attention(x, Hq, Hk, causal=True, scale=1.0 / math.sqrt(D), rope=None if fused_rope else rope)
             return o.reshape(B * T, Hq * D)
 
-        x_shard = _ColumnRow.apply(self.norm1(x_shard), self.w_qkv, None, self.w_proj, None, None, x_shard, self.ws, attend,
+        h, xr = self.norm1(x_shard, passthrough=True)     # gradients of the stream meet inside the norm's backward
+        x_shard = _ColumnRow.apply(h, self.w_qkv, None, self.w_proj, None, None, xr, self.ws, attend,
                                    (rope[0], rope[1], (Hq + Hk) * D, D, T) if fused_rope else None)
-        return _ColumnRow.apply(self.norm2(x_shard), self.w_gate_up, None, self.w_down, None, None, x_shard, self.ws, M.swiglu)
+        h, xr = self.norm2(x_shard, passthrough=True)
+        return _ColumnRow.apply(h, self.w_gate_up, None, self.w_down, None, None, xr, self.ws, M.swiglu)
 
 
 class _SeqShardEmbedding(torch.autograd.Function):

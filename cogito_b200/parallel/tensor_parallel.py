@@ -174,8 +174,10 @@ class TPBlock(nn.Module):
             p.tp_replicated = True
 
     def forward(self, x_shard, batch_tokens):
-        x_shard = self.attn(self.ln1(x_shard), x_shard, batch_tokens)
-        return self.mlp(self.ln2(x_shard), x_shard)
+        h, xr = self.ln1(x_shard, passthrough=True)       # gradients of the stream meet inside the norm's backward
+        x_shard = self.attn(h, xr, batch_tokens)
+        h, xr = self.ln2(x_shard, passthrough=True)
+        return self.mlp(h, xr)
 
 
 class _VocabParallelEmbedding(torch.autograd.Function):

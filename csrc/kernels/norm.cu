@@ -136,6 +136,15 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
   for (int i = lane; i < 2 * D; i += 32) mine[i] = 0.0f;
   __syncwarp();
   const uint4* gp = reinterpret_cast<const uint4*>(gamma);
+  // A lane sees the same columns in every row, so for rows of up to 1024 elements its partial
+  // sums of dgamma / dbeta stay in registers across all rows the warp handles and reach shared
+  // memory once, at the end (a read-modify-write of shared memory per row was the kernel's bottleneck).
+  constexpr bool REGACC = MAXV <= 4;
+  float accg[REGACC ? MAXV * 8 : 1], accb[REGACC ? MAXV * 8 : 1];
+  if (REGACC) {
+#pragma unroll
+    for (int i = 0; i < (REGACC ? MAXV * 8 : 1); ++i) { accg[i] = 0.0f; accb[i] = 0.0f; }
+  }
   for (long long row = (long long)blockIdx.x * NORM_WARPS + warp; row < rows;
        row += (long long)gridDim.x * NORM_WARPS) {
     const float mean = RMS ? 0.0f : mean_in[row];
@@ -154,9 +163,6 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
         unpack8(xr[i], xv);
         unpack8(dr[i], dv);
         unpack8(__ldg(gp + c), g);
-        float4* pg = reinterpret_cast<float4*>(mine + c * 8);
-        float4* pb = reinterpret_cast<float4*>(mine + D + c * 8);
-        float4 g0 = pg[0], g1 = pg[1], b0 = pb[0], b1 = pb[1];
         float h[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -165,11 +171,19 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
           s1 += t;
           s2 += t * h[j];
         }
-        g0.x += dv[0] * h[0]; g0.y += dv[1] * h[1]; g0.z += dv[2] * h[2]; g0.w += dv[3] * h[3];
-        g1.x += dv[4] * h[4]; g1.y += dv[5] * h[5]; g1.z += dv[6] * h[6]; g1.w += dv[7] * h[7];
-        b0.x += dv[0]; b0.y += dv[1]; b0.z += dv[2]; b0.w += dv[3];
-        b1.x += dv[4]; b1.y += dv[5]; b1.z += dv[6]; b1.w += dv[7];
-        pg[0] = g0; pg[1] = g1; pb[0] = b0; pb[1] = b1;
+        if (REGACC) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { accg[(REGACC ? i : 0) * 8 + j] += dv[j] * h[j]; accb[(REGACC ? i : 0) * 8 + j] += dv[j]; }
+        } else {
+          float4* pg = reinterpret_cast<float4*>(mine + c * 8);
+          float4* pb = reinterpret_cast<float4*>(mine + D + c * 8);
+          float4 g0 = pg[0], g1 = pg[1], b0 = pb[0], b1 = pb[1];
+          g0.x += dv[0] * h[0]; g0.y += dv[1] * h[1]; g0.z += dv[2] * h[2]; g0.w += dv[3] * h[3];
+          g1.x += dv[4] * h[4]; g1.y += dv[5] * h[5]; g1.z += dv[6] * h[6]; g1.w += dv[7] * h[7];
+          b0.x += dv[0]; b0.y += dv[1]; b0.z += dv[2]; b0.w += dv[3];
+          b1.x += dv[4]; b1.y += dv[5]; b1.z += dv[6]; b1.w += dv[7];
+          pg[0] = g0; pg[1] = g1; pb[0] = b0; pb[1] = b1;
+        }
       }
     }
     s1 = RMS ? 0.0f : warp_sum(s1) / D;
@@ -196,6 +210,16 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
           for (int j = 0; j < 8; ++j) o[j] += r[j];
         }
         op[c] = pack8(o);
+      }
+    }
+  }
+  if (REGACC) {
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int c = lane + i * 32;
+      if (c < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { mine[c * 8 + j] = accg[(REGACC ? i : 0) * 8 + j]; mine[D + c * 8 + j] = accb[(REGACC ? i : 0) * 8 + j]; }
       }
     }
   }
@@ -227,6 +251,16 @@ __global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, int np
 }  // namespace cgk
 
 using namespace cgk;
+
+// CTAs of the backward kernel: as many as fit an SM by shared memory (each holds 2 * D floats per
+// warp), up to eight per SM: a streaming kernel needs that many warps to keep the memory pipe full.
+static int norm_bwd_cap(int dev, int D) {
+  const size_t smem = (size_t)NORM_WARPS * 2 * D * sizeof(float);
+  int per_sm = (int)((200 * 1024) / (smem + 1024));
+  if (per_sm > 8) per_sm = 8;
+  if (per_sm < 1) per_sm = 1;
+  return sm_count(dev) * per_sm;
+}
 
 // rms = 0: LayerNorm (beta may be null), rms = 1: RMSNorm (beta ignored, mean unused).
 // residual / sum_out / mean / rstd may be null.  D must be a multiple of 8, D <= 8192.
@@ -269,7 +303,7 @@ CGK_API long long cgk_norm_backward_scratch_elems(int rows, int D) {
   int dev = 0;
   cudaGetDevice(&dev);
   int grid = (rows + NORM_WARPS - 1) / NORM_WARPS;
-  int cap = sm_count(dev) * 2;
+  int cap = norm_bwd_cap(dev, D);
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
   return (long long)grid * 2 * D;
@@ -289,7 +323,7 @@ CGK_API int cgk_norm_backward(const void* dy, const void* x, const void* gamma, 
   int dev = 0;
   CGK_CUDA_CHECK(cudaGetDevice(&dev));
   int grid = (rows + NORM_WARPS - 1) / NORM_WARPS;
-  int cap = sm_count(dev) * 2;
+  int cap = norm_bwd_cap(dev, D);
   if (grid > cap) grid = cap;
   const size_t smem = (size_t)NORM_WARPS * 2 * D * sizeof(float);
   const int need = (D / 8 + 31) / 32;
