@@ -188,6 +188,37 @@ def assert_device_ok() -> None:
         raise KernelError(f"index outside its range (file, line, index, limit): {bad}")
 
 
+# ---------------------------------------------------------------------------
+# Gradient slots.  A parameter's fp32 gradient buffer is ``p.main_grad``.  A model that runs two
+# parts of a batch on two streams at once gives every parameter one buffer per part
+# (``p.main_grad_slots``) so that the two backward passes never accumulate into the same memory
+# concurrently; autograd Functions note the slot that was current in their forward pass and
+# select it again around their backward pass.
+# ---------------------------------------------------------------------------
+_grad_slot = 0
+
+
+def grad_slot() -> int:
+    return _grad_slot
+
+
+def set_grad_slot(i: int) -> int:
+    """Selects the gradient slot; returns the previous one."""
+    global _grad_slot
+    prev, _grad_slot = _grad_slot, int(i)
+    return prev
+
+
+def main_grad_of(p):
+    """The fp32 buffer the gradient of ``p`` is accumulated into (None: use autograd's .grad)."""
+    if p is None:
+        return None
+    slots = getattr(p, "main_grad_slots", None)
+    if slots is not None:
+        return slots[_grad_slot]
+    return getattr(p, "main_grad", None)
+
+
 _launches = 0
 
 

@@ -31,7 +31,7 @@ def _scratch(n: int, device, dtype=torch.float32) -> torch.Tensor:
 # ---------------------------------------------------------------------------
 def _weight_grad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor):
     """dW[N, K] = dy2[M, N]^T @ x2[M, K].  Returns None when accumulated into main_grad."""
-    mg = getattr(w, "main_grad", None)
+    mg = _lib.main_grad_of(w)
     if mg is not None:
         gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=True)
         return None
@@ -61,7 +61,7 @@ def colsum(dy2: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool 
 def _bias_grad(dy2: torch.Tensor, b: torch.Tensor | None):
     if b is None:
         return None
-    mg = getattr(b, "main_grad", None)
+    mg = _lib.main_grad_of(b)
     if mg is not None:
         colsum(dy2, out=mg, accumulate=True)
         return None

@@ -110,6 +110,7 @@ class _Norm(torch.autograd.Function):
         ctx.params = (gamma, beta)
         ctx.has_res = residual is not None
         ctx.shape = x.shape
+        ctx.slot = _lib.grad_slot()
         if residual is not None:
             return y.reshape(x.shape), s.reshape(x.shape)
         if passthrough:
@@ -129,9 +130,13 @@ class _Norm(torch.autograd.Function):
             d2 = dsum.reshape(-1, D)
             if not d2.is_contiguous():
                 d2 = d2.contiguous()
-        mg_g = getattr(g, "main_grad", None)
-        mg_b = getattr(b, "main_grad", None) if b is not None else None
-        dx, dg, db = norm_backward_raw(dy2, src, gamma, mean, rstd, ctx.rms, d2, mg_g, mg_b)
+        prev = _lib.set_grad_slot(ctx.slot)
+        try:
+            mg_g = _lib.main_grad_of(g)
+            mg_b = _lib.main_grad_of(b)
+            dx, dg, db = norm_backward_raw(dy2, src, gamma, mean, rstd, ctx.rms, d2, mg_g, mg_b)
+        finally:
+            _lib.set_grad_slot(prev)
         dx = dx.reshape(ctx.shape)
         dgamma = None if mg_g is not None else dg.to(g.dtype)
         dbeta = None

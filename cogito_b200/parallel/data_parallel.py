@@ -121,8 +121,11 @@ class DPFusedAdam:
         self.ext_stats_fn = None      # callable(local {norm^2, overflow} tensor) -> tensor agreed by a larger group
         if self.cuda:
             self.reduce_ctas = max(1, min(int(reduce_ctas), 1024))
+            # buckets that are still open when the backward pass ends (the tied embedding's) are reduced
+            # with the whole GPU: nothing else runs then, and a CTA pulls only ~7 GB/s from its peers
+            self.tail_ctas = max(self.reduce_ctas, min(1024, torch.cuda.get_device_properties(dev).multi_processor_count))
             self.gsum = torch.empty(per, dtype=torch.float32, device=dev)
-            self.block_part = torch.zeros(self.nbuckets, 2 * self.reduce_ctas, dtype=torch.float32, device=dev)
+            self.block_part = torch.zeros(self.nbuckets, 2 * self.tail_ctas, dtype=torch.float32, device=dev)
             self.arrive = torch.zeros(self.nbuckets + 1, dtype=torch.int32, device=dev)
             self.bucket_stats = torch.zeros(self.nbuckets, 2, dtype=torch.float32, device=dev)
             self.comm_stream = torch.cuda.Stream(device=dev)
@@ -187,11 +190,11 @@ class DPFusedAdam:
         for b in sorted(todo, reverse=True):
             self._reduce_bucket(b, self.comm_stream)
 
-    def _reduce_bucket(self, b: int, stream) -> None:
+    def _reduce_bucket(self, b: int, stream, ctas: int | None = None) -> None:
         P = self.ranks
         begin, count, off = self.segments[b]
         a = DpBucketArgs()
-        a.rank, a.ranks, a.epoch, a.bucket, a.grid_ctas = self.rank, P, self.epoch + 1, b, self.reduce_ctas
+        a.rank, a.ranks, a.epoch, a.bucket, a.grid_ctas = self.rank, P, self.epoch + 1, b, ctas or self.reduce_ctas
         for r in range(P):
             a.grad_ptrs[r] = self.sym.ptrs[r] + self._g_off
             a.signal_ptrs[r] = self.sym.ptrs[r] + self._s_off
@@ -288,7 +291,7 @@ class DPFusedAdam:
             if not self._armed:
                 self._launched = set()
             for b in sorted(rest, reverse=True):       # what the backward pass did not release: on the main stream
-                self._reduce_bucket(b, main)
+                self._reduce_bucket(b, main, self.tail_ctas)
             if len(rest) < self.nbuckets:
                 ev = torch.cuda.Event()
                 ev.record(self.comm_stream)

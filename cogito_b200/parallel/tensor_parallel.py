@@ -55,6 +55,7 @@ class _ColumnRow(torch.autograd.Function):
         spec = None if rope is None else (rope[0], rope[1], rope[2], rope[3], rope[4], 0, False)
         h, gathered = ag_gemm(ws, x_shard, w1, bias=b1, act=act, aux_out=z, rope=spec)
         ctx.rope = rope
+        ctx.slot = _lib.grad_slot()
         if inner is not None:
             # differentiable function applied between the two GEMMs (attention); it runs
             # under its own small autograd graph, replayed in backward
@@ -74,6 +75,14 @@ class _ColumnRow(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
+        prev = _lib.set_grad_slot(ctx.slot)
+        try:
+            return _ColumnRow._backward(ctx, dy)
+        finally:
+            _lib.set_grad_slot(prev)
+
+    @staticmethod
+    def _backward(ctx, dy):
         gathered, w1, w2, z, h2 = ctx.saved_tensors
         ws, act = ctx.ws, ctx.act
         dy = dy.contiguous()
@@ -130,7 +139,7 @@ class TPAttention(nn.Module):
         self.b_proj.tp_replicated = True
         self.seq_len = None
 
-    def forward(self, h_shard, residual, batch_tokens):
+    def forward(self, h_shard, residual, batch_tokens, ws=None):
         B, T = batch_tokens
         Hl, D = self.h_local, self.hd
 
@@ -140,7 +149,7 @@ class TPAttention(nn.Module):
             return o.reshape(B * T, Hl * D)
 
         return _ColumnRow.apply(h_shard, self.w_qkv, self.b_qkv, self.w_proj, self.b_proj, None, residual,
-                                self.ws, attend)
+                                ws or self.ws, attend)
 
 
 class TPMLP(nn.Module):
@@ -159,8 +168,8 @@ class TPMLP(nn.Module):
         self.b2 = nn.Parameter(torch.zeros(d_model, device=device, dtype=dtype))
         self.b2.tp_replicated = True
 
-    def forward(self, h_shard, residual):
-        return _ColumnRow.apply(h_shard, self.w1, self.b1, self.w2, self.b2, self.act, residual, self.ws, None)
+    def forward(self, h_shard, residual, ws=None):
+        return _ColumnRow.apply(h_shard, self.w1, self.b1, self.w2, self.b2, self.act, residual, ws or self.ws, None)
 
 
 class TPBlock(nn.Module):
@@ -173,11 +182,11 @@ class TPBlock(nn.Module):
         for p in list(self.ln1.parameters()) + list(self.ln2.parameters()):
             p.tp_replicated = True
 
-    def forward(self, x_shard, batch_tokens):
+    def forward(self, x_shard, batch_tokens, ws=None):
         h, xr = self.ln1(x_shard, passthrough=True)       # gradients of the stream meet inside the norm's backward
-        x_shard = self.attn(h, xr, batch_tokens)
+        x_shard = self.attn(h, xr, batch_tokens, ws)
         h, xr = self.ln2(x_shard, passthrough=True)
-        return self.mlp(h, xr)
+        return self.mlp(h, xr, ws)
 
 
 class _VocabParallelEmbedding(torch.autograd.Function):
@@ -199,6 +208,7 @@ class _VocabParallelEmbedding(torch.autograd.Function):
         shard = (shard.float() + wpe.detach()[pos].float()).to(partial.dtype)
         ctx.save_for_backward(ids, pos)
         ctx.ws, ctx.params = ws, (wte, wpe)
+        ctx.slot = _lib.grad_slot()
         return shard
 
     @staticmethod
@@ -214,7 +224,9 @@ class _VocabParallelEmbedding(torch.autograd.Function):
             dist.all_gather_into_tensor(full, dshard, group=ws.group)
         else:
             full = dshard
-        g_wte = getattr(wte, "main_grad", None)
+        prev = _lib.set_grad_slot(ctx.slot)
+        g_wte, g_wpe = _lib.main_grad_of(wte), _lib.main_grad_of(wpe)
+        _lib.set_grad_slot(prev)
         own = g_wte is None
         if own:
             g_wte = torch.zeros(wte.shape, device=wte.device, dtype=torch.float32)
@@ -228,7 +240,6 @@ class _VocabParallelEmbedding(torch.autograd.Function):
             local = (ids.reshape(-1) - r * Vl)
             ok = (local >= 0) & (local < Vl)
             g_wte.index_add_(0, local[ok], full.float()[ok])
-        g_wpe = getattr(wpe, "main_grad", None)
         own_p = g_wpe is None
         if own_p:
             g_wpe = torch.zeros(wpe.shape, device=wpe.device, dtype=torch.float32)
@@ -297,12 +308,17 @@ class _LMHead(torch.autograd.Function):
         logits, gathered = ag_gemm(ws, h_shard, wte)
         ctx.save_for_backward(gathered, wte)
         ctx.ws = ws
+        ctx.slot = _lib.grad_slot()
         return logits
 
     @staticmethod
     def backward(ctx, dlogits):
         gathered, wte = ctx.saved_tensors
-        dw = _wgrad(dlogits, gathered, wte)
+        prev = _lib.set_grad_slot(ctx.slot)
+        try:
+            dw = _wgrad(dlogits, gathered, wte)
+        finally:
+            _lib.set_grad_slot(prev)
         dh = gemm_rs(ctx.ws, dlogits, wte, b_mn=True)
         return dh, dw, None
 
@@ -311,9 +327,12 @@ class TPGPT2(nn.Module):
     """GPT-2 with every matmul tensor-parallel: vocabulary-sharded embedding / output head,
     head-sharded attention, column/row-sharded MLP, sequence-sharded residual stream."""
 
-    def __init__(self, cfg, ws: TPWorkspace, device=None, dtype=None):
+    def __init__(self, cfg, ws: TPWorkspace, device=None, dtype=None, ws2: TPWorkspace | None = None):
         super().__init__()
         self.cfg, self.ws = cfg, ws
+        # a second workspace turns on the two-halves-on-two-streams forward / backward pass
+        self.workspaces = [ws] + ([ws2] if ws2 is not None else [])
+        self._streams = [torch.cuda.Stream(device=ws.device), torch.cuda.Stream(device=ws.device)] if ws2 is not None else []
         P = ws.ranks
         if cfg.vocab_size % P:
             raise ValueError("vocabulary must divide evenly over the tensor-parallel ranks")
@@ -329,17 +348,63 @@ class TPGPT2(nn.Module):
         for p in self.ln_f.parameters():
             p.tp_replicated = True
 
-    def forward(self, ids, targets=None, grad_scale=1.0):
+    def _forward_part(self, ids, targets, grad_scale, ws):
         B, T = ids.shape
-        self.ws.begin_step()         # the gathered activations of the previous pass are dead
-        x = _VocabParallelEmbedding.apply(ids, self.wte, self.wpe, self.ws)
+        ws.begin_step()              # the gathered activations of the previous pass are dead
+        x = _VocabParallelEmbedding.apply(ids, self.wte, self.wpe, ws)
         for blk in self.blocks:
-            x = blk(x, (B, T))
+            x = blk(x, (B, T), ws)
         h = self.ln_f(x)
-        logits = _LMHead.apply(h, self.wte, self.ws)
+        logits = _LMHead.apply(h, self.wte, ws)
         if targets is None:
             return logits
-        return _VocabParallelCE.apply(logits, targets, grad_scale, self.ws)
+        return _VocabParallelCE.apply(logits, targets, grad_scale, ws)
+
+    def forward(self, ids, targets=None, grad_scale=1.0):
+        """With a second workspace (``overlap=True`` at construction) and targets, the batch is cut in
+        two halves that run on two streams at once: while the all-gather / reduce-scatter kernels of
+        one half wait for NVLink, the attention and weight-gradient kernels of the other half have
+        the SMs (the fused kernels are capped to a part of the GPU for that).  Each half accumulates
+        its parameter gradients into its own buffer (gradient slots); ``TPGradSync`` adds them up."""
+        B, T = ids.shape
+        if len(self.workspaces) < 2 or targets is None or not ids.is_cuda or B < 2 or (B // 2) * T % (128 * self.ws.ranks):
+            return self._forward_part(ids, targets, grad_scale, self.ws)
+        main = torch.cuda.current_stream()
+        start = torch.cuda.Event()
+        start.record(main)
+        half = B // 2
+        parts = [(ids[:half], targets[:half]), (ids[half:], targets[half:])]
+        # each half's loss is a mean over its own rows: scale its gradient by its share of the batch
+        share = [half / B, (B - half) / B]
+        xs = [None, None]
+
+        def on(i, fn):
+            """Issue fn on half i's stream with half i's gradient slot selected."""
+            prev = _lib.set_grad_slot(i)
+            try:
+                with torch.cuda.stream(self._streams[i]):
+                    return fn()
+            finally:
+                _lib.set_grad_slot(prev)
+
+        # The halves are issued layer by layer in turn, so that both streams always have work queued
+        # and the backward pass (which autograd issues in the reverse of this order) alternates too.
+        for i in (0, 1):
+            self._streams[i].wait_event(start)
+            self.workspaces[i].begin_step()
+            xs[i] = on(i, lambda i=i: _VocabParallelEmbedding.apply(parts[i][0], self.wte, self.wpe, self.workspaces[i]))
+        for blk in self.blocks:
+            for i in (0, 1):
+                xs[i] = on(i, lambda i=i: blk(xs[i], (parts[i][0].shape[0], T), self.workspaces[i]))
+        losses = []
+        for i in (0, 1):
+            def tail(i=i):
+                logits = _LMHead.apply(self.ln_f(xs[i]), self.wte, self.workspaces[i])
+                return _VocabParallelCE.apply(logits, parts[i][1], grad_scale * share[i], self.workspaces[i])
+            losses.append(on(i, tail))
+        for st in self._streams:
+            main.wait_stream(st)
+        return losses[0] * share[0] + losses[1] * share[1]
 
     def ordered_parameters(self):
         """Replicated parameters first, so their gradients are one contiguous slice."""
@@ -349,13 +414,16 @@ class TPGPT2(nn.Module):
 
 
 class TPGradSync:
-    """All-reduces the gradients of the replicated parameters over the TP group."""
+    """All-reduces the gradients of the replicated parameters over the TP group; with the two-stream
+    forward pass it first gives every parameter a second gradient buffer (one per half of the
+    batch) and adds the two up before the optimizer step."""
 
     def __init__(self, model: TPGPT2):
         self.model = model
         self.n_rep = None
         self.group = model.ws.group
         self.ranks = model.ws.ranks
+        self.grad2 = None
 
     def attach(self, opt):
         rep, _ = self.model.ordered_parameters()
@@ -364,20 +432,42 @@ class TPGradSync:
             if getattr(p, "tp_replicated", False):
                 n = o + (p.numel() + 7) // 8 * 8
         self.n_rep = n
+        if len(self.model.workspaces) > 1:
+            self.grad2 = torch.zeros_like(opt.grad)
+            for p, a, b in zip(opt.fp.params, opt.fp.views(opt.grad), opt.fp.views(self.grad2)):
+                p.main_grad_slots = [a, b]
 
     def reduce_gradients(self, opt):
+        if self.grad2 is not None:
+            opt.grad.add_(self.grad2)
+            self.grad2.zero_()
         if self.ranks > 1 and self.n_rep:
             dist.all_reduce(opt.grad[:self.n_rep], group=self.group)
 
 
-def build_tp_gpt2(cfg, rank, world, dev, group=None, micro_tokens=16384):
+def build_tp_gpt2(cfg, rank, world, dev, group=None, micro_tokens=16384, overlap: bool | None = None,
+                  fused_ctas: int = 56):
+    """overlap: run the two halves of every batch on two streams at once (see ``TPGPT2.forward``).
+    None = on for GPU groups of four or more ranks, where the collectives dominate the step;
+    ``COGITO_TP_OVERLAP=0`` / ``=1`` force it off / on.  fused_ctas: CTAs of each fused collective kernel in that mode (the two
+    halves' kernels must fit on the GPU together, with room left for the compute kernels)."""
+    import os
     if group is None and world > 1:
         group = dist.group.WORLD
+    cuda = torch.device(dev).type == "cuda"
+    if overlap is None:
+        env = os.environ.get("COGITO_TP_OVERLAP", "")
+        overlap = cuda and (env not in ("", "0") if env != "" else world >= 4)
+    overlap = bool(overlap) and cuda and world > 1 and micro_tokens % (2 * 128 * world) == 0
+    tokens = micro_tokens // 2 if overlap else micro_tokens
     # room for the gathered input of every column-parallel GEMM of one pass (two per block and
     # the output head), which the backward pass reads again
-    arena = (2 * cfg.n_layer + 1) * ((micro_tokens * cfg.d_model * 2 + 255) // 256 * 256)
-    ws = TPWorkspace(dev, group, max_rows=micro_tokens, max_cols=cfg.d_model, arena_bytes=arena)
-    model = TPGPT2(cfg, ws, device=dev, dtype=torch.bfloat16 if torch.device(dev).type == "cuda" else None)
+    arena = (2 * cfg.n_layer + 1) * ((tokens * cfg.d_model * 2 + 255) // 256 * 256)
+    mk = lambda: TPWorkspace(dev, group, max_rows=tokens, max_cols=cfg.d_model, arena_bytes=arena,
+                             max_ctas=fused_ctas if overlap else 0)
+    ws = mk()
+    ws2 = mk() if overlap else None
+    model = TPGPT2(cfg, ws, device=dev, dtype=torch.bfloat16 if cuda else None, ws2=ws2)
     rep, shd = model.ordered_parameters()
     model._ordered = rep + shd
     return model, TPGradSync(model)

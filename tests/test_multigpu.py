@@ -22,13 +22,13 @@ def _free_port():
     return p
 
 
-def _run(n, *args, timeout=600):
+def _run(n, *args, timeout=600, extra_env=None):
     if torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), os.path.join(HERE, "mgpu_worker.py"), *map(str, args)]
     # guard regions around every symmetric buffer: a peer store outside its range fails the test
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", COGITO_SYMM_CANARY="1")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", COGITO_SYMM_CANARY="1", **(extra_env or {}))
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     found = re.findall(r"RESULT (\{[^{}]*\})", r.stdout)      # ranks may interleave their lines
@@ -49,6 +49,18 @@ def _close(res, tol):
 @pytest.mark.parametrize("n", [2, 4, 8])
 def test_tensor_parallel_gpt2(n):
     _close(_run(n, "tp"), 0.05)
+
+
+@pytest.mark.parametrize("n,overlap", [(2, "1"), (4, "0"), (8, "0")])
+def test_tensor_parallel_gpt2_other_schedule(n, overlap):
+    """The same comparison with the two-halves-on-two-streams schedule forced on where it is off by
+    default (2 ranks) and off where it is on by default (4 and 8 ranks)."""
+    _close(_run(n, "tp", extra_env={"COGITO_TP_OVERLAP": overlap}), 0.05)
+
+
+def test_tensor_parallel_gpt2_peer_load_transport():
+    """Without the NVSwitch multicast path: shards pulled with peer loads, partials summed by the owner."""
+    _close(_run(2, "tp", extra_env={"COGITO_TP_NVLS": "0"}), 0.05)
 
 
 @pytest.mark.parametrize("n", [2, 4, 8])
