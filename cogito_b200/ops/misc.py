@@ -167,7 +167,8 @@ class _SoftmaxDropoutResidual(torch.autograd.Function):
         V = x.shape[-1]
         x2 = x.reshape(-1, V).contiguous()
         ctx.p, ctx.seed, ctx.has_res = p, seed, residual is not None
-        ctx.save_for_backward(x2, mul.reshape(-1, V).contiguous() if mul is not None else torch.empty(0))
+        m2 = mul.reshape(-1, V).contiguous() if mul is not None else None
+        ctx.save_for_backward(x2, m2 if m2 is not None else torch.empty(0))
         ctx.has_mul = mul is not None
         ctx.shape = x.shape
         if not x.is_cuda:
@@ -178,7 +179,6 @@ class _SoftmaxDropoutResidual(torch.autograd.Function):
                 out = out + residual.reshape(-1, V).float()
             return out.to(x.dtype).reshape(x.shape)
         out = torch.empty_like(x2)
-        m2 = ctx.saved_tensors[1] if mul is not None else None
         r2 = residual.reshape(-1, V).contiguous() if residual is not None else None
         _lib.check(_lib.lib().cgk_softmax_dropout_residual(_dt(x2), x2.data_ptr(), _lib.ptr(m2), _lib.ptr(r2), out.data_ptr(),
                                                            x2.shape[0], V, float(p), int(seed), _lib.stream_ptr()),

@@ -240,13 +240,73 @@ colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, long long M, int N, l
     partial[(long long)blockIdx.y * N + c] = sh[0][threadIdx.x] + sh[1][threadIdx.x] +
                                              sh[2][threadIdx.x] + sh[3][threadIdx.x];
 }
-__global__ void colsum_final_kernel(const float* __restrict__ partial, int nparts, int N,
-                                    float* __restrict__ out, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= N) return;
+// The same for rows whose columns come in aligned groups of eight: a thread owns one 16-byte
+// column vector and every 8th row of the CTA's share, four loads in flight; a warp reads 512
+// contiguous bytes of a row.  grid.x covers 256-column strips, grid.y splits M.
+__global__ void __launch_bounds__(256)
+colsum_partial_vec_kernel(const __nv_bfloat16* __restrict__ x, long long M, int N, long long ld,
+                          float* __restrict__ partial) {
+  __shared__ float sh[8][32][9];
+  const int cx = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int c = (blockIdx.x * 32 + cx) * 8;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+  if (c < N) {
+    const long long step = (long long)gridDim.y * 8;
+    long long r = (long long)blockIdx.y * 8 + rl;
+    const __nv_bfloat16* col = x + c;
+    for (; r + 3 * step < M; r += 4 * step) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = __ldg(reinterpret_cast<const uint4*>(col + (r + u * step) * ld));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float2 t;
+        t = unpack_bf16x2(v[u].x); acc[0] += t.x; acc[1] += t.y;
+        t = unpack_bf16x2(v[u].y); acc[2] += t.x; acc[3] += t.y;
+        t = unpack_bf16x2(v[u].z); acc[4] += t.x; acc[5] += t.y;
+        t = unpack_bf16x2(v[u].w); acc[6] += t.x; acc[7] += t.y;
+      }
+    }
+    for (; r < M; r += step) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(col + r * ld));
+      float2 t;
+      t = unpack_bf16x2(v.x); acc[0] += t.x; acc[1] += t.y;
+      t = unpack_bf16x2(v.y); acc[2] += t.x; acc[3] += t.y;
+      t = unpack_bf16x2(v.z); acc[4] += t.x; acc[5] += t.y;
+      t = unpack_bf16x2(v.w); acc[6] += t.x; acc[7] += t.y;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sh[rl][cx][j] = acc[j];
+  __syncthreads();
+  // 256 threads = 256 columns of the strip
+  const int oc = blockIdx.x * 256 + threadIdx.x;
+  if (oc < N) {
+    float a = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) a += sh[w][threadIdx.x >> 3][threadIdx.x & 7];
+    partial[(long long)blockIdx.y * N + oc] = a;
+  }
+}
+// One CTA per 32 columns: 32 x 8 threads, each sums every 8th partial row.
+__global__ void __launch_bounds__(256)
+colsum_final_kernel(const float* __restrict__ partial, int nparts, int N, float* __restrict__ out,
+                    int accumulate) {
+  __shared__ float sh[8][33];
+  const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float s = 0.0f;
-  for (int p = 0; p < nparts; ++p) s += partial[(long long)p * N + c];
-  out[c] = accumulate ? out[c] + s : s;
+  if (c < N)
+    for (int p = py; p < nparts; p += 8) s += partial[(long long)p * N + c];
+  sh[py][cx] = s;
+  __syncthreads();
+  if (py == 0 && c < N) {
+#pragma unroll
+    for (int w = 1; w < 8; ++w) s += sh[w][cx];
+    out[c] = accumulate ? out[c] + s : s;
+  }
 }
 
 // ---- embedding ------------------------------------------------------------
@@ -601,7 +661,7 @@ CGK_API int cgk_reduce_all(int op, int dtype, const void* x, long long n, float*
 
 static int colsum_parts(long long M) {
   long long p = (M + 255) / 256;
-  if (p > 64) p = 64;
+  if (p > 256) p = 256;
   if (p < 1) p = 1;
   return (int)p;
 }
@@ -613,10 +673,15 @@ CGK_API int cgk_colsum_bf16(const void* x, long long M, int N, long long ld, flo
   CGK_REQUIRE(x && out && scratch, "cgk_colsum_bf16: null pointer");
   if (N == 0) return 0;
   const int parts = colsum_parts(M);
-  dim3 grid((N + 63) / 64, parts);
-  colsum_partial_kernel<<<grid, 256, 0, ST(stream)>>>((const __nv_bfloat16*)x, M, N, ld, scratch);
+  if (N % 8 == 0 && ld % 8 == 0 && ((uintptr_t)x & 15u) == 0) {
+    dim3 grid((N + 255) / 256, parts);
+    colsum_partial_vec_kernel<<<grid, 256, 0, ST(stream)>>>((const __nv_bfloat16*)x, M, N, ld, scratch);
+  } else {
+    dim3 grid((N + 63) / 64, parts);
+    colsum_partial_kernel<<<grid, 256, 0, ST(stream)>>>((const __nv_bfloat16*)x, M, N, ld, scratch);
+  }
   CGK_LAUNCH_CHECK();
-  colsum_final_kernel<<<(N + 255) / 256, 256, 0, ST(stream)>>>(scratch, parts, N, out, accumulate);
+  colsum_final_kernel<<<(N + 31) / 32, 256, 0, ST(stream)>>>(scratch, parts, N, out, accumulate);
   CGK_LAUNCH_CHECK();
   return 0;
 }

@@ -5,7 +5,8 @@
 // these keys and over every query head of the GQA group, so they need no
 // atomics.  Per query tile (128 rows):
 //     S  = Q K^T, dP = dO V^T            two MMAs into TMEM
-//     P  = exp2(S*c - LSE), dS = P*(dP - delta)*scale      (thread = query row)
+//     P  = exp2(S*c - LSE), dS = P*(dP - delta)*scale      (two warpgroups, thread = query row
+//          x 64 keys, packed two-wide fp32 arithmetic)
 //          both written once, bf16, to a 128B-swizzled [rows][keys] tile that
 //          serves as a K-major operand (dQ = dS K) and, read the other way, as
 //          an MN-major operand (dV += P^T dO, dK += dS^T Q)
@@ -124,7 +125,7 @@ static int launch_bwd(const cgk_flash_args& a, const FlashBwdDev& p, cudaStream_
   CGK_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       C::TOTAL));
   dim3 grid((a.Tk + C::BN - 1) / C::BN, a.Hk, a.B);
-  flash_bwd_kernel<D><<<grid, 384, C::TOTAL, st>>>(tq, tk, tv, tdo, tdq, p);
+  flash_bwd_kernel<D><<<grid, 512, C::TOTAL, st>>>(tq, tk, tv, tdo, tdq, p);
   CGK_LAUNCH_CHECK();
   return 0;
 }

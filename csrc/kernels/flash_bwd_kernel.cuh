@@ -28,7 +28,7 @@ struct BwdCfg {
   static constexpr int DB = D / 64;
   static constexpr int TILE_BYTES = 128 * D * 2;   // K, V, Q, dO tiles
   static constexpr int PS_BYTES = BM * BN * 2;     // P and dS tiles
-  static constexpr int STAGES = (D == 64) ? 2 : 1;
+  static constexpr int STAGES = (D == 64) ? 3 : 1;   // Q / dO slots: a slot is held from a step's S / dP until its dK / dV
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + TILE_BYTES;
   static constexpr int OFF_QDO = OFF_V + TILE_BYTES;            // [STAGES][Q, dO]
@@ -54,13 +54,39 @@ struct BwdCfg {
   static constexpr bool DQ_ALIAS = (256 + 3 * D > 512);
   static constexpr int TMEM_DQ = DQ_ALIAS ? TMEM_S : 256 + 2 * D;
   static constexpr int TMEM_COLS = 512;
+  static_assert(TOTAL <= 227 * 1024, "flash backward: shared memory budget of one CTA exceeded");
 };
 
-// Warp roles (384 threads): warp 0 TMA producer, warp 1 MMA issuer, warp 2 TMEM
-// allocator, warps 4..7 compute P / dS (thread = query row), warps 8..11 drain the
-// dQ tile into the fp32 accumulator with vector reductions.
+// Rewrites one thread's 64 S columns at s_tmem as final scores in the log2 domain: product * scale
+// + ALiBi bias where the key is visible, -inf elsewhere.  Column i is visible iff
+// (unsigned)(rel0 + i) <= span and the row sees any key at all.  Out of line: only tiles on a mask
+// edge or with a bias come here, and the hot row loop stays short.
+__device__ __noinline__ void flash_bwd_mask_scores(uint32_t s_tmem, float scale_log2, float slope,
+                                                   float bias0, int rel0, unsigned span, bool none) {
+#pragma unroll 1
+  for (int c = 0; c < 2; ++c) {
+    uint32_t r[32];
+    __syncwarp();
+    tmem_ld32(s_tmem + c * 32, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int idx = c * 32 + i;
+      const float sc = fmaf(__uint_as_float(r[i]), scale_log2, fmaf(slope, (float)idx, bias0));
+      const bool vis = ((unsigned)(rel0 + idx) <= span) && !none;
+      r[i] = __float_as_uint(vis ? sc : -INFINITY);
+    }
+    tmem_st32(s_tmem + c * 32, r);
+  }
+  tmem_st_wait();
+}
+
+// Warp roles (512 threads): warp 0 TMA producer, warp 1 MMA issuer, warp 2 TMEM allocator,
+// warps 4..11 compute P / dS (thread = query row x half of the keys), warps 12..15 drain the
+// dQ tile into the fp32 accumulator with bulk tensor reductions.  With 512 threads every thread
+// has 128 registers, which each role fits; no register reallocation is needed.
 template <int D>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(512, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                  const __grid_constant__ CUtensorMap tmDQ, const FlashBwdDev p) {
@@ -109,10 +135,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(kv_full, 1);
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_ready, 128);
+    mbar_init(pds_ready, 256);
     mbar_init(dq_full, 1);
     mbar_init(dq_drained, 128);
-    mbar_init(sdp_consumed, 128);
+    mbar_init(sdp_consumed, 256);
     *dead = 0;
     mbar_fence_init();
   }
@@ -126,7 +152,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 0) {
       // ------------------------------ TMA producer ------------------------------
       if (lane == 0 && total_steps > 0) {
@@ -238,11 +263,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
     }
-  } else if (warp < 8) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+  } else if (warp < 12) {
 #include "flash_bwd_compute.inc"
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 112;");
     // ------------------------------- dQ drain -------------------------------
     // TMEM -> registers -> swizzled fp32 staging tile -> one bulk tensor reduction
     // (add) per 32 columns into the fp32 accumulator.  Rows past the end of the
@@ -250,7 +273,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
-    const bool leader = (threadIdx.x == 256);
+    const bool leader = (threadIdx.x == 384);
     bool ok = true;
     for (int n = 0; n < total_steps && ok; ++n) {
       const int g = n / steps_per_head, i = i_lo + n % steps_per_head;

@@ -11,8 +11,14 @@
 //                          normalisation makes a stale maximum exact)
 // Warp roles: 0 = TMA producer, 1 = MMA issuer, 2 = TMEM allocator,
 // 4..7 = softmax warpgroup of query tile 0, 8..11 = of query tile 1.  The two
-// query tiles share every K/V tile, which halves the L2 -> shared traffic, and
-// their softmax phases overlap each other's MMAs.
+// query tiles share every K/V tile, which halves the L2 -> shared traffic.
+// A softmax thread owns one row: it takes the 128 scores of a key tile into
+// registers and frees the S accumulator at once, so that Q K^T of the next key
+// tile runs on the tensor cores while this tile's exponentials are computed.
+// Masked / biased tiles (the diagonal of a causal mask, a window edge, ALiBi)
+// first rewrite S in TMEM with the final scores in a separate, rarely entered
+// function; every tile then takes the one short row loop (three-input maxima,
+// packed two-wide fp32 multiply-adds and sums), which keeps the hot code small.
 //
 // Supports causal masking (bottom-right aligned when Tq != Tk), a sliding window
 // |k - q| <= w, ALiBi slopes, GQA/MQA (kv head = h * Hk / Hq), head_dim 64 / 128.
@@ -54,13 +60,37 @@ struct FwdCfg {
   static constexpr int OFF_KV = OFF_Q + 2 * Q_TILE_BYTES;
   static constexpr int OFF_P = OFF_KV + RING * KV_TILE_BYTES;
   static constexpr int OFF_BAR = OFF_P + 2 * P_TILE_BYTES;
-  // barriers: q_full, full[RING], empty[RING], s_full[2], p_ready[2], o_done[2]
-  static constexpr int NUM_BARS = 1 + 2 * RING + 6;
+  // barriers: q_full, full[RING], empty[RING], s_full[2], p_ready[2], o_done[2], s_free[2]
+  static constexpr int NUM_BARS = 1 + 2 * RING + 8;
   static constexpr int TOTAL = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
   static constexpr int TMEM_S0 = 0;
   static constexpr int TMEM_O0 = 256;
   static constexpr int TMEM_COLS = 512;
 };
+
+// Rewrites one thread's S row (128 fp32 columns at s_tmem) as final scores in the log2 domain:
+// product * scale + ALiBi bias where the key is visible, -inf elsewhere.  Column i is visible iff
+// (unsigned)(rel0 + i) <= span and the row sees any key at all.  Kept out of line: only tiles on
+// a mask edge or with a bias come here, and the hot row loop stays short.
+__device__ __noinline__ void flash_mask_scores(uint32_t s_tmem, float scale_log2, float slope, float bias0,
+                                               int rel0, unsigned span, bool none) {
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    uint32_t r[32];
+    __syncwarp();
+    tmem_ld32(s_tmem + c * 32, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int idx = c * 32 + i;
+      const float sc = fmaf(__uint_as_float(r[i]), scale_log2, fmaf(slope, (float)idx, bias0));
+      const bool vis = ((unsigned)(rel0 + idx) <= span) && !none;
+      r[i] = __float_as_uint(vis ? sc : -INFINITY);
+    }
+    tmem_st32(s_tmem + c * 32, r);
+  }
+  tmem_st_wait();
+}
 
 template <int D>
 __global__ void __launch_bounds__(384, 1)
@@ -78,6 +108,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   auto s_full = [&](int t) { return bar0 + 8u * (1 + 2 * C::RING + t); };
   auto p_ready = [&](int t) { return bar0 + 8u * (1 + 2 * C::RING + 2 + t); };
   auto o_done = [&](int t) { return bar0 + 8u * (1 + 2 * C::RING + 4 + t); };
+  auto s_free = [&](int t) { return bar0 + 8u * (1 + 2 * C::RING + 6 + t); };
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::NUM_BARS * 8);
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
@@ -119,7 +150,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < C::RING; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(s_full(t), 1); mbar_init(p_ready(t), 128); mbar_init(o_done(t), 1); }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(s_full(t), 1); mbar_init(p_ready(t), 128); mbar_init(o_done(t), 1); mbar_init(s_free(t), 128);
+    }
     *dead = 0;
     mbar_fence_init();
   }
@@ -203,64 +236,53 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         umma_commit(o_done(t));
       };
       if (!mbar_wait(q_full, 0, dead, p.status, 1200)) ok = false;
-      uint32_t kslot_next = 0;  // smem address of K_{j+1} once waited
-      if (ok) {
+      // ring order (the producer's): K_lo, then (K_{j+1}, V_j) per key tile j
+      auto take_slot = [&](int where) -> uint32_t {
         const int s = n % C::RING;
-        if (!mbar_wait(full_bar(s), (n / C::RING) & 1u, dead, p.status, 1201)) ok = false;
+        if (!mbar_wait(full_bar(s), (n / C::RING) & 1u, dead, p.status, where)) { ok = false; return 0u; }
+        tc_fence_after();
+        ++n;
+        return (uint32_t)s;
+      };
+      if (ok) {
+        const uint32_t s = take_slot(1201);
         if (ok) {
-          tc_fence_after();
           const uint32_t kb = sbase + C::OFF_KV + s * C::KV_TILE_BYTES;
           for (int t = 0; t < 2; ++t)
             if (lo < hi_t[t]) issue_s(t, kb);
           umma_commit(empty_bar(s));
-          ++n;
         }
       }
+      uint32_t fcount[2] = {0, 0};
       for (int j = lo; j < hi && ok; ++j) {
-        const bool has_next = j + 1 < hi;
-        int ks = -1, vs = -1;
-        uint32_t kaddr = 0, vaddr = 0;
-        const int t_last = (j < hi_t[1]) ? 1 : 0;
-        const int t_last_next = (j + 1 < hi_t[1]) ? 1 : 0;
+        // S of the next key tile as soon as the softmax warps hold this tile's scores in registers
+        if (j + 1 < hi) {
+          const uint32_t ks = take_slot(1220);
+          if (!ok) break;
+          const uint32_t kaddr = sbase + C::OFF_KV + ks * C::KV_TILE_BYTES;
+          for (int t = 0; t < 2 && ok; ++t) {
+            if (j + 1 >= hi_t[t]) continue;
+            if (!mbar_wait(s_free(t), fcount[t] & 1u, dead, p.status, 1240 + t)) { ok = false; break; }
+            ++fcount[t];
+            tc_fence_after();
+            issue_s(t, kaddr);
+          }
+          if (!ok) break;
+          umma_commit(empty_bar(ks));
+        }
+        // O += P V of this key tile once P is in shared memory
+        const uint32_t vs = take_slot(1230);
+        if (!ok) break;
+        const uint32_t vaddr = sbase + C::OFF_KV + vs * C::KV_TILE_BYTES;
         for (int t = 0; t < 2 && ok; ++t) {
           if (j >= hi_t[t]) continue;
           if (!mbar_wait(p_ready(t), pcount[t] & 1u, dead, p.status, 1210 + t)) { ok = false; break; }
           ++pcount[t];
           tc_fence_after();
-          if (has_next && j + 1 < hi_t[t]) {
-            if (ks < 0) {
-              ks = n % C::RING;
-              if (!mbar_wait(full_bar(ks), (n / C::RING) & 1u, dead, p.status, 1220)) { ok = false; break; }
-              tc_fence_after();
-              kaddr = sbase + C::OFF_KV + ks * C::KV_TILE_BYTES;
-              ++n;
-            }
-            issue_s(t, kaddr);
-            if (t == t_last_next) umma_commit(empty_bar(ks));
-          }
-          if (vs < 0) {
-            // the V tile follows K_{j+1} in the ring; when no tile needs K_{j+1}
-            // the producer did not load it
-            if (has_next && ks < 0) {
-              // K_{j+1} was loaded (has_next) but this tile does not use it; the
-              // other tile (t = 1) will.  Only reachable for t = 0 at its last
-              // key tile, where t = 1 still follows: take the K slot now.
-              ks = n % C::RING;
-              if (!mbar_wait(full_bar(ks), (n / C::RING) & 1u, dead, p.status, 1221)) { ok = false; break; }
-              tc_fence_after();
-              kaddr = sbase + C::OFF_KV + ks * C::KV_TILE_BYTES;
-              ++n;
-            }
-            vs = n % C::RING;
-            if (!mbar_wait(full_bar(vs), (n / C::RING) & 1u, dead, p.status, 1230)) { ok = false; break; }
-            tc_fence_after();
-            vaddr = sbase + C::OFF_KV + vs * C::KV_TILE_BYTES;
-            ++n;
-          }
           issue_pv(t, vaddr, j > lo);
-          if (t == t_last) umma_commit(empty_bar(vs));
         }
-        (void)kslot_next;
+        if (!ok) break;
+        umma_commit(empty_bar(vs));
       }
     }
    }
@@ -290,56 +312,38 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       bool need_mask = (k0 + C::BN > p.Tk);
       if (p.causal) need_mask |= (k0 + C::BN - 1 > tile_q_lo);
       if (p.window >= 0) need_mask |= (k0 < tile_q_hi - p.window) || (!p.causal && k0 + C::BN - 1 > tile_q_lo + p.window);
-      // Row-wise visible key range [klo, khi] (empty when khi < klo); one unsigned
-      // compare per element then decides visibility.  The ALiBi bias of element
-      // (c, i) is bias0 + slope * (c*32 + i).
-      int klo = 0, khi = p.Tk - 1;
-      if (p.causal) khi = min(khi, qk);
-      if (p.window >= 0) { klo = max(klo, qk - p.window); khi = min(khi, qk + p.window); }
-      const int rel0 = k0 - klo;                          // (k - klo) of the tile's first key
-      const unsigned span = khi >= klo ? (unsigned)(khi - klo) : 0u;
-      const bool none = khi < klo;
-      const float bias0 = p.alibi ? slope * (float)(k0 - qk) : 0.0f;
-      auto score = [&](uint32_t raw, int idx) -> float {    // idx = c*32 + i (compile-time)
-        const float bias = fmaf(slope, (float)idx, bias0);
-        const float sc = fmaf(__uint_as_float(raw), p.scale_log2, bias);
-        const bool vis = ((unsigned)(rel0 + idx) <= span) && !none;
-        return vis ? sc : -INFINITY;
-      };
-      // Interior tiles (no mask, no bias) take a path with the minimum instruction
-      // count per element: the softmax warps are issue- and MUFU-bound.
+      // Interior tiles (no mask, no bias) use the raw products; the others are first rewritten in
+      // TMEM as final log2-domain scores (-inf where masked), after which the multiplier is 1.
       const bool fast = !need_mask && !p.alibi && p.scale_log2 > 0.0f;
-      // The whole S row (128 fp32) comes into registers with four loads in flight
-      // and one wait; it is read from TMEM once per key tile.
+      if (!fast) {
+        // Row-wise visible key range [klo, khi] (empty when khi < klo).  The ALiBi bias of
+        // column i of the tile is bias0 + slope * i.
+        int klo = 0, khi = p.Tk - 1;
+        if (p.causal) khi = min(khi, qk);
+        if (p.window >= 0) { klo = max(klo, qk - p.window); khi = min(khi, qk + p.window); }
+        const unsigned span = khi >= klo ? (unsigned)(khi - klo) : 0u;
+        const float bias0 = p.alibi ? slope * (float)(k0 - qk) : 0.0f;
+        flash_mask_scores(s_tmem, p.scale_log2, slope, bias0, k0 - klo, span, khi < klo);
+      }
+      const float mul = fast ? p.scale_log2 : 1.0f;
+      // The whole S row (128 fp32) comes into registers with four loads in flight and one wait;
+      // the accumulator is then free for Q K^T of the next key tile.
       uint32_t r[4][32];
       __syncwarp();
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, r[c]);
       tmem_ld_wait();
-      float mx;
-      if (fast) {
-        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+      tc_fence_before();
+      mbar_arrive(s_free(t));
+      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          m0 = fmaxf(m0, __uint_as_float(r[0][i]));
-          m1 = fmaxf(m1, __uint_as_float(r[1][i]));
-          m2 = fmaxf(m2, __uint_as_float(r[2][i]));
-          m3 = fmaxf(m3, __uint_as_float(r[3][i]));
-        }
-        mx = fmaxf(m, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * p.scale_log2);
-      } else {
-        // masked / biased tile: turn the raw products into final log2-domain scores in place
-        float m0 = m;
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float sc = score(r[c][i], c * 32 + i);
-            r[c][i] = __float_as_uint(sc);
-            m0 = fmaxf(m0, sc);
-          }
-        mx = m0;
+      for (int i = 0; i < 32; i += 2) {
+        m0 = fmax3(m0, __uint_as_float(r[0][i]), __uint_as_float(r[0][i + 1]));
+        m1 = fmax3(m1, __uint_as_float(r[1][i]), __uint_as_float(r[1][i + 1]));
+        m2 = fmax3(m2, __uint_as_float(r[2][i]), __uint_as_float(r[2][i + 1]));
+        m3 = fmax3(m3, __uint_as_float(r[3][i]), __uint_as_float(r[3][i + 1]));
       }
+      const float mx = fmaxf(m, fmax3(m0, m1, fmaxf(m2, m3)) * mul);   // mul > 0
       // keep a stale maximum unless it grew by more than 2^8
       float m_use = (mx > m + 8.0f) ? mx : m;
       if (m == -INFINITY) m_use = mx;
@@ -366,18 +370,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       l *= alpha;
       m = m_use;
-      const float m_sub = (m == -INFINITY) ? 0.0f : m;
-      const float neg_m = -m_sub;
-      const float mul = fast ? p.scale_log2 : 1.0f;   // slow path: r already holds the scores
-      // P = exp2(score - m), bf16, into the swizzled operand tile
+      const float neg_m = (m == -INFINITY) ? 0.0f : -m;
+      // P = exp2(score * mul - m), bf16, into the swizzled operand tile
       float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         float e[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) e[i] = fast_exp2(fmaf(__uint_as_float(r[c][i]), mul, neg_m));
+        for (int i = 0; i < 32; i += 2) {
+          float x0, x1;
+          ffma2(x0, x1, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]), mul, mul, neg_m, neg_m);
+          e[i] = fast_exp2(x0);
+          e[i + 1] = fast_exp2(x1);
+        }
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) { s0 += e[i]; s1 += e[i + 1]; s2 += e[i + 2]; s3 += e[i + 3]; }
+        for (int i = 0; i < 32; i += 4) { fadd2(s0, s1, e[i], e[i + 1]); fadd2(s2, s3, e[i + 2], e[i + 3]); }
         uint8_t* blk = p_smem + (c >> 1) * (C::BM * 128);
         const uint32_t chunk0 = (c & 1) * 4;
 #pragma unroll

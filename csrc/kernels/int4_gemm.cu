@@ -56,10 +56,6 @@ struct Int4Dev {
 };
 
 
-__device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
 
 __global__ void __launch_bounds__(THREADS, 1)
 int4_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const Int4Dev g) {

@@ -233,19 +233,166 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
   }
 }
 
-// dgamma[c] (+)= sum_p partial[p][0][c]; dbeta likewise.  fp32 outputs.
-__global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, int nparts, int D,
-                                       float* __restrict__ dgamma, float* __restrict__ dbeta,
-                                       int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= D) return;
-  float a = 0.0f, b = 0.0f;
-  for (int p = 0; p < nparts; ++p) {
-    a += partial[(size_t)p * 2 * D + c];
-    b += partial[(size_t)p * 2 * D + D + c];
+// The same backward pass for rows of up to 1024 elements, fed by bulk copies.  Each warp owns a
+// ring of row slots in shared memory (x, dy and the residual gradient of a row per slot); lane 0
+// keeps `stages` rows of copies in flight, so the loads of later rows never wait for the arithmetic
+// of the current one and the number of bytes in flight per SM no longer depends on registers.
+// One CTA of NORM_RING_WARPS warps per SM; dgamma / dbeta partials stay in registers and are
+// combined through the ring's memory at the end.  partial: [gridDim.x, 2, D] fp32.
+constexpr int NORM_RING_WARPS = 8;
+template <int MAXV, bool RMS>
+__global__ void __launch_bounds__(NORM_RING_WARPS * 32, 1)
+norm_bwd_ring_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                     const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                     const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres_in,
+                     __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int D,
+                     int stages, int* status) {
+  extern __shared__ __align__(128) uint8_t ring_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = D >> 3;
+  const int nt = dres_in ? 3 : 2;                      // tensors per slot
+  const uint32_t row_bytes = (uint32_t)D * 2u;
+  const uint32_t slot_bytes = 3u * row_bytes;
+  const uint32_t ring_bytes = (uint32_t)NORM_RING_WARPS * stages * slot_bytes;
+  uint8_t* my_ring = ring_raw + (size_t)warp * stages * slot_bytes;
+  const uint32_t bar0 = smem_u32(ring_raw) + ring_bytes + (uint32_t)warp * stages * 8u;
+  volatile int* dead = reinterpret_cast<volatile int*>(ring_raw + ring_bytes + NORM_RING_WARPS * stages * 8);
+  if (threadIdx.x == 0) *dead = 0;
+  if (lane == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(bar0 + 8u * s, 1);
+    mbar_fence_init();
   }
-  if (dgamma) dgamma[c] = accumulate ? dgamma[c] + a : a;
-  if (dbeta) dbeta[c] = accumulate ? dbeta[c] + b : b;
+  __syncthreads();
+  const long long first = (long long)blockIdx.x * NORM_RING_WARPS + warp;
+  const long long stride = (long long)gridDim.x * NORM_RING_WARPS;
+  auto post = [&](long long row, int s) {               // lane 0 only
+    const uint32_t bar = bar0 + 8u * s;
+    const uint32_t dst = smem_u32(my_ring) + (uint32_t)s * slot_bytes;
+    mbar_expect_tx(bar, (uint32_t)nt * row_bytes);
+    bulk_load_1d(dst, x + row * D, row_bytes, bar);
+    bulk_load_1d(dst + row_bytes, dy + row * D, row_bytes, bar);
+    if (dres_in) bulk_load_1d(dst + 2u * row_bytes, dres_in + row * D, row_bytes, bar);
+  };
+  if (lane == 0)
+    for (int s = 0; s < stages; ++s)
+      if (first + s * stride < rows) post(first + s * stride, s);
+  const uint4* gp = reinterpret_cast<const uint4*>(gamma);
+  float accg[MAXV * 8], accb[MAXV * 8];
+  uint4 gr[MAXV];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    gr[i] = (lane + i * 32 < nvec) ? __ldg(gp + lane + i * 32) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { accg[i * 8 + j] = 0.0f; accb[i * 8 + j] = 0.0f; }
+  }
+  bool ok = true;
+  uint32_t k = 0;
+  // the row statistics are fetched one row ahead as well
+  float mean_next = 0.0f, rstd_next = 0.0f;
+  if (first < rows) { mean_next = RMS ? 0.0f : mean_in[first]; rstd_next = rstd_in[first]; }
+  for (long long row = first; row < rows && ok; row += stride, ++k) {
+    const int s = (int)(k % (uint32_t)stages);
+    const float mean = mean_next, rstd = rstd_next;
+    if (row + stride < rows) { mean_next = RMS ? 0.0f : mean_in[row + stride]; rstd_next = rstd_in[row + stride]; }
+    if (!mbar_wait(bar0 + 8u * s, (k / (uint32_t)stages) & 1u, dead, status, 3100)) { ok = false; break; }
+    const uint4* slot = reinterpret_cast<const uint4*>(my_ring + (size_t)s * slot_bytes);
+    uint4 xr[MAXV], dr[MAXV], rr[MAXV];
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int c = lane + i * 32;
+      if (c < nvec) {
+        xr[i] = slot[c];
+        dr[i] = slot[nvec + c];
+        rr[i] = dres_in ? slot[2 * nvec + c] : make_uint4(0, 0, 0, 0);
+      }
+    }
+    // every lane holds its part of the row: the slot can take the row `stages` ahead
+    __syncwarp();
+    if (lane == 0 && row + (long long)stages * stride < rows) post(row + (long long)stages * stride, s);
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      if (lane + i * 32 < nvec) {
+        float xv[8], dv[8], g[8];
+        unpack8(xr[i], xv);
+        unpack8(dr[i], dv);
+        unpack8(gr[i], g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float h = (xv[j] - mean) * rstd;
+          const float t = dv[j] * g[j];
+          s1 += t;
+          s2 += t * h;
+          accg[i * 8 + j] += dv[j] * h;
+          accb[i * 8 + j] += dv[j];
+        }
+      }
+    }
+    s1 = RMS ? 0.0f : warp_sum(s1) / D;
+    s2 = warp_sum(s2) / D;
+    uint4* op = reinterpret_cast<uint4*>(dx + row * D);
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int c = lane + i * 32;
+      if (c < nvec) {
+        float xv[8], dv[8], g[8], r[8], o[8];
+        unpack8(xr[i], xv);
+        unpack8(dr[i], dv);
+        unpack8(gr[i], g);
+        unpack8(rr[i], r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float h = (xv[j] - mean) * rstd;
+          o[j] = rstd * (dv[j] * g[j] - s1 - h * s2) + r[j];
+        }
+        op[c] = pack8(o);
+      }
+    }
+  }
+  // no copy is in flight any more (every posted row was waited for, unless a wait gave up, in
+  // which case the ring is left alone): the ring's memory now combines the warps' partial sums
+  __syncthreads();
+  if (*dead) { __nanosleep(100000); return; }
+  float* sm_part = reinterpret_cast<float*>(ring_raw);   // [NORM_RING_WARPS][2][D]
+  float* mine = sm_part + (size_t)warp * 2 * D;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int c = lane + i * 32;
+    if (c < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { mine[c * 8 + j] = accg[i * 8 + j]; mine[D + c * 8 + j] = accb[i * 8 + j]; }
+    }
+  }
+  __syncthreads();
+  float* out = partial + (size_t)blockIdx.x * 2 * D;
+  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) {
+    float a = 0.0f;
+#pragma unroll
+    for (int w = 0; w < NORM_RING_WARPS; ++w) a += sm_part[(size_t)w * 2 * D + i];
+    out[i] = a;
+  }
+}
+
+// dgamma[c] (+)= sum_p partial[p][0][c]; dbeta likewise.  fp32 outputs.
+// One CTA per 32 columns of the [2, D] partial rows: 32 x 8 threads, each sums every 8th partial.
+__global__ void __launch_bounds__(256)
+norm_bwd_reduce_kernel(const float* __restrict__ partial, int nparts, int D,
+                       float* __restrict__ dgamma, float* __restrict__ dbeta, int accumulate) {
+  __shared__ float sh[8][33];
+  const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;                 // column of the concatenated [dgamma | dbeta] row
+  float a = 0.0f;
+  if (c < 2 * D)
+    for (int p = py; p < nparts; p += 8) a += partial[(size_t)p * 2 * D + c];
+  sh[py][cx] = a;
+  __syncthreads();
+  if (py == 0 && c < 2 * D) {
+#pragma unroll
+    for (int w = 1; w < 8; ++w) a += sh[w][cx];
+    float* dst = c < D ? dgamma : dbeta;
+    const int cc = c < D ? c : c - D;
+    if (dst) dst[cc] = accumulate ? dst[cc] + a : a;
+  }
 }
 
 }  // namespace cgk
@@ -322,11 +469,47 @@ CGK_API int cgk_norm_backward(const void* dy, const void* x, const void* gamma, 
   cudaStream_t st = (cudaStream_t)stream_;
   int dev = 0;
   CGK_CUDA_CHECK(cudaGetDevice(&dev));
+  const int need = (D / 8 + 31) / 32;
+  const bool aligned = (((uintptr_t)dy | (uintptr_t)x | (uintptr_t)dres_in) & 15u) == 0;
+  if (need <= 4 && aligned) {
+    // rows of up to 1024 elements: the bulk-copy ring kernel, one CTA per SM
+    int stages = (int)((200 * 1024 - 1024) / ((size_t)NORM_RING_WARPS * 3 * D * 2));
+    if (stages > 6) stages = 6;
+    int grid = (rows + NORM_RING_WARPS - 1) / NORM_RING_WARPS;
+    if (grid > sm_count(dev)) grid = sm_count(dev);
+    const size_t smem = (size_t)NORM_RING_WARPS * stages * 3 * D * 2 + NORM_RING_WARPS * stages * 8 + 16;
+#define LAUNCH_RING(MAXV)                                                                          \
+  {                                                                                                \
+    if (rms) {                                                                                     \
+      CGK_CUDA_CHECK(cudaFuncSetAttribute(norm_bwd_ring_kernel<MAXV, true>,                        \
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+      norm_bwd_ring_kernel<MAXV, true><<<grid, NORM_RING_WARPS * 32, smem, st>>>(                  \
+          (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean,    \
+          rstd, (const __nv_bfloat16*)dres_in, (__nv_bfloat16*)dx, scratch, rows, D, stages,       \
+          device_status(dev));                                                                     \
+    } else {                                                                                       \
+      CGK_CUDA_CHECK(cudaFuncSetAttribute(norm_bwd_ring_kernel<MAXV, false>,                       \
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+      norm_bwd_ring_kernel<MAXV, false><<<grid, NORM_RING_WARPS * 32, smem, st>>>(                 \
+          (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma, mean,    \
+          rstd, (const __nv_bfloat16*)dres_in, (__nv_bfloat16*)dx, scratch, rows, D, stages,       \
+          device_status(dev));                                                                     \
+    }                                                                                              \
+  }
+    if (need <= 1) LAUNCH_RING(1)
+    else if (need <= 2) LAUNCH_RING(2)
+    else if (need <= 3) LAUNCH_RING(3)
+    else LAUNCH_RING(4)
+#undef LAUNCH_RING
+    CGK_LAUNCH_CHECK();
+    norm_bwd_reduce_kernel<<<(2 * D + 31) / 32, 256, 0, st>>>(scratch, grid, D, dgamma, dbeta, accumulate);
+    CGK_LAUNCH_CHECK();
+    return 0;
+  }
   int grid = (rows + NORM_WARPS - 1) / NORM_WARPS;
   int cap = norm_bwd_cap(dev, D);
   if (grid > cap) grid = cap;
   const size_t smem = (size_t)NORM_WARPS * 2 * D * sizeof(float);
-  const int need = (D / 8 + 31) / 32;
 #define LAUNCH(MAXV)                                                                              \
   {                                                                                               \
     if (rms) {                                                                                    \
@@ -351,7 +534,7 @@ CGK_API int cgk_norm_backward(const void* dy, const void* x, const void* gamma, 
   else LAUNCH(32)
 #undef LAUNCH
   CGK_LAUNCH_CHECK();
-  norm_bwd_reduce_kernel<<<(D + 127) / 128, 128, 0, st>>>(scratch, grid, D, dgamma, dbeta, accumulate);
+  norm_bwd_reduce_kernel<<<(2 * D + 31) / 32, 256, 0, st>>>(scratch, grid, D, dgamma, dbeta, accumulate);
   CGK_LAUNCH_CHECK();
   return 0;
 }

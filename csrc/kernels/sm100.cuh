@@ -131,6 +131,13 @@ __device__ __forceinline__ uint32_t mbar_try_wait_suspend(uint32_t bar, uint32_t
   return ok;
 }
 
+// Untiled bulk copy global -> shared, completing on an mbarrier.  Both addresses 16-byte aligned,
+// `bytes` a multiple of 16.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
 // Bounded wait.  `dead` is a word in shared memory that every role of the CTA
 // polls; `status` is the global status word (may be null).  Returns false when
 // the wait gave up (now or earlier).
@@ -531,6 +538,45 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// Blackwell's three-input maximum and packed two-wide fp32 arithmetic: one issue slot for two
+// elements.  The row loops of the attention kernels are bound by instruction issue, not by MUFU.
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// (d0, d1) = (a0, a1) * (b0, b1) + (c0, c1)
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1,
+                                      float c0, float c1) {
+  asm("{\n\t.reg .b64 a, b, c, d;\n\t"
+      "mov.b64 a, {%2, %3};\n\t"
+      "mov.b64 b, {%4, %5};\n\t"
+      "mov.b64 c, {%6, %7};\n\t"
+      "fma.rn.f32x2 d, a, b, c;\n\t"
+      "mov.b64 {%0, %1}, d;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+// (d0, d1) += (a0, a1)
+__device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1) {
+  asm("{\n\t.reg .b64 a, d;\n\t"
+      "mov.b64 a, {%2, %3};\n\t"
+      "mov.b64 d, {%0, %1};\n\t"
+      "add.rn.f32x2 d, d, a;\n\t"
+      "mov.b64 {%0, %1}, d;\n\t}"
+      : "+f"(d0), "+f"(d1)
+      : "f"(a0), "f"(a1));
+}
+// (d0, d1) = (a0, a1) * (b0, b1)
+__device__ __forceinline__ void fmul2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 a, b, d;\n\t"
+      "mov.b64 a, {%2, %3};\n\t"
+      "mov.b64 b, {%4, %5};\n\t"
+      "mul.rn.f32x2 d, a, b;\n\t"
+      "mov.b64 {%0, %1}, d;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
 }
 // Counter-based random bits: a hash of (seed, element index).  The dropout kernels draw their
 // keep / drop decision from it, forward and backward alike, so no mask is ever stored.
