@@ -139,8 +139,19 @@ def kernel_timeline(step, path, rank, barrier, steps=2):
         if getattr(ev, "device_type", None) is not None and "CUDA" in str(ev.device_type) and t > 0:
             rows.append({"kernel": ev.key[:120], "calls_per_step": ev.count / steps, "ms_per_step": t / 1e3 / steps})
     rows.sort(key=lambda r: -r["ms_per_step"])
+    # the launches of the last traced step in launch order (name, microseconds): calls of one kernel
+    # with different shapes can be told apart by their position in the step
+    seq = []
+    try:
+        evs = [e for e in prof.events() if "CUDA" in str(getattr(e, "device_type", "")) and e.time_range is not None]
+        evs.sort(key=lambda e: e.time_range.start)
+        evs = evs[len(evs) - len(evs) // steps:]
+        seq = [[e.name[:48], round(getattr(e, "device_time", 0.0) or (e.time_range.end - e.time_range.start), 1)] for e in evs]
+    except Exception:
+        seq = []
     with open(path, "w") as f:
-        json.dump({"steps": steps, "total_ms_per_step": sum(r["ms_per_step"] for r in rows), "kernels": rows}, f, indent=1)
+        json.dump({"steps": steps, "total_ms_per_step": sum(r["ms_per_step"] for r in rows), "kernels": rows,
+                   "last_step_launches": seq}, f, indent=1)
 
 
 def main():

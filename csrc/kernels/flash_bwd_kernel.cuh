@@ -81,7 +81,7 @@ __device__ __noinline__ void flash_bwd_mask_scores(uint32_t s_tmem, float scale_
   tmem_st_wait();
 }
 
-// Warp roles (512 threads): warp 0 TMA producer, warp 1 MMA issuer, warp 2 TMEM allocator,
+// Warp roles (512 threads): warp 0 TMA producer, warps 1 and 3 MMA issuers, warp 2 TMEM allocator,
 // warps 4..11 compute P / dS (thread = query row x half of the keys), warps 12..15 drain the
 // dQ tile into the fp32 accumulator with bulk tensor reductions.  With 512 threads every thread
 // has 128 registers, which each role fits; no register reallocation is needed.
@@ -135,10 +135,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(kv_full, 1);
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_ready, 256);
+    mbar_init(pds_ready, 8);          // one arrival per warp
     mbar_init(dq_full, 1);
-    mbar_init(dq_drained, 128);
-    mbar_init(sdp_consumed, 256);
+    mbar_init(dq_drained, 4);
+    mbar_init(sdp_consumed, 8);
     *dead = 0;
     mbar_fence_init();
   }
@@ -179,87 +179,83 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
       }
-    } else if (warp == 1) {
-      // ------------------------------- MMA issuer -------------------------------
+    } else if (warp == 1 || warp == 3) {
+      // ------------------------------- MMA issuers -------------------------------
+      // Two issuing threads: warp 1 issues S = Q K^T and dP = dO V^T of every step, warp 3 the
+      // three products that consume P / dS (dV, dK, dQ).  One thread issuing all 32 to 40 MMAs of
+      // a step was the kernel's critical path (tens of cycles per MMA, hundreds per barrier wait).
       if (lane == 0 && total_steps > 0) {
         const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);   // S, dP: both K-major
         const uint32_t idesc_kv = make_idesc_bf16(128, D, 1, 1);    // dV, dK: A and B MN-major
         const uint32_t idesc_q = make_idesc_bf16(128, D, 0, 1);     // dQ: A K-major, B MN-major
-        const uint32_t sK = sbase + C::OFF_K, sV = sbase + C::OFF_V;
-        const uint32_t sP = sbase + C::OFF_P, sDS = sbase + C::OFF_DS;
-        auto issue_sdp = [&](uint32_t sQ, uint32_t sDO) {
-#pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t o = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
-            umma_f16(tmem_base + C::TMEM_S, make_smem_desc_sw128(sQ + o, 16, 1024),
-                     make_smem_desc_sw128(sK + o, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
-          }
-#pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t o = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
-            umma_f16(tmem_base + C::TMEM_DP, make_smem_desc_sw128(sDO + o, 16, 1024),
-                     make_smem_desc_sw128(sV + o, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
-          }
-          umma_commit(sdp_full);
-        };
+        // shared-memory descriptors: one high word for all operands (1024-byte stride between
+        // 8-row groups, 128-byte swizzle); the low word = address / 16 | leading offset / 16 << 16
+        constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+        constexpr uint32_t LBO_K = (16u >> 4) << 16;               // K-major
+        constexpr uint32_t LBO_MN = ((128u * 128u) >> 4) << 16;    // MN-major: 64-wide blocks 128 rows x 128 B apart
+        auto desc = [&](uint32_t lo32) -> uint64_t { return ((uint64_t)DESC_HI << 32) | (uint64_t)lo32; };
+        auto lo16 = [&](uint32_t off) -> uint32_t { return ((sbase + off) & 0x3FFFFu) >> 4; };
+        const uint32_t k_lo = lo16(C::OFF_K), v_lo = lo16(C::OFF_V), p_lo = lo16(C::OFF_P), ds_lo = lo16(C::OFF_DS);
+        const uint32_t qdo_lo = lo16(C::OFF_QDO);
         bool ok = mbar_wait(kv_full, 0, dead, p.status, 2200);
-        if (ok) ok = mbar_wait(full_bar(0), 0, dead, p.status, 2201);
-        if (ok) {
-          tc_fence_after();
-          issue_sdp(sbase + C::OFF_QDO, sbase + C::OFF_QDO + C::TILE_BYTES);
-        }
-        auto issue_next_sdp = [&](int n) -> bool {   // S, dP of step n + 1
-          const int s1 = (n + 1) % C::STAGES;
-          const uint32_t ph1 = ((n + 1) / C::STAGES) & 1u;
-          if (!mbar_wait(full_bar(s1), ph1, dead, p.status, 2204)) return false;
-          if (C::DQ_ALIAS) {
-            // the S columns hold dQ of step n until the drain warps have read it
-            if (!mbar_wait(dq_drained, n & 1u, dead, p.status, 2205)) return false;
-          } else {
-            // S / dP of step n only have to be in registers
-            if (!mbar_wait(sdp_consumed, n & 1u, dead, p.status, 2206)) return false;
-          }
-          tc_fence_after();
-          const uint32_t q1 = sbase + C::OFF_QDO + s1 * 2 * C::TILE_BYTES;
-          issue_sdp(q1, q1 + C::TILE_BYTES);
-          return true;
-        };
-        for (int n = 0; n < total_steps && ok; ++n) {
-          const int s = n % C::STAGES;
-          const uint32_t sQ = sbase + C::OFF_QDO + s * 2 * C::TILE_BYTES;
-          const uint32_t sDO = sQ + C::TILE_BYTES;
-          // With a dQ tile of its own the next step's S / dP go first, so the
-          // compute warps never wait for the tensor core.
-          if (!C::DQ_ALIAS && n + 1 < total_steps && !issue_next_sdp(n)) { ok = false; break; }
-          if (!mbar_wait(pds_ready, n & 1u, dead, p.status, 2203)) { ok = false; break; }
-          if (!C::DQ_ALIAS && n > 0 &&
-              !mbar_wait(dq_drained, (n - 1) & 1u, dead, p.status, 2202)) { ok = false; break; }
-          tc_fence_after();
-          // reduction dimension = the 128 query rows, 16 per MMA: 16 rows x 128 B = 2048 B;
-          // 64-wide blocks of the M/N dimension are 128 rows x 128 B apart
+        if (warp == 1) {
+          for (int n = 0; n < total_steps && ok; ++n) {
+            const int s = n % C::STAGES;
+            if (!mbar_wait(full_bar(s), (n / C::STAGES) & 1u, dead, p.status, 2204)) { ok = false; break; }
+            if (n > 0) {
+              if (C::DQ_ALIAS) {
+                // the S columns hold dQ of step n - 1 until the drain warps have read it
+                if (!mbar_wait(dq_drained, (n - 1) & 1u, dead, p.status, 2205)) { ok = false; break; }
+              } else {
+                // S / dP of step n - 1 only have to be in registers
+                if (!mbar_wait(sdp_consumed, (n - 1) & 1u, dead, p.status, 2206)) { ok = false; break; }
+              }
+            }
+            tc_fence_after();
+            const uint32_t q_lo = (qdo_lo + s * (2 * C::TILE_BYTES >> 4)) | LBO_K;
+            const uint32_t do_lo = q_lo + (C::TILE_BYTES >> 4);
 #pragma unroll
-          for (int kk = 0; kk < C::BM / 16; ++kk) {
-            umma_f16(tmem_base + C::TMEM_DV, make_smem_desc_sw128(sP + kk * 2048, 128 * 128, 1024),
-                     make_smem_desc_sw128(sDO + kk * 2048, 128 * 128, 1024), idesc_kv,
-                     (n > 0 || kk != 0) ? 1u : 0u);
-          }
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint32_t o16 = (uint32_t)((kk >> 2) * (128 * 128) + (kk & 3) * 32) >> 4;
+              umma_f16(tmem_base + C::TMEM_S, desc(q_lo + o16), desc((k_lo | LBO_K) + o16), idesc_s, kk != 0 ? 1u : 0u);
+            }
 #pragma unroll
-          for (int kk = 0; kk < C::BM / 16; ++kk) {
-            umma_f16(tmem_base + C::TMEM_DK, make_smem_desc_sw128(sDS + kk * 2048, 128 * 128, 1024),
-                     make_smem_desc_sw128(sQ + kk * 2048, 128 * 128, 1024), idesc_kv,
-                     (n > 0 || kk != 0) ? 1u : 0u);
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint32_t o16 = (uint32_t)((kk >> 2) * (128 * 128) + (kk & 3) * 32) >> 4;
+              umma_f16(tmem_base + C::TMEM_DP, desc(do_lo + o16), desc((v_lo | LBO_K) + o16), idesc_s, kk != 0 ? 1u : 0u);
+            }
+            umma_commit(sdp_full);
           }
-          // dQ = dS K: reduction over the 128 keys; A = dS K-major, B = K MN-major
+        } else {
+          for (int n = 0; n < total_steps && ok; ++n) {
+            const int s = n % C::STAGES;
+            // this thread's own wait on the slot: its MMAs read Q and dO as well
+            if (!mbar_wait(full_bar(s), (n / C::STAGES) & 1u, dead, p.status, 2201)) { ok = false; break; }
+            if (!mbar_wait(pds_ready, n & 1u, dead, p.status, 2203)) { ok = false; break; }
+            if (!C::DQ_ALIAS && n > 0 &&
+                !mbar_wait(dq_drained, (n - 1) & 1u, dead, p.status, 2202)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t q_lo = (qdo_lo + s * (2 * C::TILE_BYTES >> 4)) | LBO_MN;
+            const uint32_t do_lo = q_lo + (C::TILE_BYTES >> 4);
+            // reduction dimension = the 128 query rows, 16 per MMA: 16 rows x 128 B = 2048 B
 #pragma unroll
-          for (int kk = 0; kk < C::BN / 16; ++kk) {
-            const uint32_t ao = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
-            umma_f16(tmem_base + C::TMEM_DQ, make_smem_desc_sw128(sDS + ao, 16, 1024),
-                     make_smem_desc_sw128(sK + kk * 2048, 128 * 128, 1024), idesc_q,
-                     kk != 0 ? 1u : 0u);
+            for (int kk = 0; kk < C::BM / 16; ++kk)
+              umma_f16(tmem_base + C::TMEM_DV, desc((p_lo | LBO_MN) + kk * 128u), desc(do_lo + kk * 128u), idesc_kv,
+                       (n > 0 || kk != 0) ? 1u : 0u);
+#pragma unroll
+            for (int kk = 0; kk < C::BM / 16; ++kk)
+              umma_f16(tmem_base + C::TMEM_DK, desc((ds_lo | LBO_MN) + kk * 128u), desc(q_lo + kk * 128u), idesc_kv,
+                       (n > 0 || kk != 0) ? 1u : 0u);
+            // dQ = dS K: reduction over the 128 keys; A = dS K-major, B = K MN-major
+#pragma unroll
+            for (int kk = 0; kk < C::BN / 16; ++kk) {
+              const uint32_t ao16 = (uint32_t)((kk >> 2) * (128 * 128) + (kk & 3) * 32) >> 4;
+              umma_f16(tmem_base + C::TMEM_DQ, desc((ds_lo | LBO_K) + ao16), desc((k_lo | LBO_MN) + kk * 128u), idesc_q,
+                       kk != 0 ? 1u : 0u);
+            }
+            umma_commit(empty_bar(s));
+            umma_commit(dq_full);
           }
-          umma_commit(empty_bar(s));
-          umma_commit(dq_full);
-          if (C::DQ_ALIAS && n + 1 < total_steps && !issue_next_sdp(n)) { ok = false; break; }
         }
       }
     }
@@ -293,7 +289,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               make_uint4(r[4 * q4], r[4 * q4 + 1], r[4 * q4 + 2], r[4 * q4 + 3]);
       }
       tc_fence_before();
-      if (!C::DQS_ALIAS) mbar_arrive(dq_drained);   // the TMEM tile is free again
+      if (!C::DQS_ALIAS) mbar_arrive_warp(dq_drained);   // the TMEM tile is free again
       fence_proxy_async_smem();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (leader) {
@@ -304,7 +300,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tma_store_wait_read<0>();
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");   // staging reusable
-      if (C::DQS_ALIAS) mbar_arrive(dq_drained);      // ... and so are the P / dS tiles it overlays
+      if (C::DQS_ALIAS) mbar_arrive_warp(dq_drained);      // ... and so are the P / dS tiles it overlays
     }
     if (leader) tma_store_wait_all<0>();
   }

@@ -9,7 +9,7 @@
 //                          whole key loop; it is rescaled in place only when a
 //                          row maximum grows by more than 2^8 (the final 1/l
 //                          normalisation makes a stale maximum exact)
-// Warp roles: 0 = TMA producer, 1 = MMA issuer, 2 = TMEM allocator,
+// Warp roles: 0 = TMA producer, 1 and 3 = MMA issuers of query tile 0 and 1, 2 = TMEM allocator,
 // 4..7 = softmax warpgroup of query tile 0, 8..11 = of query tile 1.  The two
 // query tiles share every K/V tile, which halves the L2 -> shared traffic.
 // A softmax thread owns one row: it takes the 128 scores of a key tile into
@@ -149,9 +149,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < C::RING; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int s = 0; s < C::RING; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 2); }   // two issuers release a slot
     for (int t = 0; t < 2; ++t) {
-      mbar_init(s_full(t), 1); mbar_init(p_ready(t), 128); mbar_init(o_done(t), 1); mbar_init(s_free(t), 128);
+      mbar_init(s_full(t), 1); mbar_init(p_ready(t), 4); mbar_init(o_done(t), 1); mbar_init(s_free(t), 4);   // one arrival per softmax warp
     }
     *dead = 0;
     mbar_fence_init();
@@ -202,40 +202,55 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (ok) load_tile(&tmV, j);
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------- MMA issuer -------------------------------
+  } else if (warp == 1 || warp == 3) {
+    // ------------------------------- MMA issuers -------------------------------
+    // One issuing thread per query tile (warp 1: tile 0, warp 3: tile 1).  A single thread
+    // issuing for both tiles was the kernel's critical path: every MMA costs it some tens of
+    // cycles and every barrier wait a few hundred, against 32 to 64 tensor cycles per MMA.
+    // Both walk the K/V ring in the producer's order; a slot is free again when both have
+    // released it (after their MMAs on it, or at once when their tile does not use it).
     if (lane == 0 && hi > lo) {
+      const int t = warp == 1 ? 0 : 1;
       const uint32_t idesc_s = make_idesc_bf16(C::BM, C::BN, 0, 0);
       const uint32_t idesc_o = make_idesc_bf16(C::BM, D, 0, 1);
+      // shared-memory descriptors: the high word is the same for every operand of this kernel
+      // (1024-byte stride between 8-row groups, 128-byte swizzle); the low word holds the
+      // address / 16 and the leading-dimension offset / 16, so stepping along a tile adds a
+      // compile-time constant to it
+      constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t LBO_K = (16u >> 4) << 16;                  // K-major operands
+      constexpr uint32_t LBO_V = ((uint32_t)(C::BN * 128) >> 4) << 16;   // V: MN-major, 64-wide head_dim blocks
+      auto desc = [&](uint32_t lo32) -> uint64_t {
+        return ((uint64_t)DESC_HI << 32) | (uint64_t)lo32;
+      };
+      const uint32_t q_lo = (((sbase + C::OFF_Q + t * C::Q_TILE_BYTES) & 0x3FFFFu) >> 4) | LBO_K;
+      const uint32_t p_lo = (((sbase + C::OFF_P + t * C::P_TILE_BYTES) & 0x3FFFFu) >> 4) | LBO_K;
+      const uint32_t kv_lo = ((sbase + C::OFF_KV) & 0x3FFFFu) >> 4;
+      const uint32_t s_tm = tmem_base + C::TMEM_S0 + t * 128;
+      const uint32_t o_tm = tmem_base + C::TMEM_O0 + t * D;
+      const int my_hi = hi_t[t];
       bool ok = true;
       uint32_t n = 0;            // ring counter (consumption order)
-      uint32_t pcount[2] = {0, 0};
-      auto issue_s = [&](int t, uint32_t kbase) {
-        const uint32_t qb = sbase + C::OFF_Q + t * C::Q_TILE_BYTES;
+      auto issue_s = [&](uint32_t slot) {
+        const uint32_t k_lo = (kv_lo + slot * (C::KV_TILE_BYTES >> 4)) | LBO_K;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t o = (kk >> 2) * (C::BM * 128) + (kk & 3) * 32;
-          umma_f16(tmem_base + C::TMEM_S0 + t * 128, make_smem_desc_sw128(qb + o, 16, 1024),
-                   make_smem_desc_sw128(kbase + o, 16, 1024), idesc_s, kk != 0 ? 1u : 0u);
+          const uint32_t o16 = (uint32_t)((kk >> 2) * (C::BM * 128) + (kk & 3) * 32) >> 4;
+          umma_f16(s_tm, desc(q_lo + o16), desc(k_lo + o16), idesc_s, kk != 0 ? 1u : 0u);
         }
         umma_commit(s_full(t));
       };
-      auto issue_pv = [&](int t, uint32_t vbase, bool acc) {
-        const uint32_t pb = sbase + C::OFF_P + t * C::P_TILE_BYTES;
+      auto issue_pv = [&](uint32_t slot, bool acc) {
+        const uint32_t v_lo = (kv_lo + slot * (C::KV_TILE_BYTES >> 4)) | LBO_V;
 #pragma unroll
         for (int kk = 0; kk < C::BN / 16; ++kk) {
-          // A = P: K-major, 64-key blocks of [128 rows x 128 B]
-          const uint32_t ao = (kk >> 2) * (C::BM * 128) + (kk & 3) * 32;
-          // B = V: MN-major (head_dim contiguous), 16 key rows per step, 64-wide
-          // head_dim blocks C::BN*128 bytes apart
-          const uint32_t bo = kk * 2048;
-          umma_f16(tmem_base + C::TMEM_O0 + t * D, make_smem_desc_sw128(pb + ao, 16, 1024),
-                   make_smem_desc_sw128(vbase + bo, C::BN * 128, 1024), idesc_o,
-                   (acc || kk != 0) ? 1u : 0u);
+          // A = P: K-major, 64-key blocks of [128 rows x 128 B]; B = V: 16 key rows per step
+          const uint32_t ao16 = (uint32_t)((kk >> 2) * (C::BM * 128) + (kk & 3) * 32) >> 4;
+          const uint32_t bo16 = (uint32_t)(kk * 2048) >> 4;
+          umma_f16(o_tm, desc(p_lo + ao16), desc(v_lo + bo16), idesc_o, (acc || kk != 0) ? 1u : 0u);
         }
         umma_commit(o_done(t));
       };
-      if (!mbar_wait(q_full, 0, dead, p.status, 1200)) ok = false;
       // ring order (the producer's): K_lo, then (K_{j+1}, V_j) per key tile j
       auto take_slot = [&](int where) -> uint32_t {
         const int s = n % C::RING;
@@ -244,45 +259,44 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         ++n;
         return (uint32_t)s;
       };
+      auto release = [&](uint32_t slot, bool used) {
+        if (used) umma_commit(empty_bar(slot));   // once the MMAs that read it are done
+        else mbar_arrive(empty_bar(slot));
+      };
+      if (!mbar_wait(q_full, 0, dead, p.status, 1200)) ok = false;
       if (ok) {
         const uint32_t s = take_slot(1201);
         if (ok) {
-          const uint32_t kb = sbase + C::OFF_KV + s * C::KV_TILE_BYTES;
-          for (int t = 0; t < 2; ++t)
-            if (lo < hi_t[t]) issue_s(t, kb);
-          umma_commit(empty_bar(s));
+          if (lo < my_hi) issue_s(s);
+          release(s, lo < my_hi);
         }
       }
-      uint32_t fcount[2] = {0, 0};
+      uint32_t fcount = 0, pcount = 0;
       for (int j = lo; j < hi && ok; ++j) {
         // S of the next key tile as soon as the softmax warps hold this tile's scores in registers
         if (j + 1 < hi) {
           const uint32_t ks = take_slot(1220);
           if (!ok) break;
-          const uint32_t kaddr = sbase + C::OFF_KV + ks * C::KV_TILE_BYTES;
-          for (int t = 0; t < 2 && ok; ++t) {
-            if (j + 1 >= hi_t[t]) continue;
-            if (!mbar_wait(s_free(t), fcount[t] & 1u, dead, p.status, 1240 + t)) { ok = false; break; }
-            ++fcount[t];
+          const bool use = j + 1 < my_hi;
+          if (use) {
+            if (!mbar_wait(s_free(t), fcount & 1u, dead, p.status, 1240 + t)) { ok = false; break; }
+            ++fcount;
             tc_fence_after();
-            issue_s(t, kaddr);
+            issue_s(ks);
           }
-          if (!ok) break;
-          umma_commit(empty_bar(ks));
+          release(ks, use);
         }
         // O += P V of this key tile once P is in shared memory
         const uint32_t vs = take_slot(1230);
         if (!ok) break;
-        const uint32_t vaddr = sbase + C::OFF_KV + vs * C::KV_TILE_BYTES;
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (j >= hi_t[t]) continue;
-          if (!mbar_wait(p_ready(t), pcount[t] & 1u, dead, p.status, 1210 + t)) { ok = false; break; }
-          ++pcount[t];
+        const bool use = j < my_hi;
+        if (use) {
+          if (!mbar_wait(p_ready(t), pcount & 1u, dead, p.status, 1210 + t)) { ok = false; break; }
+          ++pcount;
           tc_fence_after();
-          issue_pv(t, vaddr, j > lo);
+          issue_pv(vs, j > lo);
         }
-        if (!ok) break;
-        umma_commit(empty_bar(vs));
+        release(vs, use);
       }
     }
    }
@@ -334,7 +348,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, r[c]);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(s_free(t));
+      mbar_arrive_warp(s_free(t));
       float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
@@ -397,7 +411,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       l += (s0 + s1) + (s2 + s3);
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(p_ready(t));
+      mbar_arrive_warp(p_ready(t));
     }
     // epilogue: O / l -> global, LSE
     const bool have = my_hi > lo;

@@ -191,8 +191,8 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUten
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 256);
-      mbar_init(epi_bar(a), 256);
+      mbar_init(tempty_bar(a), 8);     // one arrival per epilogue warp
+      mbar_init(epi_bar(a), 8);
     }
     *dead = 0;
     mbar_fence_init();
@@ -272,8 +272,15 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUten
       const uint32_t idesc = make_idesc_bf16(BM, BN, g.a_mn, g.b_mn);
       const uint32_t a_lbo = g.a_mn ? 8192u : 16u;
       const uint32_t b_lbo = g.b_mn ? 8192u : 16u;
-      const uint32_t a_kstep = g.a_mn ? 2048u : 32u;  // bytes per 16 K elements
-      const uint32_t b_kstep = g.b_mn ? 2048u : 32u;
+      // Shared-memory descriptors: the high word (1024-byte stride between 8-row groups, 128-byte
+      // swizzle) is the same for every operand; the low word is address / 16 | leading offset / 16
+      // << 16, so a stage or a 16-element K step adds a constant to it.  The single issuing
+      // thread has about a hundred cycles per MMA: nothing but two additions belongs in the loop.
+      const uint64_t desc_hi = (uint64_t)((1024u >> 4) | (1u << 14) | (2u << 29)) << 32;
+      const uint32_t a_k16 = (g.a_mn ? 2048u : 32u) >> 4;  // 16 K elements, in 16-byte units
+      const uint32_t b_k16 = (g.b_mn ? 2048u : 32u) >> 4;
+      const uint32_t a_lo0 = ((smem_base & 0x3FFFFu) >> 4) | ((a_lbo >> 4) << 16);
+      const uint32_t b_lo0 = (((smem_base + L::A_BYTES) & 0x3FFFFu) >> 4) | ((b_lbo >> 4) << 16);
       uint32_t kit = 0;
       uint32_t it = 0;
       bool ok = true;
@@ -290,14 +297,12 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUten
           const uint32_t ph = (kit / STAGES) & 1u;
           if (!mbar_wait(full_bar(s), ph, dead, g.status, 201)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sA = smem_base + s * L::STAGE_BYTES;
-          const uint32_t sB = sA + L::A_BYTES;
+          const uint32_t a_lo = a_lo0 + (uint32_t)s * (L::STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + (uint32_t)s * (L::STAGE_BYTES >> 4);
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk) {
-            const uint64_t ad = make_smem_desc_sw128(sA + kk * a_kstep, a_lbo, 1024u);
-            const uint64_t bd = make_smem_desc_sw128(sB + kk * b_kstep, b_lbo, 1024u);
-            umma_f16(d_tmem, ad, bd, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
-          }
+          for (int kk = 0; kk < BK / 16; ++kk)
+            umma_f16(d_tmem, desc_hi | (uint64_t)(a_lo + kk * a_k16), desc_hi | (uint64_t)(b_lo + kk * b_k16), idesc,
+                     (kb != kb0 || kk != 0) ? 1u : 0u);
           umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
         }
         if (ok) umma_commit(tfull_bar(acc));

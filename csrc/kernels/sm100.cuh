@@ -106,6 +106,14 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One arrival per warp (the barrier counts warps, not threads): an arrival is an atomic on one
+// shared-memory word, and 128 or 256 of them per tile and barrier serialise.  Every lane must have
+// issued its own fences (proxy, tcgen05) before the call; the warp barrier orders the lanes'
+// earlier accesses before lane 0's releasing arrival.
+__device__ __forceinline__ void mbar_arrive_warp(uint32_t bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31u) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(

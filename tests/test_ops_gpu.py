@@ -246,5 +246,6 @@ def test_softmax_dropout_residual_kernel(dtype):
     y2 = softmax_dropout_residual(x2, None, p=0.2, seed=77)
     (g2,) = torch.autograd.grad(y2, x2, g)
     xs = x.detach().float().requires_grad_(True)
-    (r2,) = torch.autograd.grad(_dropout_apply(torch.softmax(xs, -1), 0.2, 77), xs, g.float())
+    keep = _dropout_apply(torch.ones_like(xs), 0.2, 77)          # the mask itself, scaled by 1 / (1 - p)
+    (r2,) = torch.autograd.grad(torch.softmax(xs, -1) * keep, xs, g.float())
     assert (g2.float() - r2).abs().max() < tol * max(1.0, float(r2.abs().max()))
