@@ -53,10 +53,11 @@ struct AgDev {
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux,
                const GemmDev g, const AgDev a) {
   extern __shared__ uint8_t smem_raw[];
   if ((int)blockIdx.x >= a.n_copy) {
-    gemm_tc_body<BN, STAGES>(tmA, tmB, g, (int)blockIdx.x - a.n_copy, (int)gridDim.x - a.n_copy, smem_raw);
+    gemm_tc_body<BN, STAGES>(tmA, tmB, &tmC, &tmAux, g, (int)blockIdx.x - a.n_copy, (int)gridDim.x - a.n_copy, smem_raw);
     return;
   }
   // ------------------------------ copy CTAs ------------------------------
@@ -227,7 +228,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                const GemmDev g, const RsDev r) {
   extern __shared__ uint8_t smem_raw[];
   if ((int)blockIdx.x >= r.n_reduce)
-    gemm_tc_body<BN, STAGES>(tmA, tmB, g, (int)blockIdx.x - r.n_reduce, (int)gridDim.x - r.n_reduce,
+    gemm_tc_body<BN, STAGES>(tmA, tmB, nullptr, nullptr, g, (int)blockIdx.x - r.n_reduce, (int)gridDim.x - r.n_reduce,
                              smem_raw);
   // ------------------------------ reduce phase ------------------------------
   // A few CTAs reduce from the start; every GEMM CTA joins once it has run out of
@@ -273,12 +274,15 @@ static int launch_ag(const cgk_gemm_args& ga, GemmDev g, const AgDev& a, int cta
   using L = GemmSmem<BN, STAGES>;
   g.tiles_m = (ga.M + BM - 1) / BM;
   g.tiles_n = (ga.N + BN - 1) / BN;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC, tmAux;
   int rc = make_gemm_tmaps(ga, BN, &tmA, &tmB);
   if (rc) return rc;
+  int out_ok = 0;
+  if ((rc = make_gemm_out_tmaps(ga, &tmC, &tmAux, &out_ok))) return rc;
+  g.tma_store = out_ok;
   CGK_CUDA_CHECK(cudaFuncSetAttribute(ag_gemm_kernel<BN, STAGES>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-  ag_gemm_kernel<BN, STAGES><<<ctas, GEMM_THREADS, L::TOTAL, st>>>(tmA, tmB, g, a);
+  ag_gemm_kernel<BN, STAGES><<<ctas, GEMM_THREADS, L::TOTAL, st>>>(tmA, tmB, tmC, tmAux, g, a);
   CGK_LAUNCH_CHECK();
   return 0;
 }

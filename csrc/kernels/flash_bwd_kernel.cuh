@@ -41,8 +41,8 @@ struct BwdCfg {
   static constexpr bool DQS_ALIAS = (D == 128);
   static constexpr int OFF_DQS = DQS_ALIAS ? OFF_P : OFF_DS + PS_BYTES;
   static constexpr int OFF_BAR = OFF_DS + PS_BYTES + (DQS_ALIAS ? 0 : DQS_BYTES);
-  // kv_full, full[STAGES], empty[STAGES], sdp_full, pds_ready, dq_full, dq_drained, sdp_consumed
-  static constexpr int NUM_BARS = 1 + 2 * STAGES + 5;
+  // kv_full, full[STAGES], empty[STAGES], sdp_full, pds_ready, dq_full, dq_drained, sdp_consumed, pds_free
+  static constexpr int NUM_BARS = 1 + 2 * STAGES + 6;
   static constexpr int TOTAL = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
   static constexpr int TMEM_S = 0;
   static constexpr int TMEM_DP = 128;
@@ -104,6 +104,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t dq_full = sdp_full + 16;
   const uint32_t dq_drained = sdp_full + 24;
   const uint32_t sdp_consumed = sdp_full + 32;
+  const uint32_t pds_free = sdp_full + 40;     // the MMAs that read this step's P / dS tiles are done
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::NUM_BARS * 8);
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
@@ -137,6 +138,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(sdp_full, 1);
     mbar_init(pds_ready, 8);          // one arrival per warp
     mbar_init(dq_full, 1);
+    mbar_init(pds_free, 2);           // the dV / dK issuer and the dQ issuer
     mbar_init(dq_drained, 4);
     mbar_init(sdp_consumed, 8);
     *dead = 0;
@@ -179,11 +181,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
       }
-    } else if (warp == 1 || warp == 3) {
+    } else {
       // ------------------------------- MMA issuers -------------------------------
-      // Two issuing threads: warp 1 issues S = Q K^T and dP = dO V^T of every step, warp 3 the
-      // three products that consume P / dS (dV, dK, dQ).  One thread issuing all 32 to 40 MMAs of
-      // a step was the kernel's critical path (tens of cycles per MMA, hundreds per barrier wait).
+      // Three issuing threads: warp 1 issues S = Q K^T and dP = dO V^T of every step, warp 3 the
+      // two products over the query rows (dV = P^T dO, dK = dS^T Q), warp 2 dQ = dS K.  One thread
+      // issuing all 32 to 40 MMAs of a step was the kernel's critical path (some seventy cycles
+      // per MMA, hundreds per barrier wait), and the P / dS tiles cannot be rewritten before the
+      // last of the three products has read them.
       if (lane == 0 && total_steps > 0) {
         const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);   // S, dP: both K-major
         const uint32_t idesc_kv = make_idesc_bf16(128, D, 1, 1);    // dV, dK: A and B MN-major
@@ -226,14 +230,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             umma_commit(sdp_full);
           }
-        } else {
+        } else if (warp == 3) {
           for (int n = 0; n < total_steps && ok; ++n) {
             const int s = n % C::STAGES;
-            // this thread's own wait on the slot: its MMAs read Q and dO as well
+            // this thread's own wait on the slot: its MMAs read Q and dO
             if (!mbar_wait(full_bar(s), (n / C::STAGES) & 1u, dead, p.status, 2201)) { ok = false; break; }
             if (!mbar_wait(pds_ready, n & 1u, dead, p.status, 2203)) { ok = false; break; }
-            if (!C::DQ_ALIAS && n > 0 &&
-                !mbar_wait(dq_drained, (n - 1) & 1u, dead, p.status, 2202)) { ok = false; break; }
             tc_fence_after();
             const uint32_t q_lo = (qdo_lo + s * (2 * C::TILE_BYTES >> 4)) | LBO_MN;
             const uint32_t do_lo = q_lo + (C::TILE_BYTES >> 4);
@@ -246,6 +248,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (int kk = 0; kk < C::BM / 16; ++kk)
               umma_f16(tmem_base + C::TMEM_DK, desc((ds_lo | LBO_MN) + kk * 128u), desc(q_lo + kk * 128u), idesc_kv,
                        (n > 0 || kk != 0) ? 1u : 0u);
+            umma_commit(empty_bar(s));
+            umma_commit(pds_free);
+          }
+        } else {
+          for (int n = 0; n < total_steps && ok; ++n) {
+            if (!mbar_wait(pds_ready, n & 1u, dead, p.status, 2207)) { ok = false; break; }
+            if (!C::DQ_ALIAS && n > 0 &&
+                !mbar_wait(dq_drained, (n - 1) & 1u, dead, p.status, 2202)) { ok = false; break; }
+            tc_fence_after();
             // dQ = dS K: reduction over the 128 keys; A = dS K-major, B = K MN-major
 #pragma unroll
             for (int kk = 0; kk < C::BN / 16; ++kk) {
@@ -253,8 +264,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               umma_f16(tmem_base + C::TMEM_DQ, desc((ds_lo | LBO_K) + ao16), desc((k_lo | LBO_MN) + kk * 128u), idesc_q,
                        kk != 0 ? 1u : 0u);
             }
-            umma_commit(empty_bar(s));
             umma_commit(dq_full);
+            umma_commit(pds_free);
           }
         }
       }
@@ -275,7 +286,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int g = n / steps_per_head, i = i_lo + n % steps_per_head;
       const int h = hk * group + g;
       if (!mbar_wait(dq_full, n & 1u, dead, p.status, 2301)) { ok = false; break; }
+      // where the staging tile overlays the P / dS tiles, dV and dK must have read them too
+      if (C::DQS_ALIAS && !mbar_wait(pds_free, n & 1u, dead, p.status, 2304)) { ok = false; break; }
       tc_fence_after();
+      if (!C::DQS_ALIAS && n > 0) {
+        // the previous step's reduction must have read the staging tile; it had a whole step for it
+        if (leader) tma_store_wait_read<0>();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
@@ -297,10 +315,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int c = 0; c < D / 32; ++c)
           tma_reduce_add_3d(&tmDQ, sbase + C::OFF_DQS + c * (128 * 128), h * D + c * 32, i * C::BM, b);
         tma_store_commit();
-        tma_store_wait_read<0>();
+        if (C::DQS_ALIAS) tma_store_wait_read<0>();
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");   // staging reusable
-      if (C::DQS_ALIAS) mbar_arrive_warp(dq_drained);      // ... and so are the P / dS tiles it overlays
+      if (C::DQS_ALIAS) {
+        // the staging tile overlays the P / dS tiles: they are free once the reduction has read it
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        mbar_arrive_warp(dq_drained);
+      }
     }
     if (leader) tma_store_wait_all<0>();
   }

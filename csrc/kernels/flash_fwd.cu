@@ -60,8 +60,8 @@ struct FwdCfg {
   static constexpr int OFF_KV = OFF_Q + 2 * Q_TILE_BYTES;
   static constexpr int OFF_P = OFF_KV + RING * KV_TILE_BYTES;
   static constexpr int OFF_BAR = OFF_P + 2 * P_TILE_BYTES;
-  // barriers: q_full, full[RING], empty[RING], s_full[2], p_ready[2], o_done[2], s_free[2]
-  static constexpr int NUM_BARS = 1 + 2 * RING + 8;
+  // barriers: q_full, full[RING], empty[RING], s_full[2], p_ready[2], o_done[2], s_free[2], exp_done[2]
+  static constexpr int NUM_BARS = 1 + 2 * RING + 10;
   static constexpr int TOTAL = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
   static constexpr int TMEM_S0 = 0;
   static constexpr int TMEM_O0 = 256;
@@ -109,6 +109,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   auto p_ready = [&](int t) { return bar0 + 8u * (1 + 2 * C::RING + 2 + t); };
   auto o_done = [&](int t) { return bar0 + 8u * (1 + 2 * C::RING + 4 + t); };
   auto s_free = [&](int t) { return bar0 + 8u * (1 + 2 * C::RING + 6 + t); };
+  auto exp_done = [&](int t) { return bar0 + 8u * (1 + 2 * C::RING + 8 + t); };
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::NUM_BARS * 8);
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
@@ -152,6 +153,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int s = 0; s < C::RING; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 2); }   // two issuers release a slot
     for (int t = 0; t < 2; ++t) {
       mbar_init(s_full(t), 1); mbar_init(p_ready(t), 4); mbar_init(o_done(t), 1); mbar_init(s_free(t), 4);   // one arrival per softmax warp
+      mbar_init(exp_done(t), 4);
     }
     *dead = 0;
     mbar_fence_init();
@@ -308,6 +310,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int row = quad * 32 + lane;          // row inside the query tile == TMEM lane
     const int qpos = q0 + t * C::BM + row;
     const int my_hi = hi_t[t];
+    const int n_other = hi_t[1 - t] - lo;      // steps of the other warpgroup
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t s_tmem = tmem_base + C::TMEM_S0 + t * 128 + lane_sel;
     const uint32_t o_tmem = tmem_base + C::TMEM_O0 + t * D + lane_sel;
@@ -385,17 +388,32 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       l *= alpha;
       m = m_use;
       const float neg_m = (m == -INFINITY) ? 0.0f : -m;
+      // The SM computes 16 exponentials per clock, 1024 clocks for a 128 x 128 tile, which is the
+      // longest stretch of a softmax step.  The two warpgroups therefore take turns at it (tile 0's
+      // step i, tile 1's step i, tile 0's step i + 1, ...): one exponentiates while the other
+      // loads scores, finds maxima and waits for the tensor core, instead of both halving each
+      // other's rate and then idling together.  A warpgroup that has run out of steps is not
+      // waited for.
+      if (t == 0) {
+        if (it > 0 && (int)it - 1 < n_other &&
+            !mbar_wait(exp_done(1), (it - 1) & 1u, dead, p.status, 1330)) { ok = false; break; }
+      } else {
+        if ((int)it < n_other && !mbar_wait(exp_done(0), it & 1u, dead, p.status, 1331)) { ok = false; break; }
+      }
       // P = exp2(score * mul - m), bf16, into the swizzled operand tile
       float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         float e[32];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float x0, x1;
+        for (int i = 0; i < 32; i += 4) {
+          // half of the exponentials on the special-function unit, half on the FMA pipe
+          float x0, x1, y0, y1;
           ffma2(x0, x1, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]), mul, mul, neg_m, neg_m);
+          ffma2(y0, y1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]), mul, mul, neg_m, neg_m);
           e[i] = fast_exp2(x0);
           e[i + 1] = fast_exp2(x1);
+          exp2_poly2(e[i + 2], e[i + 3], y0, y1);
         }
 #pragma unroll
         for (int i = 0; i < 32; i += 4) { fadd2(s0, s1, e[i], e[i + 1]); fadd2(s2, s3, e[i + 2], e[i + 3]); }
@@ -409,6 +427,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
       l += (s0 + s1) + (s2 + s3);
+      mbar_arrive_warp(exp_done(t));
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive_warp(p_ready(t));

@@ -10,6 +10,9 @@ namespace cgk {
 // Tensor maps of both operands for a tile width BN (box shapes depend on the
 // operand's storage order).
 int make_gemm_tmaps(const cgk_gemm_args& a, int BN, CUtensorMap* tmA, CUtensorMap* tmB);
+// Tensor maps of the bf16 output and the pre-activation output for the epilogue's bulk stores;
+// *ok = 0 (and cleared maps) when the output's layout or the epilogue's terms rule them out.
+int make_gemm_out_tmaps(const cgk_gemm_args& a, CUtensorMap* tmC, CUtensorMap* tmAux, int* ok);
 // Copies the argument struct into the device-side parameter block (hooks cleared).
 int fill_gemm_dev(const cgk_gemm_args& a, GemmDev* g);
 // True when both operands satisfy TMA's alignment rules.

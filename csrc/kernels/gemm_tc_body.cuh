@@ -16,6 +16,10 @@ struct GemmDev {
   void* out;
   long long ldc, strideC;
   int out_fp32, accumulate;
+  // 1: the bf16 output (and the pre-activation output, if any) leaves through bulk tensor stores
+  // from the epilogue's staging tiles; the launcher sets it when the output's layout allows a
+  // tensor map (16-byte aligned base, leading dimension a multiple of 8) and nothing is accumulated
+  int tma_store;
   float alpha;
   const void* bias;
   int bias_fp32;
@@ -129,12 +133,17 @@ struct GemmSmem {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  // per-warp staging tiles of the epilogue (8 warps x 4 KiB = 32 rows x 128 bytes each, 128-byte
+  // swizzle, 1024-byte aligned): outputs are transposed through them so that they leave as whole
+  // lines (bulk tensor stores, or 128-byte row segments on the reduce-scatter path)
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + 8 * 4096;
   static constexpr int NUM_BARS = 2 * STAGES + 6;
-  // per-warp transposition area of the reduce-scatter epilogue (8 warps x 4 KiB); the plain
-  // epilogue keeps the tile's bias slice there (2 x BN floats)
-  static constexpr int EPI_OFFSET = (BAR_OFFSET + NUM_BARS * 8 + 16 + 127) / 128 * 128;
-  static constexpr int TOTAL = EPI_OFFSET + 8 * 4096 + 1024;  // + alignment slack
+  // the tile's bias slice, two tiles deep: fp32 for tiles of up to 128 columns, bf16 for 256
+  // (an fp32 bias with the widest tile is read from global memory instead)
+  static constexpr int SBIAS_OFFSET = (BAR_OFFSET + NUM_BARS * 8 + 16 + 127) / 128 * 128;
+  static constexpr int TOTAL = SBIAS_OFFSET + 1024 + 1024;  // + alignment slack
+  static_assert(TOTAL <= 227 * 1024, "GEMM: shared memory budget of one CTA exceeded");
 };
 
 __device__ __forceinline__ void tile_coords(const GemmDev& g, int t, int& b, int& tm, int& tn) {
@@ -163,6 +172,7 @@ __device__ __forceinline__ void tile_coords(const GemmDev& g, int t, int& b, int
 // give some CTAs of the grid other roles).  GEMM_THREADS threads.
 template <int BN, int STAGES>
 __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUtensorMap& tmB,
+                                             const CUtensorMap* tmC, const CUtensorMap* tmAux,
                                              const GemmDev& g, int cta, int nctas,
                                              uint8_t* smem_raw) {
   using L = GemmSmem<BN, STAGES>;
