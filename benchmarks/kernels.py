@@ -2,8 +2,8 @@
 
     python benchmarks/kernels.py <case> [--iters N] [--warmup W] [--small]
 
-Cases: gemm, flash_fwd, flash_bwd, layernorm, rmsnorm, cross_entropy, adam, int4_gemm, kv_attn,
-sample, all.  Each result is one JSON line: device time per call (CUDA events on the launching
+Cases: gemm, gemm_epilogue, flash_fwd, flash_bwd, layernorm, layernorm_bwd, rmsnorm, bias_grad,
+cross_entropy, adam, int4_gemm, kv_attn, sample, all.  Each result is one JSON line: device time per call (CUDA events on the launching
 stream, median of `iters` after `warmup` untimed calls, L2 flushed by writing a 256 MiB buffer
 between calls), achieved TFLOP/s or GB/s, and the fraction of the measured peak taken from
 MEASURED_PEAKS.json beside the repository root (copy bandwidth / cuBLAS bf16 burst) when that
@@ -119,6 +119,57 @@ def _norm(t, small, rms):
 
 def case_layernorm(t, small):
     _norm(t, small, False)
+
+
+def case_layernorm_bwd(t, small):
+    """Backward of the residual-stream LayerNorm: reads x, dy and the second gradient of the
+    residual stream, writes dx (4 passes over [rows, cols]) plus the small dgamma / dbeta."""
+    from cogito_b200.ops.norm import layer_norm
+    R, C = (16384 if small else 131072), 768
+    x = torch.randn(R, C, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    g = torch.ones(C, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    b = torch.zeros(C, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = layer_norm(x, g, b)
+    dy = torch.randn_like(y)
+
+    def bwd():
+        x.grad = g.grad = b.grad = None
+        y.backward(dy, retain_graph=True)
+    emit("layernorm_bwd", t(bwd), bytes_=3.0 * R * C * 2, rows=R, cols=C)
+
+
+def case_bias_grad(t, small):
+    """Column sums of a [rows, cols] bf16 gradient (the bias gradient of a linear layer)."""
+    from cogito_b200.ops.functional import colsum
+    R = 16384 if small else 131072
+    for C in (768, 3072):
+        dy = torch.randn(R, C, device="cuda", dtype=torch.bfloat16)
+        emit("bias_grad", t(lambda: colsum(dy)), bytes_=1.0 * R * C * 2, rows=R, cols=C)
+
+
+def case_gemm_epilogue(t, small):
+    """The GPT-2 block's K = 768 projections with their epilogues (bias, GELU with the pre-activation
+    kept for backward, residual add, activation derivative)."""
+    from cogito_b200.ops.gemm import gemm
+    M = 16384 if small else 65536
+    x = torch.randn(M, 768, device="cuda", dtype=torch.bfloat16)
+    w_up = torch.randn(3072, 768, device="cuda", dtype=torch.bfloat16) * 0.02
+    w_dn = torch.randn(768, 3072, device="cuda", dtype=torch.bfloat16) * 0.02      # [out, in]: the dgrad reads it as [K, N]
+    w_pr = torch.randn(768, 768, device="cuda", dtype=torch.bfloat16) * 0.02
+    w_qkv = torch.randn(2304, 768, device="cuda", dtype=torch.bfloat16) * 0.02
+    b_up = torch.zeros(3072, device="cuda", dtype=torch.bfloat16)
+    b_pr = torch.zeros(768, device="cuda", dtype=torch.bfloat16)
+    b_qkv = torch.zeros(2304, device="cuda", dtype=torch.bfloat16)
+    aux = torch.empty(M, 3072, device="cuda", dtype=torch.bfloat16)
+    out_up = torch.empty(M, 3072, device="cuda", dtype=torch.bfloat16)
+    cases = [
+        ("qkv: bias", lambda: gemm(x, w_qkv, bias=b_qkv), 2304, 768),
+        ("proj: bias + residual", lambda: gemm(x, w_pr, bias=b_pr, residual=x), 768, 768),
+        ("mlp up: bias + gelu, pre-activation kept", lambda: gemm(x, w_up, bias=b_up, act="gelu", aux_out=aux, out=out_up), 3072, 768),
+        ("mlp down dgrad: x gelu'(pre-activation)", lambda: gemm(x, w_dn, b_mn=True, aux_in=aux, dact="gelu", out=out_up), 3072, 768),
+    ]
+    for name, fn, N, K in cases:
+        emit("gemm_epilogue", t(fn), flops=2.0 * M * N * K, what=name, M=M, N=N, K=K)
 
 
 def case_rmsnorm(t, small):

@@ -52,9 +52,20 @@ class LlamaInt4Engine:
         self.tp = dist.get_world_size(tp_group) if tp_group is not None else 1
         r = self.tp_rank = dist.get_rank(tp_group) if tp_group is not None else 0
         tp, D, d = self.tp, cfg.head_dim, cfg.d_model
-        if cfg.n_head % tp or cfg.n_kv_head % tp or cfg.d_ff % tp:
-            raise ValueError("heads, kv heads and d_ff must be divisible by the tensor-parallel size")
-        self.Hq, self.Hk, ff = cfg.n_head // tp, cfg.n_kv_head // tp, cfg.d_ff // tp
+        if cfg.n_head % tp or cfg.n_kv_head % tp:
+            raise ValueError("heads and kv heads must be divisible by the tensor-parallel size")
+        self.Hq, self.Hk = cfg.n_head // tp, cfg.n_kv_head // tp
+        # The MLP's hidden units are dealt out in blocks of the quantisation group, so that every
+        # rank's slices are cut on group boundaries (Llama-7B: 11008 = 86 blocks of 128, which 8
+        # ranks share as 11, 11, 11, 11, 11, 11, 10, 10).
+        if tp > 1:
+            if cfg.d_ff % weight_group or cfg.d_ff // weight_group < tp:
+                raise ValueError(f"d_ff must be a multiple of the weight group ({weight_group}) with at least one block per rank")
+            base, extra = divmod(cfg.d_ff // weight_group, tp)
+            ff0 = (r * base + min(r, extra)) * weight_group
+            ff = (base + (1 if r < extra else 0)) * weight_group
+        else:
+            ff0, ff = 0, cfg.d_ff
         nq, nk = cfg.n_head * D, cfg.n_kv_head * D
 
         def rows(w, *spans):                    # concatenation of row ranges [start, start + n) of a [out, in] weight
@@ -65,9 +76,9 @@ class LlamaInt4Engine:
         for blk in model.blocks:
             qkv_w, gu_w = blk.attn.qkv.weight.data, blk.mlp.gate_up.weight.data
             qkv = rows(qkv_w, (r * self.Hq * D, self.Hq * D), (nq + r * self.Hk * D, self.Hk * D), (nq + nk + r * self.Hk * D, self.Hk * D))
-            gate_up = rows(gu_w, (r * ff, ff), (cfg.d_ff + r * ff, ff))
+            gate_up = rows(gu_w, (ff0, ff), (cfg.d_ff + ff0, ff))
             proj = blk.attn.proj.weight.data[:, r * self.Hq * D:(r + 1) * self.Hq * D] if tp > 1 else blk.attn.proj.weight.data
-            down = blk.mlp.down.weight.data[:, r * ff:(r + 1) * ff] if tp > 1 else blk.mlp.down.weight.data
+            down = blk.mlp.down.weight.data[:, ff0:ff0 + ff] if tp > 1 else blk.mlp.down.weight.data
             self.layers.append(dict(
                 norm1=blk.norm1.weight.detach().to(self.dtype), norm2=blk.norm2.weight.detach().to(self.dtype),
                 qkv=Int4Linear(qkv, None, weight_group), proj=Int4Linear(proj, None, weight_group),

@@ -406,14 +406,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int c = 0; c < 4; ++c) {
         float e[32];
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          // half of the exponentials on the special-function unit, half on the FMA pipe
-          float x0, x1, y0, y1;
+        for (int i = 0; i < 32; i += 2) {
+          float x0, x1;
           ffma2(x0, x1, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]), mul, mul, neg_m, neg_m);
-          ffma2(y0, y1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]), mul, mul, neg_m, neg_m);
           e[i] = fast_exp2(x0);
           e[i + 1] = fast_exp2(x1);
-          exp2_poly2(e[i + 2], e[i + 3], y0, y1);
         }
 #pragma unroll
         for (int i = 0; i < 32; i += 4) { fadd2(s0, s1, e[i], e[i + 1]); fadd2(s2, s3, e[i + 2], e[i + 3]); }

@@ -12,7 +12,10 @@ namespace cgk {
 int make_gemm_tmaps(const cgk_gemm_args& a, int BN, CUtensorMap* tmA, CUtensorMap* tmB);
 // Tensor maps of the bf16 output and the pre-activation output for the epilogue's bulk stores;
 // *ok = 0 (and cleared maps) when the output's layout or the epilogue's terms rule them out.
-int make_gemm_out_tmaps(const cgk_gemm_args& a, CUtensorMap* tmC, CUtensorMap* tmAux, int* ok);
+// tmIn / *in_kind: the one epilogue input fetched by bulk loads (1 = activation-derivative operand,
+// 2 = residual, 0 = none).
+int make_gemm_out_tmaps(const cgk_gemm_args& a, CUtensorMap* tmC, CUtensorMap* tmAux, CUtensorMap* tmIn, int* ok,
+                        int* in_kind);
 // Copies the argument struct into the device-side parameter block (hooks cleared).
 int fill_gemm_dev(const cgk_gemm_args& a, GemmDev* g);
 // True when both operands satisfy TMA's alignment rules.

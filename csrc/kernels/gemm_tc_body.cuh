@@ -20,6 +20,10 @@ struct GemmDev {
   // from the epilogue's staging tiles; the launcher sets it when the output's layout allows a
   // tensor map (16-byte aligned base, leading dimension a multiple of 8) and nothing is accumulated
   int tma_store;
+  // 1: aux_in (2: residual) is fetched by bulk tensor loads into the epilogue's staging tiles
+  // (set together with tma_store when that operand's layout allows a tensor map and no
+  // pre-activation output needs the second half of the staging tile)
+  int tma_in;
   float alpha;
   const void* bias;
   int bias_fp32;
@@ -138,7 +142,7 @@ struct GemmSmem {
   // lines (bulk tensor stores, or 128-byte row segments on the reduce-scatter path)
   static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int BAR_OFFSET = EPI_OFFSET + 8 * 4096;
-  static constexpr int NUM_BARS = 2 * STAGES + 6;
+  static constexpr int NUM_BARS = 2 * STAGES + 6 + 8;    // + one per epilogue warp for its input tile
   // the tile's bias slice, two tiles deep: fp32 for tiles of up to 128 columns, bf16 for 256
   // (an fp32 bias with the widest tile is read from global memory instead)
   static constexpr int SBIAS_OFFSET = (BAR_OFFSET + NUM_BARS * 8 + 16 + 127) / 128 * 128;
@@ -173,6 +177,7 @@ __device__ __forceinline__ void tile_coords(const GemmDev& g, int t, int& b, int
 template <int BN, int STAGES>
 __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUtensorMap& tmB,
                                              const CUtensorMap* tmC, const CUtensorMap* tmAux,
+                                             const CUtensorMap* tmIn,
                                              const GemmDev& g, int cta, int nctas,
                                              uint8_t* smem_raw) {
   using L = GemmSmem<BN, STAGES>;
@@ -187,6 +192,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUten
   // meeting points of the 256 epilogue threads, alternating by tile parity (bounded waits,
   // unlike a named barrier)
   auto epi_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 4 + a); };
+  auto in_bar = [&](int w) { return bar_base + 8u * (2 * STAGES + 6 + w); };   // epilogue warp w's input tile has landed
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + L::BAR_OFFSET + L::NUM_BARS * 8);
   volatile int* dead = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
@@ -204,6 +210,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& tmA, const CUten
       mbar_init(tempty_bar(a), 8);     // one arrival per epilogue warp
       mbar_init(epi_bar(a), 8);
     }
+    for (int w = 0; w < 8; ++w) mbar_init(in_bar(w), 1);
     *dead = 0;
     mbar_fence_init();
   }

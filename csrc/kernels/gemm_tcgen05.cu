@@ -22,9 +22,9 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux,
-                    const GemmDev g) {
+                    const __grid_constant__ CUtensorMap tmIn, const GemmDev g) {
   extern __shared__ uint8_t smem_raw[];
-  gemm_tc_body<BN, STAGES>(tmA, tmB, &tmC, &tmAux, g, (int)blockIdx.x, (int)gridDim.x, smem_raw);
+  gemm_tc_body<BN, STAGES>(tmA, tmB, &tmC, &tmAux, &tmIn, g, (int)blockIdx.x, (int)gridDim.x, smem_raw);
 }
 
 // CUDA-core fallback for operands that TMA cannot address (leading dimension not a
@@ -103,10 +103,13 @@ int make_gemm_tmaps(const cgk_gemm_args& a, int BN, CUtensorMap* tmA, CUtensorMa
 // Tensor maps of the bf16 output and of the pre-activation output for the epilogue's bulk stores
 // (box: 32 columns x 32 rows, 64-byte swizzle).  *ok = 0 when the layout rules them out; the
 // epilogue then stores from registers.
-int make_gemm_out_tmaps(const cgk_gemm_args& a, CUtensorMap* tmC, CUtensorMap* tmAux, int* ok) {
+int make_gemm_out_tmaps(const cgk_gemm_args& a, CUtensorMap* tmC, CUtensorMap* tmAux, CUtensorMap* tmIn, int* ok,
+                        int* in_kind) {
   memset(tmC, 0, sizeof(*tmC));
   memset(tmAux, 0, sizeof(*tmAux));
+  memset(tmIn, 0, sizeof(*tmIn));
   *ok = 0;
+  *in_kind = 0;
   if (a.out_fp32 || a.accumulate || a.rope_cos || a.force_simt) return 0;
   if ((a.ldc % 8) != 0 || (((uintptr_t)a.out) & 15) != 0 || (a.batch > 1 && (a.strideC % 8) != 0)) return 0;
   if (a.aux_out && ((a.ldaux % 8) != 0 || (((uintptr_t)a.aux_out) & 15) != 0 || a.batch > 1)) return 0;
@@ -123,6 +126,20 @@ int make_gemm_out_tmaps(const cgk_gemm_args& a, CUtensorMap* tmC, CUtensorMap* t
     if (rc) return rc;
   }
   *ok = 1;
+  // one epilogue input by bulk loads: the activation-derivative operand, else the residual
+  if (!a.aux_out && a.batch == 1) {
+    const void* src = nullptr;
+    long long ld = 0;
+    int kind = 0;
+    if (a.aux_in && (a.ldauxin % 8) == 0 && (((uintptr_t)a.aux_in) & 15) == 0) { src = a.aux_in; ld = a.ldauxin; kind = 1; }
+    else if (a.residual && (a.ldr % 8) == 0 && (((uintptr_t)a.residual) & 15) == 0) { src = a.residual; ld = a.ldr; kind = 2; }
+    if (kind) {
+      uint64_t strides[2] = {(uint64_t)ld * 2, (uint64_t)((long long)a.M * ld) * 2};
+      int rc = encode_tmap(tmIn, src, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, Swz::B64);
+      if (rc) return rc;
+      *in_kind = kind;
+    }
+  }
   return 0;
 }
 
@@ -182,18 +199,19 @@ static int launch_tc(const cgk_gemm_args& a, const GemmDev& g0, int sms, cudaStr
   GemmDev g = g0;
   g.tiles_m = (a.M + BM - 1) / BM;
   g.tiles_n = (a.N + BN - 1) / BN;
-  CUtensorMap tmA, tmB, tmC, tmAux;
+  CUtensorMap tmA, tmB, tmC, tmAux, tmIn;
   int rc = make_gemm_tmaps(a, BN, &tmA, &tmB);
   if (rc) return rc;
-  int out_ok = 0;
-  if ((rc = make_gemm_out_tmaps(a, &tmC, &tmAux, &out_ok))) return rc;
+  int out_ok = 0, in_kind = 0;
+  if ((rc = make_gemm_out_tmaps(a, &tmC, &tmAux, &tmIn, &out_ok, &in_kind))) return rc;
   g.tma_store = (out_ok && g.split_k == 1) ? 1 : 0;
+  g.tma_in = g.tma_store ? in_kind : 0;
   CGK_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_tc_kernel<BN, STAGES>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
   int total = g.batch * g.tiles_m * g.tiles_n * g.split_k;
   int cap = a.max_ctas > 0 ? a.max_ctas : sms;
   int grid = total < cap ? total : cap;
-  gemm_bf16_tc_kernel<BN, STAGES><<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, tmAux, g);
+  gemm_bf16_tc_kernel<BN, STAGES><<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, tmAux, tmIn, g);
   CGK_LAUNCH_CHECK();
   return 0;
 }

@@ -581,16 +581,6 @@ __device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1) 
       : "+f"(d0), "+f"(d1)
       : "f"(a0), "f"(a1));
 }
-// (d0, d1) = (a0, a1) + (b0, b1)
-__device__ __forceinline__ void fadd2v(float& d0, float& d1, float a0, float a1, float b0, float b1) {
-  asm("{\n\t.reg .b64 a, b, d;\n\t"
-      "mov.b64 a, {%2, %3};\n\t"
-      "mov.b64 b, {%4, %5};\n\t"
-      "add.rn.f32x2 d, a, b;\n\t"
-      "mov.b64 {%0, %1}, d;\n\t}"
-      : "=f"(d0), "=f"(d1)
-      : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
-}
 // (d0, d1) = (a0, a1) * (b0, b1)
 __device__ __forceinline__ void fmul2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
   asm("{\n\t.reg .b64 a, b, d;\n\t"
@@ -600,25 +590,6 @@ __device__ __forceinline__ void fmul2(float& d0, float& d1, float a0, float a1, 
       "mov.b64 {%0, %1}, d;\n\t}"
       : "=f"(d0), "=f"(d1)
       : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
-}
-// 2^x for two values on the FMA pipe instead of the special-function unit (16 results per clock
-// and SM, the scarcest resource of a softmax row loop): x = n + f with n the nearest integer (taken
-// from the low mantissa bits after adding 1.5 * 2^23) and f in [-0.5, 0.5], 2^f by a cubic with
-// 1e-4 relative error (below bf16 rounding), n added to the exponent field.  x is clamped at -126.
-__device__ __forceinline__ void exp2_poly2(float& e0, float& e1, float x0, float x1) {
-  constexpr float MAGIC = 12582912.0f;
-  constexpr float C1 = 0.6932829022407532f, C2 = 0.24221095442771912f, C3 = 0.05500893294811249f;
-  x0 = fmaxf(x0, -126.0f);
-  x1 = fmaxf(x1, -126.0f);
-  float t0, t1, n0, n1, f0, f1, p0, p1;
-  fadd2v(t0, t1, x0, x1, MAGIC, MAGIC);
-  fadd2v(n0, n1, t0, t1, -MAGIC, -MAGIC);
-  ffma2(f0, f1, n0, n1, -1.0f, -1.0f, x0, x1);
-  ffma2(p0, p1, f0, f1, C3, C3, C2, C2);
-  ffma2(p0, p1, p0, p1, f0, f1, C1, C1);
-  ffma2(p0, p1, p0, p1, f0, f1, 1.0f, 1.0f);
-  e0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
-  e1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 // Counter-based random bits: a hash of (seed, element index).  The dropout kernels draw their
 // keep / drop decision from it, forward and backward alike, so no mask is ever stored.

@@ -28,7 +28,8 @@ def _worker(rank, world, port, q):
         manual_seed(0)
         # vocabulary 384: slices of 256 per rank, the second one half padding
         cfg = LlamaConfig(vocab_size=384, n_layer=2, d_model=256, n_head=4, n_kv_head=2, d_ff=512, max_seq_len=64)
-        dcfg = LlamaConfig(vocab_size=384, n_layer=1, d_model=256, n_head=4, n_kv_head=2, d_ff=256, max_seq_len=64)
+        # the draft's 192 hidden units are three weight groups: the ranks hold two and one of them
+        dcfg = LlamaConfig(vocab_size=384, n_layer=1, d_model=256, n_head=4, n_kv_head=2, d_ff=192, max_seq_len=64)
         target, draft = Llama(cfg), Llama(dcfg)
         group = dist.new_group(list(range(world)))
         # weight groups of 64 = one head: every slice is cut on group boundaries, so the split engines hold
