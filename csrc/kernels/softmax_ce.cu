@@ -18,6 +18,7 @@
 #include "../../include/cogito_kernels.h"
 #include "host_common.h"
 #include "sm100.cuh"
+#include <cuda_fp16.h>
 
 namespace cgk {
 
@@ -140,6 +141,147 @@ softmax_ce_fused_kernel(const __nv_bfloat16* __restrict__ logits, const long lon
     if (dlogits) row_ce_grad(row, dlogits + (long long)r * ld, V, lse, ignored ? -1 : (int)tgt,
                              ignored ? 0.0f : scale);
   }
+}
+
+// The fused kernel for rows that fit shared memory twice (V * 2 bytes <= ~110 KB: vocabularies up to
+// ~56 000): one persistent CTA per SM, rows arrive by bulk copy one row ahead of the arithmetic, and
+// every pass after the first reads shared memory, so each logit crosses HBM once in and once out.
+// Pass A: row maximum.  Pass B: e = exp(x - max), summed in fp32 and written back over the row as
+// fp16 (values in (0, 1]: 11 bits of mantissa, more than the bf16 gradient keeps), so that the
+// exponential is taken once per element - at 16 per clock and SM a second one would cost as much
+// as the memory traffic.  Pass C: d(logit) = (e / sum - [c == target]) * scale, 16 bytes per store.
+constexpr int CE_SMEM_THREADS = 512;
+__global__ void __launch_bounds__(CE_SMEM_THREADS, 1)
+softmax_ce_smem_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
+                       float* __restrict__ loss_rows, __nv_bfloat16* dlogits, int R, int V, long long ld,
+                       float scale_f, const float* __restrict__ scale_ptr, long long ignore_index,
+                       int row_stride_bytes, int* status) {
+  extern __shared__ __align__(128) uint8_t ce_raw[];
+  __shared__ float red[CE_SMEM_THREADS / 32];
+  __shared__ float bcast;
+  const uint32_t bar0 = smem_u32(ce_raw) + 2u * (uint32_t)row_stride_bytes;
+  volatile int* dead = reinterpret_cast<volatile int*>(ce_raw + 2 * (size_t)row_stride_bytes + 16);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t row_bytes = (uint32_t)V * 2u;
+  if (threadIdx.x == 0) {
+    mbar_init(bar0, 1);
+    mbar_init(bar0 + 8, 1);
+    *dead = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  const float scale = scale_f * (scale_ptr ? *scale_ptr : 1.0f);
+  auto post = [&](long long r, int s) {     // thread 0 only
+    mbar_expect_tx(bar0 + 8u * s, row_bytes);
+    bulk_load_1d(smem_u32(ce_raw) + (uint32_t)s * (uint32_t)row_stride_bytes, logits + r * ld, row_bytes, bar0 + 8u * s);
+  };
+  const long long first = blockIdx.x, stride = gridDim.x;
+  if (threadIdx.x == 0) {
+    if (first < R) post(first, 0);
+    if (first + stride < R) post(first + stride, 1);
+  }
+  auto block_max = [&](float v) -> float {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float a = red[0];
+      for (int w = 1; w < CE_SMEM_THREADS / 32; ++w) a = fmaxf(a, red[w]);
+      bcast = a;
+    }
+    __syncthreads();
+    return bcast;
+  };
+  auto block_sum = [&](float v) -> float {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();                        // everyone has read the previous broadcast
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float a = 0.0f;
+      for (int w = 0; w < CE_SMEM_THREADS / 32; ++w) a += red[w];
+      bcast = a;
+    }
+    __syncthreads();
+    return bcast;
+  };
+  const int nvec = V >> 3;
+  const float LOG2E = 1.4426950408889634f;
+  uint32_t k = 0;
+  for (long long r = first; r < R; r += stride, ++k) {
+    const int s = (int)(k & 1u);
+    uint4* buf = reinterpret_cast<uint4*>(ce_raw + (size_t)s * row_stride_bytes);
+    const long long tgt = targets[r];
+    if (tgt != ignore_index) (void)CGK_IDX(tgt, V);        // debug build: a label outside the vocabulary is reported, not just skipped
+    const bool ignored = (tgt == ignore_index) || tgt < 0 || tgt >= V;
+    if (!mbar_wait(bar0 + 8u * s, (k >> 1) & 1u, dead, status, 3200)) break;
+    const float x_t = ignored ? 0.0f : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(buf)[tgt]);
+    // pass A: maximum
+    float mx = -INFINITY;
+    for (int c = threadIdx.x; c < nvec; c += CE_SMEM_THREADS) {
+      const uint4 u = buf[c];
+      float2 f;
+      f = unpack_bf16x2(u.x); mx = fmaxf(mx, fmaxf(f.x, f.y));
+      f = unpack_bf16x2(u.y); mx = fmaxf(mx, fmaxf(f.x, f.y));
+      f = unpack_bf16x2(u.z); mx = fmaxf(mx, fmaxf(f.x, f.y));
+      f = unpack_bf16x2(u.w); mx = fmaxf(mx, fmaxf(f.x, f.y));
+    }
+    mx = block_max(mx);                      // (its barriers also order x_t's read before pass B's writes)
+    const float neg = (mx == -INFINITY) ? 0.0f : -mx * LOG2E;
+    // pass B: exponentials, once per element, kept as fp16 in place
+    float sum = 0.0f;
+    for (int c = threadIdx.x; c < nvec; c += CE_SMEM_THREADS) {
+      const uint4 u = buf[c];
+      float e[8];
+      float2 f;
+      f = unpack_bf16x2(u.x); e[0] = fast_exp2(fmaf(f.x, LOG2E, neg)); e[1] = fast_exp2(fmaf(f.y, LOG2E, neg));
+      f = unpack_bf16x2(u.y); e[2] = fast_exp2(fmaf(f.x, LOG2E, neg)); e[3] = fast_exp2(fmaf(f.y, LOG2E, neg));
+      f = unpack_bf16x2(u.z); e[4] = fast_exp2(fmaf(f.x, LOG2E, neg)); e[5] = fast_exp2(fmaf(f.y, LOG2E, neg));
+      f = unpack_bf16x2(u.w); e[6] = fast_exp2(fmaf(f.x, LOG2E, neg)); e[7] = fast_exp2(fmaf(f.y, LOG2E, neg));
+      sum += ((e[0] + e[1]) + (e[2] + e[3])) + ((e[4] + e[5]) + (e[6] + e[7]));
+      uint4 o;
+      __half2 h;
+      h = __floats2half2_rn(e[0], e[1]); o.x = *reinterpret_cast<uint32_t*>(&h);
+      h = __floats2half2_rn(e[2], e[3]); o.y = *reinterpret_cast<uint32_t*>(&h);
+      h = __floats2half2_rn(e[4], e[5]); o.z = *reinterpret_cast<uint32_t*>(&h);
+      h = __floats2half2_rn(e[6], e[7]); o.w = *reinterpret_cast<uint32_t*>(&h);
+      buf[c] = o;
+    }
+    sum = block_sum(sum);
+    const float lse = mx + __logf(sum);
+    if (threadIdx.x == 0 && loss_rows) loss_rows[r] = ignored ? 0.0f : (lse - x_t);
+    // pass C: gradient
+    if (dlogits) {
+      const float inv = ignored ? 0.0f : scale / sum;
+      const float hot = ignored ? 0.0f : scale;
+      uint4* q = reinterpret_cast<uint4*>(dlogits + r * ld);
+      const int tv = ignored ? -1 : (int)(tgt >> 3), tj = (int)(tgt & 7);
+      for (int c = threadIdx.x; c < nvec; c += CE_SMEM_THREADS) {
+        const uint4 u = buf[c];
+        float g[8];
+        float2 f;
+        f = __half22float2(*reinterpret_cast<const __half2*>(&u.x)); g[0] = f.x * inv; g[1] = f.y * inv;
+        f = __half22float2(*reinterpret_cast<const __half2*>(&u.y)); g[2] = f.x * inv; g[3] = f.y * inv;
+        f = __half22float2(*reinterpret_cast<const __half2*>(&u.z)); g[4] = f.x * inv; g[5] = f.y * inv;
+        f = __half22float2(*reinterpret_cast<const __half2*>(&u.w)); g[6] = f.x * inv; g[7] = f.y * inv;
+        if (c == tv) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (j == tj) g[j] -= hot;
+        }
+        uint4 o;
+        o.x = pack_bf16x2(g[0], g[1]); o.y = pack_bf16x2(g[2], g[3]);
+        o.z = pack_bf16x2(g[4], g[5]); o.w = pack_bf16x2(g[6], g[7]);
+        q[c] = o;
+      }
+    }
+    // every thread is done with this buffer: it can take the row two steps ahead
+    __syncthreads();
+    if (threadIdx.x == 0 && r + 2 * stride < R) post(r + 2 * stride, s);
+  }
+  if (*dead) __nanosleep(100000);
 }
 
 // Per-row partial statistics of a vocabulary shard [vocab_start, vocab_start+V).
@@ -305,6 +447,23 @@ CGK_API int cgk_softmax_ce_fused(const void* logits, const long long* targets, f
   CGK_REQUIRE(logits && targets, "cgk_softmax_ce_fused: null pointer");
   CGK_REQUIRE(R >= 0 && V > 0 && ld >= V, "cgk_softmax_ce_fused: bad shape");
   if (R == 0) return 0;
+  // rows that fit shared memory twice take the single-read kernel
+  const long long row_stride = ((long long)V * 2 + 127) / 128 * 128;
+  const bool aligned = (V % 8) == 0 && (ld % 8) == 0 && (((uintptr_t)logits) & 15) == 0 &&
+                       (!dlogits || (((uintptr_t)dlogits) & 15) == 0);
+  if (aligned && 2 * row_stride + 64 <= 220 * 1024 && V >= 4096) {
+    int dev = 0;
+    CGK_CUDA_CHECK(cudaGetDevice(&dev));
+    const int smem = (int)(2 * row_stride + 64);
+    CGK_CUDA_CHECK(cudaFuncSetAttribute(softmax_ce_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    int grid = sm_count(dev);
+    if (grid > R) grid = R;
+    softmax_ce_smem_kernel<<<grid, CE_SMEM_THREADS, smem, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)logits, targets, loss_rows, (__nv_bfloat16*)dlogits, R, V, ld, scale_f, scale_ptr,
+        ignore_index, (int)row_stride, device_status(dev));
+    CGK_LAUNCH_CHECK();
+    return 0;
+  }
   softmax_ce_fused_kernel<<<ce_grid(R), CE_THREADS, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)logits, targets, loss_rows, (__nv_bfloat16*)dlogits, R, V, ld, scale_f,
       scale_ptr, ignore_index);
