@@ -24,7 +24,10 @@ GEMM and GEMM -> reduce-scatter with NCCL collectives, the reference's unfused d
 The default arm measures that baseline too, in the same process right after its own
 timed regions (same N, same batch, same warm-up; `--baseline-steps` timed steps), and
 reports `vs_baseline` = value / baseline value, with the baseline's own numbers under
-`baseline`.
+`baseline`.  On one GPU the INT4 speculative-decoding configuration (Llama-7B shape, batch 16,
+512-token prompts, 256 new tokens, gamma 4) then runs once in a child process and is reported under
+`int4_spec_decode` (`--serving off` skips it; with several GPUs run `benchmarks/spec_decode.py` under
+the launcher).
 """
 from __future__ import annotations
 
@@ -57,6 +60,10 @@ def parse():
     ap.add_argument("--baseline-steps", type=int, default=-1,
                     help="timed steps of the PyTorch-library baseline measured in the same run (-1 = min(steps, 5), "
                          "0 = skip it and leave vs_baseline null)")
+    ap.add_argument("--serving", default="auto", choices=["auto", "on", "off"],
+                    help="on one GPU, also run the INT4 speculative-decoding configuration (Llama-7B shape, batch 16, "
+                         "512-token prompts, 256 new tokens, gamma 4) as a child process after the training "
+                         "measurements and report it under \"int4_spec_decode\" (auto = on)")
     ap.add_argument("--timeline", default="", help="after the timed regions, trace two more steps and write the device "
                     "time per kernel name (rank 0) to this JSON file; not part of any reported number")
     args = ap.parse_args()
@@ -290,6 +297,34 @@ def main():
         except Exception as e:                          # the headline number above stands on its own
             alt = {"parallelism": f"dp{world}", "error": repr(e)[:300]}
 
+    # The serving half of the reference's headline: INT4 speculative decoding at the named size.  It runs
+    # as a child process with a time limit, after the training jobs have released their memory, so that
+    # nothing that happens there can touch the numbers above; one GPU only (a child per rank would need
+    # its own rendezvous - under the launcher use benchmarks/spec_decode.py directly).
+    serving = None
+    if args.impl == "cogito" and (args.serving == "on" or (args.serving == "auto" and world == 1)) and world == 1:
+        try:
+            import gc
+            job = None
+            loss_box[0] = None
+            gc.collect()
+            torch.cuda.empty_cache()
+            here = os.path.dirname(os.path.abspath(__file__))
+            env = dict(os.environ, CUDA_VISIBLE_DEVICES=os.environ.get("CUDA_VISIBLE_DEVICES", str(local)))
+            for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+                env.pop(k, None)
+            r = subprocess.run([sys.executable, os.path.join(here, "benchmarks", "spec_decode.py")], env=env, cwd=here,
+                               capture_output=True, text=True, timeout=900)
+            line = next((ln for ln in reversed(r.stdout.splitlines()) if ln.startswith("{")), None)
+            if r.returncode == 0 and line:
+                rec = json.loads(line)
+                serving = {k: rec.get(k) for k in ("value", "unit", "ms_per_step", "steps", "acceptance_rate", "prefill_ms",
+                                                   "cuda_graph", "launches_per_step", "config")}
+            else:
+                serving = {"error": f"exit code {r.returncode}: " + (r.stderr or r.stdout)[-300:]}
+        except Exception as e:
+            serving = {"error": repr(e)[:300]}
+
     if rank == 0:
         ms_per_step = ms / args.steps
         value = tokens_per_step / (ms_per_step * 1e-3)
@@ -316,6 +351,8 @@ def main():
             out["baseline"] = baseline
         if alt is not None:
             out["alt"] = alt
+        if serving is not None:
+            out["int4_spec_decode"] = serving
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

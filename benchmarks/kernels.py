@@ -81,7 +81,13 @@ def case_gemm(t, small):
         a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
         b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-        emit("gemm", t(lambda: gemm(a, b, out=out)), flops=2.0 * M * N * K, M=M, N=N, K=K)
+        ms = t(lambda: gemm(a, b, out=out))
+        # the library GEMM on the same operands, timed the same way (not under --small: the profiler's
+        # kernel filter should see this library's kernel only)
+        lib = None if small else t(lambda: torch.matmul(a, b.t(), out=out))
+        extra = {} if lib is None else {"cublas_ms": round(lib, 5), "cublas_tflops": round(2.0 * M * N * K / lib / 1e9, 1),
+                                        "vs_cublas": round(lib / ms, 3)}
+        emit("gemm", ms, flops=2.0 * M * N * K, M=M, N=N, K=K, **extra)
 
 
 def _qkv(B, T, H, Hk, D):

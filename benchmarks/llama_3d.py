@@ -9,9 +9,9 @@ uniform random token ids).  Each data-parallel replica runs ``microbatches`` mic
 ``micro-batch`` sequences through the 1F1B pipeline schedule, with dynamic loss scaling (2^16) and
 gradient clipping on; the optimizer is the fused data-parallel Adam.  One JSON line from rank 0:
 tokens/s over the whole job (device time of ``steps`` steps, max over ranks), ms per step, peak
-memory per GPU, bytes sent between pipeline stages.  ``--impl torch`` is not offered: the
-comparison point of this configuration is the same schedule on library kernels, which
-``COGITO_TP_NVLS=0`` plus the torch arm of ``bench.py`` cover at the kernel level.
+memory per GPU, bytes sent between pipeline stages.  Weights are drawn on the device (the library's
+default initialiser draws them on the host for reproducibility across device counts, which takes
+minutes for 1.7 B parameters per rank and is not what this script measures).
 """
 from __future__ import annotations
 
@@ -55,6 +55,12 @@ def main():
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev)
     rng.manual_seed(0)
+
+    def device_normal_(t, std, g):            # same signature as utils.rng.normal_; values are irrelevant here
+        with torch.no_grad():
+            return t.normal_(0.0, std)
+    rng.normal_ = device_normal_
+    torch.cuda.manual_seed(1234 + rank)
     cfg = LlamaConfig(vocab_size=32000, d_model=4096, n_head=32, n_kv_head=32, d_ff=11008, n_layer=args.layers,
                       max_seq_len=args.seq)
     ctx = init_parallel(args.dp, args.tp, args.pp)

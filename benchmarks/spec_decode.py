@@ -25,6 +25,76 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
 
+def run(layers=32, draft_layers=2, batch=16, prompt=512, new=256, gamma=4, kv_heads=8, self_draft=False,
+        tp_graph=False, no_graph=False, group=None, dev=None):
+    """Builds the engines, runs one prefill and the decode loop, returns the result record (the same
+    on every rank).  ``group``: the tensor-parallel process group, None on one GPU."""
+    from cogito_b200.models.llama import Llama, LlamaConfig
+    from cogito_b200.ops import _lib
+    from cogito_b200.serve.engine import LlamaInt4Engine, SpeculativeDecoder
+    from cogito_b200.utils import rng
+
+    world = dist.get_world_size(group) if group is not None else 1
+    rng.manual_seed(0)
+    shape = dict(vocab_size=32000, d_model=4096, n_head=32, n_kv_head=kv_heads, d_ff=11008, max_seq_len=prompt + new + 64)
+    tcfg = LlamaConfig(n_layer=layers, **shape)
+    dcfg = LlamaConfig(n_layer=draft_layers, **shape)
+    cap = prompt + new + 32
+    # build and quantise one model at a time: the bf16 copy is dropped once its INT4 engine exists
+    model = Llama(tcfg, device=dev, dtype=torch.bfloat16)
+    target = LlamaInt4Engine(model, batch, cap, tp_group=group)
+    if self_draft:
+        model.blocks = model.blocks[:draft_layers]
+        draft = LlamaInt4Engine(model, batch, cap, tp_group=group)
+    else:
+        del model
+        draft = LlamaInt4Engine(Llama(dcfg, device=dev, dtype=torch.bfloat16), batch, cap, tp_group=group)
+    model = None
+    torch.cuda.empty_cache()
+    dec = SpeculativeDecoder(draft, target, gamma=gamma, temperature=0.8, top_k=50, top_p=0.9, seed=0,
+                             use_graph=False if no_graph else (True if tp_graph else None))
+    prompts = torch.randint(0, 32000, (batch, prompt), generator=torch.Generator().manual_seed(1)).to(dev)
+
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    dec.generate(prompts[:, :32], 8)                        # warm-up: tile reordering, workspaces
+    dec.stats.__init__()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier(group)
+    _lib.reset_launches()
+    ev[0].record()
+    last = dec.prefill(prompts)
+    ev[1].record()
+    produced, steps, generated, accepted = 0, 0, 0, 0
+    while produced < new:
+        n_acc, out, nxt = dec.advance(last)
+        n_host = n_acc.tolist()                              # the per-step host read a serving loop needs to emit tokens
+        last = nxt.clone()
+        produced += min(n_host) + 1
+        generated += sum(n + 1 for n in n_host)
+        accepted += sum(n_host)
+        steps += 1
+    ev[2].record()
+    torch.cuda.synchronize()
+    t = torch.tensor([ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    prefill_ms, decode_ms = t.tolist()
+    rec = {
+        "metric": "int4_speculative_decode_tokens_per_s", "value": round(generated / decode_ms * 1e3, 1), "unit": "tokens/s",
+        "n_gpus": world, "decode_ms": round(decode_ms, 2), "prefill_ms": round(prefill_ms, 2), "steps": steps,
+        "ms_per_step": round(decode_ms / steps, 3), "acceptance_rate": round(accepted / (steps * batch * gamma), 4),
+        "generated": generated, "cuda_graph": dec._graph is not None,
+        "launches_per_step": getattr(dec, "graph_launches", None) if dec._graph is not None else round(_lib.launches() / max(1, steps), 1),
+        "weight_bytes_per_gpu": target.weight_bytes() + draft.weight_bytes(),
+        "config": {"layers": layers, "draft_layers": draft_layers, "batch": batch, "prompt": prompt, "new": new,
+                   "gamma": gamma, "kv_heads": kv_heads, "tp": world, "self_draft": self_draft, "data": "synthetic"}}
+    dec.close()                                           # drop the captured collectives before the process group goes
+    del dec, target, draft
+    torch.cuda.empty_cache()
+    return rec
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--layers", type=int, default=32)
@@ -39,11 +109,6 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
 
-    from cogito_b200.models.llama import Llama, LlamaConfig
-    from cogito_b200.ops import _lib
-    from cogito_b200.serve.engine import LlamaInt4Engine, SpeculativeDecoder
-    from cogito_b200.utils import rng
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
@@ -52,62 +117,10 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
-    rng.manual_seed(0)
-    shape = dict(vocab_size=32000, d_model=4096, n_head=32, n_kv_head=args.kv_heads, d_ff=11008, max_seq_len=args.prompt + args.new + 64)
-    tcfg = LlamaConfig(n_layer=args.layers, **shape)
-    dcfg = LlamaConfig(n_layer=args.draft_layers, **shape)
-    cap = args.prompt + args.new + 32
-    # build and quantise one model at a time: the bf16 copy is dropped once its INT4 engine exists
-    model = Llama(tcfg, device=dev, dtype=torch.bfloat16)
-    target = LlamaInt4Engine(model, args.batch, cap, tp_group=group)
-    if args.self_draft:
-        model.blocks = model.blocks[:args.draft_layers]
-        draft = LlamaInt4Engine(model, args.batch, cap, tp_group=group)
-    else:
-        del model
-        draft = LlamaInt4Engine(Llama(dcfg, device=dev, dtype=torch.bfloat16), args.batch, cap, tp_group=group)
-    model = None
-    torch.cuda.empty_cache()
-    dec = SpeculativeDecoder(draft, target, gamma=args.gamma, temperature=0.8, top_k=50, top_p=0.9, seed=0,
-                             use_graph=False if args.no_graph else (True if args.tp_graph else None))
-    prompts = torch.randint(0, 32000, (args.batch, args.prompt), generator=torch.Generator().manual_seed(1)).to(dev)
-
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    dec.generate(prompts[:, :32], 8)                        # warm-up: tile reordering, workspaces
-    dec.stats.__init__()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    _lib.reset_launches()
-    ev[0].record()
-    last = dec.prefill(prompts)
-    ev[1].record()
-    produced, steps, generated, accepted = 0, 0, 0, 0
-    while produced < args.new:
-        n_acc, out, nxt = dec.advance(last)
-        n_host = n_acc.tolist()                              # the per-step host read a serving loop needs to emit tokens
-        last = nxt.clone()
-        produced += min(n_host) + 1
-        generated += sum(n + 1 for n in n_host)
-        accepted += sum(n_host)
-        steps += 1
-    ev[2].record()
-    torch.cuda.synchronize()
-    t = torch.tensor([ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    prefill_ms, decode_ms = t.tolist()
+    rec = run(args.layers, args.draft_layers, args.batch, args.prompt, args.new, args.gamma, args.kv_heads, args.self_draft,
+              args.tp_graph, args.no_graph, group, dev)
     if rank == 0:
-        print(json.dumps({
-            "metric": "int4_speculative_decode_tokens_per_s", "value": round(generated / decode_ms * 1e3, 1), "unit": "tokens/s",
-            "n_gpus": world, "decode_ms": round(decode_ms, 2), "prefill_ms": round(prefill_ms, 2), "steps": steps,
-            "ms_per_step": round(decode_ms / steps, 3), "acceptance_rate": round(accepted / (steps * args.batch * args.gamma), 4),
-            "generated": generated, "cuda_graph": dec._graph is not None,
-            "launches_per_step": getattr(dec, "graph_launches", None) if dec._graph is not None else round(_lib.launches() / max(1, steps), 1),
-            "weight_bytes_per_gpu": target.weight_bytes() + draft.weight_bytes(),
-            "config": {"layers": args.layers, "draft_layers": args.draft_layers, "batch": args.batch, "prompt": args.prompt, "new": args.new,
-                       "gamma": args.gamma, "kv_heads": args.kv_heads, "tp": world, "self_draft": args.self_draft, "data": "synthetic"}}), flush=True)
-    dec.close()                                           # drop the captured collectives before the process group goes
+        print(json.dumps(rec), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -409,8 +409,10 @@ CGK_API int cgk_gemm_rs(const cgk_gemm_args* pg, const cgk_rs_args* px, void* st
   const int rows = ga.M / x.ranks;
   const int sms = sm_count(dev);
   const int ctas = ga.max_ctas > 0 && ga.max_ctas < sms ? ga.max_ctas : sms;
-  // measured on 8 GPUs (131072 x 768 rows, 148 CTAs): 8 reduce CTAs 0.373 ms, 16: 0.357, 32: 0.336, 64: 0.344
-  int n_reduce = x.n_reduce_ctas > 0 ? x.n_reduce_ctas : (x.ranks >= 4 ? 32 : (x.ranks > 1 ? 16 : 4));
+  // measured on 8 GPUs (131072 x 768 rows, all 148 CTAs): 8 reduce CTAs 0.373 ms, 16: 0.357, 32: 0.336,
+  // 64: 0.344.  A kernel capped well below the machine (two of them run side by side in the two-stream
+  // schedule, 56 CTAs each) keeps 16: its GEMM tiles would otherwise become the longer part.
+  int n_reduce = x.n_reduce_ctas > 0 ? x.n_reduce_ctas : (x.ranks >= 4 && ctas >= 100 ? 32 : (x.ranks > 1 ? 16 : 4));
   if (n_reduce > ctas / 2) n_reduce = ctas / 2;
   if (n_reduce < 1) n_reduce = 1;
   const int gemm_ctas = ctas - n_reduce;
