@@ -1,5 +1,6 @@
 """Host models of the cross-GPU handshakes of the fused tensor-parallel kernels
-(csrc/comm/fused_tp.cu), checked without a GPU.
+(csrc/comm/fused_tp.cu) and of the data-parallel optimizer step (csrc/comm/dp_adam.cu), checked
+without a GPU.
 
 Every rank runs its calls in stream order; inside a call the transfer role (copy / reduce CTAs)
 and the GEMM role run side by side.  Each role is a sequence of atomic steps on words and
@@ -17,6 +18,12 @@ data and for states in which nobody can move.
   gathered buffer and sets the chunk flag there; the GEMM role waits for the flag of each source.
   Without the announcement round a fast rank's next call lands in a buffer that a slow rank
   still reads.
+* data-parallel step: per bucket "my gradients are complete" to every peer, wait for the peers',
+  sum the owned part over all ranks' gradient buffers; then Adam on the owned parts, the new
+  weights stored into every rank's parameters, "my stores are done" to every peer and a wait for
+  the peers' before the kernel ends.  The next step's forward pass then reads only new weights and
+  its backward pass never overwrites a gradient a peer has yet to read; without the closing wait
+  the explorer finds both.
 """
 import pytest
 
@@ -175,3 +182,74 @@ def test_multicast_gather_never_lands_in_a_buffer_still_being_read(P, calls):
 def test_without_the_announcement_round_the_model_finds_the_overwrite():
     problems, _, _ = all_gather_multicast(2, 2, handshake=False)
     assert any(p[0] == "shard of another call" for p in problems)
+
+
+# ------------------------------------------------------------------ data-parallel step
+def data_parallel_step(P, steps, buckets, closing_wait=True):
+    # shared: grad[rank][bucket] = step whose gradients it holds; ready[owner][bucket][from] = step announced;
+    # param[rank][part] = step whose update it holds (part p is written by rank p); done[owner][from] = step
+    zb = tuple((0,) * buckets for _ in range(P))
+    init = (zb, tuple(tuple((0,) * P for _ in range(buckets)) for _ in range(P)), tuple((0,) * P for _ in range(P)),
+            tuple((0,) * P for _ in range(P)))
+
+    def make_roles(r, e):
+        main = [("forward", q) for q in range(P)]                       # reads every part of its own parameter copy
+        for b in reversed(range(buckets)):                               # backward produces the last bucket first
+            main.append(("backward", b))
+        side = []
+        for b in reversed(range(buckets)):
+            side.append(("need_grad", b))                                # the bucket's hook has fired on the main stream
+            side += [("announce", b, q) for q in range(P) if q != r]
+            side += [("wait_ready", b, q) for q in range(P) if q != r]
+            side += [("pull", b, q) for q in range(P)]
+        side += [("store", q) for q in range(P)]
+        side += [("done", q) for q in range(P) if q != r]
+        if closing_wait:
+            side += [("wait_done", q) for q in range(P) if q != r]
+        return [main, side]
+
+    def step(shared, r, e, st):
+        grad, ready, param, done = shared
+        kind = st[0]
+        if kind == "forward":
+            got = param[r][st[1]]
+            return shared, (None if got == e - 1 else ("weights of another step", r, st[1], e, got))
+        if kind == "backward":
+            row = list(grad[r]); row[st[1]] = e
+            return (grad[:r] + (tuple(row),) + grad[r + 1:], ready, param, done), None
+        if kind == "need_grad":
+            return (shared, None) if grad[r][st[1]] == e else (None, None)
+        if kind == "announce":
+            _, b, q = st
+            rb = list(ready[q]); row = list(rb[b]); row[r] = e; rb[b] = tuple(row)
+            return (grad, ready[:q] + (tuple(rb),) + ready[q + 1:], param, done), None
+        if kind == "wait_ready":
+            _, b, q = st
+            return (shared, None) if ready[r][b][q] >= e else (None, None)
+        if kind == "pull":
+            _, b, q = st
+            got = grad[q][b]
+            return shared, (None if got == e else ("gradient of another step", r, q, b, e, got))
+        if kind == "store":
+            q = st[1]
+            row = list(param[q]); row[r] = e
+            return (grad, ready, param[:q] + (tuple(row),) + param[q + 1:], done), None
+        if kind == "done":
+            q = st[1]
+            row = list(done[q]); row[r] = e
+            return (grad, ready, param, done[:q] + (tuple(row),) + done[q + 1:]), None
+        return (shared, None) if done[r][st[1]] >= e else (None, None)           # wait_done
+
+    return _explore(P, steps, make_roles, init, step)
+
+
+@pytest.mark.parametrize("P,steps,buckets", [(2, 3, 2), (3, 2, 1)])
+def test_data_parallel_step_reads_only_its_own_steps_gradients_and_weights(P, steps, buckets):
+    problems, finals, states = data_parallel_step(P, steps, buckets)
+    assert not problems, problems[:3]
+    assert finals >= 1 and states > 50
+
+
+def test_without_the_closing_wait_the_next_step_races_with_slow_peers():
+    problems, _, _ = data_parallel_step(2, 2, 1, closing_wait=False)
+    assert any(p[0] in ("weights of another step", "gradient of another step") for p in problems)
