@@ -2,7 +2,8 @@
 // the gradient checker.  Reference surface: include/cg_tensor.h:165-195 (cg_backward),
 // src/autograd/engine.c (functional ops), src/autograd/graph.c (cg_graph_*),
 // src/autograd/grad_check.c.
-#include <unordered_set>
+#include <algorithm>
+#include <cstdint>
 
 #include "internal.hpp"
 
@@ -19,18 +20,22 @@ void attach_n(cg_tensor* out, cg_tensor* const* parents, int n, BackFn fn) {
   ensure_grad(out);
   // Only the first CG_MAX_PARENTS are visible in the public struct; further ones hang off a
   // pass-through node so that the topological walk still reaches them.
-  std::vector<cg_tensor*> ps;
+  cg_tensor* few[16];
+  std::vector<cg_tensor*> many;
+  if (n > 16) many.resize(n);
+  cg_tensor** ps = n > 16 ? many.data() : few;
+  size_t np = 0;
   for (int pass = 0; pass < 2; ++pass)          // those that want gradients first
-    for (int i = 0; i < n; ++i) if (parents[i] && wants_grad(parents[i]) == (pass == 0)) ps.push_back(parents[i]);
+    for (int i = 0; i < n; ++i) if (parents[i] && wants_grad(parents[i]) == (pass == 0)) ps[np++] = parents[i];
   cg_tensor* node = out;
   size_t at = 0;
-  while (at < ps.size()) {
-    const size_t left = ps.size() - at;
+  while (at < np) {
+    const size_t left = np - at;
     const int direct = left <= CG_MAX_PARENTS ? (int)left : CG_MAX_PARENTS - 1;
     int k = 0;
     for (int i = 0; i < direct; ++i) { node->parents[k++] = ps[at + i]; cg_tensor_retain(ps[at + i]); }
     at += direct;
-    if (at < ps.size()) {                        // the hub owns the remaining references
+    if (at < np) {                               // the hub owns the remaining references
       int one[1] = {1};
       cg_tensor* hub = make(one, 1, false);
       hub->requires_grad = wants_grad(ps[at]);
@@ -169,24 +174,52 @@ CG_EXPORT void cg_backward(cg_tensor* loss) {
   bool seeded = false;
   for (int i = 0; i < loss->size; ++i) seeded = seeded || loss->grad[i] != 0.0f;
   if (!seeded) for (int i = 0; i < loss->size; ++i) loss->grad[i] = 1.0f;
-  // iterative post-order DFS
-  std::vector<cg_tensor*> order;
-  std::unordered_set<cg_tensor*> seen;
-  std::vector<std::pair<cg_tensor*, int>> stack;
-  stack.push_back({loss, 0});
-  seen.insert(loss);
-  while (!stack.empty()) {
-    auto& top = stack.back();
+  // iterative post-order DFS.  The walk's three containers are kept between calls (a training loop
+  // walks the same few nodes every step); a backward function that itself calls cg_backward gets
+  // containers of its own.
+  struct Scratch {
+    std::vector<cg_tensor*> order, table;          // table: open addressing, power-of-two size, nullptr = free
+    std::vector<std::pair<cg_tensor*, int>> stack;
+    size_t used = 0;
+    bool insert(cg_tensor* p) {
+      if (table.empty()) table.assign(64, nullptr);
+      if ((used + 1) * 2 > table.size()) {
+        std::vector<cg_tensor*> old;
+        old.swap(table);
+        table.assign(old.size() * 2, nullptr);
+        used = 0;
+        for (cg_tensor* q : old) if (q) insert(q);
+      }
+      const size_t mask = table.size() - 1;
+      size_t h = ((uintptr_t)p >> 4) * 0x9E3779B97F4A7C15ull >> 20 & mask;
+      while (table[h]) { if (table[h] == p) return false; h = (h + 1) & mask; }
+      table[h] = p; ++used;
+      return true;
+    }
+  };
+  static thread_local Scratch shared;
+  static thread_local int depth = 0;
+  Scratch own;
+  Scratch& w = depth == 0 ? shared : own;
+  ++depth;
+  w.order.clear(); w.stack.clear();
+  if (w.used) { std::fill(w.table.begin(), w.table.end(), nullptr); w.used = 0; }
+  w.stack.push_back({loss, 0});
+  w.insert(loss);
+  while (!w.stack.empty()) {
+    auto& top = w.stack.back();
     if (top.second < top.first->num_parents) {
       cg_tensor* p = top.first->parents[top.second++];
-      if (p && p->requires_grad && seen.insert(p).second) stack.push_back({p, 0});
+      if (p && p->requires_grad && w.insert(p)) w.stack.push_back({p, 0});
     } else {
-      order.push_back(top.first);
-      stack.pop_back();
+      w.order.push_back(top.first);
+      w.stack.pop_back();
     }
   }
-  for (auto it = order.rbegin(); it != order.rend(); ++it)
-    if ((*it)->backward_fn) (*it)->backward_fn(*it);
+  for (size_t i = w.order.size(); i-- > 0;)
+    if (w.order[i]->backward_fn) w.order[i]->backward_fn(w.order[i]);
+  --depth;
+  if (w.table.size() > (1u << 16)) { Scratch().table.swap(w.table); w.used = 0; }     // a huge graph does not pin its table
 }
 
 // ---------------------------------------------------------- graph registry

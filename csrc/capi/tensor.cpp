@@ -209,13 +209,22 @@ CG_EXPORT cg_tensor* cg_tensor_randn_arena(cg_arena* arena, int* shape, int ndim
 }
 CG_EXPORT void cg_tensor_retain(cg_tensor* t) { if (t) ++t->ref_count; }
 CG_EXPORT void cg_tensor_release(cg_tensor* t) {
-  // iterative: a long chain of parents must not recurse once per node
-  std::vector<cg_tensor*> work;
-  if (t) work.push_back(t);
-  while (!work.empty()) {
-    cg_tensor* x = work.back(); work.pop_back();
+  if (!t) return;
+  if (t->ref_count > 1) { --t->ref_count; return; }     // the common case: somebody else still holds it
+  // iterative: a long chain of parents must not recurse once per node.  The first entries of the
+  // work list live on the stack; training loops free a handful of nodes per call.
+  cg_tensor* first[32];
+  int nfirst = 0;
+  std::vector<cg_tensor*> more;
+  first[nfirst++] = t;
+  while (nfirst > 0 || !more.empty()) {
+    cg_tensor* x;
+    if (!more.empty()) { x = more.back(); more.pop_back(); } else x = first[--nfirst];
     if (--x->ref_count > 0) continue;
-    for (int i = 0; i < x->num_parents; ++i) if (x->parents[i]) work.push_back(x->parents[i]);
+    for (int i = 0; i < x->num_parents; ++i) {
+      if (!x->parents[i]) continue;
+      if (nfirst < 32 && more.empty()) first[nfirst++] = x->parents[i]; else more.push_back(x->parents[i]);
+    }
     if (x->backward_ctx) {
       BackCtx* c = (BackCtx*)x->backward_ctx; x->backward_ctx = nullptr;
       delete c;
