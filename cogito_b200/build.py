@@ -32,6 +32,8 @@ NVCC_FLAGS = [
     "-Xptxas", "-v",
 ]
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-unused-function"]
+# the file that holds the host runtime's hot loops: full vectorisation, sqrt without errno
+CXX_FILE_FLAGS = {"host_simd.cpp": ["-O3", "-fno-math-errno"]}
 
 
 def _nvcc() -> str:
@@ -52,8 +54,9 @@ def _compile_one(cmd: list[str], log: Path) -> tuple[int, str]:
 
 
 def _build(sources: list[Path], headers: list[Path], out: Path, compiler: list[str],
-           link: list[str], tag: str, verbose: bool) -> bool:
-    """Compile `sources` to objects (in parallel) and link `out`. Returns True if relinked."""
+           link: list[str], tag: str, verbose: bool, file_flags: dict | None = None) -> bool:
+    """Compile `sources` to objects (in parallel) and link `out`. Returns True if relinked.
+    file_flags: extra flags by source file name (appended, so a later -O wins)."""
     obj_dir = BUILD_DIR / tag
     obj_dir.mkdir(parents=True, exist_ok=True)
     LIB_DIR.mkdir(parents=True, exist_ok=True)
@@ -70,7 +73,7 @@ def _build(sources: list[Path], headers: list[Path], out: Path, compiler: list[s
     if jobs:
         with cf.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             futs = {
-                ex.submit(_compile_one, compiler + ["-c", str(src), "-o", str(obj)],
+                ex.submit(_compile_one, compiler + (file_flags or {}).get(src.name, []) + ["-c", str(src), "-o", str(obj)],
                           obj_dir / (src.stem + ".log")): src
                 for src, obj in jobs
             }
@@ -124,7 +127,8 @@ def build_capi(verbose: bool = False) -> Path:
     _build(srcs, hdrs, out, [cxx] + CXX_FLAGS + ["-I", str(ROOT / "include")],
            # a toolchain that links libstdc++ statically must not export (or be interposed on)
            # its copy inside a process that already holds another libstdc++
-           [cxx, "-shared", "-fPIC", "-Wl,--exclude-libs,ALL", "-Wl,-Bsymbolic", "-lpthread", "-ldl"], "capi", verbose)
+           [cxx, "-shared", "-fPIC", "-Wl,--exclude-libs,ALL", "-Wl,-Bsymbolic", "-lpthread", "-ldl"], "capi", verbose,
+           file_flags=CXX_FILE_FLAGS)
     return out
 
 

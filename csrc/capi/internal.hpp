@@ -44,6 +44,11 @@ void attach_n(cg_tensor* out, cg_tensor* const* parents, int n, BackFn fn);   //
 //   ta = false: A is [M,K];  ta = true: A is [K,M]
 //   tb = false: B is [K,N];  tb = true: B is [N,K]
 void gemm(const float* A, const float* B, float* C, int M, int N, int K, bool ta, bool tb, bool accumulate);
+// host_simd.cpp (built with -O3, AVX2 + FMA copies picked at load time)
+void gemm_rows(const float* A, const float* B, float* C, int M, int N, int K, bool ta);       // C += op(A) B, B [K,N]
+void gemm_dots(const float* A, const float* B, float* C, int M, int N, int K);                // C += A B^T, B [N,K], few rows
+void adam_update(float* w, float* m, float* v, const float* g, int n, float b1, float b2, float lr, float eps,
+                 float bc1, float bc2, float decay);
 
 // ---- random streams
 struct Rng {

@@ -188,16 +188,11 @@ void adam_step(cg_optimizer* o) {
   if (!prepare(o)) return;
   ++o->t;
   const float bc1 = 1.0f - std::pow(a->beta1, (float)o->t), bc2 = 1.0f - std::pow(a->beta2, (float)o->t);
+  const float decay = a->weight_decay > 0 ? 1.0f - o->learning_rate * a->weight_decay : 1.0f;
   for (int i = 0; i < o->num_params; ++i) {
     cg_tensor* p = o->params[i];
-    float* w = weights_of(o, i); float* m = a->m[i]->data; float* v = a->v[i]->data;
-    for (int j = 0; j < p->size; ++j) {
-      const float g = p->grad[j];
-      if (a->weight_decay > 0) w[j] *= 1.0f - o->learning_rate * a->weight_decay;       // decoupled decay
-      m[j] = a->beta1 * m[j] + (1 - a->beta1) * g;
-      v[j] = a->beta2 * v[j] + (1 - a->beta2) * g * g;
-      w[j] -= o->learning_rate * (m[j] / bc1) / (std::sqrt(v[j] / bc2) + a->epsilon);
-    }
+    adam_update(weights_of(o, i), a->m[i]->data, a->v[i]->data, p->grad, p->size, a->beta1, a->beta2, o->learning_rate,
+                a->epsilon, bc1, bc2, decay);
     publish_weights(o, i);
   }
 }

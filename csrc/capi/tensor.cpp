@@ -1,6 +1,7 @@
 // Errors, arena, tensor storage and the eager tensor ops of the C API.
 // Reference surface: include/cg_tensor.h, include/cg_arena.h, src/core/tensor.c,
 // src/core/tensor_ops.c, src/core/arena.c, src/core/error.c.
+#include <algorithm>
 #include <atomic>
 
 #include "internal.hpp"
@@ -54,36 +55,26 @@ void ensure_grad(cg_tensor* t) {
   if (t->arena && t->grad) std::memset(t->grad, 0, sizeof(float) * t->size);
 }
 
+// The host GEMM: C[M,N] (+)= op(A) op(B).  Every case is brought to the form "row of C += a * row of B"
+// with unit stride along the row (B^T is transposed into a scratch buffer first); the loops themselves are
+// in host_simd.cpp.
 void gemm(const float* A, const float* B, float* C, int M, int N, int K, bool ta, bool tb, bool acc) {
   if (!acc) std::memset(C, 0, sizeof(float) * (size_t)M * N);
-  if (!tb) {
-    // C[i,:] += A(i,k) * B[k,:]  — unit-stride inner loop
-    for (int i = 0; i < M; ++i) {
-      float* c = C + (size_t)i * N;
-      for (int k = 0; k < K; ++k) {
-        const float a = ta ? A[(size_t)k * M + i] : A[(size_t)i * K + k];
-        if (a == 0.0f) continue;
-        const float* b = B + (size_t)k * N;
-        for (int j = 0; j < N; ++j) c[j] += a * b[j];
-      }
+  if (M <= 0 || N <= 0 || K <= 0) return;
+  if (!tb) { gemm_rows(A, B, C, M, N, K, ta); return; }
+  if (!ta && M < 4) { gemm_dots(A, B, C, M, N, K); return; }
+  // B is [N, K]: transpose it once (N * K moves against 2 * M * N * K flops)
+  static thread_local std::vector<float> bt;
+  if (bt.size() < (size_t)N * K) bt.resize((size_t)N * K);
+  float* t = bt.data();
+  for (int j0 = 0; j0 < N; j0 += 32)
+    for (int k0 = 0; k0 < K; k0 += 32) {
+      const int j1 = std::min(N, j0 + 32), k1 = std::min(K, k0 + 32);
+      for (int j = j0; j < j1; ++j)
+        for (int k = k0; k < k1; ++k) t[(size_t)k * N + j] = B[(size_t)j * K + k];
     }
-  } else if (!ta) {
-    for (int i = 0; i < M; ++i) {
-      const float* a = A + (size_t)i * K;
-      for (int j = 0; j < N; ++j) {
-        const float* b = B + (size_t)j * K;
-        float s = 0.0f;
-        for (int k = 0; k < K; ++k) s += a[k] * b[k];
-        C[(size_t)i * N + j] += s;
-      }
-    }
-  } else {
-    for (int k = 0; k < K; ++k)
-      for (int i = 0; i < M; ++i) {
-        const float a = A[(size_t)k * M + i];
-        for (int j = 0; j < N; ++j) C[(size_t)i * N + j] += a * B[(size_t)j * K + k];
-      }
-  }
+  gemm_rows(A, t, C, M, N, K, ta);
+  if (bt.size() > ((size_t)1 << 24)) std::vector<float>().swap(bt);      // a one-off large product does not pin 64 MB
 }
 }  // namespace cgi
 

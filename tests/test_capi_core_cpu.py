@@ -35,6 +35,42 @@ def test_tensor_ops_and_tape_gradients_match_torch():
         cg.infer_matmul_shape((3, 4), (5, 6))
 
 
+@pytest.mark.parametrize("M,K,N", [(1, 7, 5), (3, 33, 17), (4, 8, 8), (7, 65, 31), (37, 129, 70)])
+def test_host_gemm_every_operand_layout_on_ragged_sizes(M, K, N):
+    """Products as the layers issue them: x W^T (forward), G W (input gradient), G^T x (weight gradient) and the
+    plain a b with its two gradients, for row counts around the kernel's block of four and odd widths."""
+    lib = L()
+    x_np = rng.standard_normal((M, K), dtype=np.float32)
+    x_np[:, ::3] = 0.0                                                # zero activations are skipped, not mis-added
+    g_np = rng.standard_normal((M, N), dtype=np.float32)
+    lin = lib.cg_linear_new(K, N, True)
+    model = _seq(lin)
+    w_np = borrowed(lin.contents.weights)
+    x = T(x_np, True)
+    out = lib.cg_sequential_forward(model, x._ptr)
+    prod = cg.Tensor.from_ptr(out, retain=True) * T(g_np)
+    loss = prod.sum()
+    loss.backward()
+    tx, tw = torch.tensor(x_np, requires_grad=True), torch.tensor(w_np, requires_grad=True)
+    tb = torch.tensor(borrowed(lin.contents.bias))
+    ty = (tx @ tw if tuple(w_np.shape) == (K, N) else tx @ tw.T) + tb
+    (ty * torch.tensor(g_np)).sum().backward()
+    assert np.allclose(borrowed(out), ty.detach().numpy(), rtol=1e-4, atol=1e-4)
+    assert np.allclose(x.grad, tx.grad.numpy(), rtol=1e-4, atol=1e-4)
+    assert np.allclose(grad_of(lin.contents.weights), tw.grad.numpy(), rtol=1e-4, atol=1e-4)
+    del prod, loss
+    lib.cg_sequential_free(model)
+    # a b and a b^T-shaped operands through the tape
+    b_np = rng.standard_normal((K, N), dtype=np.float32)
+    a, b = T(x_np, True), T(b_np, True)
+    l2 = ((a @ b) * T(g_np)).sum()
+    l2.backward()
+    ta, tb2 = torch.tensor(x_np, requires_grad=True), torch.tensor(b_np, requires_grad=True)
+    ((ta @ tb2) * torch.tensor(g_np)).sum().backward()
+    assert np.allclose(a.grad, ta.grad.numpy(), rtol=1e-4, atol=1e-4)
+    assert np.allclose(b.grad, tb2.grad.numpy(), rtol=1e-4, atol=1e-4)
+
+
 def test_batched_matmul_cat_stack_arena():
     lib = L()
     a, b = rng.standard_normal((2, 3, 4), dtype=np.float32), rng.standard_normal((2, 4, 5), dtype=np.float32)
