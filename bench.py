@@ -27,7 +27,9 @@ reports `vs_baseline` = value / baseline value, with the baseline's own numbers 
 `baseline`.  On one GPU the INT4 speculative-decoding configuration (Llama-7B shape, batch 16,
 512-token prompts, 256 new tokens, gamma 4) then runs once in a child process and is reported under
 `int4_spec_decode` (`--serving off` skips it; with several GPUs run `benchmarks/spec_decode.py` under
-the launcher).
+the launcher).  The headline figures are fixed before any of these extras start; an extra that does not
+come back within its limit (ranks that lost each other inside it) ends the run with the line as it
+stands and an `error` entry under the extra's key.
 """
 from __future__ import annotations
 
@@ -124,6 +126,41 @@ class ClockSampler:
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "samples": len(sm), "reasons": sorted(reasons)}
+
+
+class Reporter:
+    """Holds the result line and prints it exactly once (rank 0): at the end of main(), or from a timer
+    thread when one of the extra measurements that follow the headline (library baseline, data-parallel
+    variant) does not come back, e.g. because one rank failed inside it and the others wait for it in a
+    collective.  Every rank arms the same timer, so all of them leave together."""
+
+    def __init__(self, rank: int):
+        self.rank = rank
+        self.out = None
+        self._lock = threading.Lock()
+        self._done = False
+
+    def emit(self):
+        with self._lock:
+            if self._done:
+                return
+            self._done = True
+            if self.rank == 0 and self.out is not None:
+                print(json.dumps(self.out), flush=True)
+
+    def guard(self, seconds: float, key: str) -> threading.Timer:
+        def fire():
+            if self.out is not None:
+                self.out[key] = {"error": f"no result within {seconds:.0f} s; the run ended here"}
+            self.emit()
+            sys.stderr.write(f"bench.py: '{key}' did not finish within {seconds:.0f} s, leaving\n")
+            sys.stderr.flush()
+            os._exit(0)
+
+        t = threading.Timer(seconds, fire)
+        t.daemon = True
+        t.start()
+        return t
 
 
 def kernel_timeline(step, path, rank, barrier, steps=2):
@@ -237,11 +274,34 @@ def main():
     if args.timeline:
         kernel_timeline(step_device, args.timeline, rank, barrier)
 
+    ms_per_step = ms / args.steps
+    value = tokens_per_step / (ms_per_step * 1e-3)
+    e2e_val = tokens_per_step / (ms_e2e / args.steps * 1e-3)
+    rep = Reporter(rank)
+    rep.out = out = {
+        "metric": "train tok/s/box (GPT-2-small, whole job)", "value": value, "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (uniform token ids, N(0,0.02) weights)", "impl": args.impl,
+        "config": {"model": "gpt2-small", "layers": args.layers, "d_model": 768, "heads": 12, "mlp": 3072,
+                   "vocab": 50304, "global_batch": B, "seq_len": T, "micro_batch": args.micro_batch,
+                   "parallelism": f"{args.parallelism}{world}", "optimizer": "adam",
+                   "l2": "inputs larger than L2: each step streams >10 GB of activations and weights"},
+        "clocks": clocks,
+        "e2e": {"value": e2e_val, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+                # every rank copies the whole global batch (ids and targets, int64): under tensor
+                # parallelism each rank needs all tokens; the figure is per rank
+                "h2d_bytes_per_step": host_ids.numel() * 8 + host_tg.numel() * 8, "d2h_bytes_per_step": 4},
+        "gpu_launches": launches, "final_loss": final_loss,
+        "model_tflops_per_gpu": flops_per_token * value / world / 1e12,
+    }
+
     # The comparison point: the identical configuration on PyTorch library kernels (NCCL + cuBLAS +
     # SDPA + fused AdamW), measured here and now so that both numbers come from the same GPUs.
     baseline = None
     nb = min(args.steps, 5) if args.baseline_steps < 0 else args.baseline_steps
     if args.impl == "cogito" and nb > 0:
+        watch = rep.guard(900, "baseline")
         try:
             import copy
             import gc
@@ -270,11 +330,16 @@ def main():
             torch.cuda.empty_cache()
         except Exception as e:
             baseline = {"error": repr(e)[:300]}
+        watch.cancel()
+        out["baseline"] = baseline
+        if "value" in baseline:
+            out["vs_baseline"] = value / baseline["value"]
 
     # The named configuration is tensor parallel; the same model and batch under data parallelism (the
     # fused all-reduce + Adam kernel) is measured as well and reported beside it under "alt".
     alt = None
     if world > 1 and args.impl == "cogito" and args.parallelism == "tp" and not args.no_alt:
+        watch = rep.guard(600, "alt")
         try:
             import copy
             import gc
@@ -296,6 +361,8 @@ def main():
                    "micro_batch": a2.micro_batch, "final_loss": float(loss_box[0])}
         except Exception as e:                          # the headline number above stands on its own
             alt = {"parallelism": f"dp{world}", "error": repr(e)[:300]}
+        watch.cancel()
+        out["alt"] = alt
 
     # The serving half of the reference's headline: INT4 speculative decoding at the named size.  It runs
     # as a child process with a time limit, after the training jobs have released their memory, so that
@@ -324,36 +391,9 @@ def main():
                 serving = {"error": f"exit code {r.returncode}: " + (r.stderr or r.stdout)[-300:]}
         except Exception as e:
             serving = {"error": repr(e)[:300]}
+        out["int4_spec_decode"] = serving
 
-    if rank == 0:
-        ms_per_step = ms / args.steps
-        value = tokens_per_step / (ms_per_step * 1e-3)
-        e2e_val = tokens_per_step / (ms_e2e / args.steps * 1e-3)
-        out = {
-            "metric": "train tok/s/box (GPT-2-small, whole job)", "value": value, "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": (value / baseline["value"]) if baseline and "value" in baseline else None, "dtype": "bf16",
-            "data": "synthetic (uniform token ids, N(0,0.02) weights)", "impl": args.impl,
-            "config": {"model": "gpt2-small", "layers": args.layers, "d_model": 768, "heads": 12, "mlp": 3072,
-                       "vocab": 50304, "global_batch": B, "seq_len": T, "micro_batch": args.micro_batch,
-                       "parallelism": f"{args.parallelism}{world}", "optimizer": "adam",
-                       "l2": "inputs larger than L2: each step streams >10 GB of activations and weights"},
-            "clocks": clocks,
-            "e2e": {"value": e2e_val, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
-                    # every rank copies the whole global batch (ids and targets, int64): under tensor
-                    # parallelism each rank needs all tokens; the figure is per rank
-                    "h2d_bytes_per_step": host_ids.numel() * 8 + host_tg.numel() * 8, "d2h_bytes_per_step": 4},
-            "gpu_launches": launches, "final_loss": final_loss,
-            "model_tflops_per_gpu": flops_per_token * value / world / 1e12,
-        }
-        if baseline is not None:
-            out["baseline"] = baseline
-        if alt is not None:
-            out["alt"] = alt
-        if serving is not None:
-            out["int4_spec_decode"] = serving
-        print(json.dumps(out))
+    rep.emit()
     if world > 1:
         dist.destroy_process_group()
     return 0
