@@ -27,7 +27,8 @@ DEFAULTS = {
     "seed": 0,
     "device": "auto",                      # auto | cpu | cuda
     "model": {"family": "gpt2", "vocab_size": 50304, "n_layer": 12, "d_model": 768, "n_head": 12, "n_kv_head": None,
-              "d_ff": 3072, "max_seq_len": 2048, "hidden": [512, 512], "in_features": 784, "classes": 10},
+              "d_ff": 3072, "max_seq_len": 2048, "hidden": [512, 512], "in_features": 784, "classes": 10,
+              "in_channels": 1, "image": 28, "channels": [16, 32]},
     "parallel": {"dp": 1, "tp": 1, "pp": 1, "microbatches": 1, "virtual_stages": 1},
     "train": {"steps": 10, "batch": 8, "micro_batch": None, "seq_len": 1024, "lr": 3e-4, "weight_decay": 0.0,
               "max_grad_norm": 1.0, "loss_scale": 65536.0, "optimizer": "adam"},
@@ -129,6 +130,10 @@ def cmd_train(cfg):
             from .models.mlp import MLPClassifier
             model = MLPClassifier(m["in_features"], m["hidden"], m["classes"], device=dev, dtype=dtype)
             params, parallel = list(model.parameters()), None
+        elif family == "cnn":
+            from .models.cnn import ConvClassifier
+            model = ConvClassifier(m["in_channels"], m["image"], m["channels"], m["classes"], device=dev, dtype=dtype)
+            params, parallel = list(model.parameters()), None
         else:
             raise SystemExit(f"unknown model.family {family}")
         scaler = GradScaler(dev, enabled=scaler_on, init_scale=t["loss_scale"] or 1.0)
@@ -154,6 +159,19 @@ def cmd_train(cfg):
         else:
             g = torch.Generator().manual_seed(cfg["seed"] + 1 + rank)
             x, y = torch.rand(batch_rows * t["steps"], m["in_features"], generator=g), torch.randint(0, m["classes"], (batch_rows * t["steps"],), generator=g)
+        batches = BatchIterator(x, y, batch_rows, shuffle=True, seed=cfg["seed"] + rank)
+    elif family == "cnn":
+        side, ch = m["image"], m["in_channels"]
+        if d["kind"] == "mnist":
+            x, y = load_mnist(d["images"], d["labels"])
+            x = x.view(-1, ch, side, side)
+        else:
+            # one random prototype per class plus noise: separable, so the loss shows whether training works
+            g = torch.Generator().manual_seed(cfg["seed"] + 1 + rank)
+            n = batch_rows * t["steps"]
+            proto = torch.randn(m["classes"], ch, side, side, generator=torch.Generator().manual_seed(cfg["seed"]))
+            y = torch.randint(0, m["classes"], (n,), generator=g)
+            x = 0.5 * proto[y] + 0.7 * torch.randn(n, ch, side, side, generator=g)
         batches = BatchIterator(x, y, batch_rows, shuffle=True, seed=cfg["seed"] + rank)
     else:
         batches = SyntheticTokens(m["vocab_size"], batch_rows, t["seq_len"], t["steps"], seed=cfg["seed"] + 17 * (rank // max(p["tp"] * p["pp"], 1)))
@@ -243,6 +261,8 @@ def main(argv=None):
     ap.add_argument("command", choices=["train", "generate", "info"])
     ap.add_argument("--config", default=None)
     args, rest = ap.parse_known_args(argv)
+    if args.config is None and rest and "=" not in rest[0] and not rest[0].startswith("-"):
+        args.config, rest = rest[0], rest[1:]              # `train configs/x.yaml key=value ...`
     bad = [r for r in rest if "=" not in r or r.startswith("-")]
     if bad:
         ap.error(f"expected key.sub=value overrides, got {bad}")

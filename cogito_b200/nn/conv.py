@@ -124,6 +124,9 @@ class _BatchNormFn(torch.autograd.Function):
         xf = x.float().contiguous()
         y = torch.empty_like(xf)
         mean, rstd = torch.empty(F, device=x.device), torch.empty(F, device=x.device)
+        # the kernels read fp32 scale and shift; a flat bf16 optimizer buffer may hold them in bf16
+        ctx.param_dtype = gamma.dtype
+        gamma, beta = gamma.float().contiguous(), beta.float().contiguous()
         _lib.check(_lib.lib().cgk_batchnorm_forward(xf.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr(),
                                                     running_mean.data_ptr(), running_var.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
                                                     B, F, eps, momentum, int(training), _lib.stream_ptr()), "cgk_batchnorm_forward")
@@ -144,7 +147,7 @@ class _BatchNormFn(torch.autograd.Function):
                                                      dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), B, F, _lib.stream_ptr()),
                    "cgk_batchnorm_backward")
         _lib.count_launch()
-        return dx.to(dy.dtype), dgamma, dbeta, None, None, None, None, None
+        return dx.to(dy.dtype), dgamma.to(ctx.param_dtype), dbeta.to(ctx.param_dtype), None, None, None, None, None
 
 
 class BatchNorm(nn.Module):

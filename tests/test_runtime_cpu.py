@@ -134,6 +134,31 @@ def test_cli_config_merge_and_train(tmp_path, capsys):
     assert [json.loads(l)["step"] for l in open(tmp_path / "log2.jsonl")] == [4, 5]
 
 
+def test_convolutional_classifier_trains_from_the_command_line_and_matches_torch_gradients(tmp_path):
+    from cogito_b200.models.cnn import ConvClassifier
+    from cogito_b200.utils import rng
+    # the shipped configuration, config path given positionally, a few steps
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cli_main(["train", os.path.join(root, "configs", "mnist_cnn_cpu.yaml"), "train.steps=25", "log.path=" + str(tmp_path / "cnn.jsonl")])
+    losses = [json.loads(l)["loss"] for l in open(tmp_path / "cnn.jsonl")]
+    assert len(losses) == 25 and sum(losses[-5:]) / 5 < 0.7 * sum(losses[:3]) / 3, losses
+    # gradients of the whole stack against the same network written with torch.nn.functional
+    rng.manual_seed(3)
+    m = ConvClassifier(2, 8, (3, 5), 4)
+    x, y = torch.randn(6, 2, 8, 8), torch.randint(0, 4, (6,))
+    m(x, y).backward()
+    ps = {k: v.detach().clone().requires_grad_(True) for k, v in m.named_parameters()}
+    h = x
+    for i, (ic, oc) in enumerate(((2, 3), (3, 5))):
+        h = torch.nn.functional.conv2d(h, ps[f"convs.{i}.weight"].view(oc, ic, 3, 3), ps[f"convs.{i}.bias"], padding=1)
+        h = torch.nn.functional.batch_norm(h, None, None, ps[f"norms.{i}.weight"], ps[f"norms.{i}.bias"], training=True, eps=1e-5)
+        h = torch.nn.functional.max_pool2d(torch.relu(h), 2)
+    logits = h.flatten(1) @ ps["head.weight"].T + ps["head.bias"]
+    torch.nn.functional.cross_entropy(logits, y).backward()
+    for k, v in m.named_parameters():
+        assert torch.allclose(v.grad, ps[k].grad, atol=1e-5, rtol=1e-4), k
+
+
 # ------------------------------------------------------------ failure detection
 class DictStore:
     def __init__(self):
