@@ -30,6 +30,8 @@ class Model:
     ("commit", queue, bar)         arrives on bar once everything issued earlier on the queue is done
     ("copy_out", buf)              asynchronous read of buf (bulk store / reduction from shared memory)
     ("wait_copies", buf)           block until no copy_out of buf is in flight
+    ("bulk_store", group_queue, buf)  asynchronous read of buf, one bulk async-group of its own on that queue
+    ("wait_group", group_queue, n)    block until all but the n most recent groups of the queue have read their source
     """
 
     def __init__(self, barriers, roles, check_taken=()):
@@ -43,6 +45,8 @@ class Model:
             for st in p:
                 if st[0] in ("write", "read", "tma", "copy_out", "wait_copies"):
                     bufs.add(st[1])
+                if st[0] == "bulk_store":
+                    bufs.add(st[2])
                 if st[0] == "mma":
                     queues.add(st[1])
                     bufs.update(b for b, _ in st[2])
@@ -53,7 +57,9 @@ class Model:
         self.fidx = {b: i for i, b in enumerate(self.bufs)}
         self.queues = sorted(queues)
         self.qidx = {q: i for i, q in enumerate(self.queues)}
-        self.check_taken = {self.fidx[b] for b in check_taken}     # accumulators: must be read before they are rewritten
+        self.check_taken = {self.fidx[b] for b in check_taken if b in self.fidx}     # accumulators: must be read before they are rewritten
+        self.groups = sorted({st[1] for p in self.prog for st in p if st[0] in ("bulk_store", "wait_group")})
+        self.gidx = {g: i for i, g in enumerate(self.groups)}
 
     def explore(self, limit=2_000_000):
         nb, nf = len(self.bars), len(self.bufs)
@@ -62,7 +68,8 @@ class Model:
                  tuple((0, 0) for _ in range(nb)),
                  tuple((None, True, 0, 0, 0) for _ in range(nf)),
                  tuple(() for _ in self.queues),
-                 ())
+                 (),
+                 (tuple(0 for _ in self.groups), ()))          # groups issued per queue, (queue, number, buffer) in flight
         seen, stack = {start}, [start]
         problems, finals = [], 0
 
@@ -76,7 +83,7 @@ class Model:
         while stack:
             if len(seen) > limit:
                 raise AssertionError("state space larger than expected")
-            pcs, bars, bufs, queues, tmas = stack.pop()
+            pcs, bars, bufs, queues, tmas, (issued, stores) = stack.pop()
             moves = []
             # lost phases: a role parked at a wait whose barrier ran two phases ahead
             for r, pc in enumerate(pcs):
@@ -90,7 +97,7 @@ class Model:
                     continue
                 st = self.prog[r][pc]
                 kind = st[0]
-                nbars, nbufs, nqueues, ntmas = bars, bufs, queues, tmas
+                nbars, nbufs, nqueues, ntmas, ngroups = bars, bufs, queues, tmas, (issued, stores)
                 if kind == "wait":
                     if bars[self.bidx[st[1]]][1] <= st[2]:
                         continue
@@ -147,12 +154,23 @@ class Model:
                 elif kind == "wait_copies":
                     if bufs[self.fidx[st[1]]][4]:
                         continue
-                moves.append((pcs[:r] + (pc + 1,) + pcs[r + 1:], nbars, nbufs, nqueues, ntmas))
+                elif kind == "bulk_store":
+                    gq, f = self.gidx[st[1]], self.fidx[st[2]]
+                    v, taken, rd, wr, cp = bufs[f]
+                    if wr:
+                        problems.append(("stored while being written", self.roles[r], st))
+                    nbufs = bufs[:f] + ((v, taken, rd, wr, cp + 1),) + bufs[f + 1:]
+                    ngroups = (issued[:gq] + (issued[gq] + 1,) + issued[gq + 1:], tuple(sorted(stores + ((gq, issued[gq], f),))))
+                elif kind == "wait_group":
+                    gq = self.gidx[st[1]]
+                    if any(q == gq and n < issued[gq] - st[2] for q, n, _ in stores):
+                        continue
+                moves.append((pcs[:r] + (pc + 1,) + pcs[r + 1:], nbars, nbufs, nqueues, ntmas, ngroups))
             # asynchronous completions: a TMA load lands, the oldest entry of an MMA queue finishes, a copy-out ends
             for i, (f, ver, b) in enumerate(tmas):
                 v, taken, rd, wr, cp = bufs[f]
                 nbufs = bufs[:f] + ((ver, False, rd, wr - 1, cp),) + bufs[f + 1:]
-                moves.append((pcs, arrive(bars, b), nbufs, queues, tmas[:i] + tmas[i + 1:]))
+                moves.append((pcs, arrive(bars, b), nbufs, queues, tmas[:i] + tmas[i + 1:], (issued, stores)))
             for q, items in enumerate(queues):
                 if not items:
                     continue
@@ -169,11 +187,15 @@ class Model:
                         lb[f] = (ver, False if ver != v else taken, rd, wr - 1, cp)
                 else:
                     nbars = arrive(bars, head[1])
-                moves.append((pcs, nbars, tuple(lb), queues[:q] + (items[1:],) + queues[q + 1:], tmas))
+                moves.append((pcs, nbars, tuple(lb), queues[:q] + (items[1:],) + queues[q + 1:], tmas, (issued, stores)))
             for f in range(nf):
                 v, taken, rd, wr, cp = bufs[f]
-                if cp:
-                    moves.append((pcs, bars, bufs[:f] + ((v, taken, rd, wr, cp - 1),) + bufs[f + 1:], queues, tmas))
+                if cp > sum(1 for _, _, sf in stores if sf == f):          # a copy_out (the bulk stores end below)
+                    moves.append((pcs, bars, bufs[:f] + ((v, taken, rd, wr, cp - 1),) + bufs[f + 1:], queues, tmas, (issued, stores)))
+            for i, (gq, n, f) in enumerate(stores):                       # groups end in any order
+                v, taken, rd, wr, cp = bufs[f]
+                moves.append((pcs, bars, bufs[:f] + ((v, taken, rd, wr, cp - 1),) + bufs[f + 1:], queues, tmas,
+                              (issued, stores[:i] + stores[i + 1:])))
             if not moves:
                 if any(pc < len(self.prog[r]) for r, pc in enumerate(pcs)):
                     stuck = {self.roles[r]: self.prog[r][pc] for r, pc in enumerate(pcs) if pc < len(self.prog[r])}
