@@ -301,7 +301,7 @@ def main():
     baseline = None
     nb = min(args.steps, 5) if args.baseline_steps < 0 else args.baseline_steps
     if args.impl == "cogito" and nb > 0:
-        watch = rep.guard(900, "baseline")
+        watch = rep.guard(300, "baseline")
         try:
             import copy
             import gc
@@ -339,7 +339,7 @@ def main():
     # fused all-reduce + Adam kernel) is measured as well and reported beside it under "alt".
     alt = None
     if world > 1 and args.impl == "cogito" and args.parallelism == "tp" and not args.no_alt:
-        watch = rep.guard(600, "alt")
+        watch = rep.guard(240, "alt")
         try:
             import copy
             import gc
@@ -381,7 +381,7 @@ def main():
             for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
                 env.pop(k, None)
             r = subprocess.run([sys.executable, os.path.join(here, "benchmarks", "spec_decode.py")], env=env, cwd=here,
-                               capture_output=True, text=True, timeout=900)
+                               capture_output=True, text=True, timeout=600)
             line = next((ln for ln in reversed(r.stdout.splitlines()) if ln.startswith("{")), None)
             if r.returncode == 0 and line:
                 rec = json.loads(line)
