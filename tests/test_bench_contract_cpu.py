@@ -39,3 +39,51 @@ def test_an_extra_measurement_that_never_returns_ends_the_run_with_the_headline_
 def test_other_ranks_leave_without_printing():
     p = _run("import time\nr = bench.Reporter(3); r.out = {'value': 1.0}\nr.guard(0.3, 'alt'); time.sleep(60)")
     assert p.returncode == 0 and p.stdout.strip() == ""
+
+
+_STAND_INS = '''
+import sys, time
+import torch
+real_device = torch.device
+class Ev:
+    def __init__(self, enable_timing=False): self.t = None
+    def record(self): self.t = time.time()
+    def elapsed_time(self, o): return (o.t - self.t) * 1e3 + 1.0
+torch.cuda.set_device = lambda *a, **k: None
+torch.cuda.synchronize = lambda *a, **k: None
+torch.cuda.empty_cache = lambda *a, **k: None
+torch.cuda.Event = Ev
+torch.Tensor.pin_memory = lambda self: self
+torch.device = lambda *a, **k: real_device("cpu")
+import cogito_b200.bench_support as bs
+class Job:
+    flops_per_token = 1e9
+    vocab = 50304
+    def __init__(self): self.n = 0
+    def step(self, ids, tg):
+        self.n += 1
+        return torch.tensor(9.5)
+    def reset_launch_count(self): self.n = 0
+    def launch_count(self): return self.n * 100
+bs.build_job = lambda args, rank, world, dev: Job()
+sys.argv = ["bench.py", "--steps", "2", "--warmup", "1", "--global-batch", "2", "--seq-len", "8", "--serving", "off"]
+sys.exit(bench.main())
+'''
+
+
+def test_main_prints_one_line_with_every_key_of_the_contract():
+    """main() end to end with the CUDA entry points and the job replaced by stand-ins: the control flow
+    around the timed regions, the baseline arm and the reporter, and the keys of the line."""
+    p = _run(_STAND_INS)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [ln for ln in p.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1
+    rec = json.loads(lines[0])
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                "vs_baseline", "dtype", "data", "config", "clocks", "e2e", "gpu_launches", "baseline"):
+        assert key in rec, key
+    assert rec["n_gpus"] == 1 and rec["steps"] == 2 and rec["warmup"] == 3 and rec["gpu_launches"] == 200
+    assert rec["higher_is_better"] is True and rec["dtype"] == "bf16" and rec["config"]["parallelism"] == "tp1"
+    assert set(rec["e2e"]) >= {"value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step"}
+    assert rec["e2e"]["h2d_bytes_per_step"] == 2 * 2 * 8 * 8 and rec["e2e"]["d2h_bytes_per_step"] == 4
+    assert rec["vs_baseline"] == rec["value"] / rec["baseline"]["value"]
