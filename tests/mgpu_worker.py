@@ -59,7 +59,8 @@ def main():
         ids = torch.randint(0, 2048, (2 * world, 128), generator=g).to(dev)
         tg = torch.randint(0, 2048, (2 * world, 128), generator=g).to(dev)
         tf = Trainer(full, FusedAdam(full.parameters(), lr=1e-3), micro_batch=2)
-        td = Trainer(mine, DPFusedAdam(mine.parameters(), dist.group.WORLD, lr=1e-3), micro_batch=2)
+        # several buckets (the last one short), as a full-size model has: every bucket runs its own handshake
+        td = Trainer(mine, DPFusedAdam(mine.parameters(), dist.group.WORLD, lr=1e-3, bucket_elems=300_000), micro_batch=2)
         out["ref"] = [float(tf.step(ids, tg)) for _ in range(4)]
         got = []
         for _ in range(4):
