@@ -247,10 +247,19 @@ def cmd_generate(cfg):
 
 
 def cmd_info(_cfg):
+    from . import __version__
     from .ops import _lib
-    info = {"torch": torch.__version__, "cuda": torch.cuda.is_available(), "kernel_library": _lib.available()}
+    lib_dir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib")
+    info = {"version": __version__, "torch": torch.__version__, "cuda": torch.cuda.is_available(),
+            "kernel_library": _lib.available(), "host_library": os.path.exists(os.path.join(lib_dir, "libcogito.so")),
+            "debug_kernel_library": os.path.exists(os.path.join(lib_dir, "libcogito_kernels_dbg.so"))}
     if torch.cuda.is_available():
-        info["device"] = torch.cuda.get_device_name(0)
+        prop = torch.cuda.get_device_properties(0)
+        info["device"] = prop.name
+        info["devices"] = torch.cuda.device_count()
+        info["sms"] = prop.multi_processor_count
+        info["memory_gib"] = round(prop.total_memory / 2 ** 30, 1)
+        info["compute_capability"] = f"{prop.major}.{prop.minor}"
         info["kernel_library_version"] = _lib.lib().cgk_version()
     print(json.dumps(info))
     return info
