@@ -3,12 +3,15 @@
     python benchmarks/kernels.py <case> [--iters N] [--warmup W] [--small]
 
 Cases: gemm, gemm_epilogue, flash_fwd, flash_bwd, layernorm, layernorm_bwd, rmsnorm, bias_grad,
-cross_entropy, adam, int4_gemm, kv_attn, sample, all.  Each result is one JSON line: device time per call (CUDA events on the launching
+cross_entropy, adam, int4_gemm, kv_attn, sample, elementwise, jit_chain, reduce, rope, swiglu_dropout,
+int4_quantize, spec_accept, all.  Each result is one JSON line: device time per call (CUDA events on the launching
 stream, median of `iters` after `warmup` untimed calls, L2 flushed by writing a 256 MiB buffer
 between calls), achieved TFLOP/s or GB/s, and the fraction of the measured peak taken from
 MEASURED_PEAKS.json beside the repository root (copy bandwidth / cuBLAS bf16 burst) when that
 file exists.  ``--small`` picks shapes a profiler can replay in seconds (a few GB at most, still
-larger than L2 where DRAM figures matter).
+larger than L2 where DRAM figures matter).  Under ``all`` a case that raises is reported as an error
+record and the others still run.  ``--device cpu`` runs the cases that have a host path (the last seven
+of the list) with wall-clock time on tiny shapes: a check of the script, not a measurement.
 """
 from __future__ import annotations
 
@@ -16,8 +19,11 @@ import argparse
 import json
 import os
 import sys
+import time
 
 import torch
+
+DEV = "cuda"
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
@@ -34,13 +40,21 @@ def peaks():
 class Timer:
     def __init__(self, iters, warmup):
         self.iters, self.warmup = iters, warmup
-        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if DEV == "cuda" else None
 
     def __call__(self, fn, graph=False):
         """graph=True replays the call from a CUDA graph: for kernels of a few microseconds the
         Python wrapper is slower than the device, and the events would time the host."""
         for _ in range(self.warmup):
             fn()
+        if DEV != "cuda":
+            ts = []
+            for _ in range(self.iters):
+                t0 = time.perf_counter()
+                fn()
+                ts.append((time.perf_counter() - t0) * 1e3)
+            ts.sort()
+            return ts[len(ts) // 2]
         torch.cuda.synchronize()
         if graph:
             g = torch.cuda.CUDAGraph()
@@ -231,7 +245,86 @@ def case_sample(t, small):
     emit("sample_topk_topp", t(lambda: sample(lg, 0.8, 50, 0.9, 1, step, return_probs=True), graph=True), bytes_=rows * V * 8.0, rows=rows, vocab=V)
 
 
+def _n(small, big, little):
+    """Element count: `big` for a measurement, `little` under --small, a few thousand on the host."""
+    return 4096 if DEV != "cuda" else (little if small else big)
+
+
+def case_elementwise(t, small):
+    """One unary and one broadcasting binary kernel of the elementwise library (bf16, 2 bytes in and out per element)."""
+    from cogito_b200.ops.functional import binary, unary
+    n = _n(small, 256 << 20, 64 << 20)
+    x = torch.randn(n // 1024, 1024, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(1024, device=DEV, dtype=torch.bfloat16)
+    emit("elementwise", t(lambda: unary("gelu", x)), bytes_=2.0 * n * 2, what="gelu", elements=n)
+    emit("elementwise", t(lambda: binary("add", x, b)), bytes_=2.0 * n * 2, what="add, row broadcast", elements=n)
+
+
+def case_jit_chain(t, small):
+    """A chain the tracer fuses into one generated kernel: sigmoid(a * b + c) * a, three inputs, one output."""
+    from cogito_b200.jit.fuse import fuse, sigmoid
+    n = _n(small, 128 << 20, 32 << 20)
+    a, b, c = (torch.randn(n, device=DEV, dtype=torch.bfloat16) for _ in range(3))
+    f = fuse(lambda a, b, c: sigmoid(a * b + c) * a)
+    f(a, b, c)                                                         # trace + compile outside the timed calls
+    emit("jit_chain", t(lambda: f(a, b, c)), bytes_=4.0 * n * 2, elements=n)
+
+
+def case_reduce(t, small):
+    """Sum over everything and over the rows of a [rows, 1024] bf16 matrix."""
+    from cogito_b200.ops.functional import reduce
+    n = _n(small, 256 << 20, 64 << 20)
+    x = torch.randn(n // 1024, 1024, device=DEV, dtype=torch.bfloat16)
+    emit("reduce", t(lambda: reduce("sum", x)), bytes_=1.0 * n * 2, what="sum, all", elements=n)
+    emit("reduce", t(lambda: reduce("sum", x, 1)), bytes_=1.0 * n * 2, what="sum, last axis", elements=n)
+    emit("reduce", t(lambda: reduce("max", x, 0)), bytes_=1.0 * n * 2, what="max, first axis", elements=n)
+
+
+def case_rope(t, small):
+    """Rotary embedding in place on [B, T, H, D] bf16 (one read and one write of the tensor)."""
+    from cogito_b200.ops.misc import rope_apply_, rope_tables
+    B, T, H, D = (2, 64, 2, 64) if DEV != "cuda" else ((4, 4096, 32, 128) if not small else (2, 2048, 32, 128))
+    x = torch.randn(B, T, H, D, device=DEV, dtype=torch.bfloat16)
+    cos_t, sin_t = rope_tables(T, D, device=DEV)
+    emit("rope", t(lambda: rope_apply_(x, cos_t, sin_t)), bytes_=2.0 * x.numel() * 2, B=B, T=T, H=H, D=D)
+
+
+def case_swiglu_dropout(t, small):
+    """SwiGLU split ([rows, 2F] -> [rows, F]) and dropout (counter-based mask) on bf16."""
+    from cogito_b200.ops.misc import dropout, swiglu
+    rows, F = (64, 128) if DEV != "cuda" else ((16384, 11008) if not small else (4096, 11008))
+    x = torch.randn(rows, 2 * F, device=DEV, dtype=torch.bfloat16)
+    with torch.no_grad():
+        emit("swiglu", t(lambda: swiglu(x)), bytes_=3.0 * rows * F * 2, rows=rows, features=F)
+        h = torch.randn(rows, F, device=DEV, dtype=torch.bfloat16)
+        emit("dropout", t(lambda: dropout(h, 0.1, True, seed=1)), bytes_=2.0 * rows * F * 2, rows=rows, features=F)
+
+
+def case_int4_quantize(t, small):
+    """Flat groups of 128: quantise an fp32 tensor (4 bytes in, ~0.53 out per element) and dequantise it to bf16."""
+    from cogito_b200.quant.int4 import dequantize_int4, quantize_int4
+    n = _n(small, 128 << 20, 32 << 20)
+    x = torch.randn(n, device=DEV)
+    packed, scales = quantize_int4(x, 128)
+    emit("int4_quantize", t(lambda: quantize_int4(x, 128)), bytes_=n * (4 + 0.5 + 4 / 128), elements=n)
+    emit("int4_dequantize", t(lambda: dequantize_int4(packed, scales, n, 128, torch.bfloat16)), bytes_=n * (0.5 + 4 / 128 + 2), elements=n)
+
+
+def case_spec_accept(t, small):
+    """Accept / correct / commit for 16 sequences, gamma 4, vocabulary 32000 (latency-bound), and the tree mask."""
+    from cogito_b200.serve.sampling import spec_accept, tree_attention_mask
+    B, g, V = (2, 4, 512) if DEV != "cuda" else (16, 4, 32000)
+    q = torch.softmax(torch.randn(B, g, V, device=DEV), -1)
+    p = torch.softmax(torch.randn(B, g + 1, V, device=DEV), -1)
+    tok = torch.randint(0, V, (B, g), device=DEV, dtype=torch.int32)
+    step = torch.zeros(1, dtype=torch.int64, device=DEV) if DEV == "cuda" else 0
+    emit("spec_accept", t(lambda: spec_accept(tok, q, p, 1, step), graph=DEV == "cuda"), bytes_=(2 * g + 1) * B * V * 4.0, B=B, gamma=g, vocab=V)
+    parents = torch.tensor([-1, 0, 0, 1, 1, 2, 2, 3], dtype=torch.int32, device=DEV)
+    emit("tree_mask", t(lambda: tree_attention_mask(parents, 512), graph=DEV == "cuda"), bytes_=4.0 * (512 + 8) ** 2, prefix=512, nodes=8)
+
+
 CASES = {k[5:]: v for k, v in globals().items() if k.startswith("case_")}
+HOST_CASES = ("elementwise", "jit_chain", "reduce", "rope", "swiglu_dropout", "int4_quantize", "spec_accept")
 
 
 def main():
@@ -240,14 +333,27 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"])
     args = ap.parse_args()
+    global DEV
+    DEV = args.device
+    if DEV == "cpu" and args.case != "all" and args.case not in HOST_CASES:
+        raise SystemExit(f"{args.case} has no host path; with --device cpu choose one of {', '.join(HOST_CASES)} or all")
     t = Timer(args.iters, args.warmup)
-    for name in (sorted(CASES) if args.case == "all" else [args.case]):
-        CASES[name](t, args.small)
-    from cogito_b200.ops import _lib
-    code = _lib.read_status()[0]
-    if code:
-        raise SystemExit(f"device status {code}")
+    names = [n for n in sorted(CASES) if DEV == "cuda" or n in HOST_CASES] if args.case == "all" else [args.case]
+    for name in names:
+        if args.case != "all":
+            CASES[name](t, args.small)
+            continue
+        try:
+            CASES[name](t, args.small)
+        except Exception as e:                               # one broken case must not hide the others' numbers
+            print(json.dumps({"case": name, "error": repr(e)[:300]}), flush=True)
+    if DEV == "cuda":
+        from cogito_b200.ops import _lib
+        code = _lib.read_status()[0]
+        if code:
+            raise SystemExit(f"device status {code}")
 
 
 if __name__ == "__main__":
