@@ -95,3 +95,13 @@ def test_top_level_namespace_resolves_every_name_lazily():
              "assert cg.GPT2.__module__ == 'cogito_b200.models.gpt2' and cg.nn.Linear is not None and cg.__version__\n"
              "try:\n    cg.no_such_name\nexcept AttributeError:\n    print('ok')")
     assert p.returncode == 0 and p.stdout.strip().endswith("ok"), p.stderr[-1500:]
+
+
+def test_kernel_benchmark_host_mode_runs_every_host_case():
+    p = subprocess.run([sys.executable, str(ROOT / "benchmarks" / "kernels.py"), "all", "--device", "cpu", "--iters", "1", "--warmup", "0"],
+                       capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-1500:]
+    recs = [json.loads(ln) for ln in p.stdout.splitlines() if ln.startswith("{")]
+    assert not [r for r in recs if "error" in r], recs
+    assert {r["case"] for r in recs} >= {"elementwise", "jit_chain", "reduce", "rope", "swiglu", "dropout", "int4_quantize",
+                                         "int4_dequantize", "spec_accept", "tree_mask"}
