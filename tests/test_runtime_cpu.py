@@ -283,3 +283,14 @@ def test_survivors_detect_a_lost_rank_and_resume_from_the_checkpoint(tmp_path):
         assert steps0 and steps1 and max(steps0) >= 3 and steps1[-1] == 7
         assert steps1[0] == max(steps0) + 1 or steps1[0] == max(steps0)      # resumed where the checkpoint left off
         assert sorted(set(steps0 + steps1)) == list(range(8))
+
+
+def test_python_examples_train_on_the_cpu():
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "examples", "xor.py")], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0 and "final loss 0.0000" in p.stdout, p.stdout[-500:] + p.stderr[-500:]
+    p = subprocess.run([sys.executable, os.path.join(root, "examples", "mnist_mlp.py"), "--epochs", "2", "--samples", "512", "--batch", "64"],
+                       capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0 and "accuracy 1.000" in p.stdout.splitlines()[-1], p.stdout[-500:] + p.stderr[-500:]
