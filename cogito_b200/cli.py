@@ -95,6 +95,7 @@ def cmd_train(cfg):
     scaler_on = t["loss_scale"] is not None and dev.type == "cuda"
     family = m["family"]
     step_fn, model, opt = None, None, None
+    logger = rank == 0
     if family == "llama" and world > 1:
         from .models.llama import LlamaConfig
         from .parallel.groups import init_parallel
@@ -109,6 +110,9 @@ def cmd_train(cfg):
         model, opt = t3.stage, t3.opt
         batch_rows = p["microbatches"] * mb
         step_fn = t3.step
+        # the loss exists on the last pipeline stage: its first rank of the first replica reports
+        c = ctx.coords
+        logger = c.pp_rank == c.pp - 1 and c.dp_rank == 0 and c.tp_rank == 0
     else:
         if family == "gpt2":
             from .models.gpt2 import GPT2, GPT2Config
@@ -188,7 +192,7 @@ def cmd_train(cfg):
     prof = Profiler(enabled=bool(cfg["profile"]))
     if cfg["profile"]:
         instrument(model, prof)
-    log_f = open(cfg["log"]["path"], "a") if (cfg["log"]["path"] and rank == 0) else None
+    log_f = open(cfg["log"]["path"], "a") if (cfg["log"]["path"] and logger) else None
     step, last = start, None
     t0 = time.time()
     for x, y in batches:
@@ -201,7 +205,7 @@ def cmd_train(cfg):
         if loss is not None and step % cfg["log"]["every"] == 0:
             last = float(loss)
             rec = {"step": step, "loss": last, "elapsed_s": round(time.time() - t0, 3)}
-            if rank == 0:
+            if logger:
                 print(json.dumps(rec), flush=True)
             if log_f:
                 log_f.write(json.dumps(rec) + "\n")

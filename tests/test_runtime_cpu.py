@@ -294,3 +294,17 @@ def test_python_examples_train_on_the_cpu():
     p = subprocess.run([sys.executable, os.path.join(root, "examples", "mnist_mlp.py"), "--epochs", "2", "--samples", "512", "--batch", "64"],
                        capture_output=True, text=True, timeout=300)
     assert p.returncode == 0 and "accuracy 1.000" in p.stdout.splitlines()[-1], p.stdout[-500:] + p.stderr[-500:]
+
+
+def test_cli_trains_the_3d_parallel_llama_on_eight_cpu_ranks_and_reports_from_the_last_stage(tmp_path):
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    log = tmp_path / "3d.jsonl"
+    p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "8", "--master-addr", "127.0.0.1",
+                        "--master-port", "29641", "-m", "cogito_b200", "train", os.path.join(root, "configs", "llama_tiny_3d_cpu.yaml"),
+                        "train.steps=3", f"log.path={log}"], capture_output=True, text=True, timeout=600, cwd=root)
+    assert p.returncode == 0, p.stderr[-1500:]
+    recs = [json.loads(l) for l in open(log)]
+    assert [r["step"] for r in recs] == [1, 2, 3] and all(5.0 < r["loss"] < 7.5 for r in recs)       # ln(512) = 6.24 at the start
+    assert len([l for l in p.stdout.splitlines() if l.startswith("{")]) == 3                         # one rank prints
