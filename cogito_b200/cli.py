@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import argparse
 import copy
+import itertools
 import json
 import os
 import sys
@@ -195,7 +196,8 @@ def cmd_train(cfg):
     log_f = open(cfg["log"]["path"], "a") if (cfg["log"]["path"] and logger) else None
     step, last = start, None
     t0 = time.time()
-    for x, y in batches:
+    # a resumed run goes on with the batch after the last one it trained on, as an uninterrupted run would
+    for x, y in itertools.islice(iter(batches), start, None):
         if step >= t["steps"]:
             break
         x, y = x.to(dev, non_blocking=True), y.to(dev, non_blocking=True)

@@ -131,7 +131,12 @@ def test_cli_config_merge_and_train(tmp_path, capsys):
     # resume: starts at step 3, so two more steps of a 5-step run
     cli_main(["train", "--config", str(cfg_file), f"checkpoint.dir={tmp_path}/ck", "checkpoint.resume=true", "train.steps=5",
               "log.path=" + str(tmp_path / "log2.jsonl")])
-    assert [json.loads(l)["step"] for l in open(tmp_path / "log2.jsonl")] == [4, 5]
+    resumed = [json.loads(l) for l in open(tmp_path / "log2.jsonl")]
+    assert [r["step"] for r in resumed] == [4, 5]
+    # the resumed run continues the data stream: same losses as five steps in one go
+    cli_main(["train", "--config", str(cfg_file), "train.steps=5", "log.path=" + str(tmp_path / "log3.jsonl")])
+    whole = [json.loads(l) for l in open(tmp_path / "log3.jsonl")]
+    assert [r["loss"] for r in whole[3:]] == pytest.approx([r["loss"] for r in resumed], rel=1e-6)
 
 
 def test_convolutional_classifier_trains_from_the_command_line_and_matches_torch_gradients(tmp_path):
