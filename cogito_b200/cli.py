@@ -196,6 +196,8 @@ def cmd_train(cfg):
     log_f = open(cfg["log"]["path"], "a") if (cfg["log"]["path"] and logger) else None
     step, last = start, None
     t0 = time.time()
+    t_mark, step_mark = None, start                                # the first interval (compilation, first-touch) is not a rate
+    units_per_step = batch_rows * max(p["dp"], 1) * (1 if family in ("mlp", "cnn") else t["seq_len"])
     # a resumed run goes on with the batch after the last one it trained on, as an uninterrupted run would
     for x, y in itertools.islice(iter(batches), start, None):
         if step >= t["steps"]:
@@ -205,8 +207,16 @@ def cmd_train(cfg):
         step += 1
         prof.step_end()
         if loss is not None and step % cfg["log"]["every"] == 0:
-            last = float(loss)
-            rec = {"step": step, "loss": last, "elapsed_s": round(time.time() - t0, 3)}
+            last = float(loss)                                   # waits for the step
+            now = time.time()
+            rec = {"step": step, "loss": last, "elapsed_s": round(now - t0, 3)}
+            if t_mark is not None and now > t_mark:
+                rec["per_s"] = round(units_per_step * (step - step_mark) / (now - t_mark), 1)      # tokens (samples for MLP / CNN) over the whole job
+            t_mark, step_mark = now, step
+            scaler = getattr(opt, "scaler", None)
+            if scaler is not None and scaler.enabled:
+                st = scaler.sync()
+                rec["loss_scale"], rec["skipped"] = st["scale"], st["skipped"]
             if logger:
                 print(json.dumps(rec), flush=True)
             if log_f:
