@@ -22,6 +22,7 @@ import sys
 import time
 
 import torch
+import torch.distributed as dist
 import yaml
 
 DEFAULTS = {
@@ -75,7 +76,6 @@ def _device(cfg):
 
 
 def cmd_train(cfg):
-    import torch.distributed as dist
     from .data.datasets import BatchIterator, SyntheticTokens, load_mnist
     from .io import checkpoint as ckpt
     from .optim.fused import FusedAdam, FusedSGD, GradScaler
@@ -239,6 +239,12 @@ def cmd_generate(cfg):
     from .serve.engine import LlamaInt4Engine, SpeculativeDecoder
     from .utils import rng
     dev = _device(cfg)
+    world, rank = int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("RANK", 0))
+    group = None
+    if world > 1:                                                # under a launcher: tensor-parallel serving over all ranks
+        if not dist.is_initialized():
+            dist.init_process_group("nccl" if dev.type == "cuda" else "gloo", **({"device_id": dev} if dev.type == "cuda" else {}))
+        group = dist.group.WORLD
     rng.manual_seed(cfg["seed"])
     m = cfg["model"]
     g = cfg.get("generate", {})
@@ -248,8 +254,8 @@ def cmd_generate(cfg):
     dc = LlamaConfig(vocab_size=m["vocab_size"], n_layer=g.get("draft_layers", 2), d_model=m["d_model"], n_head=m["n_head"],
                      n_kv_head=m["n_kv_head"] or m["n_head"], d_ff=m["d_ff"], max_seq_len=m["max_seq_len"])
     B, L, new = g.get("batch", 4), g.get("prompt_len", 16), g.get("new_tokens", 32)
-    target = LlamaInt4Engine(Llama(tc, device=dev, dtype=dtype), B, L + new + 16)
-    draft = LlamaInt4Engine(Llama(dc, device=dev, dtype=dtype), B, L + new + 16)
+    target = LlamaInt4Engine(Llama(tc, device=dev, dtype=dtype), B, L + new + 16, tp_group=group)
+    draft = LlamaInt4Engine(Llama(dc, device=dev, dtype=dtype), B, L + new + 16, tp_group=group)
     dec = SpeculativeDecoder(draft, target, gamma=g.get("gamma", 4), temperature=g.get("temperature", 0.8), top_k=g.get("top_k", 50),
                              top_p=g.get("top_p", 0.9), seed=cfg["seed"])
     prompts = torch.randint(0, m["vocab_size"], (B, L), generator=torch.Generator().manual_seed(cfg["seed"])).to(dev)
@@ -257,8 +263,13 @@ def cmd_generate(cfg):
     seqs, stats = dec.generate(prompts, new)
     dt = time.time() - t0
     out = {"generated": stats.generated, "steps": stats.steps, "acceptance_rate": round(stats.acceptance_rate, 4),
-           "tok_per_s": round(stats.generated / dt, 1)}
-    print(json.dumps(out))
+           "tok_per_s": round(stats.generated / dt, 1), "tp": world}
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dec.close()
+        dist.barrier()
+        dist.destroy_process_group()
     return out
 
 

@@ -313,3 +313,20 @@ def test_cli_trains_the_3d_parallel_llama_on_eight_cpu_ranks_and_reports_from_th
     recs = [json.loads(l) for l in open(log)]
     assert [r["step"] for r in recs] == [1, 2, 3] and all(5.0 < r["loss"] < 7.5 for r in recs)       # ln(512) = 6.24 at the start
     assert len([l for l in p.stdout.splitlines() if l.startswith("{")]) == 3                         # one rank prints
+
+
+def test_cli_generate_runs_alone_and_tensor_parallel_on_two_cpu_ranks():
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    over = ["device=cpu", "model.vocab_size=512", "model.n_layer=2", "model.d_model=128", "model.n_head=4", "model.n_kv_head=2",
+            "model.d_ff=256", "model.max_seq_len=128", "generate.batch=2", "generate.prompt_len=8", "generate.new_tokens=10",
+            "generate.draft_layers=1"]
+    cfg = os.path.join(root, "configs", "spec_decode_int4.yaml")
+    one = cli_main(["generate", cfg] + over)
+    assert one["generated"] >= 2 * 10 and one["tp"] == 1 and 0.0 <= one["acceptance_rate"] <= 1.0
+    p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29643", "-m", "cogito_b200", "generate", cfg] + over, capture_output=True, text=True, timeout=600, cwd=root)
+    assert p.returncode == 0, p.stderr[-1500:]
+    lines = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1 and lines[0]["tp"] == 2 and lines[0]["generated"] >= 2 * 10
