@@ -301,13 +301,22 @@ def test_python_examples_train_on_the_cpu():
     assert p.returncode == 0 and "accuracy 1.000" in p.stdout.splitlines()[-1], p.stdout[-500:] + p.stderr[-500:]
 
 
+
+def _free_port():
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
 def test_cli_trains_the_3d_parallel_llama_on_eight_cpu_ranks_and_reports_from_the_last_stage(tmp_path):
     import subprocess
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     log = tmp_path / "3d.jsonl"
     p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "8", "--master-addr", "127.0.0.1",
-                        "--master-port", "29641", "-m", "cogito_b200", "train", os.path.join(root, "configs", "llama_tiny_3d_cpu.yaml"),
+                        "--master-port", str(_free_port()), "-m", "cogito_b200", "train", os.path.join(root, "configs", "llama_tiny_3d_cpu.yaml"),
                         "train.steps=3", f"log.path={log}"], capture_output=True, text=True, timeout=600, cwd=root)
     assert p.returncode == 0, p.stderr[-1500:]
     recs = [json.loads(l) for l in open(log)]
@@ -326,7 +335,7 @@ def test_cli_generate_runs_alone_and_tensor_parallel_on_two_cpu_ranks():
     one = cli_main(["generate", cfg] + over)
     assert one["generated"] >= 2 * 10 and one["tp"] == 1 and 0.0 <= one["acceptance_rate"] <= 1.0
     p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
-                        "--master-port", "29643", "-m", "cogito_b200", "generate", cfg] + over, capture_output=True, text=True, timeout=600, cwd=root)
+                        "--master-port", str(_free_port()), "-m", "cogito_b200", "generate", cfg] + over, capture_output=True, text=True, timeout=600, cwd=root)
     assert p.returncode == 0, p.stderr[-1500:]
     lines = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{")]
     assert len(lines) == 1 and lines[0]["tp"] == 2 and lines[0]["generated"] >= 2 * 10
