@@ -301,15 +301,6 @@ def test_python_examples_train_on_the_cpu():
     assert p.returncode == 0 and "accuracy 1.000" in p.stdout.splitlines()[-1], p.stdout[-500:] + p.stderr[-500:]
 
 
-
-def _free_port():
-    import socket
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    port = s.getsockname()[1]
-    s.close()
-    return port
-
 def test_cli_trains_the_3d_parallel_llama_on_eight_cpu_ranks_and_reports_from_the_last_stage(tmp_path):
     import subprocess
     import sys
