@@ -36,6 +36,10 @@ DEFAULTS = {
               "max_grad_norm": 1.0, "loss_scale": 65536.0, "optimizer": "adam"},
     "data": {"kind": "synthetic", "images": None, "labels": None},
     "checkpoint": {"dir": None, "every": 0, "resume": False},
+    # multi-rank jobs: heartbeats in the job's store, checked before every step; a rank that stopped answering ends
+    # the run with exit code 3 (restart it with checkpoint.resume=true); device_check_every n reads the kernels'
+    # status word every n steps (a bounded device-side wait that ran out)
+    "failure": {"heartbeat": False, "interval_s": 0.5, "timeout_s": 10.0, "device_check_every": 0},
     "log": {"path": None, "every": 1},
     "profile": False,
 }
@@ -195,6 +199,11 @@ def cmd_train(cfg):
         instrument(model, prof)
     log_f = open(cfg["log"]["path"], "a") if (cfg["log"]["path"] and logger) else None
     step, last = start, None
+    fcfg, hb, failed = cfg["failure"], None, None
+    if world > 1 and fcfg["heartbeat"]:
+        from .utils.failure import Heartbeat, RankFailure, check_device
+        hb = Heartbeat(dist.distributed_c10d._get_default_store(), rank, world, interval=fcfg["interval_s"],
+                       timeout=fcfg["timeout_s"]).start()
     t0 = time.time()
     t_mark, step_mark = None, start                                # the first interval (compilation, first-touch) is not a rate
     units_per_step = batch_rows * max(p["dp"], 1) * (1 if family in ("mlp", "cnn") else t["seq_len"])
@@ -203,7 +212,17 @@ def cmd_train(cfg):
         if step >= t["steps"]:
             break
         x, y = x.to(dev, non_blocking=True), y.to(dev, non_blocking=True)
-        loss = step_fn(x, y)
+        if hb is None:
+            loss = step_fn(x, y)
+        else:
+            try:
+                hb.check()                                   # never enter a collective a dead peer cannot complete
+                loss = hb.guard(step_fn, x, y)
+                if fcfg["device_check_every"] and (step + 1) % fcfg["device_check_every"] == 0:
+                    check_device()
+            except RankFailure as e:
+                failed = e
+                break
         step += 1
         prof.step_end()
         if loss is not None and step % cfg["log"]["every"] == 0:
@@ -224,6 +243,18 @@ def cmd_train(cfg):
                 log_f.flush()
         if base and ck["every"] and step % ck["every"] == 0:
             ckpt.save_training_state(base, model, opt, step)
+    if failed is not None:
+        # the peers are gone: no collective, no barrier; the last periodic checkpoint is the restart point
+        rec = {"event": "rank_failure", "rank": rank, "dead": failed.dead, "step": step, "detail": str(failed)}
+        print(json.dumps(rec), flush=True)
+        if log_f:
+            log_f.write(json.dumps(rec) + "\n")
+            log_f.close()
+        hb.stop(announce=True)
+        sys.stdout.flush()
+        os._exit(3)
+    if hb is not None:
+        hb.stop(announce=True)
     if base:
         ckpt.save_training_state(base, model, opt, step)
     if cfg["profile"] and rank == 0:

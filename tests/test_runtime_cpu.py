@@ -330,3 +330,34 @@ def test_cli_generate_runs_alone_and_tensor_parallel_on_two_cpu_ranks():
     assert p.returncode == 0, p.stderr[-1500:]
     lines = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{")]
     assert len(lines) == 1 and lines[0]["tp"] == 2 and lines[0]["generated"] >= 2 * 10
+
+
+def _cli_failure_worker(rank, port, tmp):
+    """Two data-parallel CLI ranks; rank 1 is told to train two steps only and leaves the job there
+    (its closing barrier is replaced by an exit: a rank that is gone, not one that waits)."""
+    import torch.distributed as dist
+    os.environ.update(RANK=str(rank), WORLD_SIZE="2", LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.set_num_threads(1)
+    sys_stdout = open(os.path.join(tmp, f"out{rank}.txt"), "w")
+    os.dup2(sys_stdout.fileno(), 1)
+    if rank == 1:
+        dist.barrier = lambda *a, **k: os._exit(0)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cli_main(["train", os.path.join(root, "configs", "tiny_cpu.yaml"), "parallel.dp=2", f"train.steps={2 if rank == 1 else 40}",
+              "failure.heartbeat=true", "failure.interval_s=0.1", "failure.timeout_s=3.0"])
+    os._exit(0)
+
+
+def test_cli_with_heartbeats_ends_with_code_3_and_an_event_when_a_rank_leaves(tmp_path):
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_cli_failure_worker, args=(r, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=240)
+    assert procs[1].exitcode == 0 and procs[0].exitcode == 3, [p.exitcode for p in procs]
+    recs = [json.loads(l) for l in open(tmp_path / "out0.txt") if l.startswith("{")]
+    assert [r["step"] for r in recs if "loss" in r][:2] == [1, 2]
+    ev = [r for r in recs if r.get("event") == "rank_failure"]
+    assert len(ev) == 1 and ev[0]["dead"] == [1] and 2 <= ev[0]["step"] < 40
