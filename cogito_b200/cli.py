@@ -189,10 +189,38 @@ def cmd_train(cfg):
     ck = cfg["checkpoint"]
     start = 0
     base = None
+    # Pure data-parallel jobs write one replicated model file and one optimizer shard per rank in a layout that a
+    # job of ANOTHER size can read (the shards are re-cut for the new group): lose a GPU, restart with the rest.
+    dp_job = world > 1 and p["dp"] == world and hasattr(opt, "shard_state")
+    dp_base = os.path.join(ck["dir"], "dp") if ck["dir"] else None
+
+    def save_state(at_step):
+        if not dp_job:
+            ckpt.save_training_state(base, model, opt, at_step)
+            return
+        import glob
+        if rank == 0:
+            for f in glob.glob(glob.escape(dp_base) + ".opt.dp*of*.state"):
+                if not f.endswith(f"of{world:02d}.state"):
+                    os.remove(f)                              # shards of an earlier group size
+        dist.barrier()
+        ckpt.save_dp_optimizer_shard(dp_base, opt)
+        if rank == 0:
+            ckpt.save_model(dp_base + ".cog", model)
+            with open(dp_base + ".json", "w") as f:
+                json.dump({"step": int(at_step), "lr": float(opt.lr), "ranks": world}, f)
+        dist.barrier()                                        # the set is complete before anyone moves on
+
     if ck["dir"]:
         os.makedirs(ck["dir"], exist_ok=True)
         base = os.path.join(ck["dir"], f"rank{rank:03d}")
-        if ck["resume"] and os.path.exists(base + ".state"):
+        if ck["resume"] and dp_job and os.path.exists(dp_base + ".json"):
+            with open(dp_base + ".json") as f:
+                meta = json.load(f)
+            ckpt.load_model(dp_base + ".cog", model)
+            ckpt.load_dp_optimizer_resharded(dp_base, opt)    # whatever size the job that wrote them had
+            opt.lr, start = meta["lr"], meta["step"]
+        elif ck["resume"] and os.path.exists(base + ".state"):
             start = ckpt.load_training_state(base, model, opt)["step"]
     prof = Profiler(enabled=bool(cfg["profile"]))
     if cfg["profile"]:
@@ -242,7 +270,7 @@ def cmd_train(cfg):
                 log_f.write(json.dumps(rec) + "\n")
                 log_f.flush()
         if base and ck["every"] and step % ck["every"] == 0:
-            ckpt.save_training_state(base, model, opt, step)
+            save_state(step)
     if failed is not None:
         # the peers are gone: no collective, no barrier; the last periodic checkpoint is the restart point
         rec = {"event": "rank_failure", "rank": rank, "dead": failed.dead, "step": step, "detail": str(failed)}
@@ -256,7 +284,7 @@ def cmd_train(cfg):
     if hb is not None:
         hb.stop(announce=True)
     if base:
-        ckpt.save_training_state(base, model, opt, step)
+        save_state(step)
     if cfg["profile"] and rank == 0:
         prof.report()
     if world > 1:

@@ -361,3 +361,28 @@ def test_cli_with_heartbeats_ends_with_code_3_and_an_event_when_a_rank_leaves(tm
     assert [r["step"] for r in recs if "loss" in r][:2] == [1, 2]
     ev = [r for r in recs if r.get("event") == "rank_failure"]
     assert len(ev) == 1 and ev[0]["dead"] == [1] and 2 <= ev[0]["step"] < 40
+
+
+def test_cli_data_parallel_checkpoints_resume_exactly_and_on_a_smaller_group(tmp_path):
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def run(ranks, steps, *extra):
+        p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks), "--master-addr",
+                            "127.0.0.1", "--master-port", str(_free_port()), "-m", "cogito_b200", "train",
+                            os.path.join(root, "configs", "tiny_cpu.yaml"), "train.batch=6", f"train.steps={steps}", f"parallel.dp={ranks}",
+                            *extra], capture_output=True, text=True, timeout=600, cwd=root)
+        assert p.returncode == 0, p.stderr[-1500:]
+        return {r["step"]: r["loss"] for r in (json.loads(l) for l in p.stdout.splitlines() if l.startswith("{"))}
+
+    whole = run(3, 4)
+    ck = f"checkpoint.dir={tmp_path}/ck"
+    first = run(3, 2, ck)
+    assert first[2] == whole[2]
+    same = run(3, 4, ck, "checkpoint.resume=true")
+    assert sorted(same) == [3, 4] and same[3] == whole[3] and same[4] == whole[4]        # same group: the same run
+    assert sorted(f for f in os.listdir(tmp_path / "ck") if "of" in f) == [f"dp.opt.dp0{r}of03.state" for r in range(3)]
+    fewer = run(2, 6, ck, "checkpoint.resume=true")                                       # one rank fewer: shards re-cut
+    assert sorted(fewer) == [5, 6] and all(4.5 < v < 6.5 for v in fewer.values())
+    assert sorted(f for f in os.listdir(tmp_path / "ck") if "of" in f) == [f"dp.opt.dp0{r}of02.state" for r in range(2)]
