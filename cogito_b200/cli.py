@@ -313,17 +313,46 @@ def cmd_generate(cfg):
     dc = LlamaConfig(vocab_size=m["vocab_size"], n_layer=g.get("draft_layers", 2), d_model=m["d_model"], n_head=m["n_head"],
                      n_kv_head=m["n_kv_head"] or m["n_head"], d_ff=m["d_ff"], max_seq_len=m["max_seq_len"])
     B, L, new = g.get("batch", 4), g.get("prompt_len", 16), g.get("new_tokens", 32)
-    target = LlamaInt4Engine(Llama(tc, device=dev, dtype=dtype), B, L + new + 16, tp_group=group)
-    draft = LlamaInt4Engine(Llama(dc, device=dev, dtype=dtype), B, L + new + 16, tp_group=group)
+    if g.get("prompts"):                                          # a JSON list of B token-id lists of equal length
+        with open(g["prompts"]) as f:
+            prompts = torch.tensor(json.load(f), dtype=torch.int64)
+        if prompts.dim() != 2 or prompts.shape[0] != B:
+            raise SystemExit(f"generate.prompts must hold {B} token lists of equal length")
+        L = prompts.shape[1]
+    else:
+        prompts = torch.randint(0, m["vocab_size"], (B, L), generator=torch.Generator().manual_seed(cfg["seed"]))
+    from .io import checkpoint as ckpt
+
+    def engine(lc, weights, quantised):
+        """generate.target_int4 / draft_int4: an engine file written by LlamaInt4Engine.save (one process only);
+        generate.target_weights / draft_weights: a COG1 file of the full-precision model (save_model), quantised
+        here; neither: random weights (a timing run)."""
+        if quantised:
+            if world > 1:
+                raise SystemExit("an INT4 engine file holds one rank's unsplit engine: run one process, or give the full-precision weights")
+            return LlamaInt4Engine.load(quantised, lc, B, device=dev, max_seq_len=L + new + 16)
+        model = Llama(lc, device=dev, dtype=dtype)
+        if weights:
+            ckpt.load_model(weights, model)
+        return LlamaInt4Engine(model, B, L + new + 16, tp_group=group)
+
+    target = engine(tc, g.get("target_weights"), g.get("target_int4"))
+    draft = engine(dc, g.get("draft_weights"), g.get("draft_int4"))
+    if g.get("save_int4") and world == 1:                        # write the quantised engines for later runs
+        target.save(g["save_int4"] + ".target.cog")
+        draft.save(g["save_int4"] + ".draft.cog")
     dec = SpeculativeDecoder(draft, target, gamma=g.get("gamma", 4), temperature=g.get("temperature", 0.8), top_k=g.get("top_k", 50),
                              top_p=g.get("top_p", 0.9), seed=cfg["seed"])
-    prompts = torch.randint(0, m["vocab_size"], (B, L), generator=torch.Generator().manual_seed(cfg["seed"])).to(dev)
+    prompts = prompts.to(dev)
     t0 = time.time()
     seqs, stats = dec.generate(prompts, new)
     dt = time.time() - t0
     out = {"generated": stats.generated, "steps": stats.steps, "acceptance_rate": round(stats.acceptance_rate, 4),
            "tok_per_s": round(stats.generated / dt, 1), "tp": world}
     if rank == 0:
+        if g.get("out"):                                         # the generated sequences (prompt + new tokens)
+            with open(g["out"], "w") as f:
+                json.dump([[int(v) for v in row] for row in (seqs.tolist() if torch.is_tensor(seqs) else seqs)], f)
         print(json.dumps(out))
     if world > 1:
         dec.close()

@@ -386,3 +386,25 @@ def test_cli_data_parallel_checkpoints_resume_exactly_and_on_a_smaller_group(tmp
     fewer = run(2, 6, ck, "checkpoint.resume=true")                                       # one rank fewer: shards re-cut
     assert sorted(fewer) == [5, 6] and all(4.5 < v < 6.5 for v in fewer.values())
     assert sorted(f for f in os.listdir(tmp_path / "ck") if "of" in f) == [f"dp.opt.dp0{r}of02.state" for r in range(2)]
+
+
+def test_cli_generate_from_saved_weights_prompts_and_int4_engine_files(tmp_path):
+    import cogito_b200 as cg
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = os.path.join(root, "configs", "spec_decode_int4.yaml")
+    shape = dict(vocab_size=512, d_model=128, n_head=4, n_kv_head=2, d_ff=256, max_seq_len=128)
+    over = ["device=cpu"] + [f"model.{k}={v}" for k, v in shape.items()] + ["model.n_layer=2", "generate.batch=2", "generate.new_tokens=8",
+                                                                                  "generate.draft_layers=1"]
+    cg.manual_seed(0)
+    target, draft = cg.Llama(cg.LlamaConfig(n_layer=2, **shape)), cg.Llama(cg.LlamaConfig(n_layer=1, **shape))
+    cg.save_model(str(tmp_path / "t.cog"), target)
+    cg.save_model(str(tmp_path / "d.cog"), draft)
+    (tmp_path / "p.json").write_text(json.dumps([[1, 2, 3, 4, 5], [6, 7, 8, 9, 10]]))
+    common = [f"generate.prompts={tmp_path}/p.json"]
+    a = cli_main(["generate", cfg] + over + common + [f"generate.target_weights={tmp_path}/t.cog", f"generate.draft_weights={tmp_path}/d.cog",
+                                                       f"generate.out={tmp_path}/a.json", f"generate.save_int4={tmp_path}/eng"])
+    b = cli_main(["generate", cfg] + over + common + [f"generate.target_int4={tmp_path}/eng.target.cog", f"generate.draft_int4={tmp_path}/eng.draft.cog",
+                                                       f"generate.out={tmp_path}/b.json"])
+    sa, sb = json.load(open(tmp_path / "a.json")), json.load(open(tmp_path / "b.json"))
+    assert sa == sb and a["generated"] == b["generated"]                     # the engine files hold exactly what was quantised
+    assert [s[:5] for s in sa] == [[1, 2, 3, 4, 5], [6, 7, 8, 9, 10]] and all(len(s) >= 5 + 8 for s in sa)
