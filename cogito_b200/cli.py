@@ -35,7 +35,7 @@ DEFAULTS = {
     "train": {"steps": 10, "batch": 8, "micro_batch": None, "seq_len": 1024, "lr": 3e-4, "weight_decay": 0.0,
               "max_grad_norm": 1.0, "loss_scale": 65536.0, "optimizer": "adam"},
     "data": {"kind": "synthetic", "images": None, "labels": None},
-    "checkpoint": {"dir": None, "every": 0, "resume": False},
+    "checkpoint": {"dir": None, "every": 0, "resume": False, "init_from": None},   # init_from: COG1 file of the model (cg_save_model / save_model)
     # multi-rank jobs: heartbeats in the job's store, checked before every step; a rank that stopped answering ends
     # the run with exit code 3 (restart it with checkpoint.resume=true); device_check_every n reads the kernels'
     # status word every n steps (a bounded device-side wait that ran out)
@@ -211,6 +211,13 @@ def cmd_train(cfg):
                 json.dump({"step": int(at_step), "lr": float(opt.lr), "ranks": world}, f)
         dist.barrier()                                        # the set is complete before anyone moves on
 
+    if ck["init_from"]:
+        if p["tp"] > 1 or p["pp"] > 1:
+            raise SystemExit("checkpoint.init_from takes a whole-model file: shard it with parallel.tensor_parallel.shard_gpt2_state / "
+                             "parallel.llama_parallel.shard_llama_state for tensor- or pipeline-parallel runs")
+        ckpt.load_model(ck["init_from"], model)
+        if hasattr(opt, "refresh_master"):
+            opt.refresh_master()                              # fp32 master copies follow the loaded weights
     if ck["dir"]:
         os.makedirs(ck["dir"], exist_ok=True)
         base = os.path.join(ck["dir"], f"rank{rank:03d}")

@@ -408,3 +408,17 @@ def test_cli_generate_from_saved_weights_prompts_and_int4_engine_files(tmp_path)
     sa, sb = json.load(open(tmp_path / "a.json")), json.load(open(tmp_path / "b.json"))
     assert sa == sb and a["generated"] == b["generated"]                     # the engine files hold exactly what was quantised
     assert [s[:5] for s in sa] == [[1, 2, 3, 4, 5], [6, 7, 8, 9, 10]] and all(len(s) >= 5 + 8 for s in sa)
+
+
+def test_cli_starts_training_from_a_model_file(tmp_path):
+    import cogito_b200 as cg
+    from cogito_b200.data.datasets import SyntheticTokens
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = os.path.join(root, "configs", "tiny_cpu.yaml")
+    cli_main(["train", cfg, "train.steps=3", f"checkpoint.dir={tmp_path}/ck"])
+    got = cli_main(["train", cfg, "train.steps=1", "train.lr=0.0", f"checkpoint.init_from={tmp_path}/ck/rank000.cog"])
+    cg.manual_seed(0)
+    model = cg.GPT2(cg.GPT2Config(vocab_size=256, n_layer=2, d_model=64, n_head=4, d_ff=128, max_seq_len=64))
+    cg.load_model(str(tmp_path / "ck" / "rank000.cog"), model)
+    x, y = next(iter(SyntheticTokens(256, 4, 32, 1, seed=0)))
+    assert got == pytest.approx(float(model(x, y)), rel=1e-5)
