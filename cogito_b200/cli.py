@@ -33,7 +33,10 @@ DEFAULTS = {
               "in_channels": 1, "image": 28, "channels": [16, 32]},
     "parallel": {"dp": 1, "tp": 1, "pp": 1, "microbatches": 1, "virtual_stages": 1},
     "train": {"steps": 10, "batch": 8, "micro_batch": None, "seq_len": 1024, "lr": 3e-4, "weight_decay": 0.0,
-              "max_grad_norm": 1.0, "loss_scale": 65536.0, "optimizer": "adam"},
+              "max_grad_norm": 1.0, "loss_scale": 65536.0, "optimizer": "adam",
+              # learning-rate schedule of the reference's optimizers: "step" multiplies by gamma every step_size steps,
+              # "exp" sets lr * gamma^step
+              "schedule": {"kind": None, "step_size": 100, "gamma": 0.5}},
     "data": {"kind": "synthetic", "images": None, "labels": None},
     "checkpoint": {"dir": None, "every": 0, "resume": False, "init_from": None},   # init_from: COG1 file of the model (cg_save_model / save_model)
     # multi-rank jobs: heartbeats in the job's store, checked before every step; a rank that stopped answering ends
@@ -82,7 +85,7 @@ def _device(cfg):
 def cmd_train(cfg):
     from .data.datasets import BatchIterator, SyntheticTokens, load_mnist
     from .io import checkpoint as ckpt
-    from .optim.fused import FusedAdam, FusedSGD, GradScaler
+    from .optim.fused import FusedAdam, FusedSGD, GradScaler, exp_lr, step_lr
     from .train import Trainer
     from .utils import rng
     from .utils.profiler import Profiler, instrument
@@ -234,6 +237,9 @@ def cmd_train(cfg):
         instrument(model, prof)
     log_f = open(cfg["log"]["path"], "a") if (cfg["log"]["path"] and logger) else None
     step, last = start, None
+    sched = t["schedule"]
+    if sched["kind"] == "exp" and start:
+        exp_lr(opt, t["lr"], float(sched["gamma"]), start)
     fcfg, hb, failed = cfg["failure"], None, None
     if world > 1 and fcfg["heartbeat"]:
         from .utils.failure import Heartbeat, RankFailure, check_device
@@ -259,11 +265,17 @@ def cmd_train(cfg):
                 failed = e
                 break
         step += 1
+        if sched["kind"] == "step":
+            step_lr(opt, step, int(sched["step_size"]), float(sched["gamma"]))
+        elif sched["kind"] == "exp":
+            exp_lr(opt, t["lr"], float(sched["gamma"]), step)
+        elif sched["kind"] is not None:
+            raise SystemExit(f"unknown train.schedule.kind {sched['kind']}")
         prof.step_end()
         if loss is not None and step % cfg["log"]["every"] == 0:
             last = float(loss)                                   # waits for the step
             now = time.time()
-            rec = {"step": step, "loss": last, "elapsed_s": round(now - t0, 3)}
+            rec = {"step": step, "loss": last, "lr": float(opt.lr), "elapsed_s": round(now - t0, 3)}
             if t_mark is not None and now > t_mark:
                 rec["per_s"] = round(units_per_step * (step - step_mark) / (now - t_mark), 1)      # tokens (samples for MLP / CNN) over the whole job
             t_mark, step_mark = now, step

@@ -422,3 +422,13 @@ def test_cli_starts_training_from_a_model_file(tmp_path):
     cg.load_model(str(tmp_path / "ck" / "rank000.cog"), model)
     x, y = next(iter(SyntheticTokens(256, 4, 32, 1, seed=0)))
     assert got == pytest.approx(float(model(x, y)), rel=1e-5)
+
+
+def test_cli_learning_rate_schedules(tmp_path):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = os.path.join(root, "configs", "tiny_cpu.yaml")
+    cli_main(["train", cfg, "train.steps=4", "train.lr=0.01", "train.schedule.kind=step", "train.schedule.step_size=2", "train.schedule.gamma=0.5",
+              f"log.path={tmp_path}/a.jsonl"])
+    assert [json.loads(l)["lr"] for l in open(tmp_path / "a.jsonl")] == pytest.approx([0.01, 0.005, 0.005, 0.0025])
+    cli_main(["train", cfg, "train.steps=3", "train.lr=0.01", "train.schedule.kind=exp", "train.schedule.gamma=0.9", f"log.path={tmp_path}/b.jsonl"])
+    assert [json.loads(l)["lr"] for l in open(tmp_path / "b.jsonl")] == pytest.approx([0.009, 0.0081, 0.00729])
