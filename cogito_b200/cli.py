@@ -1,15 +1,18 @@
-"""Command line: ``python -m cogito_b200 <command> [--config file.yaml] [key=value ...]``.
+"""Command line: ``python -m cogito_b200 <command> [config.yaml] [key=value ...]``.
 
-    train     run a training job described by a YAML config (see ``DEFAULTS``)
-    generate  INT4 speculative decoding with a draft/target pair
-    bench     forwards to bench.py's job (same flags)
+    train     run a training job described by a YAML config (see ``DEFAULTS``): GPT-2, Llama, MLP or
+              convolutional classifier; data / tensor / pipeline / 3-D parallel under a launcher
+    generate  INT4 speculative decoding with a draft / target pair (tensor parallel under a launcher)
     info      versions, device, library status
 
-A config is a nested mapping; ``key.sub=value`` arguments override it.  Under torchrun the job
-is multi-rank: ``parallel: {dp, tp, pp}`` must multiply to the world size.
+A config is a nested mapping; ``section.key=value`` arguments override it (``train.steps=20``,
+``train.schedule.kind=step``).  Sections: ``model``, ``parallel``, ``train``, ``data``, ``checkpoint``
+(``dir``, ``every``, ``resume``, ``init_from``), ``failure`` (heartbeats), ``log``, ``profile``,
+``generate``.  Under torchrun the job is multi-rank: ``parallel: {dp, tp, pp}`` must multiply to the
+world size.
 
 The reference has no configuration layer: its examples hard-code sizes and hyper-parameters
-(examples/xor_example.c, examples/mnist_example.c) and the Makefile is the only switchboard.
+(examples/xor.c, examples/mnist.c) and the CMake options are the only switchboard.
 """
 from __future__ import annotations
 

@@ -5,7 +5,7 @@ copies them to the device on a side stream.
 Reference counterparts: cg_mnist_load / cg_mnist_get_batch / cg_labels_to_onehot /
 augmentations / cg_data_iter_* (include/cg_datasets.h:17-78, src/datasets/mnist.c), and
 cg_dataloader_* / cg_tensor_onehot / cg_tensor_argmax / cg_compute_accuracy
-(src/datasets/dataloader.c).
+(src/utils/dataloader.c).
 """
 from __future__ import annotations
 

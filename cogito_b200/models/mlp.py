@@ -1,6 +1,6 @@
 """MLP classifier: Linear -> ReLU -> ... -> Linear with cross-entropy, the MNIST-shaped
 data-parallel workload (784 -> 512 -> 512 -> 10) and the XOR network (2 -> 4 -> 1 with a
-sigmoid and MSE).  Reference: examples/mnist_example.c, examples/xor_example.c.
+sigmoid and MSE).  Reference: examples/mnist.c, examples/xor.c.
 
 On CUDA every Linear + activation is one tcgen05 GEMM with the bias and activation in its
 epilogue; the loss is the fused softmax-cross-entropy kernel.

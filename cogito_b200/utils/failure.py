@@ -13,8 +13,10 @@ Recovery: ``run_with_restarts`` calls the training function; on ``RankFailure`` 
 tear the process group down, agree on the new world through the store, re-initialise and call
 the function again, which resumes from the last checkpoint (see ``io.checkpoint``).
 
-The reference has no failure handling (errors are printed and ignored, src/core/error.c);
-its only related surface is CG_ERROR_TIMEOUT (include/cg_error.h).
+The reference has no failure handling: the results of its NCCL calls are ignored
+(src/pipeline/pipeline.c:111,126, src/pipeline/tensor_parallel.c:68,100), CUDA errors are turned
+into a string and the function returns (src/cuda/cg_cuda.c:33-49), and its error enumeration
+(include/cogito.h:47-53) has no code for a timeout.
 """
 from __future__ import annotations
 

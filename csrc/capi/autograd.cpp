@@ -1,7 +1,7 @@
 // One reverse-mode tape for the whole C API: functional ops, the cg_graph_* registry and
 // the gradient checker.  Reference surface: include/cg_tensor.h:165-195 (cg_backward),
-// src/autograd/engine.c (functional ops), src/autograd/graph.c (cg_graph_*),
-// src/autograd/grad_check.c.
+// src/core/autograd.c (functional ops), src/core/graph.c (cg_graph_*),
+// src/utils/grad_check.c.
 #include <algorithm>
 #include <cstdint>
 
@@ -223,7 +223,7 @@ CG_EXPORT void cg_backward(cg_tensor* loss) {
 }
 
 // ---------------------------------------------------------- graph registry
-// The reference keeps a second, global graph (src/autograd/graph.c).  Here it is a
+// The reference keeps a second, global graph (src/core/graph.c).  Here it is a
 // registry over the same tape: while active, every tensor made by cg_graph_* is owned by
 // the registry and released by cg_graph_reset, so callers need not free intermediates.
 namespace {

@@ -1,6 +1,6 @@
 // Errors, arena, tensor storage and the eager tensor ops of the C API.
 // Reference surface: include/cg_tensor.h, include/cg_arena.h, src/core/tensor.c,
-// src/core/tensor_ops.c, src/core/arena.c, src/core/error.c.
+// src/core/tensor_ops.c, src/utils/arena.c; error strings: src/core/tensor.c:443.
 #include <algorithm>
 #include <atomic>
 

@@ -1,6 +1,6 @@
 /* XOR with the C API: Linear(2,4) -> ReLU -> Linear(4,1) -> Sigmoid, MSE, SGD lr 0.5 momentum 0.9.
  * Build:  cc -std=c11 -Iinclude examples/xor.c -Lcogito_b200/lib -lcogito -lm -o xor
- * Counterpart of the reference's examples/xor_example.c. */
+ * Counterpart of the reference's examples/xor.c. */
 #include <stdio.h>
 #include <stdlib.h>
 
