@@ -294,7 +294,7 @@ CG_EXPORT void cg_cuda_stream_synchronize(void* stream_) {
 
 // One thread per element up to a grid that fills the machine a few times over; the kernels
 // iterate with a grid-stride loop, so the cap loses no elements (the reference caps at 65 535
-// blocks without such a loop, src/cuda/cg_cuda.c:507-520).
+// blocks without such a loop, src/cuda/cg_cuda.c:355-363).
 CG_EXPORT void cg_cuda_calculate_launch_dims(int n, int* grid, int* block) {
   const int b = 256;
   long long g = ((long long)(n > 0 ? n : 1) + b - 1) / b;
