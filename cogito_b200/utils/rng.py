@@ -1,7 +1,8 @@
 """Seeding.  Every layer draws its initial weights from a stream of its own,
 derived from the global seed and the layer's construction index, so equal-shaped
-layers start different (the reference reseeds with 42 inside every constructor,
-src/layers/linear.c:27-34 and src/layers/conv2d.c, which makes them identical) and
+layers start different (the reference seeds with 42 inside every constructor:
+``srand(42)`` in src/layers/linear.c:213, ``cg_tensor_randn(..., 42, ...)`` in
+src/layers/conv2d.c:292, which makes equal-shaped layers identical) and
 a model's initial weights depend only on the seed and the construction order."""
 from __future__ import annotations
 
