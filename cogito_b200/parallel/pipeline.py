@@ -2,8 +2,8 @@
 
 ``one_f_one_b`` generates one stage's program (S-1-stage warm-up forwards, steady
 one-forward/one-backward, cool-down backwards), the same program as
-``cg_pipeline_gen_1f1b_stage`` of the host library (reference: cg_schedule_action /
-cg_schedule_step / cg_pipeline_gen_1f1b, include/cg_pipeline.h:27-40,78-93; the reference
+``cg_pipeline_gen_1f1b_stage`` of the host library (reference: cg_schedule_op /
+cg_schedule_step / cg_pipeline_gen_1f1b, include/cg_pipeline.h:121-142; the reference
 generator only produces stage 0 and its executor ``cg_pipeline_forward_backward`` is declared
 only, src/pipeline/pipeline.c).
 
@@ -19,7 +19,8 @@ from dataclasses import dataclass
 import torch
 import torch.distributed as dist
 
-FORWARD, BACKWARD, SEND_FWD, RECV_FWD, SEND_BWD, RECV_BWD, OPTIMIZER = range(7)
+# the numbering of cg_schedule_op (include/cogito_ext.h): WAIT and SYNC are the reference's, unused by these generators
+FORWARD, BACKWARD, SEND_FWD, RECV_FWD, SEND_BWD, RECV_BWD, WAIT, SYNC, OPTIMIZER = range(9)
 
 
 @dataclass(frozen=True)

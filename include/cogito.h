@@ -191,7 +191,11 @@ int cg_sequential_num_params(cg_sequential* seq);
 cg_tensor** cg_sequential_get_params(cg_sequential* seq);
 
 typedef struct {
-  int hidden_size, num_heads, num_kv_heads, head_dim, intermediate_size;
+  /* hidden_dim / intermediate_dim are the reference's names (include/cg_transformer.h:19-34); hidden_size /
+   * intermediate_size name the same two fields */
+  union { int hidden_dim; int hidden_size; };
+  int num_heads, num_kv_heads, head_dim;
+  union { int intermediate_dim; int intermediate_size; };
   float norm_eps, dropout_prob;
   bool use_bias, pre_norm, use_rms_norm, use_swiglu;
 } cg_transformer_config;

@@ -78,7 +78,9 @@ void cg_calibration_compute_scales(cg_quant_calibration* calib, float* scales, f
 void cg_calibration_free(cg_quant_calibration* calib);
 
 /* -------------------------------------------------------------- attention */
-typedef enum { CG_MASK_NONE = 0, CG_MASK_CAUSAL = 1, CG_MASK_SLIDING_WINDOW = 2, CG_MASK_CUSTOM = 3 } cg_attention_mask_type;
+/* ATTN_MASK_* are the reference's enumerators (include/cg_flash_attn.h:40-45); CG_MASK_* name the same values */
+typedef enum { ATTN_MASK_NONE = 0, ATTN_MASK_CAUSAL = 1, ATTN_MASK_SLIDING_WINDOW = 2, ATTN_MASK_CUSTOM = 3,
+               CG_MASK_NONE = 0, CG_MASK_CAUSAL = 1, CG_MASK_SLIDING_WINDOW = 2, CG_MASK_CUSTOM = 3 } cg_attention_mask_type;
 typedef struct { int block_m, block_n, num_warps, num_stages; bool use_register_tiling; int split_k; } cg_flash_attn_config;
 typedef struct {
   cg_tensor* Q; cg_tensor* K; cg_tensor* V; cg_tensor* O;        /* [batch, seq, heads, d_head] */
@@ -150,6 +152,9 @@ typedef struct {
   float temperature, top_p; int top_k;
   int total_draft_tokens, accepted_draft_tokens, num_steps; float avg_acceptance_rate;
   cg_logits_fn draft_fn; cg_logits_fn target_fn; int vocab_size; unsigned int rng_state;
+  /* reference fields (include/cg_speculative.h:37-50), kept so that code written against it compiles: the reference
+   * sets accept_threshold to 0 and reads none of the four (src/inference/speculative.c:40); neither does this library */
+  float accept_threshold; bool use_typical_sampling; void* draft_kv_cache; void* target_kv_cache;
 } cg_speculative_decoder;
 typedef struct { void* base_draft; int max_branch; int* branching; } cg_eagle_draft;
 cg_speculative_decoder* cg_speculative_decoder_new(void* draft_model, void* target_model, int gamma);
@@ -181,22 +186,35 @@ int cg_sample_corrected(float* draft_probs, float* target_probs, int vocab_size)
 
 /* ---------------------------------------------------- parallel schedules */
 typedef enum { PARALLEL_DATA, PARALLEL_TENSOR, PARALLEL_PIPELINE } cg_parallel_mode;
+/* cg_schedule_op with its eight operations and the `op` field are the reference's (include/cg_pipeline.h:121-136);
+ * SCHEDULE_OPTIMIZER closes a rank's program here, and `action` / cg_schedule_action name the same field and type. */
 typedef enum { SCHEDULE_FORWARD = 0, SCHEDULE_BACKWARD, SCHEDULE_SEND_FWD, SCHEDULE_RECV_FWD,
-               SCHEDULE_SEND_BWD, SCHEDULE_RECV_BWD, SCHEDULE_OPTIMIZER } cg_schedule_action;
-typedef struct { cg_schedule_action action; int microbatch_id; int stage_id; } cg_schedule_step;
+               SCHEDULE_SEND_BWD, SCHEDULE_RECV_BWD, SCHEDULE_WAIT, SCHEDULE_SYNC, SCHEDULE_OPTIMIZER } cg_schedule_op;
+typedef cg_schedule_op cg_schedule_action;
+typedef struct { union { cg_schedule_op op; cg_schedule_op action; }; int microbatch_id; int stage_id; } cg_schedule_step;
 typedef struct { cg_parallel_mode mode; int world_size; int rank; int* ranks; void* comm; void* stream; } cg_distributed_group;
-typedef struct { int stage_id; void* layers; int num_layers; } cg_pipeline_stage;
+/* The double-buffer and event fields are the reference's (include/cg_pipeline.h:33-58); the in-process executor of this
+ * library keeps its buffers in `impl` of the pipeline and leaves them null. */
+typedef struct {
+  int stage_id; void* layers; int num_layers;
+  cg_tensor** send_buffers_a; cg_tensor** send_buffers_b; cg_tensor** recv_buffers_a; cg_tensor** recv_buffers_b;
+  cg_tensor** grad_send_a; cg_tensor** grad_send_b; cg_tensor** grad_recv_a; cg_tensor** grad_recv_b;
+  void* compute_event; void* comm_stream; void* send_event_a; void* send_event_b; void* recv_event_a; void* recv_event_b;
+} cg_pipeline_stage;
 typedef struct {
   int num_stages, micro_batch_size, num_microbatches, global_batch_size;
-  cg_pipeline_stage* stages; cg_schedule_step* schedule; int schedule_len;
+  cg_pipeline_stage* stages; cg_schedule_step* schedule;
+  union { int schedule_len; int schedule_length; };              /* schedule_length: the reference's name */
   cg_distributed_group* pp_group; cg_distributed_group* dp_group;
   bool use_recompute; void* activation_cache;
   float last_loss; void* impl;
+  cg_distributed_group* tp_group; int local_stage_id;            /* reference fields (include/cg_pipeline.h:72-77) */
 } cg_pipeline_parallel;
 typedef struct { cg_distributed_group* group; int shard_dim; bool input_is_parallel; bool output_is_parallel; } cg_tensor_parallel_linear;
 typedef struct {
   int dp_size, tp_size, pp_size; int dp_rank, tp_rank, pp_rank; int world_size, world_rank;
   cg_distributed_group* dp_group; cg_distributed_group* tp_group; cg_distributed_group* pp_group;
+  cg_pipeline_parallel* pipeline;                                /* reference field (include/cg_pipeline.h:200) */
 } cg_3d_parallel;
 cg_pipeline_parallel* cg_pipeline_new(int num_stages, int num_microbatches);
 void cg_pipeline_set_stage(cg_pipeline_parallel* pp, int stage_id, void* layers, int num_layers);   /* layers: cg_sequential* */
@@ -221,7 +239,10 @@ void cg_3d_parallel_init_from_world(cg_3d_parallel* ctx, int world_size, int wor
 void cg_3d_parallel_free(cg_3d_parallel* ctx);
 
 /* ---------------------------------------------------------------- memory */
-typedef enum { CG_ARENA_DEVICE = 0, CG_ARENA_HOST = 1 } cg_arena_type;
+/* The reference's four arenas (include/cg_memory.h:48-53) all live in the device pool here; CG_ARENA_HOST
+ * selects the pinned-host pool of the planner. */
+typedef enum { CG_ARENA_DEFAULT = 0, CG_ARENA_PARAM, CG_ARENA_ACTIVATION, CG_ARENA_GRADIENT,
+               CG_ARENA_DEVICE = 0, CG_ARENA_HOST = 4 } cg_arena_type;
 typedef struct cg_memory_pool cg_memory_pool;
 typedef struct cg_buddy_allocator cg_buddy_allocator;
 typedef struct cg_memory_planner cg_memory_planner;

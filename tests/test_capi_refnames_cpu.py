@@ -257,3 +257,48 @@ def test_conv2d_shape_inference_and_guards_check():
     lib.cg_shape_specialization_free(spec)
     lib.cg_shape_free(o)
     lib.cg_shape_free(s)
+
+
+def test_reference_field_and_enumerator_names_compile_as_c11(tmp_path):
+    """Code written against the reference's headers uses these names; they must exist here with the same meaning."""
+    import shutil
+    import subprocess
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    src = tmp_path / "names.c"
+    src.write_text(r'''
+#include <stdio.h>
+#include "cogito.h"
+int main(void) {
+  cg_transformer_config cfg = {0};
+  cfg.hidden_dim = 64; cfg.intermediate_dim = 256;                       /* include/cg_transformer.h */
+  if (cfg.hidden_size != 64 || cfg.intermediate_size != 256) return 1;
+  cg_attention_mask_type m = ATTN_MASK_SLIDING_WINDOW;                   /* include/cg_flash_attn.h */
+  if (m != CG_MASK_SLIDING_WINDOW || ATTN_MASK_CAUSAL != 1 || ATTN_MASK_CUSTOM != 3) return 2;
+  cg_arena_type a = CG_ARENA_GRADIENT;                                   /* include/cg_memory.h */
+  if (CG_ARENA_DEFAULT != 0 || a != 3 || CG_ARENA_PARAM != 1 || CG_ARENA_ACTIVATION != 2) return 3;
+  cg_schedule_step st = {0};                                             /* include/cg_pipeline.h */
+  st.op = SCHEDULE_RECV_BWD;
+  cg_schedule_op op = st.op;
+  if (st.action != SCHEDULE_RECV_BWD || op != 5 || SCHEDULE_WAIT != 6 || SCHEDULE_SYNC != 7) return 4;
+  cg_pipeline_parallel pp = {0};
+  pp.schedule_length = 7; pp.tp_group = NULL; pp.local_stage_id = 1;
+  if (pp.schedule_len != 7) return 5;
+  cg_pipeline_stage stage = {0};
+  stage.send_buffers_a = NULL; stage.grad_recv_b = NULL; stage.comm_stream = NULL; stage.recv_event_b = NULL;
+  cg_3d_parallel ctx = {0};
+  ctx.pipeline = &pp;
+  cg_speculative_decoder dec = {0};
+  dec.accept_threshold = 0.0f; dec.use_typical_sampling = false; dec.draft_kv_cache = NULL; dec.target_kv_cache = NULL;
+  cg_tensor_parallel_linear tp = {0};
+  tp.input_is_parallel = 1; tp.output_is_parallel = 0; tp.shard_dim = 1;
+  (void)stage; (void)ctx; (void)dec; (void)tp;
+  printf("ok\n");
+  return 0;
+}
+''')
+    cc = shutil.which("gcc") or shutil.which("cc")
+    exe = tmp_path / "names"
+    p = subprocess.run([cc, "-std=c11", "-Wall", "-Werror", "-I", str(root / "include"), str(src), "-o", str(exe)], capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr
+    assert subprocess.run([str(exe)], capture_output=True, text=True).stdout.strip() == "ok"

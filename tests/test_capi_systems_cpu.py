@@ -248,7 +248,7 @@ def test_token_tree_mask_and_eagle_tree():
 
 
 # ---------------------------------------------------------------------- pipeline
-FWD, BWD, SEND_F, RECV_F, SEND_B, RECV_B, OPT = range(7)
+FWD, BWD, SEND_F, RECV_F, SEND_B, RECV_B, WAIT, SYNC, OPT = range(9)          # cg_schedule_op
 
 
 @pytest.mark.parametrize("S,M", [(1, 1), (2, 4), (4, 8), (4, 2), (8, 8)])
