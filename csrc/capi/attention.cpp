@@ -148,9 +148,11 @@ CG_EXPORT void cg_flash_attn_params_free(cg_flash_attn_params* p) {
 // Tile shapes of the sm_100a kernels: two 128-row query tiles per CTA against 128-key tiles,
 // a 4-deep (d<=64) or 3-deep K/V ring; short-query decode splits the keys over the SMs.
 CG_EXPORT cg_flash_attn_config cg_flash_attn_autotune(int tq, int tk, int d, int sm_count) {
-  cg_flash_attn_config c;
+  cg_flash_attn_config c{};
   c.block_m = tq >= 256 ? 256 : 128; c.block_n = 128; c.num_warps = 12;
   c.num_stages = d <= 64 ? 4 : 3; c.use_register_tiling = true; c.split_k = 1;
+  c.sm_count = sm_count;
+  c.use_persistent = sm_count > 0 && (tq + c.block_m - 1) / c.block_m > sm_count;
   if (tq <= 16 && sm_count > 0) {
     const int tiles = (tk + c.block_n - 1) / c.block_n;
     int split = tiles < sm_count ? tiles : sm_count;

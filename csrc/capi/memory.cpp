@@ -304,9 +304,15 @@ CG_EXPORT cg_memory_stats cg_memory_get_stats(cg_memory_planner* p) {
   for (cg_memory_pool* q : p->pools) {
     s.total_allocated += q->st.total_allocated; s.total_cached += q->st.total_cached; s.peak_allocated += q->st.peak_allocated;
     s.num_allocs += q->st.num_allocs; s.num_frees += q->st.num_frees; s.cache_hits += q->st.cache_hits; s.cache_misses += q->st.cache_misses;
+    for (const auto& l : q->free_list) s.num_bins_used += l.empty() ? 0 : 1;
+    for (const auto& l : q->sub_free) s.num_bins_used += l.empty() ? 0 : 1;
   }
   const double all = (double)s.total_allocated + (double)s.total_cached;
   s.fragmentation = all > 0 ? (float)(s.total_cached / all) : 0.0f;
+  s.total_in_use = s.total_allocated;
+  s.peak_usage = s.peak_allocated;
+  const long long req = (long long)s.cache_hits + s.cache_misses;
+  s.cache_hit_rate = req > 0 ? (size_t)(100LL * s.cache_hits / req) : 0;
   return s;
 }
 CG_EXPORT void cg_memory_print_stats(cg_memory_planner* p) {

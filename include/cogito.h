@@ -154,7 +154,9 @@ typedef struct { cg_layer base; } cg_softmax;
 typedef struct { cg_layer base; float p; bool training; cg_tensor* mask; } cg_dropout;
 typedef struct {
   cg_layer base; int num_features; float epsilon; float momentum;
-  cg_tensor* running_mean; cg_tensor* running_var; cg_tensor* x_norm; cg_tensor* std_inv;
+  cg_tensor* running_mean; cg_tensor* running_var;
+  union { cg_tensor* x_norm; cg_tensor* input_normalized; };    /* input_normalized: the reference's name */
+  cg_tensor* std_inv;
   bool training; cg_tensor* param_ptrs[2];
 } cg_batchnorm;
 typedef struct { cg_layer base; int normalized_shape; float epsilon; cg_tensor* inv_rms; cg_tensor* param_ptrs[1]; } cg_rmsnorm;
@@ -202,8 +204,11 @@ typedef struct {
 typedef struct {
   cg_layer base; cg_transformer_config config;
   cg_layer* norm1; cg_layer* norm2;
-  cg_linear* q_proj; cg_linear* k_proj; cg_linear* v_proj; cg_linear* o_proj;
-  cg_linear* gate_proj; cg_linear* up_proj; cg_linear* down_proj;
+  /* attn_*_proj / mlp_* are the reference's names (include/cg_transformer.h); a cg_linear starts with its cg_layer */
+  union { cg_linear* q_proj; cg_layer* attn_q_proj; }; union { cg_linear* k_proj; cg_layer* attn_k_proj; };
+  union { cg_linear* v_proj; cg_layer* attn_v_proj; }; union { cg_linear* o_proj; cg_layer* attn_o_proj; };
+  union { cg_linear* gate_proj; cg_layer* mlp_gate; }; union { cg_linear* up_proj; cg_layer* mlp_up; };
+  union { cg_linear* down_proj; cg_layer* mlp_down; };
   cg_tensor** param_cache; int n_params;
 } cg_transformer_block;
 cg_transformer_block* cg_transformer_block_new(cg_transformer_config config);

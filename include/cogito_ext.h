@@ -22,10 +22,19 @@ typedef struct {
   int shape[CG_MAX_DIMS]; int ndim; int size; bool requires_grad;
 } cg_tensor_bf16;
 typedef struct {
-  cg_tensor** params; cg_tensor_bf16** model_params; int num_params;
-  float loss_scale, min_loss_scale, max_loss_scale, scale_factor; int scale_window, steps_since_overflow;
+  /* second names: the reference's (include/cg_bf16.h) */
+  union { cg_tensor** params; cg_tensor** master_params; };
+  cg_tensor_bf16** model_params; int num_params;
+  float loss_scale;
+  union { float min_loss_scale; float loss_scale_min; };
+  union { float max_loss_scale; float loss_scale_max; };
+  float scale_factor;
+  union { int scale_window; int scale_growth_interval; };
+  union { int steps_since_overflow; int steps_since_update; };
   bool found_overflow; float max_grad_norm; float learning_rate;
-  int num_skipped, num_steps;
+  union { int num_skipped; int overflow_count; };
+  int num_steps;
+  void* optimizer;              /* the caller's; cg_mp_step applies its own update rule */
 } cg_mixed_precision;
 cg_tensor_bf16* cg_tensor_bf16_new(int* shape, int ndim, bool requires_grad);
 cg_tensor_bf16* cg_tensor_bf16_from_fp32(cg_tensor* fp32);
@@ -56,7 +65,7 @@ typedef struct {
   uint8_t* k_cache; uint8_t* v_cache; float* k_scales; float* v_scales;
   int current_len, max_seq_len, num_layers, n_heads, head_dim, group_size;
 } cg_kv_cache_int4;
-typedef struct { float* min_vals; float* max_vals; float* abs_max; int channels; int num_samples; } cg_quant_calibration;
+typedef struct { float* min_vals; float* max_vals; union { float* abs_max; float* absmax; }; int channels; int num_samples; } cg_quant_calibration;
 cg_tensor_quant* cg_quantize_int4(cg_tensor* tensor, int group_size);
 cg_tensor_quant* cg_quantize_gptq(cg_tensor* tensor, cg_tensor* hessian, int group_size, int bits);
 cg_tensor_quant* cg_quantize_awq(cg_tensor* tensor, cg_tensor* activations, int group_size);
@@ -81,14 +90,24 @@ void cg_calibration_free(cg_quant_calibration* calib);
 /* ATTN_MASK_* are the reference's enumerators (include/cg_flash_attn.h:40-45); CG_MASK_* name the same values */
 typedef enum { ATTN_MASK_NONE = 0, ATTN_MASK_CAUSAL = 1, ATTN_MASK_SLIDING_WINDOW = 2, ATTN_MASK_CUSTOM = 3,
                CG_MASK_NONE = 0, CG_MASK_CAUSAL = 1, CG_MASK_SLIDING_WINDOW = 2, CG_MASK_CUSTOM = 3 } cg_attention_mask_type;
-typedef struct { int block_m, block_n, num_warps, num_stages; bool use_register_tiling; int split_k; } cg_flash_attn_config;
+/* use_register_tile, use_persistent and sm_count are the reference's names (include/cg_flash_attn.h:27-35) */
+typedef struct {
+  int block_m, block_n, num_warps, num_stages;
+  union { bool use_register_tiling; bool use_register_tile; };
+  int split_k;
+  bool use_persistent;          /* more query tiles than SMs: a CTA loops over tiles */
+  int sm_count;
+} cg_flash_attn_config;
 typedef struct {
   cg_tensor* Q; cg_tensor* K; cg_tensor* V; cg_tensor* O;        /* [batch, seq, heads, d_head] */
   cg_tensor* dO; cg_tensor* dQ; cg_tensor* dK; cg_tensor* dV;
   cg_tensor* L;                                                   /* logsumexp [batch, heads, seq] */
   cg_tensor* mask;
-  int batch_size, seqlen_q, seqlen_k, n_heads, n_kv_heads, d_head;
-  float softmax_scale, dropout_prob;
+  int batch_size, seqlen_q, seqlen_k, n_heads;
+  union { int n_kv_heads; int n_heads_k; };                      /* n_heads_k, scale: the reference's names */
+  int d_head;
+  union { float softmax_scale; float scale; };
+  float dropout_prob;
   cg_attention_mask_type mask_type; int window_size;
   float* alibi_slopes;
   cg_flash_attn_config config;
@@ -113,7 +132,7 @@ void cg_alibi_slopes(float* slopes, int n_heads);
 typedef struct { cg_tensor* images; cg_tensor* labels; int num_samples; int rows, cols; } cg_mnist;
 typedef struct {
   cg_tensor* data; cg_tensor* labels; int batch_size; bool shuffle; unsigned int seed;
-  int* indices; int position; int num_samples; cg_tensor* batch_data; cg_tensor* batch_labels;
+  int* indices; union { int position; int current_idx; }; int num_samples; cg_tensor* batch_data; cg_tensor* batch_labels;
 } cg_data_iter;
 typedef cg_data_iter cg_dataloader_state;
 typedef struct { cg_data_iter it; int epoch; } cg_dataloader;
@@ -156,7 +175,9 @@ typedef struct {
    * sets accept_threshold to 0 and reads none of the four (src/inference/speculative.c:40); neither does this library */
   float accept_threshold; bool use_typical_sampling; void* draft_kv_cache; void* target_kv_cache;
 } cg_speculative_decoder;
-typedef struct { void* base_draft; int max_branch; int* branching; } cg_eagle_draft;
+/* feature_proj, uncertainty_head and feature_cache are the reference's fields (include/cg_speculative.h); its EAGLE
+ * functions are declared only and nothing reads them there or here */
+typedef struct { void* base_draft; int max_branch; int* branching; void* feature_proj; void* uncertainty_head; float* feature_cache; } cg_eagle_draft;
 cg_speculative_decoder* cg_speculative_decoder_new(void* draft_model, void* target_model, int gamma);
 void cg_speculative_set_models(cg_speculative_decoder* d, cg_logits_fn draft_fn, cg_logits_fn target_fn, int vocab_size);
 cg_tensor* cg_speculative_generate(cg_speculative_decoder* decoder, cg_tensor* input_ids, int max_new_tokens,
@@ -249,6 +270,9 @@ typedef struct cg_memory_planner cg_memory_planner;
 typedef struct {
   size_t total_allocated, total_cached, peak_allocated; int num_allocs, num_frees, cache_hits, cache_misses;
   int buddy_splits, buddy_coalesces; float fragmentation;
+  /* the reference's names (include/cg_memory.h:303-310): bytes handed out, their peak, hits per 100 requests, size
+   * classes that hold cached blocks */
+  size_t total_in_use, peak_usage, cache_hit_rate; int num_bins_used;
 } cg_memory_stats;
 cg_memory_pool* cg_memory_pool_new(void);
 void* cg_pool_alloc(cg_memory_pool* pool, size_t size);

@@ -49,7 +49,7 @@ class KVCache(Structure):
 
 class FlashConfig(Structure):
     _fields_ = [("block_m", c_int), ("block_n", c_int), ("num_warps", c_int), ("num_stages", c_int),
-                ("use_register_tiling", c_bool), ("split_k", c_int)]
+                ("use_register_tiling", c_bool), ("split_k", c_int), ("use_persistent", c_bool), ("sm_count", c_int)]
 
 
 class FlashParams(Structure):
@@ -105,7 +105,8 @@ class SpecDecoder(Structure):
 class MemoryStats(Structure):
     _fields_ = [("total_allocated", c_size_t), ("total_cached", c_size_t), ("peak_allocated", c_size_t), ("num_allocs", c_int),
                 ("num_frees", c_int), ("cache_hits", c_int), ("cache_misses", c_int), ("buddy_splits", c_int),
-                ("buddy_coalesces", c_int), ("fragmentation", c_float)]
+                ("buddy_coalesces", c_int), ("fragmentation", c_float), ("total_in_use", c_size_t), ("peak_usage", c_size_t),
+                ("cache_hit_rate", c_size_t), ("num_bins_used", c_int)]
 
 
 class IrNode(Structure):

@@ -292,13 +292,38 @@ int main(void) {
   dec.accept_threshold = 0.0f; dec.use_typical_sampling = false; dec.draft_kv_cache = NULL; dec.target_kv_cache = NULL;
   cg_tensor_parallel_linear tp = {0};
   tp.input_is_parallel = 1; tp.output_is_parallel = 0; tp.shard_dim = 1;
-  (void)stage; (void)ctx; (void)dec; (void)tp;
+  cg_flash_attn_config fc = cg_flash_attn_autotune(4096, 4096, 128, 148);  /* include/cg_flash_attn.h */
+  if (fc.sm_count != 148 || fc.use_register_tile != fc.use_register_tiling || fc.use_persistent) return 6;
+  if (!cg_flash_attn_autotune(128 * 1024, 1024, 64, 148).use_persistent) return 7;
+  cg_flash_attn_params fp = {0};
+  fp.n_heads_k = 8; fp.scale = 0.125f;
+  if (fp.n_kv_heads != 8 || fp.softmax_scale != 0.125f) return 8;
+  cg_quant_calibration qc = {0}; qc.absmax = NULL;                         /* include/cg_quantize.h */
+  cg_data_iter it = {0}; it.current_idx = 3; if (it.position != 3) return 9;  /* include/cg_datasets.h */
+  cg_eagle_draft eg = {0}; eg.feature_proj = NULL; eg.uncertainty_head = NULL; eg.feature_cache = NULL;
+  cg_mixed_precision mp = {0};                                             /* include/cg_bf16.h */
+  mp.loss_scale_min = 1.0f; mp.loss_scale_max = 65536.0f; mp.scale_growth_interval = 2000; mp.steps_since_update = 0;
+  mp.overflow_count = 2; mp.master_params = NULL; mp.optimizer = NULL;
+  if (mp.min_loss_scale != 1.0f || mp.max_loss_scale != 65536.0f || mp.scale_window != 2000 || mp.num_skipped != 2) return 10;
+  cg_batchnorm bn; bn.input_normalized = NULL; if (bn.x_norm != NULL) return 11;          /* include/cg_layers.h */
+  cg_transformer_block blk; blk.attn_q_proj = NULL; blk.mlp_down = NULL;                   /* include/cg_transformer.h */
+  if (blk.q_proj != NULL || blk.down_proj != NULL) return 12;
+  cg_memory_pool* pool = cg_memory_pool_new();                                              /* include/cg_memory.h */
+  void* a1 = cg_pool_alloc(pool, 1000); cg_pool_free(pool, a1); void* a2 = cg_pool_alloc(pool, 1000);
+  cg_memory_planner* planner = cg_memory_planner_new();
+  cg_memory_stats ms = cg_memory_get_stats(planner);
+  if (ms.total_in_use != ms.total_allocated || ms.peak_usage != ms.peak_allocated || ms.cache_hit_rate > 100 || ms.num_bins_used < 0) return 13;
+  cg_pool_free(pool, a2);
+  (void)stage; (void)ctx; (void)dec; (void)tp; (void)qc; (void)eg;
   printf("ok\n");
   return 0;
 }
 ''')
     cc = shutil.which("gcc") or shutil.which("cc")
     exe = tmp_path / "names"
-    p = subprocess.run([cc, "-std=c11", "-Wall", "-Werror", "-I", str(root / "include"), str(src), "-o", str(exe)], capture_output=True, text=True)
+    lib = root / "cogito_b200" / "lib"
+    p = subprocess.run([cc, "-std=c11", "-Wall", "-Werror", "-I", str(root / "include"), str(src), "-L", str(lib), "-lcogito", "-lm",
+                        f"-Wl,-rpath,{lib}", "-o", str(exe)], capture_output=True, text=True)
     assert p.returncode == 0, p.stderr
-    assert subprocess.run([str(exe)], capture_output=True, text=True).stdout.strip() == "ok"
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout.strip() == "ok", (r.returncode, r.stdout, r.stderr)
