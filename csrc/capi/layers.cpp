@@ -404,7 +404,7 @@ static cg_tensor* conv2d_forward(cg_layer* L, cg_tensor* x) {
 }
 static void conv2d_free(cg_layer* L) { cg_conv2d* l = (cg_conv2d*)L; if (l->col_buffer) cg_tensor_release(l->col_buffer); plain_free(L); }
 static cg_tensor** conv2d_gp(cg_layer* L) { return ((cg_conv2d*)L)->param_ptrs; }
-CG_EXPORT cg_conv2d* cg_conv2d_new(int ic, int oc, int k, int stride, int padding) {
+CG_EXPORT cg_conv2d* cg_conv2d_new(int ic, int oc, int k, int stride, int padding, bool use_bias) {
   if (ic <= 0 || oc <= 0 || k <= 0 || stride <= 0 || padding < 0) return fail(CG_ERROR_INVALID_ARGUMENT, (cg_conv2d*)nullptr);
   auto* l = new_layer<cg_conv2d>("Conv2D");
   if (!l) return nullptr;
@@ -415,9 +415,9 @@ CG_EXPORT cg_conv2d* cg_conv2d_new(int ic, int oc, int k, int stride, int paddin
   const float std_ = std::sqrt(2.0f / (ic * k * k));            // Kaiming normal
   for (int i = 0; i < l->base.weights->size; ++i) l->base.weights->data[i] = rng.normal() * std_;
   int bs[1] = {oc};
-  l->base.bias = make(bs, 1, true);
+  l->base.bias = use_bias ? make(bs, 1, true) : nullptr;
   l->param_ptrs[0] = l->base.weights; l->param_ptrs[1] = l->base.bias;
-  finish(&l->base, conv2d_forward, conv2d_free, two_params, conv2d_gp);
+  finish(&l->base, conv2d_forward, conv2d_free, linear_np, conv2d_gp);       // one or two parameters, like Linear
   return l;
 }
 

@@ -20,7 +20,7 @@ CG_EXPORT cg_symbolic_expr* cg_expr_binary(cg_expr_type t, cg_symbolic_expr* l, 
   e->data.binary.left = l; e->data.binary.right = r;
   if (l->type == EXPR_CONST && r->type == EXPR_CONST) {
     int64_t v;
-    if (cg_expr_eval(e, nullptr, nullptr, 0, &v)) { cg_expr_free(e); return cg_expr_const(v); }
+    if (cg_expr_try_eval(e, nullptr, nullptr, 0, &v)) { cg_expr_free(e); return cg_expr_const(v); }
   }
   return e;
 }
@@ -37,7 +37,7 @@ static cg_symbolic_expr* expr_clone(const cg_symbolic_expr* e) {
   c->data.binary.left = expr_clone(e->data.binary.left); c->data.binary.right = expr_clone(e->data.binary.right);
   return c;
 }
-CG_EXPORT bool cg_expr_eval(cg_symbolic_expr* e, int64_t* vals, const char** names, int n, int64_t* out) {
+CG_EXPORT bool cg_expr_try_eval(cg_symbolic_expr* e, int64_t* vals, const char** names, int n, int64_t* out) {
   if (!e || !out) return false;
   if (e->type == EXPR_CONST) { *out = e->data.constant; return true; }
   if (e->type == EXPR_VAR) {
@@ -45,7 +45,7 @@ CG_EXPORT bool cg_expr_eval(cg_symbolic_expr* e, int64_t* vals, const char** nam
     return false;
   }
   int64_t a, b;
-  if (!cg_expr_eval(e->data.binary.left, vals, names, n, &a) || !cg_expr_eval(e->data.binary.right, vals, names, n, &b)) return false;
+  if (!cg_expr_try_eval(e->data.binary.left, vals, names, n, &a) || !cg_expr_try_eval(e->data.binary.right, vals, names, n, &b)) return false;
   switch (e->type) {
     case EXPR_ADD: *out = a + b; return true;
     case EXPR_SUB: *out = a - b; return true;
@@ -57,6 +57,13 @@ CG_EXPORT bool cg_expr_eval(cg_symbolic_expr* e, int64_t* vals, const char** nam
     case EXPR_MIN: *out = a < b ? a : b; return true;
     default: return false;
   }
+}
+// The reference's evaluator (include/cg_symbolic.h, src/core/symbolic.c:88-140): the value, or -1 for an unbound
+// variable or an operation it cannot carry out (it prints "Unbound variable" there; here the error code says so).
+CG_EXPORT int64_t cg_expr_eval(cg_symbolic_expr* e, int64_t* vals, const char** names, int n) {
+  int64_t v = -1;
+  if (!cg_expr_try_eval(e, vals, names, n, &v)) { set_error(CG_ERROR_INVALID_ARGUMENT); return -1; }
+  return v;
 }
 static void expr_str(const cg_symbolic_expr* e, std::string& s) {
   if (!e) { s += "?"; return; }
@@ -126,7 +133,7 @@ CG_EXPORT int64_t cg_dim_resolve(cg_symbolic_dim* d, int64_t* vals, const char**
   if (!d) return -1;
   int64_t v = -1;
   if (d->type == DIM_CONSTANT) v = d->value;
-  else if (d->type == DIM_INFERRED) { if (!cg_expr_eval(d->expr, vals, names, n, &v)) return -1; }
+  else if (d->type == DIM_INFERRED) { if (!cg_expr_try_eval(d->expr, vals, names, n, &v)) return -1; }
   else {
     bool found = false;
     for (int i = 0; i < n && d->name; ++i) if (names[i] && !std::strcmp(names[i], d->name)) { v = vals[i]; found = true; break; }

@@ -180,7 +180,7 @@ void cg_batchnorm_set_training(cg_batchnorm* layer, bool training);
 cg_rmsnorm* cg_rmsnorm_new(int normalized_shape, float epsilon);
 cg_swiglu* cg_swiglu_new(void);
 cg_tensor* cg_swiglu_forward_split(cg_tensor* input);
-cg_conv2d* cg_conv2d_new(int in_channels, int out_channels, int kernel_size, int stride, int padding);
+cg_conv2d* cg_conv2d_new(int in_channels, int out_channels, int kernel_size, int stride, int padding, bool use_bias);
 cg_maxpool2d* cg_maxpool2d_new(int kernel_size, int stride);
 cg_flatten* cg_flatten_new(void);
 cg_sequential* cg_sequential_new(void);

@@ -47,7 +47,10 @@ cg_symbolic_expr* cg_expr_mul(cg_symbolic_expr* left, cg_symbolic_expr* right);
 cg_symbolic_expr* cg_expr_div(cg_symbolic_expr* left, cg_symbolic_expr* right);
 cg_symbolic_expr* cg_expr_floordiv(cg_symbolic_expr* left, cg_symbolic_expr* right);
 cg_symbolic_expr* cg_expr_binary(cg_expr_type type, cg_symbolic_expr* left, cg_symbolic_expr* right);
-bool cg_expr_eval(cg_symbolic_expr* expr, int64_t* bindings, const char** binding_names, int num_bindings, int64_t* out);
+/* the value; -1 (and CG_ERROR_INVALID_ARGUMENT) for an unbound variable or a division by zero, as in the reference */
+int64_t cg_expr_eval(cg_symbolic_expr* expr, int64_t* bindings, const char** binding_names, int num_bindings);
+/* the same with the outcome separate from the value: false when the expression cannot be evaluated */
+bool cg_expr_try_eval(cg_symbolic_expr* expr, int64_t* bindings, const char** binding_names, int num_bindings, int64_t* out);
 char* cg_expr_to_string(cg_symbolic_expr* expr);                 /* caller frees */
 void cg_expr_free(cg_symbolic_expr* expr);
 cg_symbolic_shape* cg_shape_new(cg_symbolic_dim** dims, int ndim);   /* takes ownership of the dims */

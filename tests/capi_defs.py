@@ -167,7 +167,7 @@ def L():
         "cg_linear_new": (LayerP, I, I, B), "cg_relu_new": (LayerP,), "cg_sigmoid_new": (LayerP,), "cg_tanh_new": (LayerP,),
         "cg_softmax_new": (LayerP,), "cg_dropout_new": (LayerP, F), "cg_dropout_set_training": (V, LayerP, B),
         "cg_batchnorm_new": (LayerP, I, F, F), "cg_batchnorm_set_training": (V, LayerP, B), "cg_rmsnorm_new": (LayerP, I, F),
-        "cg_swiglu_new": (LayerP,), "cg_conv2d_new": (LayerP, I, I, I, I, I), "cg_maxpool2d_new": (LayerP, I, I),
+        "cg_swiglu_new": (LayerP,), "cg_conv2d_new": (LayerP, I, I, I, I, I, B), "cg_maxpool2d_new": (LayerP, I, I),
         "cg_flatten_new": (LayerP,), "cg_layer_free": (V, LayerP), "cg_sequential_new": (LayerP,),
         "cg_sequential_add": (V, LayerP, LayerP), "cg_sequential_forward": (TensorP, LayerP, TensorP),
         "cg_sequential_backward": (V, LayerP, TensorP), "cg_sequential_free": (V, LayerP),

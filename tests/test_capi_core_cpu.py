@@ -168,7 +168,7 @@ def test_layers_match_torch_forward_and_backward():
     lib = L()
     # conv -> batchnorm -> relu -> maxpool -> flatten -> linear, loss = sum(out * w)
     x_np = rng.standard_normal((2, 3, 8, 8), dtype=np.float32)
-    conv, bn, pool, flat, lin = lib.cg_conv2d_new(3, 4, 3, 1, 1), lib.cg_batchnorm_new(4, 1e-5, 0.1), lib.cg_maxpool2d_new(2, 2), lib.cg_flatten_new(), lib.cg_linear_new(64, 5, True)
+    conv, bn, pool, flat, lin = lib.cg_conv2d_new(3, 4, 3, 1, 1, True), lib.cg_batchnorm_new(4, 1e-5, 0.1), lib.cg_maxpool2d_new(2, 2), lib.cg_flatten_new(), lib.cg_linear_new(64, 5, True)
     model = _seq(conv, bn, lib.cg_relu_new(), pool, flat, lin)
     x = T(x_np, True)
     out = lib.cg_sequential_forward(model, x._ptr)
@@ -193,6 +193,28 @@ def test_layers_match_torch_forward_and_backward():
     assert np.allclose(grad_of(lin.contents.weights), lw.grad.numpy(), atol=1e-4)
     assert np.allclose(grad_of(bn.contents.weights), g.grad.numpy(), atol=1e-3)
     del prod, loss
+    lib.cg_sequential_free(model)
+
+
+def test_conv2d_without_bias_has_one_parameter_and_matches_torch():
+    lib = L()
+    conv = lib.cg_conv2d_new(2, 3, 3, 2, 1, False)
+    assert not conv.contents.bias and conv.contents.num_params(conv) == 1
+    x_np = rng.standard_normal((2, 2, 7, 7), dtype=np.float32)
+    x = T(x_np, True)
+    model = _seq(conv)
+    out = lib.cg_sequential_forward(model, x._ptr)
+    y = cg.Tensor.from_ptr(out, retain=True)
+    loss = (y * y).sum()
+    loss.backward()
+    tx = torch.tensor(x_np, requires_grad=True)
+    tw = torch.tensor(borrowed(conv.contents.weights)).view(3, 2, 3, 3).requires_grad_()
+    ty = Fn.conv2d(tx, tw, None, stride=2, padding=1)
+    (ty * ty).sum().backward()
+    assert np.allclose(borrowed(out), ty.detach().numpy(), atol=1e-4)
+    assert np.allclose(x.grad, tx.grad.numpy(), atol=1e-3)
+    assert np.allclose(grad_of(conv.contents.weights).reshape(3, 2, 3, 3), tw.grad.numpy(), atol=1e-3)
+    del y, loss
     lib.cg_sequential_free(model)
 
 
