@@ -374,7 +374,11 @@ CG_EXPORT cg_tensor_bf16* cg_tensor_bf16_new(int* shape, int ndim, bool rg) {
   for (int i = 0; i < ndim; ++i) { t->shape[i] = shape[i]; n *= shape[i]; }
   t->ndim = ndim; t->size = (int)n; t->requires_grad = rg;
   t->data = (cg_bf16*)std::calloc(n ? n : 1, sizeof(cg_bf16));
-  if (rg) { t->master = (float*)std::calloc(n ? n : 1, sizeof(float)); t->grad = (float*)std::calloc(n ? n : 1, sizeof(float)); }
+  if (rg) {
+    t->master = (float*)std::calloc(n ? n : 1, sizeof(float)); t->grad_fp32 = (float*)std::calloc(n ? n : 1, sizeof(float));
+    t->grad = (cg_bf16*)std::calloc(n ? n : 1, sizeof(cg_bf16));
+    t->has_master_copy = true;
+  }
   return t;
 }
 CG_EXPORT cg_tensor_bf16* cg_tensor_bf16_from_fp32(cg_tensor* s) {
@@ -389,7 +393,9 @@ CG_EXPORT cg_tensor* cg_tensor_bf16_to_fp32(cg_tensor_bf16* s) {
   if (t) for (int i = 0; i < s->size; ++i) t->data[i] = cg_bf16_to_fp32(s->data[i]);
   return t;
 }
-CG_EXPORT void cg_tensor_bf16_free(cg_tensor_bf16* t) { if (t) { std::free(t->data); std::free(t->master); std::free(t->grad); std::free(t); } }
+CG_EXPORT void cg_tensor_bf16_free(cg_tensor_bf16* t) {
+  if (t) { std::free(t->data); std::free(t->master); std::free(t->grad); std::free(t->grad_fp32); std::free(t); }
+}
 
 #define BF(x) cg_bf16_to_fp32(x)
 CG_EXPORT void cg_bf16_add(cg_tensor_bf16* a, cg_tensor_bf16* b, cg_tensor_bf16* o) {

@@ -17,9 +17,13 @@ float cg_bf16_to_fp32(cg_bf16 h);
 /* the reference's spellings (static inline there, include/cg_bf16.h:22-32) */
 static inline cg_bf16 cg_float_to_bf16(float f) { return cg_fp32_to_bf16(f); }
 static inline float cg_bf16_to_float(cg_bf16 b) { return cg_bf16_to_fp32(b); }
+/* The reference's layout (include/cg_bf16.h:38-50): bf16 values and gradient, fp32 master copy and fp32 gradient
+ * accumulator of a trainable tensor (null otherwise); `master` names data_fp32. */
 typedef struct {
-  cg_bf16* data; float* master; float* grad;
-  int shape[CG_MAX_DIMS]; int ndim; int size; bool requires_grad;
+  cg_bf16* data; cg_bf16* grad;
+  union { float* data_fp32; float* master; };
+  float* grad_fp32;
+  int shape[CG_MAX_DIMS]; int ndim; int size; bool requires_grad; bool has_master_copy;
 } cg_tensor_bf16;
 typedef struct {
   /* second names: the reference's (include/cg_bf16.h) */

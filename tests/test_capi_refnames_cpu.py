@@ -314,6 +314,14 @@ int main(void) {
   cg_memory_stats ms = cg_memory_get_stats(planner);
   if (ms.total_in_use != ms.total_allocated || ms.peak_usage != ms.peak_allocated || ms.cache_hit_rate > 100 || ms.num_bins_used < 0) return 13;
   cg_pool_free(pool, a2);
+  int shp[2] = {2, 3};
+  cg_tensor_bf16* hb = cg_tensor_bf16_new(shp, 2, true);                                    /* include/cg_bf16.h:38-50 */
+  if (!hb->has_master_copy || !hb->data_fp32 || !hb->grad_fp32 || !hb->grad || hb->size != 6) return 14;
+  hb->data_fp32[0] = 1.5f; if (hb->master[0] != 1.5f) return 15;
+  cg_tensor_bf16_free(hb);
+  cg_tensor_bf16* plain = cg_tensor_bf16_new(shp, 2, false);
+  if (plain->has_master_copy || plain->data_fp32 || plain->grad_fp32 || plain->grad) return 16;
+  cg_tensor_bf16_free(plain);
   (void)stage; (void)ctx; (void)dec; (void)tp; (void)qc; (void)eg;
   printf("ok\n");
   return 0;
