@@ -136,6 +136,8 @@ CG_EXPORT cg_flash_attn_params* cg_flash_attn_params_new(cg_tensor* Q, cg_tensor
   p->O = make_like(Q, false);
   int ls[3] = {d.B, d.H, d.Tq};
   p->L = make(ls, 3, false);
+  p->softmax_lse = p->L ? p->L->data : nullptr;
+  p->is_training = Q->requires_grad || K->requires_grad || V->requires_grad;
   return p;
 }
 // Frees the block and the tensors it created (O, L, dQ, dK, dV); Q, K, V, dO, mask stay the caller's.

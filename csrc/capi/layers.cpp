@@ -197,6 +197,7 @@ static cg_tensor* batchnorm_forward(cg_layer* L, cg_tensor* x) {
   cg_tensor* xn = l->x_norm = make_like(x, false);
   int fs[1] = {F};
   cg_tensor* si = l->std_inv = make(fs, 1, false);
+  if (!l->batch_mean) { l->batch_mean = make(fs, 1, false); l->batch_var = make(fs, 1, false); }
   auto at = [=](int n, int f, int s) { return ((size_t)n * F + f) * S + s; };
   for (int f = 0; f < F; ++f) {
     float mean, var;
@@ -212,6 +213,7 @@ static cg_tensor* batchnorm_forward(cg_layer* L, cg_tensor* x) {
     } else { mean = l->running_mean->data[f]; var = l->running_var->data[f]; }
     const float inv = 1.0f / std::sqrt(var + l->epsilon);
     si->data[f] = inv;
+    l->batch_mean->data[f] = mean; l->batch_var->data[f] = var;        // the statistics this pass normalised with
     for (int n = 0; n < N; ++n) for (int s = 0; s < S; ++s) {
       const size_t i = at(n, f, s);
       xn->data[i] = (x->data[i] - mean) * inv;
@@ -237,7 +239,7 @@ static cg_tensor* batchnorm_forward(cg_layer* L, cg_tensor* x) {
 }
 static void batchnorm_free(cg_layer* L) {
   cg_batchnorm* l = (cg_batchnorm*)L;
-  cg_tensor* ts[4] = {l->running_mean, l->running_var, l->x_norm, l->std_inv};
+  cg_tensor* ts[6] = {l->running_mean, l->running_var, l->x_norm, l->std_inv, l->batch_mean, l->batch_var};
   for (cg_tensor* t : ts) if (t) cg_tensor_release(t);
   plain_free(L);
 }

@@ -158,6 +158,7 @@ typedef struct {
   union { cg_tensor* x_norm; cg_tensor* input_normalized; };    /* input_normalized: the reference's name */
   cg_tensor* std_inv;
   bool training; cg_tensor* param_ptrs[2];
+  cg_tensor* batch_mean; cg_tensor* batch_var;                   /* reference fields: mean / biased variance of the last pass */
 } cg_batchnorm;
 typedef struct { cg_layer base; int normalized_shape; float epsilon; cg_tensor* inv_rms; cg_tensor* param_ptrs[1]; } cg_rmsnorm;
 typedef struct { cg_layer base; } cg_swiglu;
@@ -210,6 +211,8 @@ typedef struct {
   union { cg_linear* gate_proj; cg_layer* mlp_gate; }; union { cg_linear* up_proj; cg_layer* mlp_up; };
   union { cg_linear* down_proj; cg_layer* mlp_down; };
   cg_tensor** param_cache; int n_params;
+  /* reference fields; the block applies its activation and dropout itself and leaves these null */
+  cg_layer* act_fn; cg_layer* drop1; cg_layer* drop2;
 } cg_transformer_block;
 cg_transformer_block* cg_transformer_block_new(cg_transformer_config config);
 cg_tensor* cg_transformer_forward(cg_layer* layer, cg_tensor* input, cg_tensor* mask);   /* input [seq, hidden] */

@@ -115,6 +115,9 @@ typedef struct {
   cg_attention_mask_type mask_type; int window_size;
   float* alibi_slopes;
   cg_flash_attn_config config;
+  /* reference fields (include/cg_flash_attn.h:51-88): softmax_lse points at L's values; the attention functions carry
+   * dropout_prob but apply no dropout, so the mask stays null */
+  bool is_training; float* softmax_lse; float* dropout_mask;
 } cg_flash_attn_params;
 void cg_flash_attention_forward(cg_flash_attn_params* params);
 void cg_flash_attention_forward_cpu(cg_flash_attn_params* params);
@@ -167,7 +170,12 @@ void cg_save_model(const char* filename, cg_tensor** tensors, const char** names
 void cg_load_model(const char* filename, cg_tensor*** out_tensors, char*** out_names, int* out_count);
 
 /* ------------------------------------------------ sampling / speculative */
-typedef struct cg_token_tree { int* tokens; float** probs; int* parents; int depth; int num_tokens; int capacity; int vocab_size; } cg_token_tree;
+/* The second line holds the reference's fields (include/cg_speculative.h); its tree functions are declared only, and the
+ * functions of this library keep parents and one distribution per node instead and leave them null / 0. */
+typedef struct cg_token_tree {
+  int* tokens; float** probs; int* parents; int depth; int num_tokens; int capacity; int vocab_size;
+  float* draft_probs; float* target_probs; bool* accepted; cg_tensor* hidden_states; int* branch_points; int num_branches;
+} cg_token_tree;
 /* A model is a callback: logits_out[n_positions * vocab] for the LAST n_positions of ids. */
 typedef void (*cg_logits_fn)(void* model, const int* ids, int len, int n_positions, float* logits_out);
 typedef struct {

@@ -22,6 +22,12 @@ def lib():
     lib.cg_cuda_shutdown()
 
 
+@pytest.fixture(autouse=True)
+def _fresh_error_state(lib):
+    lib.cg_last_error()          # reading clears it: an error left by an earlier test of the same process is not this test's
+    yield
+
+
 def test_memory_round_trip(lib):
     c1.case_memory(lib)
 

@@ -322,6 +322,22 @@ int main(void) {
   cg_tensor_bf16* plain = cg_tensor_bf16_new(shp, 2, false);
   if (plain->has_master_copy || plain->data_fp32 || plain->grad_fp32 || plain->grad) return 16;
   cg_tensor_bf16_free(plain);
+  cg_batchnorm* bnl = cg_batchnorm_new(3, 1e-5f, 0.1f);                                     /* batch statistics of the last pass */
+  int xs[2] = {4, 3};
+  cg_tensor* xin = cg_tensor_randn(xs, 2, 1u, false);
+  cg_tensor* yout = bnl->base.forward(&bnl->base, xin);
+  if (!yout || !bnl->batch_mean || !bnl->batch_var || bnl->batch_mean->size != 3 || !(bnl->batch_var->data[0] > 0.0f)) return 17;
+  if (bnl->input_normalized != bnl->x_norm) return 18;
+  cg_transformer_block tb; tb.act_fn = NULL; tb.drop1 = NULL; tb.drop2 = NULL; (void)tb;
+  cg_token_tree tt = {0}; tt.draft_probs = NULL; tt.target_probs = NULL; tt.accepted = NULL; tt.hidden_states = NULL;
+  tt.branch_points = NULL; tt.num_branches = 0; (void)tt;
+  int qs[4] = {1, 4, 2, 8};
+  cg_tensor* q = cg_tensor_randn(qs, 4, 2u, true); cg_tensor* kk = cg_tensor_randn(qs, 4, 3u, false); cg_tensor* vv = cg_tensor_randn(qs, 4, 4u, false);
+  cg_flash_attn_params* ap = cg_flash_attn_params_new(q, kk, vv, ATTN_MASK_CAUSAL, 0.0f);
+  if (!ap || !ap->is_training || ap->softmax_lse != ap->L->data || ap->dropout_mask) return 19;
+  cg_flash_attention_forward(ap);
+  if (!(ap->softmax_lse[0] == ap->softmax_lse[0])) return 20;
+  cg_flash_attn_params_free(ap);
   (void)stage; (void)ctx; (void)dec; (void)tp; (void)qc; (void)eg;
   printf("ok\n");
   return 0;
