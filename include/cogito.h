@@ -29,6 +29,12 @@ extern "C" {
 #define COGITO_VERSION_MINOR 0
 #define COGITO_VERSION_PATCH 0
 #define COGITO_API_VERSION 1
+/* binds an exported function to a symbol version (GNU toolchains); a no-op elsewhere */
+#if defined(__linux__) && defined(__GNUC__)
+#define CG_API_VERSIONed(func, ver) __asm__(".symver " #func "," #func "@" #ver)
+#else
+#define CG_API_VERSIONed(func, ver)
+#endif
 
 typedef enum {
   CG_SUCCESS = 0, CG_ERROR_NULL_POINTER, CG_ERROR_SHAPE_MISMATCH, CG_ERROR_OUT_OF_MEMORY,

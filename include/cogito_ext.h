@@ -94,6 +94,20 @@ void cg_calibration_free(cg_quant_calibration* calib);
 /* ATTN_MASK_* are the reference's enumerators (include/cg_flash_attn.h:40-45); CG_MASK_* name the same values */
 typedef enum { ATTN_MASK_NONE = 0, ATTN_MASK_CAUSAL = 1, ATTN_MASK_SLIDING_WINDOW = 2, ATTN_MASK_CUSTOM = 3,
                CG_MASK_NONE = 0, CG_MASK_CAUSAL = 1, CG_MASK_SLIDING_WINDOW = 2, CG_MASK_CUSTOM = 3 } cg_attention_mask_type;
+/* Tile shape of the sm_100a attention kernels, under the reference's macro names (64 x 64 tiles and 4 / 8 warps there,
+ * include/cg_flash_attn.h:18-21, include/cg_flash_attn_kernels.h:24-30): 128 query rows x 128 keys per tile (two query
+ * tiles per CTA), the whole head dimension (up to 128) in one piece, 12 warps. */
+#define FLASH_BLOCK_M_DEFAULT 128
+#define FLASH_BLOCK_N_DEFAULT 128
+#define FLASH_BLOCK_M FLASH_BLOCK_M_DEFAULT
+#define FLASH_BLOCK_N FLASH_BLOCK_N_DEFAULT
+#define FLASH_BLOCK_K 128
+#define FLASH_WARPS 12
+#define FA_BLOCK_M 128
+#define FA_BLOCK_N 128
+#define FA_BLOCK_K 128
+#define FA_THREADS 384
+#define FA_WARPS 12
 /* use_register_tile, use_persistent and sm_count are the reference's names (include/cg_flash_attn.h:27-35) */
 typedef struct {
   int block_m, block_n, num_warps, num_stages;
@@ -276,6 +290,19 @@ void cg_3d_parallel_free(cg_3d_parallel* ctx);
  * selects the pinned-host pool of the planner. */
 typedef enum { CG_ARENA_DEFAULT = 0, CG_ARENA_PARAM, CG_ARENA_ACTIVATION, CG_ARENA_GRADIENT,
                CG_ARENA_DEVICE = 0, CG_ARENA_HOST = 4 } cg_arena_type;
+/* Size classes of the caching pool: powers of two from 2^CG_MIN_BIN to 2^CG_MAX_BIN bytes plus the three exact sizes
+ * (the reference stops at 2^36, include/cg_memory.h:32-35,84-86).  The buddy allocator hands out blocks from
+ * 2^CG_BUDDY_MIN_ORDER bytes up to the largest power of two that fits its region; CG_BUDDY_MAX_ORDER bounds that. */
+#define CG_SUBBIN_768 768
+#define CG_SUBBIN_1024 1024
+#define CG_SUBBIN_4096 4096
+#define CG_NUM_SUBBINS 3
+#define CG_MIN_BIN 5
+#define CG_MAX_BIN 40
+#define CG_NUM_BINS (CG_MAX_BIN - CG_MIN_BIN + 1)
+#define CG_BUDDY_MIN_ORDER 8
+#define CG_BUDDY_MAX_ORDER 40
+#define CG_BUDDY_NUM_ORDERS (CG_BUDDY_MAX_ORDER - CG_BUDDY_MIN_ORDER + 1)
 typedef struct cg_memory_pool cg_memory_pool;
 typedef struct cg_buddy_allocator cg_buddy_allocator;
 typedef struct cg_memory_planner cg_memory_planner;

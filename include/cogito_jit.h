@@ -78,7 +78,9 @@ typedef enum {
   OP_FUSED_ATTENTION, OP_FUSED_LAYERNORM, OP_FUSED_LAYERNORM_GELU_LINEAR,
   OP_FUSED_SOFTMAX_DROPOUT_RESIDUAL, OP_FUSED_QKV_ROPE, OP_CUSTOM
 } cg_ir_opcode;
-typedef enum { NODE_FUSION_NONE = 0, NODE_FUSION_VERTICAL, NODE_FUSION_HORIZONTAL, NODE_FUSION_CUSTOM } cg_node_fusion;
+typedef enum { NODE_FUSION_NONE = 0, NODE_FUSION_VERTICAL, NODE_FUSION_HORIZONTAL, NODE_FUSION_CUSTOM,
+               FUSION_VERTICAL = 1, FUSION_HORIZONTAL = 2 /* the reference's names for the two marks (include/cg_jit.h:65-70) */
+} cg_node_fusion;
 typedef enum { FUSION_NONE = 0, FUSION_ELEMENTWISE, FUSION_REDUCTION, FUSION_EPILOGUE, FUSION_ATTENTION,
                FUSION_LAYERNORM, FUSION_CUSTOM } cg_fusion_type;
 typedef struct cg_ir_node {

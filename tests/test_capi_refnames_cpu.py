@@ -338,6 +338,11 @@ int main(void) {
   cg_flash_attention_forward(ap);
   if (!(ap->softmax_lse[0] == ap->softmax_lse[0])) return 20;
   cg_flash_attn_params_free(ap);
+  /* constant macros and the two per-node fusion marks of the reference */
+  if (CG_NUM_SUBBINS != 3 || CG_SUBBIN_768 != 768 || CG_NUM_BINS != CG_MAX_BIN - CG_MIN_BIN + 1 || CG_BUDDY_NUM_ORDERS < 1) return 21;
+  if (FLASH_BLOCK_M != fc.block_n || FA_WARPS * 32 != FA_THREADS || FLASH_WARPS != fc.num_warps || FA_BLOCK_K < 64 || FLASH_BLOCK_K < 64) return 22;
+  cg_node_fusion nf = FUSION_VERTICAL; if (nf != NODE_FUSION_VERTICAL || FUSION_HORIZONTAL != NODE_FUSION_HORIZONTAL) return 23;
+  if (cg_subbin_index(CG_SUBBIN_4096) != 2 || cg_subbin_index(100) != -1) return 24;
   (void)stage; (void)ctx; (void)dec; (void)tp; (void)qc; (void)eg;
   printf("ok\n");
   return 0;
