@@ -268,6 +268,20 @@ def test_reference_field_and_enumerator_names_compile_as_c11(tmp_path):
     src = tmp_path / "names.c"
     src.write_text(r'''
 #include <stdio.h>
+#include "cg_tensor.h"            /* the reference's header names forward to cogito.h / cogito_cuda.h */
+#include "cg_layers.h"
+#include "cg_transformer.h"
+#include "cg_flash_attn.h"
+#include "cg_flash_attn_kernels.h"
+#include "cg_memory.h"
+#include "cg_pipeline.h"
+#include "cg_speculative.h"
+#include "cg_quantize.h"
+#include "cg_datasets.h"
+#include "cg_bf16.h"
+#include "cg_jit.h"
+#include "cg_fusion.h"
+#include "cg_cuda.h"
 #include "cogito.h"
 int main(void) {
   cg_transformer_config cfg = {0};
