@@ -293,6 +293,7 @@ cg_tensor* layernorm_fwd(cg_layer* Lr, cg_tensor* x) {
     }
   });
   if (x) cg_tensor_retain(x);
+  if (y) cg_tensor_retain(y);                       // the layer's reference; the first one is the caller's
   if (Lr->input) cg_tensor_release(Lr->input);
   if (Lr->output) cg_tensor_release(Lr->output);
   Lr->input = x; Lr->output = y;
@@ -376,7 +377,7 @@ CG_EXPORT cg_tensor* cg_transformer_forward(cg_layer* layer, cg_tensor* x, cg_te
   if (mask && mask->size != T * T) return fail(CG_ERROR_SHAPE_MISMATCH, (cg_tensor*)nullptr);
   std::vector<cg_tensor*> temps;        // functional results owned here; the tape keeps what it needs
   auto keep = [&](cg_tensor* t) { temps.push_back(t); return t; };
-  auto fwd = [](void* l, cg_tensor* in) { cg_layer* L = (cg_layer*)l; return L->forward(L, in); };
+  auto fwd = [&](void* l, cg_tensor* in) { cg_layer* L = (cg_layer*)l; return keep(L->forward(L, in)); };   // sub-layer outputs are ours to release
   cg_tensor* h = c.pre_norm ? fwd(b->norm1, x) : x;
   cg_tensor* q = fwd(b->q_proj, h); cg_tensor* k = fwd(b->k_proj, h); cg_tensor* v = fwd(b->v_proj, h);
   cg_tensor* a = keep(attention_op(q, k, v, mask, c.num_heads, c.num_kv_heads, c.head_dim));
@@ -402,7 +403,8 @@ CG_EXPORT cg_tensor* cg_transformer_forward(cg_layer* layer, cg_tensor* x, cg_te
   } else act = keep(gelu_op(up));
   cg_tensor* down = fwd(b->down_proj, act);
   cg_tensor* y = cg_add(x1, down);
-  if (!c.pre_norm) { temps.push_back(y); y = fwd(b->norm2, y); cg_tensor_retain(y); }
+  if (!c.pre_norm) { temps.push_back(y); y = fwd(b->norm2, y); cg_tensor_retain(y); }   // the caller's reference
+  cg_tensor_retain(y);                              // the block's own
   cg_tensor_retain(x);
   if (layer->input) cg_tensor_release(layer->input);
   if (layer->output) cg_tensor_release(layer->output);

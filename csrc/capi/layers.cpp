@@ -15,8 +15,11 @@ template <class T> T* new_layer(const char* name) {
   return l;
 }
 // Takes ownership of `out`; keeps `in` alive for the per-layer backward.
+// The reference's ownership rule (src/layers/linear.c:60-97): the layer keeps a reference to its input and one to
+// its output, and the output's first reference goes to the caller, who releases it when done.
 cg_tensor* publish(cg_layer* L, cg_tensor* in, cg_tensor* out) {
   if (in) cg_tensor_retain(in);
+  if (out) cg_tensor_retain(out);
   if (L->input) cg_tensor_release(L->input);
   if (L->output) cg_tensor_release(L->output);
   L->input = in; L->output = out;
@@ -507,9 +510,16 @@ CG_EXPORT void cg_sequential_add(cg_sequential* s, cg_layer* layer) {
 }
 CG_EXPORT cg_tensor* cg_sequential_forward(cg_sequential* s, cg_tensor* x) {
   if (!s || !x) return fail(CG_ERROR_NULL_POINTER, (cg_tensor*)nullptr);
-  cg_tensor* cur = x;
-  for (int i = 0; i < s->num_layers && cur; ++i) cur = s->layers[i]->forward(s->layers[i], cur);
-  s->base.output = cur;     // borrowed from the last layer
+  // Every layer hands its output to us and keeps references to its input and output itself: an intermediate can go
+  // once the next layer has taken it; the last output is the caller's.
+  cg_tensor* cur = x; cg_tensor* mine = nullptr;
+  for (int i = 0; i < s->num_layers && cur; ++i) {
+    cg_tensor* next = s->layers[i]->forward(s->layers[i], cur);
+    if (mine) cg_tensor_release(mine);
+    mine = cur = next;
+  }
+  if (s->num_layers == 0) cg_tensor_retain(x);      // nothing ran: the caller still gets a reference of its own
+  s->base.output = cur;     // not counted: the last layer holds it
   return cur;
 }
 CG_EXPORT void cg_sequential_backward(cg_sequential* s, cg_tensor* grad_output) {

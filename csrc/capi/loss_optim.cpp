@@ -67,11 +67,25 @@ CG_EXPORT cg_tensor* cg_bce_with_logits_loss(cg_tensor* x, cg_tensor* t, cg_redu
 // pred and target [N, C] (target: one-hot or soft labels).  MEAN divides by N.
 CG_EXPORT cg_tensor* cg_cross_entropy_loss(cg_tensor* p, cg_tensor* t, bool from_logits, cg_reduction red) {
   if (!p || !t) return fail(CG_ERROR_NULL_POINTER, (cg_tensor*)nullptr);
-  if (p->size != t->size || p->ndim < 1) return fail(CG_ERROR_SHAPE_MISMATCH, (cg_tensor*)nullptr);
+  if (p->ndim < 1) return fail(CG_ERROR_SHAPE_MISMATCH, (cg_tensor*)nullptr);
   const int C = cols_of(p), N = rows_of(p);
+  // Targets: probabilities / one-hot rows of the prediction's shape, or - the reference's convention
+  // (src/layers/loss.c:58-78) - one class index per row.  Indices are expanded to one-hot rows here.
+  cg_tensor* expanded = nullptr;
+  if (t->size == N && t->size != p->size) {
+    expanded = make_like(p, false);
+    if (!expanded) return nullptr;
+    for (int r = 0; r < N; ++r) {
+      const int lbl = (int)t->data[r];
+      if (lbl < 0 || lbl >= C) { cg_tensor_release(expanded); return fail(CG_ERROR_INVALID_ARGUMENT, (cg_tensor*)nullptr); }
+      expanded->data[(size_t)r * C + lbl] = 1.0f;
+    }
+    t = expanded;
+  }
+  if (p->size != t->size) return fail(CG_ERROR_SHAPE_MISMATCH, (cg_tensor*)nullptr);
   int os[1] = {red == CG_REDUCTION_NONE ? N : 1};
   cg_tensor* o = make(os, 1, false);
-  if (!o) return nullptr;
+  if (!o) { if (expanded) cg_tensor_release(expanded); return nullptr; }
   std::vector<float> prob(from_logits ? p->size : 0);
   const float eps = 1e-7f;
   double total = 0;
@@ -105,6 +119,7 @@ CG_EXPORT cg_tensor* cg_cross_entropy_loss(cg_tensor* p, cg_tensor* t, bool from
       }
     }
   });
+  if (expanded) cg_tensor_release(expanded);       // the tape holds it from here on (or nobody needs it)
   return o;
 }
 CG_EXPORT cg_tensor* cg_softmax_cross_entropy_loss(cg_tensor* logits, cg_tensor* t, cg_reduction red) {

@@ -167,7 +167,7 @@ CG_EXPORT void cg_pipeline_forward_backward(cg_pipeline_parallel* pp, cg_tensor*
           if (s == 0) in[s][m] = slice(input, m, false);
           cg_tensor* y = cg_sequential_forward((cg_sequential*)pp->stages[s].layers, in[s][m]);
           if (!y) { failed = true; break; }
-          cg_tensor_retain(y); out[s][m] = y;
+          out[s][m] = y;                                   // ours: the stage handed us a reference
           if (s == S - 1) {
             cg_tensor* tm = slice(target, m, false);
             loss[s][m] = impl_of(pp)->loss_kind == 1 ? cg_softmax_cross_entropy_loss(y, tm, CG_REDUCTION_MEAN) : cg_mse_loss(y, tm, CG_REDUCTION_MEAN);

@@ -66,6 +66,7 @@ int main(int argc, char** argv) {
       seen += n;
       ++batches;
       cg_tensor_release(loss);
+      cg_tensor_release(logits);                         /* a layer's output is handed to the caller, who releases it */
     }
     cg_dataloader_reset(loader);
     mean = (float)(total / batches);

@@ -31,10 +31,12 @@ int main(int argc, char** argv) {
     last = loss->data[0];
     if (e % 1000 == 0) printf("epoch %d loss %.6f\n", e, last);
     cg_tensor_release(loss);
+    cg_tensor_release(pred);               /* a layer's output is handed to the caller, who releases it */
   }
   cg_tensor* pred = cg_sequential_forward(model, x);
   for (int i = 0; i < 4; ++i) printf("%g xor %g -> %.4f\n", xs[2 * i], xs[2 * i + 1], pred->data[i]);
   printf("final loss %.6f\n", last);
+  cg_tensor_release(pred);
   cg_optimizer_free(&opt->base);
   cg_sequential_free(model);
   cg_tensor_release(x);

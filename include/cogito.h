@@ -139,6 +139,10 @@ bool cg_grad_check(void (*forward_fn)(cg_tensor* in, cg_tensor* out), cg_tensor*
                    cg_tensor* grad_output, float epsilon, float tolerance);
 
 /* ----------------------------------------------------------------- layers */
+/* Ownership, as in the reference (src/layers/linear.c:60-97): forward() returns a tensor whose first reference is
+ * the caller's (release it when done); the layer keeps references of its own to its last input and output until the
+ * next forward() or cg_layer_free().  cg_sequential_forward releases the intermediate outputs itself and hands the last
+ * one to the caller. */
 typedef struct cg_layer cg_layer;
 struct cg_layer {
   const char* name;

@@ -48,7 +48,7 @@ def test_host_gemm_every_operand_layout_on_ragged_sizes(M, K, N):
     w_np = borrowed(lin.contents.weights)
     x = T(x_np, True)
     out = lib.cg_sequential_forward(model, x._ptr)
-    prod = cg.Tensor.from_ptr(out, retain=True) * T(g_np)
+    prod = cg.Tensor.from_ptr(out) * T(g_np)
     loss = prod.sum()
     loss.backward()
     tx, tw = torch.tensor(x_np, requires_grad=True), torch.tensor(w_np, requires_grad=True)
@@ -121,6 +121,7 @@ def test_xor_converges_through_cg_backward():
         lib.cg_optimizer_step(opt)
         value = loss.contents.data[0]
         lib.cg_tensor_release(loss)
+        lib.cg_tensor_release(pred)          # the caller's reference to the model's output (the last layer keeps its own)
     assert value < 0.01
     assert lib.cg_tensor_live_count() <= live0 + 16          # no per-step leak
     lib.cg_optimizer_free(opt)
@@ -173,7 +174,7 @@ def test_layers_match_torch_forward_and_backward():
     x = T(x_np, True)
     out = lib.cg_sequential_forward(model, x._ptr)
     w_np = rng.standard_normal((2, 5), dtype=np.float32)
-    prod = cg.Tensor.from_ptr(out, retain=True) * T(w_np)
+    prod = cg.Tensor.from_ptr(out) * T(w_np)
     loss = prod.sum()
     loss.backward()
     tx = torch.tensor(x_np, requires_grad=True)
@@ -204,7 +205,7 @@ def test_conv2d_without_bias_has_one_parameter_and_matches_torch():
     x = T(x_np, True)
     model = _seq(conv)
     out = lib.cg_sequential_forward(model, x._ptr)
-    y = cg.Tensor.from_ptr(out, retain=True)
+    y = cg.Tensor.from_ptr(out)
     loss = (y * y).sum()
     loss.backward()
     tx = torch.tensor(x_np, requires_grad=True)
@@ -226,7 +227,7 @@ def test_rmsnorm_swiglu_softmax_dropout():
     model = _seq(rn, sw, sm)
     out = lib.cg_sequential_forward(model, x._ptr)
     w_np = rng.standard_normal((4, 4), dtype=np.float32)
-    loss = (cg.Tensor.from_ptr(out, retain=True) * T(w_np)).sum()
+    loss = (cg.Tensor.from_ptr(out) * T(w_np)).sum()
     loss.backward()
     tx = torch.tensor(x_np, requires_grad=True)
     h = tx * torch.rsqrt(tx.pow(2).mean(-1, keepdim=True) + 1e-6)
@@ -454,7 +455,7 @@ def test_transformer_block_gradients(llama_style):
         return float((borrowed(out) * w.numpy()).sum())
 
     out = lib.cg_transformer_forward(blk, x._ptr, None)
-    loss = (cg.Tensor.from_ptr(out, retain=True) * w).sum()
+    loss = (cg.Tensor.from_ptr(out) * w).sum()
     loss.backward()
     params = blk.contents.get_params(blk)
     xs = x.numpy()
