@@ -5,6 +5,7 @@ import ctypes
 from ctypes import POINTER, c_bool, c_char_p, c_float, c_int, c_size_t, c_void_p
 
 import numpy as np
+import pytest
 
 from capi_defs import FusionGroup, IrGraph, JitCompiler, L, T, TensorP, borrowed, cg
 
@@ -370,3 +371,35 @@ int main(void) {
     assert p.returncode == 0, p.stderr
     r = subprocess.run([str(exe)], capture_output=True, text=True)
     assert r.returncode == 0 and r.stdout.strip() == "ok", (r.returncode, r.stdout, r.stderr)
+
+
+def _reference_dir():
+    import os
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    cand = Path(os.environ.get("COGITO_REFERENCE_DIR", root.parent / "reference"))
+    return cand if (cand / "tests" / "test_tensor.c").exists() else None
+
+
+@pytest.mark.skipif(_reference_dir() is None, reason="the reference checkout is not beside this repository (or in COGITO_REFERENCE_DIR)")
+def test_the_references_own_test_programs_pass_against_this_library(tmp_path):
+    """tests/test_tensor.c, tests/test_autograd.c and tests/test_cuda.c of the reference, unchanged, compiled against
+    these headers and linked against libcogito.so.  Its build passes 31, 10 (then crashes) and 46; here 31, 16 and 43:
+    the three flash-attention checks of test_cuda.c fill cg_flash_attn_params with raw float pointers."""
+    import re
+    import shutil
+    import subprocess
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    ref, lib = _reference_dir(), root / "cogito_b200" / "lib"
+    cc = shutil.which("gcc") or shutil.which("cc")
+    want = {"test_tensor": (31, 0), "test_autograd": (16, 0), "test_cuda": (43, 3)}
+    for name, (passed, failed) in want.items():
+        exe = tmp_path / name
+        p = subprocess.run([cc, "-std=gnu11", "-O1", "-w", "-I", str(root / "include"), str(ref / "tests" / f"{name}.c"), "-L", str(lib), "-lcogito",
+                            "-lm", f"-Wl,-rpath,{lib}", "-o", str(exe)], capture_output=True, text=True)
+        assert p.returncode == 0, (name, p.stderr[-1500:])
+        r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120, env=dict(__import__("os").environ, COGITO_FORCE_HOST="1"))
+        m = re.search(r"Results: (\d+) passed, (\d+) failed", r.stdout)
+        assert m, (name, r.returncode, r.stdout[-800:], r.stderr[-400:])
+        assert (int(m.group(1)), int(m.group(2))) == (passed, failed), (name, m.group(0))
