@@ -18,12 +18,21 @@ constexpr size_t kSub[3] = {768, 1024, 4096};
 struct Block { size_t size; int bin; };             // bin >= 0 power-of-two, -1-i sub-bin i
 }  // namespace
 
-struct cg_memory_pool {
+struct PoolImpl : cg_memory_pool {
+  PoolImpl() : cg_memory_pool{} {}
   std::vector<void*> free_list[kBins];
   std::vector<void*> sub_free[3];
   std::unordered_map<void*, Block> live, cached;
   cg_memory_stats st{};
+  size_t sub_hits = 0;
+  // the counters of the public struct (the reference's names) follow the internal ones
+  void sync() {
+    total_in_use = st.total_allocated; total_allocated = st.total_allocated + st.total_cached; peak_usage = st.peak_allocated;
+    num_allocs = (size_t)st.num_allocs; num_frees = (size_t)st.num_frees; cache_hits = (size_t)st.cache_hits;
+    cache_misses = (size_t)st.cache_misses; subbin_hits = sub_hits;
+  }
 };
+static PoolImpl* impl(cg_memory_pool* x) { return static_cast<PoolImpl*>(x); }
 
 static int bin_of(size_t size) {
   int b = 0; size_t cap = (size_t)1 << kMinShift;
@@ -31,12 +40,13 @@ static int bin_of(size_t size) {
   return cap >= size ? b : -1;
 }
 CG_EXPORT int cg_subbin_index(size_t size) { for (int i = 0; i < 3; ++i) if (size == kSub[i]) return i; return -1; }
-CG_EXPORT cg_memory_pool* cg_memory_pool_new(void) { return new cg_memory_pool(); }
-static void* pool_take(cg_memory_pool* p, std::vector<void*>& list, size_t cap, int bin, size_t want) {
+CG_EXPORT cg_memory_pool* cg_memory_pool_new(void) { return new PoolImpl(); }
+static void* pool_take(cg_memory_pool* p_, std::vector<void*>& list, size_t cap, int bin, size_t want) { auto* p = impl(p_);
   void* ptr;
   if (!list.empty()) {
     ptr = list.back(); list.pop_back();
     p->cached.erase(ptr); p->st.total_cached -= cap; ++p->st.cache_hits;
+    if (bin < 0) ++p->sub_hits;
   } else {
     if (posix_memalign(&ptr, 256, cap) != 0) return fail(CG_ERROR_OUT_OF_MEMORY, (void*)nullptr);
     ++p->st.cache_misses;
@@ -45,9 +55,10 @@ static void* pool_take(cg_memory_pool* p, std::vector<void*>& list, size_t cap, 
   p->st.total_allocated += cap; ++p->st.num_allocs;
   if (p->st.total_allocated > p->st.peak_allocated) p->st.peak_allocated = p->st.total_allocated;
   (void)want;
+  p->sync();
   return ptr;
 }
-CG_EXPORT void* cg_pool_alloc(cg_memory_pool* p, size_t size) {
+CG_EXPORT void* cg_pool_alloc(cg_memory_pool* p_, size_t size) { auto* p = impl(p_);
   if (!p) return fail(CG_ERROR_NULL_POINTER, (void*)nullptr);
   if (size == 0) size = 1;
   const int sb = cg_subbin_index(size);
@@ -56,11 +67,11 @@ CG_EXPORT void* cg_pool_alloc(cg_memory_pool* p, size_t size) {
   if (b < 0) return fail(CG_ERROR_INVALID_ARGUMENT, (void*)nullptr);
   return pool_take(p, p->free_list[b], (size_t)1 << (kMinShift + b), b, size);
 }
-CG_EXPORT void* cg_pool_alloc_subbin(cg_memory_pool* p, size_t size) {
+CG_EXPORT void* cg_pool_alloc_subbin(cg_memory_pool* p_, size_t size) { auto* p = impl(p_);
   if (cg_subbin_index(size) < 0) return fail(CG_ERROR_INVALID_ARGUMENT, (void*)nullptr);
   return cg_pool_alloc(p, size);
 }
-CG_EXPORT void cg_pool_free(cg_memory_pool* p, void* ptr) {
+CG_EXPORT void cg_pool_free(cg_memory_pool* p_, void* ptr) { auto* p = impl(p_);
   if (!p || !ptr) return;
   auto it = p->live.find(ptr);
   if (it == p->live.end()) { set_error(CG_ERROR_INVALID_ARGUMENT); return; }
@@ -69,16 +80,18 @@ CG_EXPORT void cg_pool_free(cg_memory_pool* p, void* ptr) {
   (b.bin >= 0 ? p->free_list[b.bin] : p->sub_free[-1 - b.bin]).push_back(ptr);
   p->cached[ptr] = b;
   p->st.total_allocated -= b.size; p->st.total_cached += b.size; ++p->st.num_frees;
+  p->sync();
 }
-CG_EXPORT void cg_pool_trim(cg_memory_pool* p) {
+CG_EXPORT void cg_pool_trim(cg_memory_pool* p_) { auto* p = impl(p_);
   if (!p) return;
   for (auto& kv : p->cached) std::free(kv.first);
   p->cached.clear();
   for (auto& l : p->free_list) l.clear();
   for (auto& l : p->sub_free) l.clear();
   p->st.total_cached = 0;
+  p->sync();
 }
-CG_EXPORT void cg_memory_pool_free(cg_memory_pool* p) {
+CG_EXPORT void cg_memory_pool_free(cg_memory_pool* p_) { auto* p = impl(p_);
   if (!p) return;
   cg_pool_trim(p);
   for (auto& kv : p->live) std::free(kv.first);
@@ -86,34 +99,38 @@ CG_EXPORT void cg_memory_pool_free(cg_memory_pool* p) {
 }
 // The host library has one address space; the arena only selects the accounting bucket on the
 // GPU side (device memory vs pinned host memory).
-CG_EXPORT void* cg_pool_alloc_arena(cg_memory_pool* p, size_t size, cg_arena_type) { return cg_pool_alloc(p, size); }
-CG_EXPORT void cg_pool_free_arena(cg_memory_pool* p, void* ptr, cg_arena_type) { cg_pool_free(p, ptr); }
+CG_EXPORT void* cg_pool_alloc_arena(cg_memory_pool* p_, size_t size, cg_arena_type) { auto* p = impl(p_); return cg_pool_alloc(p, size); }
+CG_EXPORT void cg_pool_free_arena(cg_memory_pool* p_, void* ptr, cg_arena_type) { auto* p = impl(p_); cg_pool_free(p, ptr); }
 // Share of the pool's bytes that sit unused in the cache.
-CG_EXPORT float cg_memory_fragmentation(cg_memory_pool* p) {
+CG_EXPORT float cg_memory_fragmentation(cg_memory_pool* p_) { auto* p = impl(p_);
   if (!p) return 0.0f;
   const double all = (double)p->st.total_allocated + (double)p->st.total_cached;
   return all > 0 ? (float)(p->st.total_cached / all) : 0.0f;
 }
-CG_EXPORT bool cg_memory_needs_compact(cg_memory_pool* p, float threshold) { return cg_memory_fragmentation(p) > threshold; }
+CG_EXPORT bool cg_memory_needs_compact(cg_memory_pool* p_, float threshold) { auto* p = impl(p_); return cg_memory_fragmentation(p) > threshold; }
 
 // ------------------------------------------------------------------- buddy
-struct cg_buddy_allocator {
+struct BuddyImpl : cg_buddy_allocator {
+  BuddyImpl() : cg_buddy_allocator{} {}
   char* base; size_t size; int max_order;            // block of order k = kMin << k
   std::vector<std::set<size_t>> free_at;             // offsets per order
   int splits = 0, coalesces = 0;
+  void sync() { base_ptr = base; total_size = size; buddy_splits = (size_t)splits; buddy_coalesces = (size_t)coalesces; }
 };
+static BuddyImpl* impl(cg_buddy_allocator* x) { return static_cast<BuddyImpl*>(x); }
 static constexpr size_t kBuddyMin = 256;
 static int order_for(size_t size) { int k = 0; size_t cap = kBuddyMin; while (cap < size) { cap <<= 1; ++k; } return k; }
 CG_EXPORT cg_buddy_allocator* cg_buddy_new(void* base, size_t size) {
   if (!base || size < kBuddyMin) return fail(CG_ERROR_INVALID_ARGUMENT, (cg_buddy_allocator*)nullptr);
-  cg_buddy_allocator* b = new cg_buddy_allocator();
+  BuddyImpl* b = new BuddyImpl();
   int k = 0; while ((kBuddyMin << (k + 1)) <= size) ++k;        // largest power of two that fits
   b->base = (char*)base; b->size = kBuddyMin << k; b->max_order = k;
   b->free_at.resize(k + 1);
   b->free_at[k].insert(0);
+  b->sync();
   return b;
 }
-CG_EXPORT void* cg_buddy_alloc(cg_buddy_allocator* b, size_t size) {
+CG_EXPORT void* cg_buddy_alloc(cg_buddy_allocator* b_, size_t size) { auto* b = impl(b_);
   if (!b || size == 0) return fail(CG_ERROR_INVALID_ARGUMENT, (void*)nullptr);
   const int want = order_for(size);
   int k = want;
@@ -122,13 +139,16 @@ CG_EXPORT void* cg_buddy_alloc(cg_buddy_allocator* b, size_t size) {
   size_t off = *b->free_at[k].begin();
   b->free_at[k].erase(b->free_at[k].begin());
   while (k > want) { --k; b->free_at[k].insert(off + (kBuddyMin << k)); ++b->splits; }
+  b->allocated += kBuddyMin << want;
+  b->sync();
   return b->base + off;
 }
-CG_EXPORT void cg_buddy_free(cg_buddy_allocator* b, void* ptr, size_t size) {
+CG_EXPORT void cg_buddy_free(cg_buddy_allocator* b_, void* ptr, size_t size) { auto* b = impl(b_);
   if (!b || !ptr) return;
   size_t off = (char*)ptr - b->base;
   int k = order_for(size);
   if (off >= b->size || off % (kBuddyMin << k)) { set_error(CG_ERROR_INVALID_ARGUMENT); return; }
+  b->allocated -= (kBuddyMin << k) <= b->allocated ? (kBuddyMin << k) : b->allocated;
   while (k < b->max_order) {
     const size_t buddy = off ^ (kBuddyMin << k);
     auto it = b->free_at[k].find(buddy);
@@ -138,17 +158,19 @@ CG_EXPORT void cg_buddy_free(cg_buddy_allocator* b, void* ptr, size_t size) {
     ++k; ++b->coalesces;
   }
   b->free_at[k].insert(off);
+  b->sync();
 }
-CG_EXPORT void cg_buddy_destroy(cg_buddy_allocator* b) { delete b; }
-CG_EXPORT int cg_buddy_splits(cg_buddy_allocator* b) { return b ? b->splits : 0; }
-CG_EXPORT int cg_buddy_coalesces(cg_buddy_allocator* b) { return b ? b->coalesces : 0; }
+CG_EXPORT void cg_buddy_destroy(cg_buddy_allocator* b_) { auto* b = impl(b_); delete b; }
+CG_EXPORT int cg_buddy_splits(cg_buddy_allocator* b_) { auto* b = impl(b_); return b ? b->splits : 0; }
+CG_EXPORT int cg_buddy_coalesces(cg_buddy_allocator* b_) { auto* b = impl(b_); return b ? b->coalesces : 0; }
 
 // ----------------------------------------------------------------- planner
 namespace {
 struct Life { int first = -1, last = -1; size_t bytes = 0; size_t offset = 0; bool planned = false; bool pinned = false; };
 struct Trace { int tensor_id; size_t size; void* ptr; };
 }  // namespace
-struct cg_memory_planner {
+struct PlannerImpl : cg_memory_planner {
+  PlannerImpl() : cg_memory_planner{} {}
   cg_memory_pool* pools[2];
   std::map<int, Life> life;                         // tensor id -> lifetime and planned offset
   size_t plan_bytes = 0; char* slab = nullptr; size_t slab_bytes = 0;
@@ -157,13 +179,16 @@ struct cg_memory_planner {
   bool capturing = false, captured = false, replaying = false, stale = true;
   std::vector<Trace> trace; size_t cursor = 0;
 };
+static PlannerImpl* impl(cg_memory_planner* x) { return static_cast<PlannerImpl*>(x); }
 CG_EXPORT cg_memory_planner* cg_memory_planner_new(void) {
-  cg_memory_planner* p = new cg_memory_planner();
+  PlannerImpl* p = new PlannerImpl();
   p->pools[0] = cg_memory_pool_new(); p->pools[1] = cg_memory_pool_new();
+  p->device_pool = p->pools[0]; p->host_pool = p->pools[1];
+  p->frag_threshold = 0.5f; p->defrag_enabled = true;
   return p;
 }
-CG_EXPORT cg_memory_pool* cg_memory_planner_pool(cg_memory_planner* p, cg_arena_type a) { return p ? p->pools[a == CG_ARENA_HOST ? 1 : 0] : nullptr; }
-CG_EXPORT void cg_memory_planner_free(cg_memory_planner* p) {
+CG_EXPORT cg_memory_pool* cg_memory_planner_pool(cg_memory_planner* p_, cg_arena_type a) { auto* p = impl(p_); return p ? p->pools[a == CG_ARENA_HOST ? 1 : 0] : nullptr; }
+CG_EXPORT void cg_memory_planner_free(cg_memory_planner* p_) { auto* p = impl(p_);
   if (!p) return;
   cg_memory_pool_free(p->pools[0]); cg_memory_pool_free(p->pools[1]);
   std::free(p->slab);
@@ -171,7 +196,7 @@ CG_EXPORT void cg_memory_planner_free(cg_memory_planner* p) {
 }
 // Lifetime of every tensor of the graph: produced at its node's position, dead after its last
 // reader.  Graph inputs and outputs are pinned for the whole run.
-CG_EXPORT void cg_analyze_tensor_lifetimes(cg_memory_planner* p, void* ir_graph) {
+CG_EXPORT void cg_analyze_tensor_lifetimes(cg_memory_planner* p_, void* ir_graph) { auto* p = impl(p_);
   cg_ir_graph* g = (cg_ir_graph*)ir_graph;
   if (!p || !g) { set_error(CG_ERROR_NULL_POINTER); return; }
   p->life.clear();
@@ -194,7 +219,7 @@ CG_EXPORT void cg_analyze_tensor_lifetimes(cg_memory_planner* p, void* ir_graph)
     if (kv.second.pinned) { kv.second.first = 0; kv.second.last = pos; }
   }
 }
-CG_EXPORT bool cg_can_reuse_memory(cg_memory_planner* p, int a, int b) {
+CG_EXPORT bool cg_can_reuse_memory(cg_memory_planner* p_, int a, int b) { auto* p = impl(p_);
   if (!p) return false;
   auto ia = p->life.find(a), ib = p->life.find(b);
   if (ia == p->life.end() || ib == p->life.end() || ia->second.pinned || ib->second.pinned) return false;
@@ -202,7 +227,7 @@ CG_EXPORT bool cg_can_reuse_memory(cg_memory_planner* p, int a, int b) {
 }
 // Greedy offset assignment, largest first: a tensor takes the lowest offset at which it
 // overlaps no already-placed tensor whose lifetime intersects its own.
-CG_EXPORT void cg_find_reuse_opportunities(cg_memory_planner* p) {
+CG_EXPORT void cg_find_reuse_opportunities(cg_memory_planner* p_) { auto* p = impl(p_);
   if (!p) return;
   std::vector<int> ids;
   for (auto& kv : p->life) { kv.second.planned = false; if (kv.second.bytes) ids.push_back(kv.first); }
@@ -223,17 +248,17 @@ CG_EXPORT void cg_find_reuse_opportunities(cg_memory_planner* p) {
   }
   p->stale = true;
 }
-CG_EXPORT void cg_memory_plan_analyze(cg_memory_planner* p, void* ir_graph) {
+CG_EXPORT void cg_memory_plan_analyze(cg_memory_planner* p_, void* ir_graph) { auto* p = impl(p_);
   cg_analyze_tensor_lifetimes(p, ir_graph);
   cg_find_reuse_opportunities(p);
 }
-CG_EXPORT size_t cg_memory_plan_bytes(cg_memory_planner* p) { return p ? p->plan_bytes : 0; }
-CG_EXPORT size_t cg_memory_plan_offset(cg_memory_planner* p, int tensor_id) {
+CG_EXPORT size_t cg_memory_plan_bytes(cg_memory_planner* p_) { auto* p = impl(p_); return p ? p->plan_bytes : 0; }
+CG_EXPORT size_t cg_memory_plan_offset(cg_memory_planner* p_, int tensor_id) { auto* p = impl(p_);
   if (!p) return (size_t)-1;
   auto it = p->life.find(tensor_id);
   return it == p->life.end() || !it->second.planned ? (size_t)-1 : it->second.offset;
 }
-CG_EXPORT void* cg_planned_alloc(cg_memory_planner* p, size_t size, int tensor_id) {
+CG_EXPORT void* cg_planned_alloc(cg_memory_planner* p_, size_t size, int tensor_id) { auto* p = impl(p_);
   if (!p) return fail(CG_ERROR_NULL_POINTER, (void*)nullptr);
   if (p->replaying) {                                    // same sequence of requests -> same addresses
     if (p->cursor < p->trace.size() && p->trace[p->cursor].tensor_id == tensor_id && p->trace[p->cursor].size >= size) return p->trace[p->cursor++].ptr;
@@ -255,7 +280,7 @@ CG_EXPORT void* cg_planned_alloc(cg_memory_planner* p, size_t size, int tensor_i
   if (p->capturing && ptr) p->trace.push_back({tensor_id, size, ptr});
   return ptr;
 }
-CG_EXPORT void cg_planned_free(cg_memory_planner* p, void* ptr, int tensor_id) {
+CG_EXPORT void cg_planned_free(cg_memory_planner* p_, void* ptr, int tensor_id) { auto* p = impl(p_);
   if (!p || !ptr) return;
   auto it = p->handed.find(tensor_id);
   if (it != p->handed.end() && it->second == ptr) { p->handed.erase(it); return; }
@@ -264,8 +289,10 @@ CG_EXPORT void cg_planned_free(cg_memory_planner* p, void* ptr, int tensor_id) {
 }
 // Slides the live planned tensors towards offset 0 in address order (contents move with
 // them) and shrinks the plan to the bytes in use.
-CG_EXPORT void cg_memory_sliding_compact(cg_memory_planner* p) {
-  if (!p || !p->slab) return;
+CG_EXPORT void cg_memory_sliding_compact(cg_memory_planner* p_) { auto* p = impl(p_);
+  if (!p) return;
+  cg_pool_trim(p->pools[0]); cg_pool_trim(p->pools[1]);      // blocks that wait in the caches are the pools' fragmentation
+  if (!p->slab) return;
   std::vector<int> ids;
   for (auto& kv : p->handed) ids.push_back(kv.first);
   std::sort(ids.begin(), ids.end(), [&](int a, int b) { return p->life[a].offset < p->life[b].offset; });
@@ -277,15 +304,15 @@ CG_EXPORT void cg_memory_sliding_compact(cg_memory_planner* p) {
   }
   p->stale = true;
 }
-CG_EXPORT void cg_memory_defrag(cg_memory_planner* p) {
+CG_EXPORT void cg_memory_defrag(cg_memory_planner* p_) { auto* p = impl(p_);
   if (!p) return;
   cg_pool_trim(p->pools[0]); cg_pool_trim(p->pools[1]);
   cg_memory_sliding_compact(p);
 }
-CG_EXPORT void cg_memory_maybe_defrag(cg_memory_planner* p) {
+CG_EXPORT void cg_memory_maybe_defrag(cg_memory_planner* p_) { auto* p = impl(p_);
   if (p && (cg_memory_needs_compact(p->pools[0], 0.5f) || cg_memory_needs_compact(p->pools[1], 0.5f))) cg_memory_defrag(p);
 }
-CG_EXPORT void* cg_planned_lookup(cg_memory_planner* p, int tensor_id) {
+CG_EXPORT void* cg_planned_lookup(cg_memory_planner* p_, int tensor_id) { auto* p = impl(p_);
   if (!p) return nullptr;
   auto it = p->handed.find(tensor_id);
   return it == p->handed.end() ? nullptr : it->second;
@@ -293,15 +320,16 @@ CG_EXPORT void* cg_planned_lookup(cg_memory_planner* p, int tensor_id) {
 // Allocation trace for graph capture: between begin and end every planned allocation is
 // recorded; replay hands the same addresses back in the same order, which is what a captured
 // CUDA graph needs.  A request that deviates from the trace marks it stale.
-CG_EXPORT void cg_cuda_graph_capture_begin(cg_memory_planner* p) { if (p) { p->trace.clear(); p->capturing = true; p->captured = false; p->replaying = false; } }
-CG_EXPORT void cg_cuda_graph_capture_end(cg_memory_planner* p) { if (p && p->capturing) { p->capturing = false; p->captured = true; p->stale = false; } }
-CG_EXPORT void cg_cuda_graph_replay(cg_memory_planner* p) { if (p && p->captured && !p->stale) { p->replaying = true; p->cursor = 0; } }
-CG_EXPORT bool cg_cuda_graph_needs_update(cg_memory_planner* p) { return !p || !p->captured || p->stale; }
+CG_EXPORT void cg_cuda_graph_capture_begin(cg_memory_planner* p_) { auto* p = impl(p_); if (p) { p->trace.clear(); p->capturing = true; p->captured = false; p->replaying = false; p->graph_captured = false; } }
+CG_EXPORT void cg_cuda_graph_capture_end(cg_memory_planner* p_) { auto* p = impl(p_); if (p && p->capturing) { p->capturing = false; p->captured = true; p->stale = false; p->graph_captured = true; } }
+CG_EXPORT void cg_cuda_graph_replay(cg_memory_planner* p_) { auto* p = impl(p_); if (p && p->captured && !p->stale) { p->replaying = true; p->cursor = 0; } }
+CG_EXPORT bool cg_cuda_graph_needs_update(cg_memory_planner* p_) { auto* p = impl(p_); return !p || !p->captured || p->stale; }
 
-CG_EXPORT cg_memory_stats cg_memory_get_stats(cg_memory_planner* p) {
+CG_EXPORT cg_memory_stats cg_memory_get_stats(cg_memory_planner* p_) { auto* p = impl(p_);
   cg_memory_stats s{};
   if (!p) return s;
-  for (cg_memory_pool* q : p->pools) {
+  for (cg_memory_pool* q_ : p->pools) {
+    PoolImpl* q = impl(q_);
     s.total_allocated += q->st.total_allocated; s.total_cached += q->st.total_cached; s.peak_allocated += q->st.peak_allocated;
     s.num_allocs += q->st.num_allocs; s.num_frees += q->st.num_frees; s.cache_hits += q->st.cache_hits; s.cache_misses += q->st.cache_misses;
     for (const auto& l : q->free_list) s.num_bins_used += l.empty() ? 0 : 1;
@@ -315,7 +343,7 @@ CG_EXPORT cg_memory_stats cg_memory_get_stats(cg_memory_planner* p) {
   s.cache_hit_rate = req > 0 ? (size_t)(100LL * s.cache_hits / req) : 0;
   return s;
 }
-CG_EXPORT void cg_memory_print_stats(cg_memory_planner* p) {
+CG_EXPORT void cg_memory_print_stats(cg_memory_planner* p_) { auto* p = impl(p_);
   const cg_memory_stats s = cg_memory_get_stats(p);
   std::printf("memory: allocated %zu B, cached %zu B, peak %zu B, allocs %d, frees %d, hits %d, misses %d, fragmentation %.1f%%, plan %zu B\n",
               s.total_allocated, s.total_cached, s.peak_allocated, s.num_allocs, s.num_frees, s.cache_hits, s.cache_misses,

@@ -303,9 +303,19 @@ typedef enum { CG_ARENA_DEFAULT = 0, CG_ARENA_PARAM, CG_ARENA_ACTIVATION, CG_ARE
 #define CG_BUDDY_MIN_ORDER 8
 #define CG_BUDDY_MAX_ORDER 40
 #define CG_BUDDY_NUM_ORDERS (CG_BUDDY_MAX_ORDER - CG_BUDDY_MIN_ORDER + 1)
-typedef struct cg_memory_pool cg_memory_pool;
-typedef struct cg_buddy_allocator cg_buddy_allocator;
-typedef struct cg_memory_planner cg_memory_planner;
+/* The counters and pointers the reference exposes (include/cg_memory.h:73-133), kept current by the functions below;
+ * the bins, free lists and lifetime tables themselves are private to the library (created by the *_new functions only). */
+typedef struct cg_buddy_allocator {
+  void* base_ptr; size_t total_size; size_t allocated; size_t buddy_splits; size_t buddy_coalesces;
+} cg_buddy_allocator;
+typedef struct cg_memory_pool {
+  cg_buddy_allocator* buddy;                  /* null: the pool caches whole blocks; the buddy allocator is used on its own */
+  size_t total_allocated, total_in_use, peak_usage, num_allocs, num_frees, cache_hits, cache_misses, subbin_hits, buddy_coalesces;
+} cg_memory_pool;
+typedef struct cg_memory_planner {
+  cg_memory_pool* device_pool; cg_memory_pool* host_pool;
+  bool graph_captured; float frag_threshold; bool defrag_enabled; int num_tensors;
+} cg_memory_planner;
 typedef struct {
   size_t total_allocated, total_cached, peak_allocated; int num_allocs, num_frees, cache_hits, cache_misses;
   int buddy_splits, buddy_coalesces; float fragmentation;
