@@ -2,6 +2,8 @@
 // kernels), RoPE, ALiBi, launch heuristics, and the transformer block built on them.
 // Reference surface: include/cg_flash_attn.h, src/attention/flash_attn.c,
 // include/cg_transformer.h, src/layers/transformer.c.
+#include <algorithm>
+
 #include "internal.hpp"
 
 using namespace cgi;
@@ -35,9 +37,53 @@ inline float bias_of(const cg_flash_attn_params* p, const Dims& d, int b, int h,
   return v;
 }
 cg_tensor* ensure_like(cg_tensor*& slot, const cg_tensor* like) { if (!slot) slot = make_like(like, false); return slot; }
+
+// A parameter block filled the reference's way (include/cg_flash_attn.h:51-88): raw fp32 arrays in the operand slots.
+// The arrays are wrapped in tensor headers that do not own them, the tensor path runs, the headers go.
+struct RawBlock {
+  cg_flash_attn_params t;
+  std::vector<cg_tensor*> headers;
+  bool ok = false;
+  cg_tensor* wrap(void* data, int a, int b, int c, int d4) {
+    if (!data) return nullptr;
+    int shape[4] = {a, b, c, d4};
+    cg_tensor* h = make_header(shape, d4 > 0 ? 4 : (c > 0 ? 3 : 2), false);
+    if (!h) return nullptr;
+    h->data = (float*)data; h->is_view = true;
+    headers.push_back(h);
+    return h;
+  }
+  RawBlock(const cg_flash_attn_params* p, bool backward) {
+    std::memset(&t, 0, sizeof(t));
+    const int B = p->batch_size, Tq = p->seqlen_q, Tk = p->seqlen_k > 0 ? p->seqlen_k : p->seqlen_q, H = p->n_heads;
+    const int Hk = p->n_kv_heads > 0 ? p->n_kv_heads : H, D = p->d_head;
+    if (B <= 0 || Tq <= 0 || H <= 0 || D <= 0 || !p->Q || !p->K || !p->V || !p->O) return;
+    t.operand_mode = CG_FLASH_TENSOR_MODE;
+    t.Q = wrap(p->Q, B, Tq, H, D); t.K = wrap(p->K, B, Tk, Hk, D); t.V = wrap(p->V, B, Tk, Hk, D); t.O = wrap(p->O, B, Tq, H, D);
+    if (p->softmax_lse) t.L = wrap(p->softmax_lse, B, H, Tq, 0);
+    if (p->mask_type == CG_MASK_CUSTOM && p->mask) t.mask = wrap(p->mask, Tq, Tk, 0, 0);
+    if (backward) { t.dO = wrap(p->dO, B, Tq, H, D); t.dQ = wrap(p->dQ, B, Tq, H, D); t.dK = wrap(p->dK, B, Tk, Hk, D); t.dV = wrap(p->dV, B, Tk, Hk, D); }
+    t.batch_size = B; t.seqlen_q = Tq; t.seqlen_k = Tk; t.n_heads = H; t.n_kv_heads = Hk; t.d_head = D;
+    t.softmax_scale = p->softmax_scale; t.dropout_prob = p->dropout_prob; t.mask_type = p->mask_type; t.window_size = p->window_size;
+    t.alibi_slopes = p->alibi_slopes; t.config = p->config;
+    ok = t.Q && t.K && t.V && t.O && (!backward || (t.dO && t.dQ && t.dK && t.dV && t.L));
+  }
+  ~RawBlock() {
+    if (t.L && std::find(headers.begin(), headers.end(), t.L) == headers.end()) cg_tensor_release(t.L);   // made by the forward pass
+    for (cg_tensor* h : headers) cg_tensor_release(h);
+  }
+};
+inline bool raw_block(const cg_flash_attn_params* p) { return p && p->operand_mode != CG_FLASH_TENSOR_MODE; }
 }  // namespace
+namespace cgi { bool flash_raw_block(const cg_flash_attn_params* p) { return raw_block(p); } }
 
 CG_EXPORT void cg_flash_attention_forward_cpu(cg_flash_attn_params* p) {
+  if (raw_block(p)) {
+    RawBlock r(p, false);
+    if (!r.ok) { set_error(CG_ERROR_INVALID_ARGUMENT); return; }
+    cg_flash_attention_forward_cpu(&r.t);
+    return;
+  }
   Dims d;
   if (!dims_of(p, &d)) { set_error(CG_ERROR_SHAPE_MISMATCH); return; }
   ensure_like(p->O, p->Q);
@@ -82,6 +128,12 @@ CG_EXPORT void cg_flash_attention_forward_cpu(cg_flash_attn_params* p) {
 
 // Needs O and L from the forward pass and dO; fills (overwrites) dQ, dK, dV.
 CG_EXPORT void cg_flash_attention_backward_cpu(cg_flash_attn_params* p) {
+  if (raw_block(p)) {
+    RawBlock r(p, true);
+    if (!r.ok) { set_error(CG_ERROR_INVALID_ARGUMENT); return; }
+    cg_flash_attention_backward_cpu(&r.t);
+    return;
+  }
   Dims d;
   if (!dims_of(p, &d) || !p->O || !p->L || !p->dO || p->dO->size != p->Q->size) { set_error(CG_ERROR_SHAPE_MISMATCH); return; }
   ensure_like(p->dQ, p->Q); ensure_like(p->dK, p->K); ensure_like(p->dV, p->V);
@@ -115,11 +167,13 @@ CG_EXPORT void cg_flash_attention_backward_cpu(cg_flash_attn_params* p) {
 CG_EXPORT void cg_flash_attention_forward(cg_flash_attn_params* p) { cg_flash_attention_forward_cpu(p); }
 CG_EXPORT void cg_flash_attention_backward(cg_flash_attn_params* p) { cg_flash_attention_backward_cpu(p); }
 CG_EXPORT void cg_flash_attention_mqa(cg_flash_attn_params* p) {
+  if (raw_block(p)) { if (p->n_kv_heads != 1) { set_error(CG_ERROR_SHAPE_MISMATCH); return; } cg_flash_attention_forward(p); return; }
   if (!p || !p->K || p->K->ndim != 4 || p->K->shape[2] != 1) { set_error(CG_ERROR_SHAPE_MISMATCH); return; }
   p->n_kv_heads = 1;
   cg_flash_attention_forward(p);
 }
 CG_EXPORT void cg_flash_attention_gqa(cg_flash_attn_params* p, int num_kv_groups) {
+  if (raw_block(p)) { if (num_kv_groups <= 0) { set_error(CG_ERROR_SHAPE_MISMATCH); return; } p->n_kv_heads = num_kv_groups; cg_flash_attention_forward(p); return; }
   if (!p || !p->K || p->K->ndim != 4 || num_kv_groups <= 0 || p->K->shape[2] != num_kv_groups) { set_error(CG_ERROR_SHAPE_MISMATCH); return; }
   p->n_kv_heads = num_kv_groups;
   cg_flash_attention_forward(p);
@@ -128,6 +182,7 @@ CG_EXPORT cg_flash_attn_params* cg_flash_attn_params_new(cg_tensor* Q, cg_tensor
   if (!Q || !K || !V) return fail(CG_ERROR_NULL_POINTER, (cg_flash_attn_params*)nullptr);
   cg_flash_attn_params* p = (cg_flash_attn_params*)std::calloc(1, sizeof(cg_flash_attn_params));
   p->Q = Q; p->K = K; p->V = V; p->mask_type = mt; p->dropout_prob = dropout;
+  p->operand_mode = CG_FLASH_TENSOR_MODE;
   Dims d;
   if (!dims_of(p, &d)) { std::free(p); return fail(CG_ERROR_SHAPE_MISMATCH, (cg_flash_attn_params*)nullptr); }
   p->batch_size = d.B; p->seqlen_q = d.Tq; p->seqlen_k = d.Tk; p->n_heads = d.H; p->n_kv_heads = d.Hk; p->d_head = d.D;
@@ -220,6 +275,7 @@ cg_tensor* attention_op(cg_tensor* q, cg_tensor* k, cg_tensor* v, cg_tensor* mas
     p->Q = Q4; p->K = K4; p->V = V4;
     p->mask_type = mask ? CG_MASK_CUSTOM : CG_MASK_CAUSAL; p->mask = mask;
     p->softmax_scale = 1.0f / std::sqrt((float)D);
+    p->operand_mode = CG_FLASH_TENSOR_MODE;
   };
   auto view4 = [T, D](cg_tensor* t, int heads) { cg_tensor w = *t; w.ndim = 4; w.shape[0] = 1; w.shape[1] = T; w.shape[2] = heads; w.shape[3] = D; return w; };
   cg_tensor Q4 = view4(q, H), K4 = view4(k, Hk), V4 = view4(v, Hk);

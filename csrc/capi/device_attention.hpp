@@ -84,6 +84,7 @@ void rope_impl(float* x, int B, int T, int H, int D, float* cos_c, float* sin_c,
 }  // namespace
 
 CG_EXPORT void cg_flash_attention_forward_cuda(cg_flash_attn_params* p) {
+  if (dev() && flash_raw_block(p)) { note_error("raw-array parameter blocks run on the host; on a device use cg_flash_attn_params_new"); set_error(CG_ERROR_INVALID_ARGUMENT); return; }
   if (!dev()) { cg_flash_attention_forward_cpu(p); return; }
   AttnDims d;
   if (!attn_dims(p, &d)) { set_error(CG_ERROR_SHAPE_MISMATCH); return; }
@@ -100,6 +101,7 @@ CG_EXPORT void cg_flash_attention_forward_cuda(cg_flash_attn_params* p) {
 }
 
 CG_EXPORT void cg_flash_attention_backward_cuda(cg_flash_attn_params* p) {
+  if (dev() && flash_raw_block(p)) { note_error("raw-array parameter blocks run on the host; on a device use cg_flash_attn_params_new"); set_error(CG_ERROR_INVALID_ARGUMENT); return; }
   if (!dev()) { cg_flash_attention_backward_cpu(p); return; }
   AttnDims d;
   if (!attn_dims(p, &d)) { set_error(CG_ERROR_SHAPE_MISMATCH); return; }
@@ -124,12 +126,16 @@ CG_EXPORT void cg_flash_attention_backward_cuda(cg_flash_attn_params* p) {
 }
 
 CG_EXPORT void cg_flash_attention_mqa_cuda(cg_flash_attn_params* p) {
+  if (dev() && flash_raw_block(p)) { note_error("raw-array parameter blocks run on the host; on a device use cg_flash_attn_params_new"); set_error(CG_ERROR_INVALID_ARGUMENT); return; }
+  if (flash_raw_block(p)) { cg_flash_attention_mqa(p); return; }                    // host mode
   if (!p || !p->K) { set_error(CG_ERROR_NULL_POINTER); return; }
   if (p->K->ndim != 4 || p->K->shape[2] != 1) { set_error(CG_ERROR_SHAPE_MISMATCH); return; }
   p->n_kv_heads = 1;
   cg_flash_attention_forward_cuda(p);
 }
 CG_EXPORT void cg_flash_attention_gqa_cuda(cg_flash_attn_params* p, int num_kv_groups) {
+  if (dev() && flash_raw_block(p)) { note_error("raw-array parameter blocks run on the host; on a device use cg_flash_attn_params_new"); set_error(CG_ERROR_INVALID_ARGUMENT); return; }
+  if (flash_raw_block(p)) { cg_flash_attention_gqa(p, num_kv_groups); return; }     // host mode
   if (!p || !p->K || !p->Q) { set_error(CG_ERROR_NULL_POINTER); return; }
   if (num_kv_groups <= 0 || p->K->ndim != 4 || p->K->shape[2] != num_kv_groups || p->Q->shape[2] % num_kv_groups) {
     set_error(CG_ERROR_SHAPE_MISMATCH); return;
@@ -138,6 +144,8 @@ CG_EXPORT void cg_flash_attention_gqa_cuda(cg_flash_attn_params* p, int num_kv_g
   cg_flash_attention_forward_cuda(p);
 }
 CG_EXPORT void cg_flash_attention_sliding_window_cuda(cg_flash_attn_params* p, int window_size) {
+  if (dev() && flash_raw_block(p)) { note_error("raw-array parameter blocks run on the host; on a device use cg_flash_attn_params_new"); set_error(CG_ERROR_INVALID_ARGUMENT); return; }
+  if (flash_raw_block(p)) { p->mask_type = CG_MASK_SLIDING_WINDOW; p->window_size = window_size; cg_flash_attention_forward_cpu(p); return; }   // host mode
   if (!p) { set_error(CG_ERROR_NULL_POINTER); return; }
   p->mask_type = CG_MASK_SLIDING_WINDOW;
   p->window_size = window_size;
@@ -156,6 +164,8 @@ CG_EXPORT void cg_rope_backward_cuda(float* dx, int batch, int seqlen, int n_hea
 
 // RoPE on Q and K (in place, as the reference's fused entry point leaves them), then attention.
 CG_EXPORT void cg_flash_attention_forward_rope_cuda(cg_flash_attn_params* p, float* cos_cache, float* sin_cache, int position_offset) {
+  if (dev() && flash_raw_block(p)) { note_error("raw-array parameter blocks run on the host; on a device use cg_flash_attn_params_new"); set_error(CG_ERROR_INVALID_ARGUMENT); return; }
+  if (flash_raw_block(p)) { set_error(CG_ERROR_INVALID_ARGUMENT); return; }         // rotary embedding and paged keys take tensor blocks
   AttnDims d;
   if (!attn_dims(p, &d)) { set_error(CG_ERROR_SHAPE_MISMATCH); return; }
   if (!operands_ok({p->Q, p->K})) return;
@@ -172,6 +182,8 @@ CG_EXPORT void cg_flash_attention_forward_rope_cuda(cg_flash_attn_params* p, flo
 // keys.  (The reference's entry point only prints "not yet implemented",
 // src/cuda/flash_attn_kernels.c:601-611.)
 CG_EXPORT void cg_flash_attention_paged_cuda(cg_flash_attn_params* p, int* block_tables, int block_size, int max_context_len) {
+  if (dev() && flash_raw_block(p)) { note_error("raw-array parameter blocks run on the host; on a device use cg_flash_attn_params_new"); set_error(CG_ERROR_INVALID_ARGUMENT); return; }
+  if (flash_raw_block(p)) { set_error(CG_ERROR_INVALID_ARGUMENT); return; }
   if (!p || !p->Q || !p->K || !p->V || !block_tables) { set_error(CG_ERROR_NULL_POINTER); return; }
   if (p->Q->ndim != 4 || p->K->ndim != 4 || p->V->ndim != 4 || block_size <= 0 || max_context_len <= 0 ||
       p->K->shape[1] != block_size || p->V->size != p->K->size) { set_error(CG_ERROR_SHAPE_MISMATCH); return; }

@@ -44,6 +44,8 @@ void attach_n(cg_tensor* out, cg_tensor* const* parents, int n, BackFn fn);   //
 //   ta = false: A is [M,K];  ta = true: A is [K,M]
 //   tb = false: B is [K,N];  tb = true: B is [N,K]
 void gemm(const float* A, const float* B, float* C, int M, int N, int K, bool ta, bool tb, bool accumulate);
+// attention.cpp: true when a flash-attention parameter block holds raw fp32 arrays (filled the reference's way) rather than tensors
+bool flash_raw_block(const cg_flash_attn_params* p);
 // host_simd.cpp (built with -O3, AVX2 + FMA copies picked at load time)
 void gemm_rows(const float* A, const float* B, float* C, int M, int N, int K, bool ta);       // C += op(A) B, B [K,N]
 void gemm_dots(const float* A, const float* B, float* C, int M, int N, int K);                // C += A B^T, B [N,K], few rows

@@ -132,7 +132,12 @@ typedef struct {
   /* reference fields (include/cg_flash_attn.h:51-88): softmax_lse points at L's values; the attention functions carry
    * dropout_prob but apply no dropout, so the mask stays null */
   bool is_training; float* softmax_lse; float* dropout_mask;
+  /* CG_FLASH_TENSOR_MODE (set by cg_flash_attn_params_new): the operand slots hold tensors.  Anything else - a block a
+   * caller zero-filled and set up the reference's way - means they hold raw fp32 arrays [batch, seq, heads, d_head],
+   * described by batch_size .. d_head, with the output in O and the log-sum-exp rows in softmax_lse (host memory). */
+  unsigned int operand_mode;
 } cg_flash_attn_params;
+#define CG_FLASH_TENSOR_MODE 0x43475450u
 void cg_flash_attention_forward(cg_flash_attn_params* params);
 void cg_flash_attention_forward_cpu(cg_flash_attn_params* params);
 void cg_flash_attention_backward(cg_flash_attn_params* params);
