@@ -57,7 +57,8 @@ class FlashParams(Structure):
                 ("dK", TensorP), ("dV", TensorP), ("L", TensorP), ("mask", TensorP),
                 ("batch_size", c_int), ("seqlen_q", c_int), ("seqlen_k", c_int), ("n_heads", c_int), ("n_kv_heads", c_int),
                 ("d_head", c_int), ("softmax_scale", c_float), ("dropout_prob", c_float), ("mask_type", c_int),
-                ("window_size", c_int), ("alibi_slopes", FP), ("config", FlashConfig)]
+                ("window_size", c_int), ("alibi_slopes", FP), ("config", FlashConfig), ("is_training", c_bool), ("softmax_lse", FP),
+                ("dropout_mask", FP), ("operand_mode", c_uint)]
 
 
 class TransformerConfig(Structure):

@@ -41,3 +41,35 @@ def test_argument_structs_match_the_header(tmp_path):
         assert got[(cname, ".")] == ctypes.sizeof(cls), cname
         for field in cls._fields_:
             assert got[(cname, field[0])] == getattr(cls, field[0]).offset, (cname, field[0])
+
+
+@pytest.mark.skipif(shutil.which("gcc") is None and shutil.which("cc") is None, reason="needs a C compiler")
+def test_host_library_mirrors_used_by_the_tests_match_the_public_headers(tmp_path):
+    """The ctypes mirrors in tests/capi_defs.py (shared by the CPU and the B200 test files) against include/cogito.h:
+    every mirrored field sits at the header's offset; a mirror may stop before the end of a struct the library allocates."""
+    import sys
+    sys.path.insert(0, str(ROOT / "tests"))
+    import capi_defs as d
+    pairs = [("cg_flash_attn_config", d.FlashConfig, True), ("cg_flash_attn_params", d.FlashParams, True),
+             ("cg_memory_stats", d.MemoryStats, True), ("cg_schedule_step", d.ScheduleStep, True),
+             ("cg_transformer_config", d.TransformerConfig, True), ("cg_mixed_precision", d.MixedPrecision, False),
+             ("cg_speculative_decoder", d.SpecDecoder, False), ("cg_3d_parallel", d.Parallel3D, False)]
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "cogito.h"', 'int main(void) {']
+    for cname, cls, _ in pairs:
+        lines.append(f'  printf("{cname} . %zu\\n", sizeof({cname}));')
+        for field in cls._fields_:
+            lines.append(f'  printf("{cname} {field[0]} %zu\\n", offsetof({cname}, {field[0]}));')
+    lines += ['  return 0;', '}']
+    src = tmp_path / "host_layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "host_layout"
+    cc = shutil.which("gcc") or shutil.which("cc")
+    subprocess.run([cc, "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True, capture_output=True, text=True)
+    got = {}
+    for ln in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines():
+        s, f, v = ln.split()
+        got[(s, f)] = int(v)
+    for cname, cls, whole in pairs:
+        assert ctypes.sizeof(cls) == got[(cname, ".")] if whole else ctypes.sizeof(cls) <= got[(cname, ".")], cname
+        for field in cls._fields_:
+            assert got[(cname, field[0])] == getattr(cls, field[0]).offset, (cname, field[0])
