@@ -328,7 +328,25 @@ std::map<std::string, Prof> g_prof;
 std::vector<std::string> g_prof_order;
 bool g_prof_on = false;
 int g_prof_steps = 0;
+cg_profiler g_state = {nullptr, 0, 0, false, 0};            // the public view of the tables above
+void publish_profile() {
+  const int n = (int)g_prof_order.size();
+  if (n > g_state.capacity) {
+    const int cap = n * 2 > 16 ? n * 2 : 16;
+    cg_layer_stat* grown = (cg_layer_stat*)std::realloc(g_state.layers, sizeof(cg_layer_stat) * cap);
+    if (!grown) return;
+    g_state.layers = grown; g_state.capacity = cap;
+  }
+  for (int i = 0; i < n; ++i) {
+    const Prof& p = g_prof[g_prof_order[i]];
+    cg_layer_stat& s = g_state.layers[i];
+    std::snprintf(s.name, sizeof(s.name), "%s", g_prof_order[i].c_str());
+    s.start_event = s.stop_event = nullptr; s.total_ms = (float)p.total_ms; s.count = p.count;
+  }
+  g_state.num_layers = n; g_state.enabled = g_prof_on; g_state.current_epoch = g_prof_steps;
+}
 }  // namespace
+CG_EXPORT cg_profiler* cg_profiler_state(void) { publish_profile(); return &g_state; }
 CG_EXPORT void cg_profiler_init(void) { g_prof.clear(); g_prof_order.clear(); g_prof_steps = 0; g_prof_on = true; }
 CG_EXPORT void cg_profiler_enable(bool e) { g_prof_on = e; }
 CG_EXPORT void cg_profiler_begin_layer(const char* name) {

@@ -368,6 +368,13 @@ size_t cg_memory_plan_offset(cg_memory_planner* planner, int tensor_id); /* (siz
 void* cg_planned_lookup(cg_memory_planner* planner, int tensor_id);      /* current address (moves on compaction) */
 
 /* --------------------------------------------------------------- profiler */
+/* The reference's public profiler state (include/cg_profiler.h:13-30): one entry per named region in first-use order,
+ * kept current by the functions below (the event slots stay null: regions are timed on the host clock here, device
+ * time per layer is the Python profiler's job).  g_profiler names the library's instance. */
+typedef struct { char name[64]; void* start_event; void* stop_event; float total_ms; int count; } cg_layer_stat;
+typedef struct { cg_layer_stat* layers; int num_layers; int capacity; bool enabled; int current_epoch; } cg_profiler;
+cg_profiler* cg_profiler_state(void);
+#define g_profiler (*cg_profiler_state())
 void cg_profiler_init(void);
 void cg_profiler_enable(bool enable);
 void cg_profiler_begin_layer(const char* name);

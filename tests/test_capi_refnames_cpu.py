@@ -283,6 +283,7 @@ def test_reference_field_and_enumerator_names_compile_as_c11(tmp_path):
 #include "cg_jit.h"
 #include "cg_fusion.h"
 #include "cg_cuda.h"
+#include "cg_profiler.h"
 #include "cogito.h"
 int main(void) {
   cg_transformer_config cfg = {0};
@@ -358,6 +359,16 @@ int main(void) {
   if (FLASH_BLOCK_M != fc.block_n || FA_WARPS * 32 != FA_THREADS || FLASH_WARPS != fc.num_warps || FA_BLOCK_K < 64 || FLASH_BLOCK_K < 64) return 22;
   cg_node_fusion nf = FUSION_VERTICAL; if (nf != NODE_FUSION_VERTICAL || FUSION_HORIZONTAL != NODE_FUSION_HORIZONTAL) return 23;
   if (cg_subbin_index(CG_SUBBIN_4096) != 2 || cg_subbin_index(100) != -1) return 24;
+  cg_profiler_init();                                                                       /* include/cg_profiler.h */
+  cg_profiler_begin_layer("fc1"); cg_profiler_end_layer("fc1");
+  cg_profiler_begin_layer("fc2"); cg_profiler_end_layer("fc2");
+  cg_profiler_begin_layer("fc1"); cg_profiler_end_layer("fc1");
+  cg_profiler_step_end();
+  if (!g_profiler.enabled || g_profiler.num_layers != 2 || g_profiler.current_epoch != 1 || g_profiler.capacity < 2) return 25;
+  cg_layer_stat* st0 = &g_profiler.layers[0];
+  if (st0->count != 2 || st0->name[0] != 'f' || st0->name[2] != '1' || st0->total_ms < 0.0f || g_profiler.layers[1].count != 1) return 26;
+  cg_profiler_reset();
+  if (g_profiler.num_layers != 0) return 27;
   (void)stage; (void)ctx; (void)dec; (void)tp; (void)qc; (void)eg;
   printf("ok\n");
   return 0;
