@@ -474,3 +474,14 @@ def test_transformer_block_gradients(llama_style):
     assert np.allclose(base[:4], moved[:4], atol=1e-6) and not np.allclose(base[4], moved[4])
     del loss
     lib.cg_layer_free(blk)
+
+
+def test_transformer_block_loop_in_c_keeps_the_live_tensor_count_flat(tmp_path):
+    cc = shutil.which("gcc") or shutil.which("cc")
+    exe = tmp_path / "block_loop"
+    lib = ROOT / "cogito_b200" / "lib"
+    p = subprocess.run([cc, "-std=c11", "-Wall", "-Werror", "-I", str(ROOT / "include"), str(ROOT / "tests" / "capi_block_loop.c"), "-L", str(lib),
+                        "-lcogito", "-lm", f"-Wl,-rpath,{lib}", "-o", str(exe)], capture_output=True, text=True)
+    assert p.returncode == 0, p.stderr
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and r.stdout.strip() == "live 0", (r.returncode, r.stdout, r.stderr)
